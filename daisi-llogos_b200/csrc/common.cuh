@@ -1,0 +1,103 @@
+// Shared helpers of the kernels: element types, error reporting, reductions.
+//
+// Every exported function is `extern "C"`, takes raw device pointers and the
+// stream to launch on, validates its sizes on the host and returns 0 on success.
+// On failure it returns non-zero and leaves a message for llg_last_error().
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#define LLG_API extern "C" __attribute__((visibility("default")))
+
+enum { LLG_F32 = 0, LLG_BF16 = 1 };
+
+// Tokens per page of the key/value cache.  Python reads it through llg_page_size().
+#define LLG_PAGE 64
+
+static thread_local char g_llg_error[512];
+
+static inline int llg_fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+#include <stdarg.h>
+static inline int llg_fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_llg_error, sizeof(g_llg_error), fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+static inline int llg_check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return llg_fail("%s: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+#define LLG_REQUIRE(cond, ...)            \
+  do {                                    \
+    if (!(cond)) return llg_fail(__VA_ARGS__); \
+  } while (0)
+
+// ---- element access ---------------------------------------------------------------
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// ---- reductions -------------------------------------------------------------------
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats.  All threads get the sum.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// Row of the paged key/value store that holds position `pos` of the sequence in `slot`,
+// for key/value head `kvh`.  Pages are [n_pages][n_kv][LLG_PAGE][head_dim]; a sequence's
+// logical page j lies at table[slot][j % ring_pages] (ring_pages = table width for a group
+// that keeps all keys).
+__device__ __forceinline__ long long kv_row(const int* __restrict__ table, int table_width,
+                                            int ring_pages, int slot, int pos, int kvh, int n_kv) {
+  const int lp = (pos / LLG_PAGE) % ring_pages;
+  const int page = table[(long long)slot * table_width + lp];
+  return ((long long)page * n_kv + kvh) * LLG_PAGE + (pos % LLG_PAGE);
+}

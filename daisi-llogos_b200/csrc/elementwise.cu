@@ -1,0 +1,353 @@
+// Memory-bound kernels of the decoder: embedding rows, residual add + RMSNorm,
+// query/key preparation (per-head norm, bias, rotation, cache write), SiLU-gating,
+// cache writes and small index updates.  All statistics and the residual stream are
+// float32; activations are float32 or bfloat16.
+//
+// Counterparts in the reference (formulas only): Daisi.Llogos.Cuda/kernels/elementwise.cu
+// rms_norm :18-48, add_rms_norm_residual :703-733, rope :243-290, swiglu :942-950,
+// embedding_lookup :402-457; kernels/composite_ops.cu per_head_rms_norm :106-136,
+// kv_cache_write :198-224.
+#include "common.cuh"
+
+LLG_API const char* llg_last_error() { return g_llg_error; }
+LLG_API int llg_page_size() { return LLG_PAGE; }
+
+// ---- embedding ----------------------------------------------------------------------
+
+template <typename TT>
+__global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
+                                  float* __restrict__ out, int hidden, int vocab) {
+  const int n = blockIdx.x;
+  int id = ids[n];
+  if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of range
+  const TT* row = table + (long long)id * hidden;
+  float* o = out + (long long)n * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+// residual[n][:] = table[ids[n]][:]   (no scaling; Inference/ForwardPass.cs:205)
+LLG_API int llg_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embed_rows: bad sizes n=%d hidden=%d vocab=%d",
+              n_tokens, hidden, vocab);
+  if (n_tokens == 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == LLG_F32)
+    embed_rows_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+  else if (table_dtype == LLG_BF16)
+    embed_rows_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out,
+                                                                       hidden, vocab);
+  else
+    return llg_fail("embed_rows: unknown table dtype %d", table_dtype);
+  return llg_check_launch("embed_rows");
+}
+
+// ---- residual add + RMSNorm ---------------------------------------------------------
+
+// For output row j (token r = rows ? rows[j] : j):
+//   v = residual[r] + sum_s branch[s][r]   (written back to residual when there is a branch)
+//   out[j] = v * rsqrt(mean(v^2) + eps) * weight         (eps inside the root, weight after)
+template <typename OT, typename WT>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ branch,
+                                   int n_partials, long long partial_stride, const WT* __restrict__ weight,
+                                   float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  __shared__ float red[32];
+  const int j = blockIdx.x;
+  const int r = rows ? rows[j] : j;
+  float* res = residual + (long long)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = res[i];
+    if (branch) {
+      const float* b = branch + (long long)r * hidden + i;
+      for (int s = 0; s < n_partials; ++s) v += b[s * partial_stride];
+      res[i] = v;
+    }
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  OT* o = out + (long long)j * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    o[i] = from_f32<OT>(res[i] * inv * to_f32(weight[i]));
+}
+
+LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials, long long partial_stride,
+                            const void* weight, int weight_dtype, float eps, void* out, int out_dtype,
+                            const int* rows, int n_out, int hidden, cudaStream_t stream) {
+  LLG_REQUIRE(n_out >= 0 && hidden > 0, "add_rmsnorm: bad sizes n_out=%d hidden=%d", n_out, hidden);
+  LLG_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
+  LLG_REQUIRE(!branch || n_partials >= 1, "add_rmsnorm: a branch needs n_partials >= 1");
+  if (n_out == 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+#define LAUNCH(OT, WT)                                                                              \
+  add_rmsnorm_kernel<OT, WT><<<n_out, threads, 0, stream>>>(residual, branch, n_partials, partial_stride, \
+                                                            (const WT*)weight, eps, (OT*)out, rows, hidden)
+  if (out_dtype == LLG_F32 && weight_dtype == LLG_F32) LAUNCH(float, float);
+  else if (out_dtype == LLG_F32 && weight_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (out_dtype == LLG_BF16 && weight_dtype == LLG_F32) LAUNCH(__nv_bfloat16, float);
+  else if (out_dtype == LLG_BF16 && weight_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return llg_fail("add_rmsnorm: unknown dtypes out=%d weight=%d", out_dtype, weight_dtype);
+#undef LAUNCH
+  return llg_check_launch("add_rmsnorm");
+}
+
+// ---- query/key preparation ----------------------------------------------------------
+
+struct QkPrepArgs {
+  const void* qkv;            // [n_partials][n_tokens][(nh + 2 nkv) * hd], float32 or bfloat16
+  int qkv_dtype;
+  int n_partials;
+  long long partial_stride;   // elements between partials
+  const void* q_norm_w;       // [hd] or null
+  const void* k_norm_w;       // [hd] or null
+  int norm_w_dtype;
+  float norm_eps;
+  const void* bias;           // [(nh + 2 nkv) * hd] or null
+  int bias_dtype;
+  const float* cos_table;     // [positions][rotary_dim / 2] or null
+  const float* sin_table;
+  int rotary_dim;
+  int pairing;                // 0: (i, i + rotary_dim/2), 1: (2i, 2i+1)
+  int table_positions;
+  const int* positions;       // [n_tokens]
+  void* q_out;                // [n_tokens][nh][hd]
+  void* k_new;                // [n_tokens][nkv][hd] or null
+  void* v_new;
+  void* k_pages;              // paged store or null
+  void* v_pages;
+  const int* page_table;
+  int table_width;
+  int ring_pages;
+  const int* seq_of_token;    // [n_tokens] -> index into slots
+  const int* slots;
+  int n_tokens, nh, nkv, hd;
+};
+
+template <typename IT, typename OT, typename WT>
+__global__ void qk_prep_kernel(QkPrepArgs a) {
+  extern __shared__ float sm[];
+  const int warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = a.nh + 2 * a.nkv;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)a.n_tokens * heads) return;
+  const int n = (int)(item / heads);
+  const int h = (int)(item % heads);
+  const int hd = a.hd;
+  float* x = sm + warp * hd;
+  const int kind = h < a.nh ? 0 : (h < a.nh + a.nkv ? 1 : 2);  // 0 query, 1 key, 2 value
+  const long long off = (long long)n * heads * hd + (long long)h * hd;
+  const IT* src = (const IT*)a.qkv + off;
+
+  float ss = 0.f;
+  for (int d = lane; d < hd; d += 32) {
+    float v = 0.f;
+    for (int s = 0; s < a.n_partials; ++s) v += to_f32(src[s * a.partial_stride + d]);
+    x[d] = v;
+    ss += v * v;
+  }
+  const WT* nw = kind == 0 ? (const WT*)a.q_norm_w : (kind == 1 ? (const WT*)a.k_norm_w : nullptr);
+  if (nw) {  // per-head RMSNorm first, then bias, then rotation (Inference/ForwardPass.cs:372-385)
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hd + a.norm_eps);
+    for (int d = lane; d < hd; d += 32) x[d] = x[d] * inv * to_f32(nw[d]);
+  }
+  if (a.bias) {
+    const WT* b = (const WT*)a.bias + (long long)h * hd;
+    for (int d = lane; d < hd; d += 32) x[d] += to_f32(b[d]);
+  }
+  __syncwarp();
+  const int pos = a.positions[n];
+  if (kind != 2 && a.cos_table) {
+    const int half = a.rotary_dim >> 1;
+    const int p = pos < a.table_positions ? pos : a.table_positions - 1;  // bounded; host checks capacity
+    const float* c = a.cos_table + (long long)p * half;
+    const float* s = a.sin_table + (long long)p * half;
+    for (int i = lane; i < half; i += 32) {
+      const int i0 = a.pairing == 0 ? i : 2 * i;
+      const int i1 = a.pairing == 0 ? i + half : 2 * i + 1;
+      const float x0 = x[i0], x1 = x[i1];
+      const float cs = c[i], sn = s[i];
+      x[i0] = x0 * cs - x1 * sn;
+      x[i1] = x0 * sn + x1 * cs;
+    }
+    __syncwarp();
+  }
+  if (kind == 0) {
+    OT* o = (OT*)a.q_out + ((long long)n * a.nh + h) * hd;
+    for (int d = lane; d < hd; d += 32) o[d] = from_f32<OT>(x[d]);
+    return;
+  }
+  const int kvh = kind == 1 ? h - a.nh : h - a.nh - a.nkv;
+  void* packed = kind == 1 ? a.k_new : a.v_new;
+  if (packed) {
+    OT* o = (OT*)packed + ((long long)n * a.nkv + kvh) * hd;
+    for (int d = lane; d < hd; d += 32) o[d] = from_f32<OT>(x[d]);
+  }
+  void* pages = kind == 1 ? a.k_pages : a.v_pages;
+  if (pages) {
+    const int slot = a.slots[a.seq_of_token[n]];
+    const long long row = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv);
+    OT* o = (OT*)pages + row * hd;
+    for (int d = lane; d < hd; d += 32) o[d] = from_f32<OT>(x[d]);
+  }
+}
+
+LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stream) {
+  const QkPrepArgs& a = *args;
+  LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.nkv >= 0 && a.hd > 0, "qk_prep: bad sizes");
+  LLG_REQUIRE(a.hd <= 1024, "qk_prep: head_dim %d is larger than 1024", a.hd);
+  LLG_REQUIRE(!a.cos_table || (a.rotary_dim > 0 && a.rotary_dim % 2 == 0 && a.rotary_dim <= a.hd),
+              "qk_prep: rotary_dim %d must be even and at most head_dim %d", a.rotary_dim, a.hd);
+  LLG_REQUIRE(a.n_partials >= 1, "qk_prep: n_partials must be >= 1");
+  LLG_REQUIRE(!a.k_pages || (a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
+              "qk_prep: a cache write needs page_table, slots and seq_of_token");
+  if (a.n_tokens == 0) return 0;
+  const int warps = 4;
+  const long long items = (long long)a.n_tokens * (a.nh + 2 * a.nkv);
+  const unsigned grid = (unsigned)((items + warps - 1) / warps);
+  const size_t smem = (size_t)warps * a.hd * sizeof(float);
+  const bool w_bf16 = (a.q_norm_w || a.k_norm_w) ? a.norm_w_dtype == LLG_BF16
+                                                 : (a.bias ? a.bias_dtype == LLG_BF16 : false);
+  if ((a.q_norm_w || a.k_norm_w) && a.bias)
+    LLG_REQUIRE(a.norm_w_dtype == a.bias_dtype, "qk_prep: norm weights and bias must share a dtype");
+#define LAUNCH(IT, OT, WT) qk_prep_kernel<IT, OT, WT><<<grid, warps * 32, smem, stream>>>(a)
+  if (out_dtype == LLG_F32) {
+    LLG_REQUIRE(a.qkv_dtype == LLG_F32, "qk_prep: float32 output needs float32 input");
+    if (w_bf16) LAUNCH(float, float, __nv_bfloat16); else LAUNCH(float, float, float);
+  } else if (out_dtype == LLG_BF16) {
+    if (a.qkv_dtype == LLG_F32) {
+      if (w_bf16) LAUNCH(float, __nv_bfloat16, __nv_bfloat16); else LAUNCH(float, __nv_bfloat16, float);
+    } else {
+      if (w_bf16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+      else LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
+    }
+  } else {
+    return llg_fail("qk_prep: unknown output dtype %d", out_dtype);
+  }
+#undef LAUNCH
+  return llg_check_launch("qk_prep");
+}
+
+// ---- cache write after a prompt step ------------------------------------------------
+
+// Copies this step's keys and values [n_tokens][nkv][hd] into the paged store.  A token whose
+// ring position would be overwritten by a later token of the same step is skipped.
+template <typename T>
+__global__ void kv_write_kernel(const T* __restrict__ k_new, const T* __restrict__ v_new, T* __restrict__ k_pages,
+                                T* __restrict__ v_pages, const int* __restrict__ page_table, int table_width,
+                                int ring_pages, const int* __restrict__ positions,
+                                const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                                const int* __restrict__ cu_tokens, const int* __restrict__ len_before,
+                                int n_tokens, int nkv, int hd) {
+  const int warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)n_tokens * nkv) return;
+  const int n = (int)(item / nkv), kvh = (int)(item % nkv);
+  const int b = seq_of_token[n];
+  const int pos = positions[n];
+  const int len_after = len_before[b] + (cu_tokens[b + 1] - cu_tokens[b]);
+  if (pos < len_after - ring_pages * LLG_PAGE) return;
+  const long long row = kv_row(page_table, table_width, ring_pages, slots[b], pos, kvh, nkv);
+  const T* ks = k_new + ((long long)n * nkv + kvh) * hd;
+  const T* vs = v_new + ((long long)n * nkv + kvh) * hd;
+  T* kd = k_pages + row * hd;
+  T* vd = v_pages + row * hd;
+  for (int d = lane; d < hd; d += 32) {
+    kd[d] = ks[d];
+    vd[d] = vs[d];
+  }
+}
+
+LLG_API int llg_kv_write(const void* k_new, const void* v_new, void* k_pages, void* v_pages,
+                         const int* page_table, int table_width, int ring_pages, const int* positions,
+                         const int* seq_of_token, const int* slots, const int* cu_tokens,
+                         const int* len_before, int n_tokens, int nkv, int hd, int dtype,
+                         cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && nkv > 0 && hd > 0 && ring_pages > 0 && table_width >= ring_pages,
+              "kv_write: bad sizes");
+  if (n_tokens == 0) return 0;
+  const int warps = 4;
+  const unsigned grid = (unsigned)(((long long)n_tokens * nkv + warps - 1) / warps);
+  if (dtype == LLG_F32)
+    kv_write_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        (const float*)k_new, (const float*)v_new, (float*)k_pages, (float*)v_pages, page_table, table_width,
+        ring_pages, positions, seq_of_token, slots, cu_tokens, len_before, n_tokens, nkv, hd);
+  else if (dtype == LLG_BF16)
+    kv_write_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (__nv_bfloat16*)k_pages,
+        (__nv_bfloat16*)v_pages, page_table, table_width, ring_pages, positions, seq_of_token, slots,
+        cu_tokens, len_before, n_tokens, nkv, hd);
+  else
+    return llg_fail("kv_write: unknown dtype %d", dtype);
+  return llg_check_launch("kv_write");
+}
+
+// ---- SiLU gating --------------------------------------------------------------------
+
+// out[n][i] = silu(g) * u with g = sum_s gu[s][n][i], u = sum_s gu[s][n][inter + i];
+// silu(g) = g / (1 + exp(-g))  (Daisi.Llogos.Cpu/Silu.cs:9-16).
+template <typename IT, typename OT>
+__global__ void silu_mul_kernel(const IT* __restrict__ gu, int n_partials, long long partial_stride,
+                                OT* __restrict__ out, long long total, int inter) {
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long n = idx / inter;
+    const int i = (int)(idx % inter);
+    const IT* p = gu + n * 2 * inter + i;
+    float g = 0.f, u = 0.f;
+    for (int s = 0; s < n_partials; ++s) {
+      g += to_f32(p[s * partial_stride]);
+      u += to_f32(p[s * partial_stride + inter]);
+    }
+    out[idx] = from_f32<OT>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+LLG_API int llg_silu_mul(const void* gu, int in_dtype, int n_partials, long long partial_stride, void* out,
+                         int out_dtype, int n_tokens, int inter, cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && inter > 0 && n_partials >= 1, "silu_mul: bad sizes");
+  const long long total = (long long)n_tokens * inter;
+  if (total == 0) return 0;
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+#define LAUNCH(IT, OT) \
+  silu_mul_kernel<IT, OT><<<(unsigned)blocks, threads, 0, stream>>>((const IT*)gu, n_partials, partial_stride, (OT*)out, total, inter)
+  if (in_dtype == LLG_F32 && out_dtype == LLG_F32) LAUNCH(float, float);
+  else if (in_dtype == LLG_F32 && out_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (in_dtype == LLG_BF16 && out_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return llg_fail("silu_mul: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+#undef LAUNCH
+  return llg_check_launch("silu_mul");
+}
+
+// ---- small index updates ------------------------------------------------------------
+
+__global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx,
+                                   const int* __restrict__ val, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[idx[i]] = val[i];
+}
+
+// dst[idx[i]] = val[i]: new page-table entries of a step, applied in one launch.
+LLG_API int llg_scatter_i32(int* dst, const int* idx, const int* val, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, idx, val, n);
+  return llg_check_launch("scatter_i32");
+}
+
+__global__ void zero_rows_kernel(unsigned char* __restrict__ base, const int* __restrict__ rows,
+                                 long long row_bytes) {
+  unsigned char* p = base + (long long)rows[blockIdx.x] * row_bytes;
+  for (long long i = threadIdx.x; i < row_bytes; i += blockDim.x) p[i] = 0;
+}
+
+// Zeroes the fixed-size state of the given slots (a sequence's state starts from zero).
+LLG_API int llg_zero_rows(void* base, const int* rows, int n_rows, long long row_bytes, cudaStream_t stream) {
+  if (n_rows <= 0 || row_bytes <= 0) return 0;
+  zero_rows_kernel<<<n_rows, 256, 0, stream>>>((unsigned char*)base, rows, row_bytes);
+  return llg_check_launch("zero_rows");
+}

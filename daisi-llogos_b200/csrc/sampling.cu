@@ -1,0 +1,387 @@
+// Choosing the next token on the device, one block per sequence, all arithmetic in float32.
+//
+// The pipeline is the reference sampler's (Inference/Sampler.cs:26-85): penalties over the
+// recent tokens (:89-143), greedy shortcut, temperature, top-k (:249-276), min-p (:150-170),
+// softmax over the candidates (:278-295), typical-p (:178-230), top-p (:297-332), and a draw by
+// inverse CDF from one uniform number (:334-345).  The reference sorts candidates on the host;
+// here every filter is a threshold found by bisection over the whole vocabulary, so no sort is
+// needed and nothing is truncated.  Differences that follow from that: elements that tie with
+// a threshold are all kept, and the draw walks the kept tokens in index order (the reference
+// walks them by descending probability); the distribution drawn from is the same.
+//
+// The uniform number of (seed, sequence id, step) comes from a counter-based generator, so a
+// sequence's tokens do not depend on what else is in its batch.
+#include "common.cuh"
+
+LLG_API const char* llg_last_error() { return g_llg_error; }
+
+namespace {
+
+constexpr int THREADS = 1024;
+
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+// Uniform in [0, 1) with 24 bits, a function of (seed, sequence id, step) only.
+__device__ __forceinline__ float uniform_of(unsigned long long seed, int seq_id, int step) {
+  unsigned long long h = splitmix64(seed);
+  h = splitmix64(h ^ (0xD1B54A32D192ED03ull * (unsigned long long)(seq_id + 1)));
+  h = splitmix64(h ^ (0x8CB92BA72F3D8DD7ull * (unsigned long long)(step + 1)));
+  return (float)(h >> 40) * (1.0f / 16777216.0f);
+}
+
+// Monotone map float -> unsigned: a < b  <=>  key(a) < key(b)  (no NaNs expected).
+__device__ __forceinline__ unsigned f2key(float f) {
+  unsigned u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(unsigned k) {
+  unsigned u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+  return __uint_as_float(u);
+}
+
+__device__ __forceinline__ int block_sum_int(int v, int* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  int t = lane < (THREADS >> 5) ? scratch[lane] : 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+// Lowest index among the maxima of x[0..n).
+__device__ int block_argmax(const float* __restrict__ x, int n, float* fs, int* is) {
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    const float v = x[i];
+    if (v > best || (v == best && i < bi)) {
+      best = v;
+      bi = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) {
+    fs[warp] = best;
+    is[warp] = bi;
+  }
+  __syncthreads();
+  best = lane < (THREADS >> 5) ? fs[lane] : -INFINITY;
+  bi = lane < (THREADS >> 5) ? is[lane] : 0x7fffffff;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) {
+      best = ov;
+      bi = oi;
+    }
+  }
+  if (bi == 0x7fffffff) bi = 0;  // all NaN or n == 0
+  return bi;
+}
+
+__global__ void __launch_bounds__(THREADS) argmax_kernel(const float* __restrict__ logits, int vocab,
+                                                         int* __restrict__ out) {
+  __shared__ float fs[32];
+  __shared__ int is[32];
+  const int b = blockIdx.x;
+  const int r = block_argmax(logits + (long long)b * vocab, vocab, fs, is);
+  if (threadIdx.x == 0) out[b] = r;
+}
+
+struct SampleArgs {
+  const float* logits;     // [B][V]
+  float* work;             // [B][V] scratch: scaled logits, then probabilities
+  int* out;                // [B]
+  float* probs_out;        // [B][V] or null: the distribution drawn from (for tests)
+  const int* seq_ids;      // [B] or null (then the row index)
+  const int* history;      // [B][history_stride] recent tokens, or null
+  const int* history_len;  // [B]
+  int history_stride;
+  int n_seqs, vocab;
+  float temperature;
+  int top_k;
+  float top_p, min_p, typical_p;
+  int min_keep;
+  float repetition_penalty, frequency_penalty, presence_penalty;
+  int penalize_newline;
+  unsigned long long seed;
+  int step;
+  const int* banned;       // [n_banned] tokens whose logit becomes -inf (PreventEOS), or null
+  int n_banned;
+};
+
+// k-th largest value (k >= 1) of key(x[i]) over elements with keep(i); bisection over the 32 key bits.
+template <typename KeyFn>
+__device__ unsigned kth_largest_key(int n, int k, KeyFn key, int* is) {
+  unsigned lo = 0u;  // largest t such that count(key >= t) >= k
+  for (int bit = 31; bit >= 0; --bit) {
+    const unsigned t = lo | (1u << bit);
+    int c = 0;
+    for (int i = threadIdx.x; i < n; i += THREADS) c += key(i) >= t ? 1 : 0;
+    c = block_sum_int(c, is);
+    if (c >= k) lo = t;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
+  __shared__ float fs[32];
+  __shared__ int is[32];
+  __shared__ int chosen;
+  const int b = blockIdx.x, n = a.vocab, tid = threadIdx.x;
+  const float* logits = a.logits + (long long)b * n;
+  float* w = a.work + (long long)b * n;
+
+  // 1. copy, penalties over the recent tokens, banned tokens
+  for (int i = tid; i < n; i += THREADS) w[i] = logits[i];
+  __syncthreads();
+  const bool penal = a.history && (a.repetition_penalty != 1.0f || a.frequency_penalty != 0.f ||
+                                   a.presence_penalty != 0.f);
+  if (penal) {
+    const int hl = a.history_len[b];
+    const int* hist = a.history + (long long)b * a.history_stride;
+    // One thread per distinct recent token: the first occurrence owns the token.
+    for (int j = tid; j < hl; j += THREADS) {
+      const int t = hist[j];
+      if (t < 0 || t >= n) continue;
+      if (!a.penalize_newline && (t == 10 || t == 13)) continue;
+      int count = 0;
+      bool first = true;
+      for (int q = 0; q < hl; ++q)
+        if (hist[q] == t) {
+          if (q < j) first = false;
+          ++count;
+        }
+      if (!first) continue;
+      float v = w[t];
+      if (a.repetition_penalty != 1.0f) {
+        // applied once per occurrence in the window, as the reference's loop does
+        for (int c = 0; c < count; ++c) v = v > 0.f ? v / a.repetition_penalty : v * a.repetition_penalty;
+      }
+      if (a.frequency_penalty != 0.f || a.presence_penalty != 0.f)
+        v -= a.frequency_penalty * (float)count + a.presence_penalty;
+      w[t] = v;
+    }
+    __syncthreads();
+  }
+  for (int j = tid; j < a.n_banned; j += THREADS) {
+    const int t = a.banned[j];
+    if (t >= 0 && t < n) w[t] = -INFINITY;
+  }
+  __syncthreads();
+
+  // 2. greedy
+  if (a.temperature == 0.f) {
+    const int r = block_argmax(w, n, fs, is);
+    if (tid == 0) a.out[b] = r;
+    if (a.probs_out)
+      for (int i = tid; i < n; i += THREADS) a.probs_out[(long long)b * n + i] = i == r ? 1.f : 0.f;
+    return;
+  }
+
+  // 3. temperature
+  const float inv_t = 1.0f / a.temperature;
+  float mx = -INFINITY;
+  for (int i = tid; i < n; i += THREADS) {
+    const float v = w[i] * inv_t;
+    w[i] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = block_max(mx, fs);
+  const int min_keep = a.min_keep > 1 ? a.min_keep : 1;
+
+  // 4. top-k and min-p as one lower bound on the scaled logit
+  float bound = -INFINITY;
+  if (a.top_k > 0 && a.top_k < n)
+    bound = key2f(kth_largest_key(n, a.top_k, [&](int i) { return f2key(w[i]); }, is));
+  if (a.min_p > 0.f && a.min_p < 1.0f) {
+    float mb = mx + logf(a.min_p);
+    if (min_keep > 1) {
+      const float kb = key2f(kth_largest_key(n, min(min_keep, n), [&](int i) { return f2key(w[i]); }, is));
+      mb = fminf(mb, kb);
+    }
+    bound = fmaxf(bound, mb);
+  }
+
+  // 5. softmax over the kept tokens
+  float z = 0.f;
+  for (int i = tid; i < n; i += THREADS) {
+    const float v = w[i];
+    const float e = v >= bound ? expf(v - mx) : 0.f;
+    w[i] = e;
+    z += e;
+  }
+  z = block_sum(z, fs);
+  const float inv_z = 1.0f / z;
+  for (int i = tid; i < n; i += THREADS) w[i] *= inv_z;
+  __syncthreads();
+
+  // 6. typical-p: keep the tokens whose surprise is nearest the entropy until their mass reaches typical_p
+  if (a.typical_p > 0.f && a.typical_p < 1.0f) {
+    float ent = 0.f;
+    for (int i = tid; i < n; i += THREADS) {
+      const float p = w[i];
+      if (p > 0.f) ent -= p * logf(p);
+    }
+    ent = block_sum(ent, fs);
+    auto dev = [&](int i) -> float {
+      const float p = w[i];
+      return p > 0.f ? fabsf(-logf(p) - ent) : INFINITY;
+    };
+    // least deviation (as float bits; deviations are >= 0) whose inclusive mass reaches typical_p:
+    // the largest t with mass(bits < t) < typical_p
+    unsigned thr = 0u;
+    for (int bit = 30; bit >= 0; --bit) {
+      const unsigned t = thr | (1u << bit);
+      float mass = 0.f;
+      for (int i = tid; i < n; i += THREADS)
+        if (__float_as_uint(dev(i)) < t) mass += w[i];
+      mass = block_sum(mass, fs);
+      if (mass < a.typical_p) thr = t;
+    }
+    if (min_keep > 1) {  // at least min_keep tokens: the min_keep-th smallest deviation
+      const unsigned kk = kth_largest_key(n, min(min_keep, n), [&](int i) { return ~__float_as_uint(dev(i)); }, is);
+      thr = max(thr, ~kk);
+    }
+    float s = 0.f;
+    for (int i = tid; i < n; i += THREADS) {
+      const float d = dev(i);
+      const float p = (__float_as_uint(d) <= thr) ? w[i] : 0.f;
+      s += p;
+      w[i] = p;
+    }
+    s = block_sum(s, fs);
+    if (s > 0.f) {
+      const float r = 1.0f / s;
+      for (int i = tid; i < n; i += THREADS) w[i] *= r;
+    }
+    __syncthreads();
+  }
+
+  // 7. top-p: the smallest set of most probable tokens whose mass exceeds top_p
+  if (a.top_p > 0.f && a.top_p < 1.0f) {
+    // largest t (a float's bits, probabilities are >= 0) with mass(p >= t) > top_p
+    unsigned cur = 0u;
+    for (int bit = 30; bit >= 0; --bit) {
+      const unsigned t = cur | (1u << bit);
+      float mass = 0.f;
+      for (int i = tid; i < n; i += THREADS) {
+        const float p = w[i];
+        if (p > 0.f && __float_as_uint(p) >= t) mass += p;
+      }
+      mass = block_sum(mass, fs);
+      if (mass > a.top_p) cur = t;
+    }
+    unsigned thr = cur;
+    if (min_keep > 1) {
+      const unsigned kk = kth_largest_key(n, min(min_keep, n), [&](int i) { return __float_as_uint(w[i]); }, is);
+      thr = min(thr, kk);
+    }
+    float s = 0.f;
+    for (int i = tid; i < n; i += THREADS) {
+      const float p = w[i];
+      const float q = (p > 0.f && __float_as_uint(p) >= thr) ? p : 0.f;
+      w[i] = q;
+      s += q;
+    }
+    s = block_sum(s, fs);
+    if (s > 0.f) {
+      const float r = 1.0f / s;
+      for (int i = tid; i < n; i += THREADS) w[i] *= r;
+    }
+    __syncthreads();
+  }
+  if (a.probs_out)
+    for (int i = tid; i < n; i += THREADS) a.probs_out[(long long)b * n + i] = w[i];
+
+  // 8. draw: first index whose cumulative probability exceeds u * total
+  const int seq = a.seq_ids ? a.seq_ids[b] : b;
+  const float u = uniform_of(a.seed, seq, a.step);
+  const int per = (n + THREADS - 1) / THREADS;
+  const int i0 = tid * per, i1 = min(n, i0 + per);
+  float mine = 0.f;
+  for (int i = i0; i < i1; ++i) mine += w[i];
+  // inclusive scan of the per-thread sums
+  __shared__ float scan[THREADS];
+  scan[tid] = mine;
+  __syncthreads();
+  for (int o = 1; o < THREADS; o <<= 1) {
+    const float add = tid >= o ? scan[tid - o] : 0.f;
+    __syncthreads();
+    scan[tid] += add;
+    __syncthreads();
+  }
+  const float total = scan[THREADS - 1];
+  const float target = u * total;
+  if (tid == 0) chosen = 0x7fffffff;
+  __syncthreads();
+  const float before = scan[tid] - mine;
+  if (target >= before && target < scan[tid]) {
+    float c = before;
+    int pick = -1;
+    for (int i = i0; i < i1; ++i) {
+      c += w[i];
+      if (w[i] > 0.f && target < c) {
+        pick = i;
+        break;
+      }
+    }
+    if (pick < 0)  // rounding left the target past the last token of this chunk: take its last kept token
+      for (int i = i1 - 1; i >= i0; --i)
+        if (w[i] > 0.f) {
+          pick = i;
+          break;
+        }
+    if (pick >= 0) atomicMin(&chosen, pick);
+  }
+  __syncthreads();
+  if (chosen == 0x7fffffff) {
+    // target == total through rounding: take the most probable token
+    const int r = block_argmax(w, n, fs, is);
+    if (tid == 0) chosen = r;
+    __syncthreads();
+  }
+  if (tid == 0) a.out[b] = chosen;
+}
+
+}  // namespace
+
+// out[b] = lowest index among the maxima of logits[b][:]  (greedy; Inference/Sampler.cs:234-247)
+LLG_API int llg_argmax(const float* logits, int n_seqs, int vocab, int* out, cudaStream_t stream) {
+  LLG_REQUIRE(n_seqs >= 0 && vocab > 0, "argmax: bad sizes");
+  if (n_seqs == 0) return 0;
+  argmax_kernel<<<n_seqs, THREADS, 0, stream>>>(logits, vocab, out);
+  return llg_check_launch("argmax");
+}
+
+LLG_API int llg_sample(const SampleArgs* args, cudaStream_t stream) {
+  const SampleArgs& a = *args;
+  LLG_REQUIRE(a.n_seqs >= 0 && a.vocab > 0, "sample: bad sizes");
+  LLG_REQUIRE(a.temperature >= 0.f, "sample: temperature must not be negative");
+  LLG_REQUIRE(a.work != nullptr, "sample: needs a work buffer of n_seqs * vocab floats");
+  LLG_REQUIRE(!(a.history) || (a.history_len && a.history_stride > 0), "sample: history needs lengths and a stride");
+  LLG_REQUIRE(a.repetition_penalty > 0.f, "sample: repetition penalty must be positive");
+  if (a.n_seqs == 0) return 0;
+  sample_kernel<<<a.n_seqs, THREADS, 0, stream>>>(a);
+  return llg_check_launch("sample");
+}

@@ -1,0 +1,270 @@
+"""The step function: a batch of sequences, the tokens each brings now, logits where wanted.
+
+One call runs exactly the tokens it is given, as one packed batch, against the cache that
+earlier calls left; it never re-runs old tokens and never pads.  A step in which every
+sequence brings one token takes the decode kernels (and, once a batch size has been seen, a
+CUDA graph of the whole step); any other step takes the prompt kernels.  The reference has
+four entry points for one sequence (Inference/IForwardPass.cs:8-50) and replays its token step
+as a CUDA graph (Daisi.Llogos.Cuda/CudaBackend.cs:99-141); here there is one entry point for
+a batch.
+
+All checks happen on the host before anything is launched: unknown or repeated slots, empty
+token lists, token ids outside the vocabulary, wanted positions outside the step, no room in
+the cache.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.slots import CacheError
+from ..cache.store import PAGE, SequenceCache
+from .context import StepContext, Workspace
+from .model import DecoderModel
+
+_TILE_Q = 16   # queries per block of the prompt attention kernel
+
+
+class StepError(ValueError):
+    """A step was asked for that cannot run; nothing was launched and the cache is unchanged."""
+
+
+class _Staging:
+    """Pinned host buffers that alternate, so that filling one never races a copy still in flight."""
+
+    def __init__(self, device: torch.device, depth: int = 3):
+        self.device = device
+        self.cuda = device.type == "cuda"
+        self.bufs: List[Optional[torch.Tensor]] = [None] * depth
+        self.events: List[Optional[torch.cuda.Event]] = [None] * depth
+        self.i = 0
+
+    def upload(self, host: np.ndarray, dst: torch.Tensor) -> None:
+        n = host.size
+        self.i = (self.i + 1) % len(self.bufs)
+        buf = self.bufs[self.i]
+        if self.events[self.i] is not None:
+            self.events[self.i].synchronize()
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 256), dtype=torch.int32, pin_memory=self.cuda)
+            self.bufs[self.i] = buf
+        buf[:n].numpy()[:] = host
+        dst[:n].copy_(buf[:n], non_blocking=True)
+        if self.cuda:
+            ev = self.events[self.i] or torch.cuda.Event()
+            ev.record()
+            self.events[self.i] = ev
+
+
+class _DecodeState:
+    """Static buffers (and later the CUDA graph) of decode steps of one batch size."""
+
+    def __init__(self, b: int, device: torch.device):
+        self.b = b
+        self.meta = torch.zeros(6 * b + 1, dtype=torch.int32, device=device)
+        self.workspace = Workspace(device)
+        self.rows = torch.arange(b, dtype=torch.int32, device=device)
+        self.graph = None
+        self.logits: Optional[torch.Tensor] = None
+        self.eager_runs = 0
+
+
+class Engine:
+    """A model, its cache and the step function.
+
+    ``max_tokens``: tokens that live sequences may hold together, each rounded up to whole pages
+    of 64.  ``max_seq_len``: longest single sequence (default: the smaller of the model's
+    position limit and ``max_tokens``).  ``n_slots``: most sequences alive at once.
+    """
+
+    def __init__(self, model: DecoderModel, *, max_tokens: int, max_seq_len: Optional[int] = None,
+                 n_slots: Optional[int] = None, use_graphs: bool = True):
+        self.model = model
+        self.device = model.device
+        self.dtype = model.dtype
+        self.ops = model.env.ops
+        n_pages = (max_tokens + PAGE - 1) // PAGE
+        if max_seq_len is None:
+            max_seq_len = min(model.spec.max_positions, n_pages * PAGE)
+        if n_slots is None:
+            n_slots = max(1, min(n_pages, 1024))
+        self.cache = SequenceCache(model.cache_needs(), max_tokens=max_tokens, max_seq_len=max_seq_len,
+                                   n_slots=n_slots, dtype=self.dtype, device=self.device)
+        model.prepare(self.cache.max_seq_len)
+        self.vocab = model.spec.vocab_size
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self._staging = _Staging(self.device)
+        self._meta = torch.zeros(1024, dtype=torch.int32, device=self.device)
+        self._workspace = Workspace(self.device)
+        self._decode: Dict[int, _DecodeState] = {}
+        self.launch_count = 0       # kernels and graph launches issued by step(), for reporting
+
+    # ---- sequences -----------------------------------------------------------------------
+    def open(self) -> int:
+        """Starts a sequence: returns its slot (length 0)."""
+        return self.cache.acquire()
+
+    def close(self, slot: int) -> None:
+        """Ends a sequence: its slot and pages go back to the free lists."""
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ------------------------------------------------------------------------
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """Runs ``tokens`` of every ``(slot, tokens)`` entry; returns float32 logits ``[n_wanted, vocab]``.
+
+        ``want[i]`` lists positions among entry i's tokens (0-based) whose logits are returned, in
+        the order of the entries and of ``want``; ``None`` means the last token of every entry.
+        The returned tensor is valid until the next call of ``step``.
+        """
+        if len(entries) == 0:
+            raise StepError("a step needs at least one sequence")
+        slots = [int(s) for s, _ in entries]
+        toks = [np.asarray(t, dtype=np.int64).reshape(-1) for _, t in entries]
+        counts = [int(t.size) for t in toks]
+        if want is None:
+            want = [[c - 1] for c in counts]
+        if len(want) != len(entries):
+            raise StepError("want must have one list per entry")
+        for i, (t, c) in enumerate(zip(toks, counts)):
+            if c == 0:
+                raise StepError(f"entry {i} (slot {slots[i]}) brings no tokens")
+            if t.min() < 0 or t.max() >= self.vocab:
+                bad = int(t[(t < 0) | (t >= self.vocab)][0])
+                raise StepError(f"entry {i} (slot {slots[i]}): token id {bad} is outside the vocabulary [0, {self.vocab})")
+            for w in want[i]:
+                if not 0 <= int(w) < c:
+                    raise StepError(f"entry {i} (slot {slots[i]}): wanted position {w} is outside its {c} tokens")
+        growth = list(zip(slots, counts))
+        try:
+            self.cache.check_room(growth)
+        except CacheError as e:
+            raise StepError(str(e)) from None
+
+        len_before = [self.cache.length(s) for s in slots]
+        updates = self.cache.grow(growth)
+        b = len(entries)
+        decode = all(c == 1 for c in counts)
+        if decode:
+            logits = self._decode_step(b, slots, toks, len_before, updates, want)
+        else:
+            logits = self._prompt_step(b, slots, toks, counts, len_before, updates, want)
+        self.cache.commit(growth)
+        return logits
+
+    # ---- page-table updates ----------------------------------------------------------------
+    def _apply_updates(self, updates, extra_host: List[np.ndarray]) -> List[Tuple[object, int, int]]:
+        """Appends (index, value) lists to the host block; returns (group, offset, n) per group."""
+        plan = []
+        off = sum(a.size for a in extra_host)
+        for g, ups in updates:
+            if not ups:
+                continue
+            idx = np.fromiter((u[0] for u in ups), dtype=np.int32, count=len(ups))
+            val = np.fromiter((u[1] for u in ups), dtype=np.int32, count=len(ups))
+            extra_host.append(idx)
+            extra_host.append(val)
+            plan.append((g, off, len(ups)))
+            off += 2 * len(ups)
+        return plan
+
+    def _ensure_meta(self, n: int) -> torch.Tensor:
+        if self._meta.numel() < n:
+            self._meta = torch.zeros(max(n, 2 * self._meta.numel()), dtype=torch.int32, device=self.device)
+        return self._meta
+
+    # ---- prompt step -----------------------------------------------------------------------
+    def _prompt_step(self, b, slots, toks, counts, len_before, updates, want) -> torch.Tensor:
+        n = sum(counts)
+        cu = np.zeros(b + 1, dtype=np.int32)
+        np.cumsum(counts, out=cu[1:])
+        token_ids = np.concatenate(toks).astype(np.int32)
+        positions = np.concatenate([np.arange(lb, lb + c, dtype=np.int32) for lb, c in zip(len_before, counts)])
+        seq_of = np.repeat(np.arange(b, dtype=np.int32), counts)
+        tiles = np.array([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, _TILE_Q)],
+                         dtype=np.int32).reshape(-1)
+        rows = np.array([cu[i] + int(w) for i in range(b) for w in want[i]], dtype=np.int32)
+        host = [token_ids, positions, seq_of, np.asarray(slots, dtype=np.int32), cu,
+                np.asarray(len_before, dtype=np.int32), tiles, rows]
+        plan = self._apply_updates(updates, host)
+        block = np.concatenate(host)
+        meta = self._ensure_meta(block.size)
+        self._staging.upload(block, meta)
+        o = 0
+
+        def take(k):
+            nonlocal o
+            v = meta[o:o + k]
+            o += k
+            return v
+
+        ctx = StepContext(
+            n_tokens=n, n_seqs=b, decode=False, counts=counts, max_count=max(counts),
+            token_ids=take(n), positions=take(n), seq_of_token=take(n), slots=take(b), cu_tokens=take(b + 1),
+            len_before=take(b), prefill_tiles=take(tiles.size).view(-1, 2), dtype=self.dtype, device=self.device,
+            ops=self.ops, workspace=self._workspace,
+            max_len_after=max(lb + c for lb, c in zip(len_before, counts)))
+        rows_dev = take(rows.size)
+        for g, off, k in plan:
+            self.ops.scatter_i32(g.page_table, meta[off:off + k], meta[off + k:off + 2 * k])
+        return self.model.forward(ctx, self.cache, rows_dev)
+
+    # ---- decode step -----------------------------------------------------------------------
+    def _decode_step(self, b, slots, toks, len_before, updates, want) -> torch.Tensor:
+        st = self._decode.get(b)
+        if st is None:
+            st = self._decode[b] = _DecodeState(b, self.device)
+        token_ids = np.concatenate(toks).astype(np.int32)
+        ar = np.arange(b, dtype=np.int32)
+        lb = np.asarray(len_before, dtype=np.int32)
+        # layout: token_ids | positions | seq_of_token | slots | cu_tokens (b + 1) | len_before
+        host = [token_ids, lb, ar, np.asarray(slots, dtype=np.int32), np.arange(b + 1, dtype=np.int32), lb]
+        fixed = 6 * b + 1
+        plan = self._apply_updates(updates, host)
+        block = np.concatenate(host)
+        if plan:
+            # page-table updates travel through the general buffer, the fixed part through the static one
+            meta2 = self._ensure_meta(block.size)
+            self._staging.upload(block, meta2)
+            for g, off, k in plan:
+                self.ops.scatter_i32(g.page_table, meta2[off:off + k], meta2[off + k:off + 2 * k])
+            st.meta.copy_(meta2[:fixed], non_blocking=True)
+        else:
+            self._staging.upload(block, st.meta)
+        m = st.meta
+        if st.graph is not None:
+            st.graph.replay()
+            self.launch_count += 1
+            logits = st.logits
+        else:
+            ctx = StepContext(
+                n_tokens=b, n_seqs=b, decode=True, counts=[1] * b, max_count=1,
+                token_ids=m[0:b], positions=m[b:2 * b], seq_of_token=m[2 * b:3 * b], slots=m[3 * b:4 * b],
+                cu_tokens=m[4 * b:5 * b + 1], len_before=m[5 * b + 1:6 * b + 1], prefill_tiles=None,
+                dtype=self.dtype, device=self.device, ops=self.ops, workspace=st.workspace,
+                max_len_after=self.cache.max_seq_len)
+            if self.use_graphs and st.eager_runs >= 1:
+                # the buffers exist since the eager run; record the same launches and replay them
+                graph = torch.cuda.CUDAGraph()
+                st.workspace.frozen = True
+                with torch.cuda.graph(graph):
+                    st.logits = self.model.forward(ctx, self.cache, st.rows)
+                st.graph = graph
+                graph.replay()
+                self.launch_count += 1
+                logits = st.logits
+            else:
+                logits = self.model.forward(ctx, self.cache, st.rows)
+                st.eager_runs += 1
+        flat_want = [(i, int(w)) for i in range(b) for w in want[i]]
+        if len(flat_want) == b and all(i == j for j, (i, _) in enumerate(flat_want)):
+            return logits
+        if not flat_want:
+            return logits[:0]
+        idx = torch.tensor([i for i, _ in flat_want], dtype=torch.long, device=self.device)
+        return logits.index_select(0, idx)

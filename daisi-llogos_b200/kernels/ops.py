@@ -1,0 +1,356 @@
+"""Python face of the CUDA kernels: every function takes torch CUDA tensors, checks them,
+and launches on the current stream.  Nothing here computes on the CPU, and nothing falls
+back: a tensor that is not on the GPU, or a library that cannot be built, is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_library
+
+F32, BF16 = 0, 1
+PAGE = 64  # tokens per cache page; checked against the library at first use
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _ptr(t: Optional[torch.Tensor], dtype=None) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("a kernel was given a tensor that is not on the GPU; there is no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"a kernel was given a non-contiguous tensor of shape {tuple(t.shape)}")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"expected {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(lib, rc: int) -> None:
+    if rc != 0:
+        raise KernelError(lib.llg_last_error().decode("utf-8", "replace"))
+
+
+# ---- libraries and prototypes ---------------------------------------------------------
+
+class _QkPrepArgs(Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("qkv_dtype", c_int), ("n_partials", c_int), ("partial_stride", c_longlong),
+        ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("norm_w_dtype", c_int), ("norm_eps", c_float),
+        ("bias", c_void_p), ("bias_dtype", c_int),
+        ("cos_table", c_void_p), ("sin_table", c_void_p), ("rotary_dim", c_int), ("pairing", c_int),
+        ("table_positions", c_int), ("positions", c_void_p),
+        ("q_out", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p),
+        ("k_pages", c_void_p), ("v_pages", c_void_p), ("page_table", c_void_p),
+        ("table_width", c_int), ("ring_pages", c_int),
+        ("seq_of_token", c_void_p), ("slots", c_void_p),
+        ("n_tokens", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int),
+    ]
+
+
+class _PrefillArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p), ("k_pages", c_void_p), ("v_pages", c_void_p),
+        ("page_table", c_void_p), ("table_width", c_int), ("ring_pages", c_int),
+        ("tiles", c_void_p), ("cu_tokens", c_void_p), ("len_before", c_void_p), ("slots", c_void_p),
+        ("out", c_void_p),
+        ("n_tiles", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int),
+        ("scale", c_float), ("window", c_int),
+    ]
+
+
+class _DecodeArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k_pages", c_void_p), ("v_pages", c_void_p), ("page_table", c_void_p),
+        ("table_width", c_int), ("ring_pages", c_int), ("slots", c_void_p), ("len_before", c_void_p),
+        ("part_o", c_void_p), ("part_ml", c_void_p),
+        ("n_seqs", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("n_splits", c_int),
+        ("scale", c_float), ("window", c_int),
+    ]
+
+
+class _SampleArgs(Structure):
+    _fields_ = [
+        ("logits", c_void_p), ("work", c_void_p), ("out", c_void_p), ("probs_out", c_void_p),
+        ("seq_ids", c_void_p), ("history", c_void_p), ("history_len", c_void_p), ("history_stride", c_int),
+        ("n_seqs", c_int), ("vocab", c_int),
+        ("temperature", c_float), ("top_k", c_int),
+        ("top_p", c_float), ("min_p", c_float), ("typical_p", c_float), ("min_keep", c_int),
+        ("repetition_penalty", c_float), ("frequency_penalty", c_float), ("presence_penalty", c_float),
+        ("penalize_newline", c_int), ("seed", c_ulonglong), ("step", c_int),
+        ("banned", c_void_p), ("n_banned", c_int),
+    ]
+
+
+_protos_done = set()
+
+
+def _lib(name: str):
+    lib = load_library(name)
+    if name in _protos_done:
+        return lib
+    if name == "elementwise":
+        lib.llg_page_size.restype = c_int
+        if lib.llg_page_size() != PAGE:
+            raise KernelError(f"the kernels use pages of {lib.llg_page_size()} tokens, Python expects {PAGE}")
+        lib.llg_embed_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.llg_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float,
+                                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
+        lib.llg_qk_prep.argtypes = [POINTER(_QkPrepArgs), c_int, c_void_p]
+        lib.llg_kv_write.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_silu_mul.argtypes = [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.llg_scatter_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        lib.llg_zero_rows.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
+    elif name == "gemm_simt":
+        lib.llg_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    elif name == "attention_simt":
+        lib.llg_attn_prefill_simt.argtypes = [POINTER(_PrefillArgs), c_int, c_void_p]
+        lib.llg_attn_decode_simt.argtypes = [POINTER(_DecodeArgs), c_void_p, c_int, c_void_p]
+        lib.llg_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+        lib.llg_attn_decode_scratch_floats.restype = c_longlong
+    elif name == "sampling":
+        lib.llg_argmax.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p]
+        lib.llg_sample.argtypes = [POINTER(_SampleArgs), c_void_p]
+    _protos_done.add(name)
+    return lib
+
+
+def require_gpu() -> None:
+    """Fails loudly when there is no GPU or the kernels cannot be loaded."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device: this library runs on the GPU only and has no CPU path")
+    _lib("elementwise")
+
+
+# ---- kernels ------------------------------------------------------------------------
+
+def embed_rows(table: torch.Tensor, token_ids: torch.Tensor, out_residual: torch.Tensor) -> None:
+    """out_residual[n] = table[token_ids[n]] as float32."""
+    lib = _lib("elementwise")
+    vocab, hidden = table.shape
+    n = token_ids.numel()
+    assert out_residual.shape == (n, hidden)
+    _check(lib, lib.llg_embed_rows(_ptr(table), _dt(table), _ptr(token_ids, torch.int32),
+                                   _ptr(out_residual, torch.float32), n, hidden, vocab, _stream()))
+
+
+def add_rmsnorm(residual: torch.Tensor, branch: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """residual += sum of branch partials (if any); out[j] = RMSNorm(residual[rows[j] or j]) * weight.
+
+    ``residual`` is float32 ``[N, H]``; ``branch`` float32 ``[S, N, H]`` or None; ``out`` ``[M, H]``.
+    """
+    lib = _lib("elementwise")
+    n, hidden = residual.shape
+    m = out.shape[0]
+    assert out.shape[1] == hidden and weight.shape == (hidden,)
+    if rows is not None:
+        assert rows.numel() == m
+    else:
+        assert m == n
+    n_part, stride = 0, 0
+    if branch is not None:
+        assert branch.dim() == 3 and branch.shape[1:] == (n, hidden), (branch.shape, residual.shape)
+        n_part, stride = branch.shape[0], n * hidden
+    _check(lib, lib.llg_add_rmsnorm(_ptr(residual, torch.float32), _ptr(branch, torch.float32), n_part, stride,
+                                    _ptr(weight), _dt(weight), float(eps), _ptr(out), _dt(out),
+                                    _ptr(rows, torch.int32), m, hidden, _stream()))
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, o] = sum_k x[n, k] w[o, k] on the CUDA cores, float32 accumulation."""
+    lib = _lib("gemm_simt")
+    n, k = x.shape
+    o, k2 = w.shape
+    assert k == k2 and out.shape == (n, o), (x.shape, w.shape, out.shape)
+    _check(lib, lib.llg_gemm_simt(_ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(out), _dt(out), n, o, k, _stream()))
+
+
+def qk_prep(qkv: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
+            q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], norm_eps: float,
+            bias: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+            rotary_dim: int, pairing: int, positions: torch.Tensor, q_out: torch.Tensor,
+            k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
+            k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+            page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
+            seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
+    """Per-head norm (optional), bias (optional), rotation, and the writes of q, k, v.
+
+    ``qkv`` is ``[S, N, (nh + 2 nkv) * hd]`` (partials are summed).  Queries go to ``q_out``;
+    keys and values go to ``k_new``/``v_new`` (packed, for a prompt step) and/or straight into
+    the cache pages (for a one-token step).
+    """
+    lib = _lib("elementwise")
+    s, n, width = qkv.shape
+    assert width == (n_heads + 2 * n_kv_heads) * head_dim
+    a = _QkPrepArgs()
+    a.qkv, a.qkv_dtype, a.n_partials, a.partial_stride = _ptr(qkv), _dt(qkv), s, n * width
+    a.q_norm_w, a.k_norm_w = _ptr(q_norm_w), _ptr(k_norm_w)
+    a.norm_w_dtype = _dt(q_norm_w) if q_norm_w is not None else F32
+    a.norm_eps = float(norm_eps)
+    a.bias = _ptr(bias)
+    a.bias_dtype = _dt(bias) if bias is not None else F32
+    if cos is not None:
+        assert cos.shape == sin.shape and cos.shape[1] * 2 == rotary_dim
+        a.cos_table, a.sin_table = _ptr(cos, torch.float32), _ptr(sin, torch.float32)
+        a.table_positions = cos.shape[0]
+    a.rotary_dim, a.pairing = rotary_dim, pairing
+    a.positions = _ptr(positions, torch.int32)
+    a.q_out, a.k_new, a.v_new = _ptr(q_out), _ptr(k_new), _ptr(v_new)
+    a.k_pages, a.v_pages = _ptr(k_pages), _ptr(v_pages)
+    if page_table is not None:
+        a.page_table, a.table_width = _ptr(page_table, torch.int32), page_table.shape[1]
+    a.ring_pages = ring_pages
+    a.seq_of_token, a.slots = _ptr(seq_of_token, torch.int32), _ptr(slots, torch.int32)
+    a.n_tokens, a.nh, a.nkv, a.hd = n, n_heads, n_kv_heads, head_dim
+    for t in (k_new, v_new, k_pages, v_pages):
+        if t is not None and t.dtype != q_out.dtype:
+            raise KernelError("qk_prep: all outputs must share one dtype")
+    _check(lib, lib.llg_qk_prep(byref(a), _dt(q_out), _stream()))
+
+
+def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, seq_of_token, slots,
+             cu_tokens, len_before) -> None:
+    """Copies a prompt step's packed keys/values ``[N, nkv, hd]`` into the cache pages."""
+    lib = _lib("elementwise")
+    n, nkv, hd = k_new.shape
+    assert k_pages.dtype == k_new.dtype == v_new.dtype == v_pages.dtype
+    _check(lib, lib.llg_kv_write(_ptr(k_new), _ptr(v_new), _ptr(k_pages), _ptr(v_pages),
+                                 _ptr(page_table, torch.int32), page_table.shape[1], ring_pages,
+                                 _ptr(positions, torch.int32), _ptr(seq_of_token, torch.int32),
+                                 _ptr(slots, torch.int32), _ptr(cu_tokens, torch.int32),
+                                 _ptr(len_before, torch.int32), n, nkv, hd, _dt(k_new), _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, i] = silu(g) * u, g and u the two halves of the summed partials ``[S, N, 2I]``."""
+    lib = _lib("elementwise")
+    s, n, two_i = gate_up.shape
+    inter = two_i // 2
+    assert out.shape == (n, inter) and two_i == 2 * inter
+    _check(lib, lib.llg_silu_mul(_ptr(gate_up), _dt(gate_up), s, n * two_i, _ptr(out), _dt(out), n, inter, _stream()))
+
+
+def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None:
+    """dst.flat[idx[i]] = val[i]."""
+    lib = _lib("elementwise")
+    assert idx.numel() == val.numel()
+    _check(lib, lib.llg_scatter_i32(_ptr(dst, torch.int32), _ptr(idx, torch.int32), _ptr(val, torch.int32),
+                                    idx.numel(), _stream()))
+
+
+def zero_rows(base: torch.Tensor, rows: torch.Tensor) -> None:
+    """Zeroes ``base[rows[i]]`` for a 2-D (or flattened-per-row) tensor."""
+    lib = _lib("elementwise")
+    row_bytes = (base.numel() // base.shape[0]) * base.element_size() if base.shape[0] else 0
+    _check(lib, lib.llg_zero_rows(_ptr(base), _ptr(rows, torch.int32), rows.numel(), row_bytes, _stream()))
+
+
+def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tiles, cu_tokens, len_before,
+                 slots, out, *, scale: float, window: int) -> None:
+    """Causal attention for a step with several tokens per sequence (see csrc/attention_simt.cu)."""
+    lib = _lib("attention_simt")
+    n, nh, hd = q.shape
+    nkv = k_new.shape[1]
+    assert out.shape == (n, nh * hd)
+    a = _PrefillArgs()
+    a.q, a.k_new, a.v_new = _ptr(q), _ptr(k_new, q.dtype), _ptr(v_new, q.dtype)
+    a.k_pages, a.v_pages = _ptr(k_pages, q.dtype), _ptr(v_pages, q.dtype)
+    a.page_table, a.table_width, a.ring_pages = _ptr(page_table, torch.int32), page_table.shape[1], ring_pages
+    a.tiles, a.cu_tokens = _ptr(tiles, torch.int32), _ptr(cu_tokens, torch.int32)
+    a.len_before, a.slots = _ptr(len_before, torch.int32), _ptr(slots, torch.int32)
+    a.out = _ptr(out, q.dtype)
+    a.n_tiles, a.nh, a.nkv, a.hd = tiles.shape[0], nh, nkv, hd
+    a.scale, a.window = float(scale), int(window)
+    _check(lib, lib.llg_attn_prefill_simt(byref(a), _dt(q), _stream()))
+
+
+PREFILL_QUERIES_PER_TILE = 16
+
+
+def attn_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
+    return _lib("attention_simt").llg_attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)
+
+
+def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
+                n_splits: int, scale: float, window: int) -> None:
+    """Attention of one new token per sequence over the cache; ``scratch`` holds the split partials."""
+    lib = _lib("attention_simt")
+    b, nh, hd = q.shape
+    nkv = k_pages.shape[1]
+    need = b * nh * n_splits * (hd + 2)
+    if scratch.numel() < need or scratch.dtype != torch.float32:
+        raise KernelError(f"attn_decode: scratch of {scratch.numel()} floats, {need} needed")
+    a = _DecodeArgs()
+    a.q, a.k_pages, a.v_pages = _ptr(q), _ptr(k_pages, q.dtype), _ptr(v_pages, q.dtype)
+    a.page_table, a.table_width, a.ring_pages = _ptr(page_table, torch.int32), page_table.shape[1], ring_pages
+    a.slots, a.len_before = _ptr(slots, torch.int32), _ptr(len_before, torch.int32)
+    base = _ptr(scratch)
+    a.part_o = base
+    a.part_ml = base + 4 * b * nh * n_splits * hd
+    a.n_seqs, a.nh, a.nkv, a.hd, a.n_splits = b, nh, nkv, hd, n_splits
+    a.scale, a.window = float(scale), int(window)
+    _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()))
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    lib = _lib("sampling")
+    b, v = logits.shape
+    _check(lib, lib.llg_argmax(_ptr(logits, torch.float32), b, v, _ptr(out, torch.int32), _stream()))
+
+
+def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k: int = 0,
+           top_p: float = 1.0, min_p: float = 0.0, typical_p: float = 1.0, min_keep: int = 1,
+           repetition_penalty: float = 1.0, frequency_penalty: float = 0.0, presence_penalty: float = 0.0,
+           penalize_newline: bool = False, seed: int = 0, step: int = 0,
+           seq_ids: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None,
+           history_len: Optional[torch.Tensor] = None, banned: Optional[torch.Tensor] = None,
+           probs_out: Optional[torch.Tensor] = None) -> None:
+    """One token per row of ``logits`` by the sampling pipeline of csrc/sampling.cu."""
+    lib = _lib("sampling")
+    b, v = logits.shape
+    assert work.numel() >= b * v and work.dtype == torch.float32
+    a = _SampleArgs()
+    a.logits, a.work, a.out = _ptr(logits, torch.float32), _ptr(work), _ptr(out, torch.int32)
+    a.probs_out = _ptr(probs_out, torch.float32)
+    a.seq_ids = _ptr(seq_ids, torch.int32)
+    if history is not None:
+        a.history, a.history_len = _ptr(history, torch.int32), _ptr(history_len, torch.int32)
+        a.history_stride = history.shape[1]
+    a.n_seqs, a.vocab = b, v
+    a.temperature, a.top_k = float(temperature), int(top_k)
+    a.top_p, a.min_p, a.typical_p, a.min_keep = float(top_p), float(min_p), float(typical_p), int(min_keep)
+    a.repetition_penalty = float(repetition_penalty)
+    a.frequency_penalty, a.presence_penalty = float(frequency_penalty), float(presence_penalty)
+    a.penalize_newline = int(bool(penalize_newline))
+    a.seed, a.step = int(seed) & 0xFFFFFFFFFFFFFFFF, int(step)
+    if banned is not None and banned.numel():
+        a.banned, a.n_banned = _ptr(banned, torch.int32), banned.numel()
+    _check(lib, lib.llg_sample(byref(a), _stream()))

@@ -1,0 +1,26 @@
+"""Arrangements of norms, a mixer and a feed-forward around the residual stream.
+
+``PreNormBlock`` is the reference's order (Inference/ForwardPass.cs:215-250): the output of the
+previous feed-forward is added to the residual inside this block's first norm; the attention
+output is added inside the second norm; the block returns its feed-forward output still to
+be added (by the next block's first norm, or by the model's final norm).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+from .base import Block, Branch, register_part
+
+
+class PreNormBlock(Block):
+    """roles: norm1, mixer, norm2, ffn."""
+
+    def forward(self, residual, pending: Optional[Branch], ctx, cache) -> Optional[Branch]:
+        p = self.parts
+        h = p["norm1"].forward(residual, pending, ctx)
+        a = p["mixer"].forward(h, ctx, cache)
+        h = p["norm2"].forward(residual, a, ctx)
+        return p["ffn"].forward(h, ctx)
+
+
+register_part("block", "prenorm", PreNormBlock)
