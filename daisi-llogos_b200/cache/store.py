@@ -111,6 +111,7 @@ class SequenceCache:
             raise ValueError("max_tokens, max_seq_len and n_slots must be positive")
         self.dtype = dtype
         self.device = device
+        self.page = PAGE
         self.n_pages = pages_for(max_tokens)
         self.max_seq_len = min(max_seq_len, self.n_pages * PAGE)
         self.slots = SlotTable(n_slots)

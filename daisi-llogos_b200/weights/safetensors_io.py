@@ -84,10 +84,8 @@ class SafetensorsFile:
         return t.view(shape)
 
     def close(self) -> None:
-        try:
-            self._mm.close()
-        except BufferError:
-            pass  # views of the mapping are still alive; the OS unmaps at exit
+        """Closes the file.  The mapping itself lives as long as tensors view it (they hold a
+        reference to it) and is unmapped when the last of them is gone."""
         self._f.close()
 
 

@@ -1,0 +1,123 @@
+"""The step function's host logic, run on CPU tensors with stand-ins for the kernels (no GPU):
+what it checks before launching, how it lays tokens out, how slots and pages come back."""
+import pytest
+import torch
+
+import cpu_ops
+import plain_model as P
+from conftest import TINY, read_weights, random_tokens
+
+
+@pytest.fixture(scope="module")
+def setup(llogos, model_dirs):
+    out = {}
+    for name in TINY:
+        model = llogos.weights.load_model(model_dirs[name], dtype=torch.float32, device="cpu", ops=cpu_ops)
+        out[name] = (model, read_weights(llogos, model_dirs[name]))
+    return out
+
+
+def engine_for(llogos, model, **kw):
+    kw.setdefault("max_tokens", 64 * 12)
+    return llogos.engine.Engine(model, use_graphs=False, **kw)
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_schedules_agree_with_plain(llogos, setup, name):
+    model, w = setup[name]
+    cfg = TINY[name]
+    eng = engine_for(llogos, model)
+    seqs = random_tokens(cfg["vocab_size"], [3, 70, 33, 100], 5)
+    refs = [P.forward(w, cfg, s) for s in seqs]
+    tol = 2e-4
+    for s, r in zip(seqs, refs):                       # each alone and whole
+        slot = eng.open()
+        lg = eng.step([(slot, s)], [list(range(len(s)))])
+        assert float((lg.double() - r).abs().max()) < tol
+        eng.close(slot)
+    for rnd in range(2):                               # unequal batch, decoded on, shorter ones end earlier
+        slots = [eng.open() for _ in seqs]
+        cut = [max(1, len(s) - 3 - i) for i, s in enumerate(seqs)]
+        lg = eng.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)])
+        for i, (s, c) in enumerate(zip(seqs, cut)):
+            assert float((lg[i].double() - refs[i][c - 1]).abs().max()) < tol
+        pos = list(cut)
+        live = list(range(len(seqs)))
+        while live:
+            lg = eng.step([(slots[i], [seqs[i][pos[i]]]) for i in live])
+            for j, i in enumerate(live):
+                assert float((lg[j].double() - refs[i][pos[i]]).abs().max()) < tol
+                pos[i] += 1
+            for i in [i for i in live if pos[i] == len(seqs[i])]:
+                eng.close(slots[i])
+            live = [i for i in live if pos[i] < len(seqs[i])]
+        eng.cache.audit()
+    assert eng.cache.slots.free_count == eng.cache.slots.n_slots
+
+
+def test_chunked_prompt_and_mixed_step(llogos, setup):
+    model, w = setup["qwen2"]
+    cfg = TINY["qwen2"]
+    eng = engine_for(llogos, model)
+    a, b = random_tokens(cfg["vocab_size"], [150, 20], 6)
+    ra, rb = P.forward(w, cfg, a), P.forward(w, cfg, b)
+    sa, sb = eng.open(), eng.open()
+    eng.step([(sa, a[:90])], [[]])
+    lg = eng.step([(sa, a[90:]), (sb, b)], [[0, 59], [19]])           # a continues while b starts
+    assert float((lg[0].double() - ra[90]).abs().max()) < 2e-4
+    assert float((lg[1].double() - ra[149]).abs().max()) < 2e-4
+    assert float((lg[2].double() - rb[19]).abs().max()) < 2e-4
+
+
+def test_errors_come_before_any_launch(llogos, setup):
+    model, _ = setup["llama"]
+    eng = engine_for(llogos, model, max_tokens=64 * 3, n_slots=2)
+    E = llogos.engine.StepError
+    s = eng.open()
+    with pytest.raises(E, match="at least one sequence"):
+        eng.step([])
+    with pytest.raises(E, match="no tokens"):
+        eng.step([(s, [])])
+    with pytest.raises(E, match="outside the vocabulary"):
+        eng.step([(s, [1, 256])])
+    with pytest.raises(E, match="outside the vocabulary"):
+        eng.step([(s, [-1])])
+    with pytest.raises(E, match="wanted position"):
+        eng.step([(s, [1, 2])], [[2]])
+    with pytest.raises(E, match="twice"):
+        eng.step([(s, [1]), (s, [2])])
+    with pytest.raises(E, match="not in use"):
+        eng.step([(1, [1])])
+    with pytest.raises(E, match="longest sequence|cache full"):
+        eng.step([(s, [1] * (64 * 3 + 1))])
+    assert eng.length(s) == 0                       # nothing happened
+    eng.step([(s, [1] * 130)])
+    t = eng.open()
+    with pytest.raises(E, match="cache full"):
+        eng.step([(t, [1] * 1)])
+    eng.close(s)
+    eng.step([(t, [1] * 65)])
+    eng.cache.audit()
+
+
+def test_padding_free_layout(llogos, setup):
+    """Exactly the given tokens run: the packed layout has no padding rows."""
+    model, _ = setup["llama"]
+    eng = engine_for(llogos, model)
+    seen = {}
+    real = cpu_ops.embed_rows
+
+    class Spy:
+        def __getattr__(self, k):
+            return getattr(cpu_ops, k)
+
+        def embed_rows(self, table, ids, out):
+            seen["n"] = ids.numel()
+            return real(table, ids, out)
+
+    eng.ops = Spy()
+    s1, s2, s3 = eng.open(), eng.open(), eng.open()
+    eng.step([(s1, [1] * 5), (s2, [2] * 9), (s3, [3] * 13)])
+    assert seen["n"] == 27
+    eng.step([(s1, [1]), (s3, [3])])
+    assert seen["n"] == 2

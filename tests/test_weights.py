@@ -1,0 +1,134 @@
+"""Safetensors input/output, the checked loader and random initialisation (no GPU)."""
+import json
+import os
+import shutil
+
+import pytest
+import torch
+
+import cpu_ops
+from conftest import INIT, TINY_LLAMA, TINY_QWEN3, read_weights
+
+
+def test_safetensors_round_trip(llogos, tmp_path):
+    W = llogos.weights
+    t = {"a.weight": torch.randn(3, 5).to(torch.bfloat16), "b": torch.arange(7, dtype=torch.int32),
+         "c.f32": torch.randn(4, 2), "d.f16": torch.randn(2, 2).to(torch.float16)}
+    path = str(tmp_path / "x.safetensors")
+    W.write_safetensors(path, t, {"note": "hi"})
+    f = W.SafetensorsFile(path)
+    assert set(f.names()) == set(t)
+    assert f.metadata["note"] == "hi"
+    for n, v in t.items():
+        got = f.tensor(n)
+        assert got.dtype == v.dtype and got.shape == v.shape and torch.equal(got, v)
+
+
+def test_safetensors_is_readable_by_the_safetensors_package(llogos, tmp_path):
+    st = pytest.importorskip("safetensors.torch")
+    t = {"w": torch.randn(6, 4).to(torch.bfloat16), "v": torch.randn(3)}
+    path = str(tmp_path / "y.safetensors")
+    llogos.weights.write_safetensors(path, t)
+    back = st.load_file(path)
+    assert all(torch.equal(back[n], t[n]) for n in t)
+    st.save_file(t, str(tmp_path / "z.safetensors"))
+    f = llogos.weights.SafetensorsFile(str(tmp_path / "z.safetensors"))
+    assert all(torch.equal(f.tensor(n), t[n]) for n in t)
+
+
+def test_bad_files(llogos, tmp_path):
+    W = llogos.weights
+    p = tmp_path / "short.safetensors"
+    p.write_bytes(b"abc")
+    with pytest.raises(W.SafetensorsError):
+        W.SafetensorsFile(str(p))
+    p = tmp_path / "hdr.safetensors"
+    p.write_bytes((1000).to_bytes(8, "little") + b"{}")
+    with pytest.raises(W.SafetensorsError):
+        W.SafetensorsFile(str(p))
+    with pytest.raises(W.SafetensorsError):
+        W.ModelFiles(str(tmp_path))
+
+
+def test_random_model_folder(llogos, model_dirs):
+    d = model_dirs["qwen3"]
+    assert sorted(os.listdir(d)) == ["config.json", "model.safetensors"]
+    assert json.load(open(os.path.join(d, "config.json")))["architectures"] == ["Qwen3ForCausalLM"]
+    w = read_weights(llogos, d)
+    assert "lm_head.weight" not in w                      # tied
+    assert w["model.layers.1.self_attn.q_proj.bias"].shape == (6 * 32,)
+    assert w["model.layers.2.self_attn.k_norm.weight"].shape == (32,)
+    assert all(t.dtype == torch.bfloat16 for t in w.values())
+    norm = w["model.layers.0.input_layernorm.weight"].float()
+    assert abs(float(norm.mean()) - 1.0) < 0.1 and float(norm.std()) > 0.01
+    assert abs(float(w["model.layers.0.mlp.up_proj.weight"].float().std()) - INIT["std"]) < 0.02
+
+
+def test_same_seed_same_weights(llogos, tmp_path):
+    W = llogos.weights
+    a, b, c = (str(tmp_path / n) for n in "abc")
+    W.write_random_model(a, TINY_LLAMA, seed=5)
+    W.write_random_model(b, TINY_LLAMA, seed=5)
+    W.write_random_model(c, TINY_LLAMA, seed=6)
+    wa, wb, wc = (read_weights(llogos, x) for x in (a, b, c))
+    assert all(torch.equal(wa[n], wb[n]) for n in wa)
+    assert not torch.equal(wa["model.norm.weight"], wc["model.norm.weight"]) or \
+        not torch.equal(wa["lm_head.weight"], wc["lm_head.weight"])
+
+
+def test_loader_binds_and_keeps_types(llogos, model_dirs):
+    m = llogos.weights.load_model(model_dirs["llama"], dtype=torch.bfloat16, device="cpu", ops=cpu_ops)
+    att = m.blocks[0].parts["mixer"]
+    assert att.w_qkv.shape == ((4 + 2 * 2) * 16, 64) and att.w_qkv.dtype == torch.bfloat16
+    assert m.blocks[1].parts["ffn"].w_gate_up.shape == (2 * 176, 64)
+    m32 = llogos.weights.load_model(model_dirs["llama"], dtype=torch.float32, device="cpu", ops=cpu_ops)
+    assert m32.blocks[0].parts["mixer"].w_qkv.dtype == torch.float32
+    assert torch.equal(m32.blocks[0].parts["mixer"].w_qkv, att.w_qkv.float())
+
+
+def test_tensor_stored_in_32_bit_stays_so(llogos, model_dirs, tmp_path):
+    d = str(tmp_path / "m")
+    shutil.copytree(model_dirs["llama"], d)
+    w = read_weights(llogos, d)
+    w["model.norm.weight"] = w["model.norm.weight"].float() + 1e-4      # not representable in bfloat16
+    llogos.weights.write_safetensors(os.path.join(d, "model.safetensors"), w)
+    m = llogos.weights.load_model(d, dtype=torch.bfloat16, device="cpu", ops=cpu_ops)
+    assert m.final_norm.weight.dtype == torch.float32
+    assert torch.equal(m.final_norm.weight, w["model.norm.weight"])
+    assert m.embedding.weight.dtype == torch.bfloat16
+
+
+def test_one_error_lists_everything(llogos, model_dirs, tmp_path):
+    d = str(tmp_path / "m")
+    shutil.copytree(model_dirs["qwen3"], d)
+    w = read_weights(llogos, d)
+    del w["model.layers.1.mlp.down_proj.weight"]
+    del w["model.layers.2.self_attn.q_norm.weight"]
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
+    w["lm_head.weight"] = torch.zeros(384, 96, dtype=torch.bfloat16)        # tied model: not expected
+    w["model.layers.0.self_attn.k_proj.weight"] = torch.zeros(96, 95, dtype=torch.bfloat16)
+    llogos.weights.write_safetensors(os.path.join(d, "model.safetensors"), w)
+    with pytest.raises(llogos.weights.WeightsError) as e:
+        llogos.weights.load_model(d, dtype=torch.float32, device="cpu", ops=cpu_ops)
+    msg = str(e.value)
+    for needle in ("missing (2)", "model.layers.1.mlp.down_proj.weight", "model.layers.2.self_attn.q_norm.weight",
+                   "unexpected (2)", "rotary_emb.inv_freq", "lm_head.weight", "wrong shape (1)",
+                   "model.layers.0.self_attn.k_proj.weight", "(96, 95)", "(96, 96)"):
+        assert needle in msg, (needle, msg)
+
+
+def test_missing_bias_when_config_wants_it(llogos, model_dirs, tmp_path):
+    d = str(tmp_path / "m")
+    shutil.copytree(model_dirs["llama"], d)
+    cfg = json.load(open(os.path.join(d, "config.json")))
+    cfg["attention_bias"] = True
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    with pytest.raises(llogos.weights.WeightsError, match="q_proj.bias"):
+        llogos.weights.load_model(d, dtype=torch.float32, device="cpu", ops=cpu_ops)
+
+
+def test_no_gpu_is_an_error_not_a_fallback(llogos, model_dirs):
+    if torch.cuda.is_available():
+        pytest.skip("this box has a GPU")
+    with pytest.raises(Exception, match="CUDA|GPU|cuda"):
+        llogos.weights.load_model(model_dirs["llama"], dtype=torch.float32, device="cuda:0")
