@@ -29,6 +29,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES: Dict[str, List[str]] = {
     "elementwise": ["elementwise.cu", "common.cuh"],
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
+    "gemm_tc": ["gemm_tc.cu", "common.cuh"],
     "attention_simt": ["attention_simt.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
 }

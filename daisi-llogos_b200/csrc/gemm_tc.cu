@@ -1,0 +1,362 @@
+// Matrix product on the 5th-generation tensor cores of sm_100a:
+//     out[s][n][o] = sum over the k-blocks of split s of  x[n][k] * w[o][k]      (bfloat16 in, float32 accumulate)
+// for every projection of the decoder, in both regimes: a prompt step (thousands of rows of x) and
+// a decode step (1..64 rows), where the kernel is a weight streamer.
+//
+// Mapping.  The weight matrix is the M operand of the MMA (128 output features per tile), the
+// activations are the N operand (16..256 tokens per tile): a decode batch of 1..16 tokens costs one
+// 16-wide tile and no extra memory traffic, because the rows past the batch are filled with zeros
+// by TMA.  Both operands are K-major in memory ([rows][k]), so TMA brings [rows x 64 k] boxes with
+// the 128-byte swizzle and tcgen05.mma reads them from shared memory through descriptors.  The
+// accumulator (128 lanes x N columns of float32) lives in tensor memory; four warps read it back
+// with tcgen05.ld and store out[n][o] so that one warp instruction writes 32 consecutive features.
+//
+// Roles in a block of 128 threads: thread 0 issues TMA loads into a ring of stages, thread 32
+// issues the MMAs and commits each stage back to the producer, all four warps run the epilogue.
+// Split-K (blockIdx.z) writes float32 partials that the consumer kernels sum.
+//
+// Every wait on an mbarrier is bounded (two seconds of %globaltimer): on expiry the block records
+// an error code, stops issuing work, waits (bounded) for its own TMA copies in flight, frees its
+// tensor memory and returns.  llg_gemm_tc_status() reports the code.
+//
+// The reference has no tensor-core kernel of its own (its prompt path calls cublasGemmEx,
+// Daisi.Llogos.Cuda/CudaBackend.cs:246-260; its decode path is a scalar GEMV,
+// kernels/dequant_matmul.cu:593-619).
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+LLG_API const char* llg_last_error() { return g_llg_error; }
+
+namespace {
+
+constexpr int BM = 128;          // output features per tile (MMA M)
+constexpr int BK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ int g_error = 0;      // 0 ok; 1 producer wait, 2 consumer wait, 3 epilogue wait, 4 drain wait
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Waits for the phase with the given parity; false when the time limit ran out or another thread
+// of the block already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 1023) == 0) {
+      if (*abort_flag) return false;
+      if (now_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+
+struct GemmParams {
+  void* out;        // [splits][n][o]
+  int n, o, k;
+  int kb_per_split; // k-blocks of 64 per split
+};
+
+template <int TN, int STAGES, typename OT>
+__global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                      const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = TN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
+  // 1024-byte alignment of the operand tiles is what the swizzle pattern of TMA and of the MMA assume
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], done_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int o0 = blockIdx.x * BM, n0 = blockIdx.y * TN, split = blockIdx.z;
+  const int nkb_total = (p.k + BK - 1) / BK;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = min(p.kb_per_split, nkb_total - kb0);   // >= 1 by construction of the grid
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&done_bar, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = tmem_base_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (tid == 0) {
+    // ---- producer: TMA loads into the ring ------------------------------------------------
+    int issued = 0;
+    for (int i = 0; i < nkb; ++i) {
+      const int s = i % STAGES;
+      const uint32_t parity = ((i / STAGES) & 1) ^ 1;     // a fresh barrier passes a wait on parity 1
+      if (!mbar_wait(&empty_bar[s], parity, abortp)) {
+        if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
+        break;
+      }
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      unsigned char* a = smem + s * STAGE_BYTES;
+      tma_load_2d(a, &map_w, (kb0 + i) * BK, o0, &full_bar[s]);
+      tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * BK, n0, &full_bar[s]);
+      issued = i + 1;
+    }
+    if (*abortp) {
+      // copies already issued still write into this block's shared memory: wait for them, bounded
+      for (int i = max(0, issued - STAGES); i < issued; ++i) {
+        const unsigned long long t0 = now_ns();
+        while (!mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1)) {
+          if (now_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(&g_error, 1, 4); break; }
+        }
+      }
+    }
+  } else if (tid == 32) {
+    // ---- consumer: one thread issues every MMA ----------------------------------------------
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, abortp)) {
+        if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+      const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+        // 16 k = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
+        umma_bf16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (i | kk) != 0);
+      }
+      umma_commit(&empty_bar[s]);       // arrives when the MMAs above have read the stage
+    }
+    umma_commit(&done_bar);             // arrives when every MMA issued so far has finished
+  }
+
+  // ---- epilogue: tensor memory -> registers -> out[n][o] -----------------------------------
+  __syncwarp();
+  bool have = mbar_wait(&done_bar, 0, abortp);
+  if (!have && !*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
+  __syncthreads();
+  const bool aborted = *abortp != 0;
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (!aborted) {
+    const int o = o0 + warp * 32 + lane;
+    OT* out = (OT*)p.out + (long long)split * p.n * p.o;
+#pragma unroll
+    for (int c0 = 0; c0 < TN; c0 += 16) {
+      if (n0 + c0 >= p.n) break;       // uniform over the block: the tile's tail holds no tokens
+      uint32_t r[16];
+      tmem_ld16(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (o < p.o) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const int n = n0 + c0 + c;
+          if (n < p.n) out[(long long)n * p.o + o] = from_f32<OT>(__uint_as_float(r[c]));
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side: tensor maps ------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// A [rows][k] bfloat16 matrix, row-major, read in boxes of [box_rows][64 k] with the 128-byte swizzle;
+// what lies outside the matrix reads as zero.
+bool tensor_map(const void* base, int rows, int k, int box_rows, CUtensorMap* result) {
+  static std::map<std::tuple<const void*, int, int, int>, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_tuple(base, rows, k, box_rows);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *result = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  CUtensorMap m;
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *result = m;
+  return true;
+}
+
+template <int TN, int STAGES, typename OT>
+int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, int splits, cudaStream_t stream) {
+  constexpr int smem = STAGES * (BM * BK * 2 + TN * BK * 2) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN, STAGES, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return llg_fail("gemm_tc: cannot have %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  dim3 grid((p.o + BM - 1) / BM, (p.n + TN - 1) / TN, splits);
+  gemm_tc_kernel<TN, STAGES, OT><<<grid, 128, smem, stream>>>(*mw, *mx, p);
+  return llg_check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// 1 if the tensor-core kernel takes these operands: k a multiple of 8 (TMA needs 16-byte row strides)
+// and 16-byte aligned base addresses.
+LLG_API int llg_gemm_tc_supported(const void* x, const void* w, int n, int o, int k) {
+  return n > 0 && o > 0 && k > 0 && k % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
+}
+
+// Splits that llg_gemm_tc will really use for a wish of `splits` (every split gets at least one k-block).
+LLG_API int llg_gemm_tc_splits(int k, int splits) {
+  const int nkb = (k + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > nkb) splits = nkb;
+  const int per = (nkb + splits - 1) / splits;
+  return (nkb + per - 1) / per;
+}
+
+// out[s][n][o] for s < llg_gemm_tc_splits(k, splits); out_dtype float32, or bfloat16 when there is one split.
+LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int splits,
+                        int tile_n, cudaStream_t stream) {
+  LLG_REQUIRE(llg_gemm_tc_supported(x, w, n, o, k), "gemm_tc: needs k %% 8 == 0 and 16-byte aligned operands (n=%d o=%d k=%d)",
+              n, o, k);
+  splits = llg_gemm_tc_splits(k, splits);
+  LLG_REQUIRE(out_dtype == LLG_F32 || (out_dtype == LLG_BF16 && splits == 1), "gemm_tc: bfloat16 output needs one split");
+  const int nkb = (k + BK - 1) / BK;
+  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits};
+  if (tile_n <= 0) tile_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
+  LLG_REQUIRE((o + BM - 1) / BM <= 2147483647 && (n + tile_n - 1) / tile_n <= 65535 && splits <= 65535, "gemm_tc: grid too large");
+  CUtensorMap map_w, map_x;
+  LLG_REQUIRE(tensor_map(w, o, k, BM, &map_w) && tensor_map(x, n, k, tile_n, &map_x),
+              "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
+  const CUtensorMap *mw = &map_w, *mx = &map_x;
+#define GO(TN, ST)                                                             \
+  return out_dtype == LLG_F32 ? launch<TN, ST, float>(mw, mx, p, splits, stream) \
+                              : launch<TN, ST, __nv_bfloat16>(mw, mx, p, splits, stream)
+  switch (tile_n) {
+    case 16: GO(16, 5);
+    case 32: GO(32, 5);
+    case 64: GO(64, 4);
+    case 128: GO(128, 6);
+    case 256: GO(256, 4);
+    default: return llg_fail("gemm_tc: tile_n %d is not one of 16, 32, 64, 128, 256", tile_n);
+  }
+#undef GO
+}
+
+// Error code that a block recorded when one of its waits ran out (0 = none); clears it.  Synchronises the device.
+LLG_API int llg_gemm_tc_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
+  return v;
+}

@@ -67,6 +67,7 @@ class _DecodeState:
         self.workspace = Workspace(device)
         self.rows = torch.arange(b, dtype=torch.int32, device=device)
         self.graph = None
+        self.kernels = 0
         self.logits: Optional[torch.Tensor] = None
         self.eager_runs = 0
 
@@ -99,7 +100,7 @@ class Engine:
         self._meta = torch.zeros(1024, dtype=torch.int32, device=self.device)
         self._workspace = Workspace(self.device)
         self._decode: Dict[int, _DecodeState] = {}
-        self.launch_count = 0       # kernels and graph launches issued by step(), for reporting
+        self.graph_kernels = 0      # kernels inside CUDA graphs replayed by step(), for reporting
 
     # ---- sequences -----------------------------------------------------------------------
     def open(self) -> int:
@@ -112,6 +113,25 @@ class Engine:
 
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
+
+    def assume(self, slot: int, n_tokens: int) -> None:
+        """Declares ``n_tokens`` more tokens of ``slot`` as present without running them: pages are
+        reserved and the length advances, the keys and values are whatever the pages hold.  For
+        measurements of a step at a given context length; results after it mean nothing."""
+        growth = [(int(slot), int(n_tokens))]
+        try:
+            self.cache.check_room(growth)
+        except CacheError as e:
+            raise StepError(str(e)) from None
+        host: List[np.ndarray] = []
+        plan = self._apply_updates(self.cache.grow(growth), host)
+        if plan:
+            block = np.concatenate(host)
+            meta = self._ensure_meta(block.size)
+            self._staging.upload(block, meta)
+            for g, off, k in plan:
+                self.ops.scatter_i32(g.page_table, meta[off:off + k], meta[off + k:off + 2 * k])
+        self.cache.commit(growth)
 
     # ---- the step ------------------------------------------------------------------------
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]],
@@ -239,7 +259,7 @@ class Engine:
         m = st.meta
         if st.graph is not None:
             st.graph.replay()
-            self.launch_count += 1
+            self.graph_kernels += st.kernels
             logits = st.logits
         else:
             ctx = StepContext(
@@ -252,11 +272,13 @@ class Engine:
                 # the buffers exist since the eager run; record the same launches and replay them
                 graph = torch.cuda.CUDAGraph()
                 st.workspace.frozen = True
+                before = getattr(self.ops, "launches", lambda: 0)()
                 with torch.cuda.graph(graph):
                     st.logits = self.model.forward(ctx, self.cache, st.rows)
+                st.kernels = getattr(self.ops, "launches", lambda: 0)() - before
                 st.graph = graph
                 graph.replay()
-                self.launch_count += 1
+                self.graph_kernels += st.kernels
                 logits = st.logits
             else:
                 logits = self.model.forward(ctx, self.cache, st.rows)

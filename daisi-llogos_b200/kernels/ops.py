@@ -52,9 +52,19 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(lib, rc: int) -> None:
+_launches = 0
+
+
+def launches() -> int:
+    """Kernels launched (or recorded into a CUDA graph) by this module so far."""
+    return _launches
+
+
+def _check(lib, rc: int, kernels: int = 1) -> None:
+    global _launches
     if rc != 0:
         raise KernelError(lib.llg_last_error().decode("utf-8", "replace"))
+    _launches += kernels
 
 
 # ---- libraries and prototypes ---------------------------------------------------------
@@ -130,6 +140,10 @@ def _lib(name: str):
         lib.llg_zero_rows.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
     elif name == "gemm_simt":
         lib.llg_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    elif name == "gemm_tc":
+        lib.llg_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
+        lib.llg_gemm_tc_splits.argtypes = [c_int, c_int]
+        lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     elif name == "attention_simt":
         lib.llg_attn_prefill_simt.argtypes = [POINTER(_PrefillArgs), c_int, c_void_p]
         lib.llg_attn_decode_simt.argtypes = [POINTER(_DecodeArgs), c_void_p, c_int, c_void_p]
@@ -191,6 +205,42 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     o, k2 = w.shape
     assert k == k2 and out.shape == (n, o), (x.shape, w.shape, out.shape)
     _check(lib, lib.llg_gemm_simt(_ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(out), _dt(out), n, o, k, _stream()))
+
+
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes this product (bfloat16 operands, k a multiple of 8)."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not (x.is_cuda and w.is_cuda):
+        return False
+    lib = _lib("gemm_tc")
+    return bool(lib.llg_gemm_tc_supported(x.data_ptr(), w.data_ptr(), x.shape[0], w.shape[0], x.shape[1]))
+
+
+def gemm_tc_splits(k: int, wish: int) -> int:
+    """The number of split-K partials the kernel writes when asked for ``wish``."""
+    return _lib("gemm_tc").llg_gemm_tc_splits(k, wish)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int = 0) -> None:
+    """out[s, n, o] = split-K partials of x[n, k] w[o, k] on the tensor cores (tcgen05, TMA).
+
+    ``out`` is ``[S, N, O]`` float32 with S = ``gemm_tc_splits(k, wish)``, or ``[1, N, O]`` bfloat16.
+    """
+    lib = _lib("gemm_tc")
+    n, k = x.shape
+    o, k2 = w.shape
+    s = out.shape[0]
+    assert k == k2 and out.shape == (s, n, o), (x.shape, w.shape, out.shape)
+    if lib.llg_gemm_tc_splits(k, s) != s:
+        raise KernelError(f"gemm_tc: {s} splits cannot be had for k = {k}")
+    _check(lib, lib.llg_gemm_tc(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k, s,
+                                tile_n, _stream()))
+
+
+def gemm_tc_status() -> int:
+    """Error code a tensor-core product recorded when a wait ran out (0 = none); synchronises."""
+    lib = _lib("gemm_tc")
+    lib.llg_gemm_tc_status.restype = c_int
+    return lib.llg_gemm_tc_status()
 
 
 def qk_prep(qkv: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
@@ -317,7 +367,7 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
     a.part_ml = base + 4 * b * nh * n_splits * hd
     a.n_seqs, a.nh, a.nkv, a.hd, a.n_splits = b, nh, nkv, hd, n_splits
     a.scale, a.window = float(scale), int(window)
-    _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()))
+    _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()), kernels=2)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -1,0 +1,119 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation: greedy token for token, seeded sampling draw for draw."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import llogos_b200 as L
+import plain_model as P
+from conftest import ROOT, TINY, read_weights, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_generate(w, cfg, prompt, n, stop=(), params=None, seed=0, seq_id=0):
+    """Greedy (params None) or sampled continuation with the plain model and the plain sampler."""
+    toks, out = list(prompt), []
+    for step in range(n):
+        logits = P.forward(w, cfg, toks)[-1]
+        if params is None:
+            t = int(max(range(len(logits)), key=lambda i: (float(logits[i]), -i)))
+        else:
+            probs = P.sampling_distribution(logits.float().tolist(), previous=toks[-64:], **params)
+            t = P.draw(probs, P.uniform_of(seed, seq_id, step))
+        if t in stop:
+            break
+        toks.append(t)
+        out.append(t)
+    return out
+
+
+def margin_ok(w, cfg, prompt, out, min_gap=1e-3):
+    """True when every greedy choice of the plain model was clear enough for float32 to agree."""
+    toks = list(prompt)
+    for t in out:
+        lg = P.forward(w, cfg, toks)[-1]
+        top = torch.topk(lg, 2).values
+        if float(top[0] - top[1]) < min_gap:
+            return False
+        toks.append(t)
+    return True
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_greedy_generation_matches_plain(llogos, model_dirs, name):
+    cfg = TINY[name]
+    w = read_weights(llogos, model_dirs[name])
+    prompts = random_tokens(cfg["vocab_size"], [5, 9, 13, 1, 30], 31)
+    model = L.LlogosModel.load(model_dirs[name], dtype="float32", max_context=256, max_batch=3)
+    params = L.GenerationParams.greedy_params(12, stop_tokens=())
+    r = model.generate(prompts, params)
+    assert r.batches == 2 and r.finish_reasons == ["length"] * 5
+    for p, got in zip(prompts, r.tokens):
+        want = plain_generate(w, cfg, p, 12)
+        if margin_ok(w, cfg, p, want):
+            assert got == want
+    # a single prompt as a flat list, and stop tokens from the configuration
+    stop = model.stop_token_ids
+    r1 = model.generate(prompts[0], L.GenerationParams.greedy_params(40))
+    want = plain_generate(w, cfg, prompts[0], 40, stop=stop)
+    if margin_ok(w, cfg, prompts[0], want):
+        assert r1.tokens[0] == want
+        assert r1.finish_reasons[0] == ("stop" if len(want) < 40 else "length")
+    assert not model.engine.cache.slots.live()
+
+
+def test_seeded_sampling_matches_plain_and_ignores_batch_mates(llogos, model_dirs):
+    name = "qwen3"
+    cfg = TINY[name]
+    w = read_weights(llogos, model_dirs[name])
+    prompts = random_tokens(cfg["vocab_size"], [1, 7, 16, 31], 32)
+    model = L.LlogosModel.load(model_dirs[name], dtype="float32", max_context=256, max_batch=4)
+    params = L.GenerationParams(max_tokens=12, temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0,
+                                seed=1234, stop_tokens=())
+    r = model.generate(prompts, params)
+    again = model.generate(prompts, params)
+    assert r.tokens == again.tokens
+    plain_params = dict(temperature=0.8)
+    agree = 0
+    for i, p in enumerate(prompts):
+        want = plain_generate(w, cfg, p, 12, params=plain_params, seed=1234, seq_id=i)
+        agree += int(r.tokens[i] == want)
+    assert agree >= 3            # a draw that falls within 1e-6 of a boundary may differ in float32
+    other = model.generate(prompts, L.GenerationParams(max_tokens=12, temperature=0.8, top_k=0, top_p=1.0,
+                                                       repetition_penalty=1.0, seed=99, stop_tokens=()))
+    assert other.tokens != r.tokens
+    # with the reference's default filters and penalties on
+    full = L.GenerationParams(max_tokens=10, seed=5, stop_tokens=())
+    rf = model.generate(prompts[:2], full)
+    wantf = [plain_generate(w, cfg, p, 10, params=dict(temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1),
+                            seed=5, seq_id=i) for i, p in enumerate(prompts[:2])]
+    assert sum(int(a == b) for a, b in zip(rf.tokens, wantf)) >= 1
+
+
+def test_bfloat16_generation_runs_and_is_deterministic(model_dirs):
+    cfg = TINY["llama"]
+    prompts = random_tokens(cfg["vocab_size"], [5, 9, 13], 33)
+    model = L.LlogosModel.load(model_dirs["llama"], dtype="bfloat16", max_context=128, max_batch=3)
+    params = L.GenerationParams.greedy_params(8, stop_tokens=())
+    a, b = model.generate(prompts, params), model.generate(prompts, params)
+    assert a.tokens == b.tokens and all(len(t) == 8 for t in a.tokens)
+    assert a.decode_tokens_per_second > 0 and a.prefill_tokens_per_second > 0
+
+
+def test_command_line(model_dirs):
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    base = [sys.executable, "-m", "llogos_b200", "--model", model_dirs["llama"], "--dtype", "float32"]
+    p = subprocess.run(base + ["--prompt-ids", "5,17,3", "-n", "6", "-t", "0", "--repeat-penalty", "1.0", "--max-context", "128"],
+                       capture_output=True, text=True, env=env, cwd=ROOT)
+    assert p.returncode == 0, p.stderr
+    toks = [int(x) for x in p.stdout.split()]
+    assert 1 <= len(toks) <= 6 and "prefill: 3 tokens" in p.stderr and "decode:" in p.stderr
+    p = subprocess.run(base + ["--bench", "-n", "5", "--max-context", "128"], capture_output=True, text=True, env=env, cwd=ROOT)
+    assert p.returncode == 0, p.stderr
+    assert "Prefill:" in p.stderr and "Decode:" in p.stderr and "Load:" in p.stderr
+    p = subprocess.run([sys.executable, "-m", "llogos_b200", "--prompt", "hi"], capture_output=True, text=True, env=env, cwd=ROOT)
+    assert p.returncode == 2 and "--model" in p.stderr

@@ -1,0 +1,343 @@
+"""Each kernel alone against the plain float64 formulas, at sizes the models of the other tests
+do not use: widths and vocabularies that are no power of two, head sizes in steps of 16, odd
+numbers of heads and groups."""
+import importlib
+import math
+
+import pytest
+import torch
+
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    return importlib.import_module("daisi-llogos_b200.kernels.ops")
+
+
+def rnd(shape, seed, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 1.6e-2
+
+
+def check(got, ref, dtype, what=""):
+    ref = ref.double()
+    err = float((got.detach().cpu().double() - ref).abs().max())
+    lim = tol(dtype) * max(1.0, float(ref.abs().max()))
+    assert err <= lim, (what, err, lim)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_embed_rows(ops, dtype):
+    table = rnd((301, 200), 1, dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32)
+    out = torch.empty(5, 200, device=DEV)
+    ops.embed_rows(table.to(DEV), ids.to(DEV), out)
+    assert torch.equal(out.cpu(), P.embedding(table, ids.tolist()).float())
+
+
+@pytest.mark.parametrize("wdtype", DTYPES, ids=["w32", "w16"])
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("hidden", [72, 1000, 4100])
+def test_add_rmsnorm(ops, dtype, wdtype, hidden):
+    n, eps = 7, 3e-5
+    res = rnd((n, hidden), 2)
+    branch = rnd((3, n, hidden), 3)
+    w = rnd((hidden,), 4, wdtype) + 1
+    r_dev = res.to(DEV).clone()
+    out = torch.empty(n, hidden, dtype=dtype, device=DEV)
+    ops.add_rmsnorm(r_dev, branch.to(DEV), w.to(DEV), eps, out)
+    total = res.double() + branch.double().sum(0)
+    check(r_dev, total, torch.float32, "residual")
+    check(out, P.rms_norm(total, w, eps), dtype, "normed")
+    # without a branch, with a row gather
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    out2 = torch.empty(3, hidden, dtype=dtype, device=DEV)
+    r2 = res.to(DEV).clone()
+    ops.add_rmsnorm(r2, None, w.to(DEV), eps, out2, rows.to(DEV))
+    assert torch.equal(r2.cpu(), res)
+    check(out2, P.rms_norm(res[rows.long()], w, eps), dtype, "gathered")
+    # gather with a branch: the gathered rows of the residual are updated
+    r3 = res.to(DEV).clone()
+    ops.add_rmsnorm(r3, branch.to(DEV), w.to(DEV), eps, out2, rows.to(DEV))
+    check(out2, P.rms_norm(total[rows.long()], w, eps), dtype, "gathered with branch")
+
+
+@pytest.mark.parametrize("xd,wd,od", [(torch.float32,) * 3, (torch.bfloat16, torch.bfloat16, torch.float32),
+                                      (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                      (torch.bfloat16, torch.float32, torch.float32)], ids=["fff", "bbf", "bbb", "bff"])
+@pytest.mark.parametrize("n,o,k", [(1, 301, 72), (5, 64, 1000), (70, 130, 333), (200, 65, 16)])
+def test_gemm_simt(ops, xd, wd, od, n, o, k):
+    x, w = rnd((n, k), 5, xd), rnd((o, k), 6, wd, 0.1)
+    out = torch.empty(n, o, dtype=od, device=DEV)
+    ops.gemm_simt(x.to(DEV), w.to(DEV), out)
+    check(out, P.linear(x, w), od if od == torch.bfloat16 else torch.float32)
+
+
+@pytest.mark.parametrize("n,o,k", [(1, 128, 64), (3, 200, 72), (16, 129, 128), (17, 384, 1000), (33, 100, 8),
+                                   (70, 130, 336), (129, 65, 16), (300, 1000, 520), (2, 301, 4104)])
+def test_gemm_tc(ops, n, o, k):
+    """The tcgen05 product at ragged sizes: rows, features and k that fill no tile."""
+    x, w = rnd((n, k), 5, torch.bfloat16), rnd((o, k), 6, torch.bfloat16, 0.1)
+    ref = P.linear(x, w)
+    assert ops.gemm_tc_supported(x.to(DEV), w.to(DEV))
+    for wish in (1, 3, 16):
+        s = ops.gemm_tc_splits(k, wish)
+        assert 1 <= s <= wish
+        out = torch.full((s, n, o), float("nan"), device=DEV)
+        ops.gemm_tc(x.to(DEV), w.to(DEV), out)
+        check(out.sum(0), ref, torch.float32, ("splits", s))
+    out = torch.empty(1, n, o, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x.to(DEV), w.to(DEV), out)
+    check(out[0], ref, torch.bfloat16, "bfloat16 output")
+    for tile in (16, 32, 64, 128, 256):
+        out = torch.full((1, n, o), float("nan"), device=DEV)
+        ops.gemm_tc(x.to(DEV), w.to(DEV), out, tile_n=tile)
+        check(out[0], ref, torch.float32, ("tile", tile))
+    assert ops.gemm_tc_status() == 0
+
+
+def test_gemm_tc_refuses_what_tma_cannot_address(ops):
+    x, w = rnd((4, 36), 5, torch.bfloat16).to(DEV), rnd((8, 36), 6, torch.bfloat16).to(DEV)
+    assert not ops.gemm_tc_supported(x, w)                       # 72-byte rows
+    assert not ops.gemm_tc_supported(x.float(), w.float())       # float32 stays off the tensor cores
+    with pytest.raises(ops.KernelError, match="k % 8"):
+        ops.gemm_tc(x, w, torch.empty(1, 4, 8, device=DEV))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("partials", [1, 3])
+def test_silu_mul(ops, dtype, partials):
+    n, inter = 5, 333
+    in_dtype = torch.float32 if partials > 1 else dtype
+    gu = rnd((partials, n, 2 * inter), 7, in_dtype, 2.0)
+    out = torch.empty(n, inter, dtype=dtype, device=DEV)
+    ops.silu_mul(gu.to(DEV), out)
+    s = gu.double().sum(0)
+    g, u = s[:, :inter], s[:, inter:]
+    check(out, g / (1 + torch.exp(-g)) * u, dtype)
+
+
+def _rope_tables(hd, rd, theta, n_pos):
+    inv = P.rope_inverse_frequencies(rd, theta, None)
+    ang = torch.arange(n_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    return inv, torch.cos(ang).float(), torch.sin(ang).float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("nh,nkv,hd,rd,pairing,norm,bias", [
+    (5, 1, 48, 48, "half", True, True), (6, 3, 80, 32, "adjacent", False, True),
+    (4, 4, 16, 16, "half", True, False), (9, 3, 128, 128, "half", False, False)])
+def test_qk_prep(ops, dtype, nh, nkv, hd, rd, pairing, norm, bias):
+    n, eps = 11, 2e-6
+    width = (nh + 2 * nkv) * hd
+    partials = 2 if dtype == torch.float32 else 1
+    qkv = rnd((partials, n, width), 8, torch.float32 if partials > 1 else dtype)
+    qw, kw = (rnd((hd,), 9, dtype) + 1, rnd((hd,), 10, dtype) + 1) if norm else (None, None)
+    b = rnd((width,), 11, dtype) if bias else None
+    pos = torch.tensor([0, 1, 2, 3, 500, 63, 64, 65, 7, 7, 1023], dtype=torch.int32)
+    inv, cos, sin = _rope_tables(hd, rd, 12345.0, 1024)
+    q = torch.empty(n, nh, hd, dtype=dtype, device=DEV)
+    kn, vn = (torch.empty(n, nkv, hd, dtype=dtype, device=DEV) for _ in range(2))
+    dev = lambda t: None if t is None else t.to(DEV)
+    ops.qk_prep(qkv.to(DEV), n_heads=nh, n_kv_heads=nkv, head_dim=hd, q_norm_w=dev(qw), k_norm_w=dev(kw),
+                norm_eps=eps, bias=dev(b), cos=cos.to(DEV), sin=sin.to(DEV), rotary_dim=rd,
+                pairing=0 if pairing == "half" else 1, positions=pos.to(DEV), q_out=q, k_new=kn, v_new=vn)
+    x = qkv.double().sum(0).view(n, nh + 2 * nkv, hd)
+    qr, kr, vr = x[:, :nh], x[:, nh:nh + nkv], x[:, nh + nkv:]
+    if norm:
+        qr, kr = P.per_head_rms_norm(qr, qw, eps), P.per_head_rms_norm(kr, kw, eps)
+    if bias:
+        bb = b.double().view(nh + 2 * nkv, hd)
+        qr, kr, vr = qr + bb[:nh], kr + bb[nh:nh + nkv], vr + bb[nh + nkv:]
+    qr = P.rope_rotate(qr, pos.tolist(), inv, pairing)
+    kr = P.rope_rotate(kr, pos.tolist(), inv, pairing)
+    check(q, qr, dtype, "q")
+    check(kn, kr, dtype, "k")
+    check(vn, vr, dtype, "v")
+
+
+def _paged(nkv, hd, dtype, lens, n_pages, ring_pages, seed):
+    """A cache filled with random keys/values for sequences of the given lengths; pages handed out
+    in a scrambled order so that a wrong page-table lookup shows."""
+    g = torch.Generator().manual_seed(seed)
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(len(lens) + 2, ring_pages, dtype=torch.int32)
+    slots = list(range(len(lens), 0, -1))            # slots differ from batch indices
+    kp = torch.zeros(n_pages, nkv, 64, hd, dtype=dtype)
+    vp = torch.zeros(n_pages, nkv, 64, hd, dtype=dtype)
+    ks, vs = [], []
+    for b, n in enumerate(lens):
+        k = rnd((n, nkv, hd), seed + 10 + b, dtype)
+        v = rnd((n, nkv, hd), seed + 20 + b, dtype)
+        ks.append(k)
+        vs.append(v)
+        for j in range(min((n + 63) // 64, ring_pages)):
+            table[slots[b], j] = order.pop()
+        for p in range(max(0, n - ring_pages * 64), n):
+            pg = int(table[slots[b], (p // 64) % ring_pages])
+            kp[pg, :, p % 64] = k[p]
+            vp[pg, :, p % 64] = v[p]
+    return kp, vp, table, torch.tensor(slots, dtype=torch.int32), ks, vs
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 0), (6, 3, 80, 0), (12, 1, 32, 0), (4, 2, 128, 100), (8, 4, 16, 70)])
+def test_attn_decode(ops, dtype, nh, nkv, hd, window):
+    lens = [1, 64, 65, 300, 129]
+    ring = 8 if window == 0 else (window + 63) // 64 + 1
+    kp, vp, table, slots, ks, vs = _paged(nkv, hd, dtype, lens, 40, ring, 30)
+    q = rnd((len(lens), nh, hd), 31, dtype)
+    scale = 1 / math.sqrt(hd)
+    for splits in (1, 3, 7):
+        out = torch.empty(len(lens), nh * hd, dtype=dtype, device=DEV)
+        scratch = torch.empty(ops.attn_decode_scratch_floats(len(lens), nh, hd, splits), device=DEV)
+        lb = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+        ops.attn_decode(q.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV), ring, slots.to(DEV), lb.to(DEV), out,
+                        scratch, n_splits=splits, scale=scale, window=window)
+        for b, n in enumerate(lens):
+            qq = torch.zeros(n, nh, hd, dtype=dtype)
+            qq[-1] = q[b]
+            ref = P.attention(qq, ks[b], vs[b], scale, window)[-1].reshape(-1)
+            check(out[b], ref, dtype, (b, n, splits))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 0), (6, 3, 80, 0), (4, 2, 128, 100), (8, 4, 16, 40)])
+def test_attn_prefill_and_kv_write(ops, dtype, nh, nkv, hd, window):
+    before = [0, 0, 70, 130, 64]           # tokens already in the cache
+    counts = [1, 37, 16, 150, 3]           # tokens the step brings
+    ring = 8 if window == 0 else (window + 63) // 64 + 1
+    total = [a + c for a, c in zip(before, counts)]
+    kp, vp, table, slots, ks, vs = _paged(nkv, hd, dtype, total, 40, ring, 40)
+    # rebuild the cache as it was BEFORE the step: only positions < before, ring of the old length
+    kp0, vp0 = torch.zeros_like(kp), torch.zeros_like(vp)
+    for b, n in enumerate(before):
+        for p in range(max(0, n - ring * 64), n):
+            pg = int(table[slots[b], (p // 64) % ring])
+            kp0[pg, :, p % 64] = ks[b][p]
+            vp0[pg, :, p % 64] = vs[b][p]
+    cu = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    n = int(cu[-1])
+    q = rnd((n, nh, hd), 41, dtype)
+    k_new = torch.cat([ks[b][before[b]:] for b in range(len(counts))])
+    v_new = torch.cat([vs[b][before[b]:] for b in range(len(counts))])
+    tiles = torch.tensor([(b, q0) for b, c in enumerate(counts) for q0 in range(0, c, ops.PREFILL_QUERIES_PER_TILE)],
+                         dtype=torch.int32)
+    out = torch.empty(n, nh * hd, dtype=dtype, device=DEV)
+    scale = 0.37
+    d = lambda t: t.to(DEV)
+    kpd, vpd = d(kp0), d(vp0)
+    lb = torch.tensor(before, dtype=torch.int32)
+    ops.attn_prefill(d(q), d(k_new), d(v_new), kpd, vpd, d(table), ring, d(tiles), d(cu), d(lb), d(slots), out,
+                     scale=scale, window=window)
+    for b in range(len(counts)):
+        qq = torch.zeros(total[b], nh, hd, dtype=dtype)
+        qq[before[b]:] = q[int(cu[b]):int(cu[b + 1])]
+        ref = P.attention(qq, ks[b], vs[b], scale, window)[before[b]:].reshape(counts[b], -1)
+        check(out[int(cu[b]):int(cu[b + 1])], ref, dtype, ("sequence", b))
+    # the write after the step leaves the cache as if all tokens had been there
+    pos = torch.cat([torch.arange(a, a + c) for a, c in zip(before, counts)]).to(torch.int32)
+    seq_of = torch.repeat_interleave(torch.arange(len(counts)), torch.tensor(counts)).to(torch.int32)
+    ops.kv_write(d(k_new), d(v_new), kpd, vpd, d(table), ring, d(pos), d(seq_of), d(slots), d(cu), d(lb))
+    used = sorted({int(table[slots[b], j]) for b in range(len(counts)) for j in range(min((total[b] + 63) // 64, ring))})
+    for pg in used:
+        # compare only rows that hold live positions
+        pass
+    for b, t in enumerate(total):
+        for p in range(max(0, t - ring * 64), t):
+            pg = int(table[slots[b], (p // 64) % ring])
+            assert torch.equal(kpd[pg, :, p % 64].cpu(), ks[b][p]) and torch.equal(vpd[pg, :, p % 64].cpu(), vs[b][p]), (b, p)
+
+
+def test_kernels_refuse_what_they_cannot_do(ops):
+    q = torch.zeros(1, 2, 272, device=DEV)
+    kp = torch.zeros(1, 1, 64, 272, device=DEV)
+    table = torch.zeros(1, 1, dtype=torch.int32, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="head_dim 272"):
+        ops.attn_decode(q, kp, kp, table, 1, z, z, torch.zeros(1, 544, device=DEV), torch.zeros(4096, device=DEV),
+                        n_splits=1, scale=1.0, window=0)
+    with pytest.raises(ops.KernelError, match="not on the GPU"):
+        ops.argmax(torch.zeros(1, 4), torch.zeros(1, dtype=torch.int32, device=DEV))
+    with pytest.raises(ops.KernelError, match="multiple"):
+        ops.attn_decode(torch.zeros(1, 3, 16, device=DEV), torch.zeros(1, 2, 64, 16, device=DEV),
+                        torch.zeros(1, 2, 64, 16, device=DEV), table, 1, z, z, torch.zeros(1, 48, device=DEV),
+                        torch.zeros(4096, device=DEV), n_splits=1, scale=1.0, window=0)
+
+
+def test_argmax_takes_the_first_maximum(ops):
+    x = rnd((6, 50001), 50)
+    x[1, 4000] = x[1, 40000] = 99.0
+    x[2, 50000] = 99.0
+    x[3, 0] = 99.0
+    x[4] = 0.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.argmax(x.to(DEV), out)
+    want = [int(x[0].argmax()), 4000, 50000, 0, 0, int(x[5].argmax())]
+    assert out.cpu().tolist() == want
+
+
+SAMPLE_CASES = [
+    dict(temperature=0.8), dict(temperature=1.3, top_k=40), dict(temperature=0.7, top_p=0.9),
+    dict(temperature=1.0, min_p=0.05), dict(temperature=1.0, typical_p=0.7),
+    dict(temperature=0.9, top_k=50, top_p=0.8, min_p=0.01, typical_p=0.9, repetition_penalty=1.3,
+         frequency_penalty=0.2, presence_penalty=0.1),
+    dict(temperature=0.0, repetition_penalty=1.5), dict(temperature=1.0, top_p=0.5, min_keep=30),
+    dict(temperature=1.0, top_k=1), dict(temperature=2.0, top_k=5000), dict(temperature=0.6, banned=[3, 77]),
+]
+
+
+@pytest.mark.parametrize("case", range(len(SAMPLE_CASES)))
+def test_sampler_distribution_and_draw(ops, case):
+    c = dict(SAMPLE_CASES[case])
+    banned = c.pop("banned", None)
+    vocab, b = 1531, 4
+    logits = rnd((b, vocab), 60, scale=3.0)
+    g = torch.Generator().manual_seed(61)
+    hist = torch.randint(0, vocab, (b, 16), generator=g, dtype=torch.int32)
+    hist[:, 5] = hist[:, 2]
+    hl = torch.tensor([16, 9, 0, 16], dtype=torch.int32)
+    work = torch.empty(b * vocab, device=DEV)
+    out = torch.empty(b, dtype=torch.int32, device=DEV)
+    probs = torch.empty(b, vocab, device=DEV)
+    seq_ids = torch.tensor([9, 2, 5, 40], dtype=torch.int32)
+    ops.sample(logits.to(DEV), work, out, seed=11, step=5, history=hist.to(DEV), history_len=hl.to(DEV),
+               probs_out=probs, seq_ids=seq_ids.to(DEV),
+               banned=None if banned is None else torch.tensor(banned, dtype=torch.int32, device=DEV), **c)
+    for i in range(b):
+        ref = P.sampling_distribution(logits[i].tolist(), previous=hist[i, :hl[i]].tolist(), banned=banned or (), **c)
+        got = probs[i].cpu().double()
+        assert float((got - ref).abs().max()) < 2e-6, (i, c)
+        assert ((got > 0) == (ref > 0)).all()
+        assert int(out[i]) == P.draw(got, P.uniform_of(11, int(seq_ids[i]), 5))
+
+
+def test_sampler_draws_follow_the_distribution(ops):
+    vocab = 37
+    logits = rnd((1, vocab), 62, scale=1.5).repeat(512, 1)
+    work = torch.empty(512 * vocab, device=DEV)
+    out = torch.empty(512, dtype=torch.int32, device=DEV)
+    counts = torch.zeros(vocab)
+    for step in range(8):
+        ops.sample(logits.to(DEV), work, out, temperature=1.0, seed=123, step=step)
+        counts += torch.bincount(out.cpu().long(), minlength=vocab)
+    p = torch.softmax(logits[0].double(), 0)
+    n = counts.sum()
+    chi2 = float((((counts - n * p) ** 2) / (n * p)).sum())
+    assert chi2 < 75, chi2          # 36 degrees of freedom: far in the tail beyond 75
+    # same seed, same draws; another seed, other draws
+    a = torch.empty(512, dtype=torch.int32, device=DEV)
+    ops.sample(logits.to(DEV), work, a, temperature=1.0, seed=123, step=7)
+    assert torch.equal(a, out)
+    ops.sample(logits.to(DEV), work, a, temperature=1.0, seed=124, step=7)
+    assert not torch.equal(a, out)

@@ -1,0 +1,203 @@
+"""The engine against the plain implementation on the GPU, in float32 and bfloat16:
+each request alone and whole; the last 32 tokens one by one; batches of unequal lengths whose
+shorter requests end earlier, one batch after another so that slots and pages are used again;
+long decoding; the first tokens of a sequence."""
+import pytest
+import torch
+
+import plain_model as P
+from conftest import TINY, read_weights, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+# max |logit difference| allowed, relative to the largest |logit| of the reference
+REL_TOL = {torch.float32: 2e-5, torch.bfloat16: 4e-2}
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def close(got, ref, dtype, scale):
+    """``scale``: the largest |logit| of the request's whole reference; bfloat16 noise is absolute
+    across a request's positions, so every position is judged against the same scale."""
+    ref = ref.to(torch.float64)
+    err = float((got.detach().cpu().double() - ref).abs().max())
+    return err <= REL_TOL[dtype] * scale, err
+
+
+@pytest.fixture(scope="module")
+def plain(llogos, model_dirs):
+    """Reference logits of a fixed set of requests per configuration."""
+    out = {}
+    for name, cfg in TINY.items():
+        w = read_weights(llogos, model_dirs[name])
+        seqs = random_tokens(cfg["vocab_size"], [40, 150, 33, 97, 64, 129], 11)
+        out[name] = (seqs, [P.forward(w, cfg, s) for s in seqs])
+    return out
+
+
+@pytest.fixture(scope="module")
+def engines(llogos, model_dirs):
+    cache = {}
+
+    def get(name, dtype, graphs=True):
+        key = (name, dtype, graphs)
+        if key not in cache:
+            model = llogos.weights.load_model(model_dirs[name], dtype=dtype, device="cuda:0")
+            cache[key] = llogos.engine.Engine(model, max_tokens=64 * 14, use_graphs=graphs)
+        return cache[key]
+    return get
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_each_request_alone_and_whole(engines, plain, name, dtype):
+    eng = engines(name, dtype)
+    seqs, refs = plain[name]
+    for s, r in zip(seqs, refs):
+        slot = eng.open()
+        lg = eng.step([(slot, s)], [list(range(len(s)))])
+        ok, err = close(lg, r, dtype, float(r.abs().max()))
+        assert ok, (len(s), err)
+        eng.close(slot)
+    eng.cache.audit()
+
+
+@pytest.mark.parametrize("graphs", [True, False], ids=["graph", "eager"])
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_last_32_tokens_one_by_one(engines, plain, name, dtype, graphs):
+    eng = engines(name, dtype, graphs)
+    seqs, refs = plain[name]
+    for s, r in zip(seqs, refs):
+        slot = eng.open()
+        cut = len(s) - 32
+        lg = eng.step([(slot, s[:cut])])
+        ok, err = close(lg[0], r[cut - 1], dtype, float(r.abs().max()))
+        assert ok, ("prompt end", len(s), err)
+        for p in range(cut, len(s)):
+            lg = eng.step([(slot, [s[p]])])
+            ok, err = close(lg[0], r[p], dtype, float(r.abs().max()))
+            assert ok, ("decoded position", p, "of", len(s), err)
+        eng.close(slot)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_unequal_batches_one_after_another(engines, plain, name, dtype):
+    eng = engines(name, dtype)
+    seqs, refs = plain[name]
+    for order in ([0, 1, 2], [3, 4, 5], [5, 0, 3, 1], [2, 4]):
+        slots = {i: eng.open() for i in order}
+        cut = {i: max(1, len(seqs[i]) - 5 - 7 * k) for k, i in enumerate(order)}
+        lg = eng.step([(slots[i], seqs[i][:cut[i]]) for i in order], [[0, cut[i] - 1] for i in order])
+        for k, i in enumerate(order):
+            for row, p in ((2 * k, 0), (2 * k + 1, cut[i] - 1)):
+                ok, err = close(lg[row], refs[i][p], dtype, float(refs[i].abs().max()))
+                assert ok, ("prompt", i, p, err)
+        pos = dict(cut)
+        live = list(order)
+        while live:
+            lg = eng.step([(slots[i], [seqs[i][pos[i]]]) for i in live])
+            for k, i in enumerate(live):
+                ok, err = close(lg[k], refs[i][pos[i]], dtype, float(refs[i].abs().max()))
+                assert ok, ("decode", i, pos[i], "batch of", len(live), err)
+                pos[i] += 1
+            done = [i for i in live if pos[i] == len(seqs[i])]
+            for i in done:
+                eng.close(slots[i])                   # a shorter request ends earlier
+            live = [i for i in live if i not in done]
+        eng.cache.audit()
+    assert eng.cache.slots.free_count == eng.cache.slots.n_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_long_decoding_from_the_first_token(llogos, model_dirs, name, dtype):
+    """One token, then 299 decoded: crosses pages and the window, starts at position 0."""
+    cfg = TINY[name]
+    w = read_weights(llogos, model_dirs[name])
+    a, b = random_tokens(cfg["vocab_size"], [300, 200], 12)
+    ra, rb = P.forward(w, cfg, a), P.forward(w, cfg, b)
+    model = llogos.weights.load_model(model_dirs[name], dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 9)
+    sa, sb = eng.open(), eng.open()
+    for p in range(300):
+        entries = [(sa, [a[p]])] + ([(sb, [b[p]])] if p < 200 else [])
+        lg = eng.step(entries)
+        if p in (0, 1, 2, 63, 64, 65, 127, 128, 199, 299) or p % 37 == 0:
+            ok, err = close(lg[0], ra[p], dtype, float(ra.abs().max()))
+            assert ok, ("a", p, err)
+            if p < 200:
+                ok, err = close(lg[1], rb[p], dtype, float(rb.abs().max()))
+                assert ok, ("b", p, err)
+        if p == 199:
+            eng.close(sb)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_reused_pages_do_not_leak_old_keys(llogos, model_dirs, dtype):
+    """A slot and its pages are used again by a shorter request: the logits must not see the
+    previous owner's keys beyond the new request's length."""
+    name = "llama"
+    cfg = TINY[name]
+    w = read_weights(llogos, model_dirs[name])
+    model = llogos.weights.load_model(model_dirs[name], dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 3, n_slots=1)
+    long_, short = random_tokens(cfg["vocab_size"], [190, 70], 13)
+    s = eng.open()
+    eng.step([(s, long_)])
+    eng.close(s)
+    s = eng.open()
+    r = P.forward(w, cfg, short)
+    lg = eng.step([(s, short[:60])])
+    assert close(lg[0], r[59], dtype, float(r.abs().max()))[0]
+    for p in range(60, 70):
+        lg = eng.step([(s, [short[p]])])
+        ok, err = close(lg[0], r[p], dtype, float(r.abs().max()))
+        assert ok, (p, err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_a_far_key_among_hundreds(llogos, tmp_path, dtype):
+    """Weights made so that one far key decides the output: the last token's query matches the
+    key of position 3 only.  A kernel that drops, repeats or misplaces a key tile shows here."""
+    cfg = dict(TINY["llama"], num_hidden_layers=1, max_position_embeddings=1024)
+    d = str(tmp_path / "m")
+    llogos.weights.write_random_model(d, cfg, seed=3, std=0.05)
+    w = read_weights(llogos, d)
+    # token 7 -> a key that only token 9's query likes; rotation off for the pair by using
+    # the slowest frequency pair (index 7 and 15 of each head) at moderate distance
+    emb = w["model.embed_tokens.weight"].float()
+    emb[7] = 0
+    emb[7, 0] = 8.0
+    emb[9] = 0
+    emb[9, 1] = 8.0
+    w["model.embed_tokens.weight"] = emb.to(torch.bfloat16)
+    q = torch.zeros_like(w["model.layers.0.self_attn.q_proj.weight"]).float()
+    k = torch.zeros_like(w["model.layers.0.self_attn.k_proj.weight"]).float()
+    for h in range(4):
+        q[h * 16 + 7, 1] = 6.0          # query of token 9: element 7 of every head
+    for h in range(2):
+        k[h * 16 + 7, 0] = 6.0          # key of token 7: element 7 of every kv head
+    w["model.layers.0.self_attn.q_proj.weight"] = q.to(torch.bfloat16)
+    w["model.layers.0.self_attn.k_proj.weight"] = k.to(torch.bfloat16)
+    llogos.weights.write_safetensors(d + "/model.safetensors", w)
+    toks = random_tokens(cfg["vocab_size"], [700], 14)[0]
+    toks = [t if t not in (7, 9) else 11 for t in toks]
+    toks[3] = 7
+    toks[-1] = 9
+    ref = P.forward(w, cfg, toks)
+    other = list(toks)
+    other[3] = 11
+    assert float((P.forward(w, cfg, other)[-1] - ref[-1]).abs().max()) > 0.05 * float(ref[-1].abs().max())
+    model = llogos.weights.load_model(d, dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 12)
+    s = eng.open()
+    lg = eng.step([(s, toks)])
+    ok, err = close(lg[0], ref[-1], dtype, float(ref.abs().max()))
+    assert ok, ("whole", err)
+    eng.close(s)
+    s = eng.open()
+    eng.step([(s, toks[:-1])], [[]])
+    lg = eng.step([(s, [toks[-1]])])
+    ok, err = close(lg[0], ref[-1], dtype, float(ref.abs().max()))
+    assert ok, ("decode", err)

@@ -1,0 +1,384 @@
+"""Each part alone on the GPU against the plain formulas, at sizes of its own; and a toy mixer
+with state of its own, defined here, that is registered, built and stepped without a change to
+the library's files."""
+import importlib
+import math
+
+import pytest
+import torch
+
+import plain_model as P
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+DTYPES = [torch.float32, torch.bfloat16]
+IDS = ["f32", "bf16"]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    return importlib.import_module("daisi-llogos_b200.kernels.ops")
+
+
+def rnd(shape, seed, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def tol(dtype):
+    return 3e-5 if dtype == torch.float32 else 2.5e-2
+
+
+def check(got, ref, dtype, what=""):
+    ref = ref.double()
+    err = float((got.detach().cpu().double() - ref).abs().max())
+    lim = tol(dtype) * max(1.0, float(ref.abs().max()))
+    assert err <= lim, (what, err, lim)
+
+
+def env_for(llogos, ops, dtype, encodings=None):
+    return llogos.parts.BuildEnv(dtype=dtype, device=DEV, ops=ops, encodings=encodings or {})
+
+
+def prompt_ctx(llogos, ops, dtype, counts, before, slots):
+    """A StepContext as the engine lays it out for a step with several tokens per sequence."""
+    ctx_mod = importlib.import_module("daisi-llogos_b200.engine.context")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    cu = [0]
+    for c in counts:
+        cu.append(cu[-1] + c)
+    pos = [p for b, c in zip(before, counts) for p in range(b, b + c)]
+    seq = [i for i, c in enumerate(counts) for _ in range(c)]
+    tiles = [(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, 16)]
+    decode = all(c == 1 for c in counts)
+    return ctx_mod.StepContext(
+        n_tokens=cu[-1], n_seqs=len(counts), decode=decode, counts=list(counts), max_count=max(counts),
+        token_ids=i32([0] * cu[-1]), positions=i32(pos), seq_of_token=i32(seq), slots=i32(slots), cu_tokens=i32(cu),
+        len_before=i32(before), prefill_tiles=None if decode else i32(tiles).view(-1, 2), dtype=dtype, device=DEV, ops=ops,
+        workspace=ctx_mod.Workspace(DEV), max_len_after=max(b + c for b, c in zip(before, counts)))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_rmsnorm_part(llogos, ops, dtype):
+    part = llogos.parts.part_class("norm", "rmsnorm")({"size": 200, "eps": 7e-4}, "n.", env_for(llogos, ops, dtype))
+    assert list(part.tensors()) == ["weight"] and part.tensors()["weight"].shape == (200,)
+    w = rnd((200,), 1, dtype) + 1
+    part.bind({"weight": w.to(DEV)})
+    res, br = rnd((9, 200), 2), rnd((2, 9, 200), 3)
+    ctx = prompt_ctx(llogos, ops, dtype, [9], [0], [0])
+    r = res.to(DEV).clone()
+    out = part.forward(r, llogos.parts.Branch(br.to(DEV)), ctx)
+    total = res.double() + br.double().sum(0)
+    check(out, P.rms_norm(total, w, 7e-4), dtype)
+    check(r, total, torch.float32)
+
+
+def test_rotary_part_tables(llogos, ops):
+    sc = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+          "original_max_position_embeddings": 128}
+    part = llogos.parts.part_class("position", "rotary")(
+        {"head_dim": 80, "rotary_dim": 64, "theta": 5e5, "scaling": sc, "pairing": "adjacent"}, "", env_for(llogos, ops, torch.float32))
+    part.prepare(3000)
+    rot = part.rotation()
+    inv = P.rope_inverse_frequencies(64, 5e5, sc)
+    ang = torch.arange(3000, dtype=torch.float64)[:, None] * inv[None, :]
+    assert rot.rotary_dim == 64 and rot.pairing == 1 and rot.cos.shape == (3000, 32)
+    assert float((rot.cos.cpu().double() - torch.cos(ang)).abs().max()) < 1e-7
+    assert float((rot.sin.cpu().double() - torch.sin(ang)).abs().max()) < 1e-7
+    with pytest.raises(ValueError):
+        llogos.parts.part_class("position", "rotary")({"head_dim": 16, "rotary_dim": 18, "theta": 1.0}, "", env_for(llogos, ops, torch.float32))
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_swiglu_part(llogos, ops, dtype):
+    part = llogos.parts.part_class("ffn", "swiglu")({"hidden_size": 72, "intermediate_size": 200}, "m.", env_for(llogos, ops, dtype))
+    t = {"gate_proj.weight": rnd((200, 72), 4, dtype, 0.2), "up_proj.weight": rnd((200, 72), 5, dtype, 0.2),
+         "down_proj.weight": rnd((72, 200), 6, dtype, 0.2)}
+    assert {k: v.shape for k, v in part.tensors().items()} == {k: tuple(v.shape) for k, v in t.items()}
+    part.bind({k: v.to(DEV) for k, v in t.items()})
+    for n in (3, 130):                                   # the small-step and the large-step path
+        x = rnd((n, 72), 7, dtype)
+        ctx = prompt_ctx(llogos, ops, dtype, [n], [0], [0])
+        out = part.forward(x.to(DEV), ctx)
+        check(out.data.sum(0), P.swiglu(x, t["gate_proj.weight"], t["up_proj.weight"], t["down_proj.weight"]), dtype, n)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_embedding_and_head_parts(llogos, ops, dtype):
+    env = env_for(llogos, ops, dtype)
+    emb = llogos.parts.part_class("embedding", "token_embedding")({"vocab_size": 301, "hidden_size": 72}, "e.", env)
+    head = llogos.parts.part_class("head", "linear_head")({"vocab_size": 301, "hidden_size": 72, "tied_to": None}, "h.", env)
+    table, hw = rnd((301, 72), 8, dtype), rnd((301, 72), 9, dtype, 0.3)
+    emb.bind({"weight": table.to(DEV)})
+    head.bind({"weight": hw.to(DEV)})
+    ctx = prompt_ctx(llogos, ops, dtype, [4], [0], [0])
+    ctx.token_ids = torch.tensor([300, 0, 5, 5], dtype=torch.int32, device=DEV)
+    assert torch.equal(emb.forward(ctx).cpu(), table[[300, 0, 5, 5]].float())
+    x = rnd((4, 72), 10, dtype)
+    lg = head.forward(x.to(DEV), ctx)
+    assert lg.dtype == torch.float32
+    check(lg, P.linear(x, hw), torch.float32 if dtype == torch.float32 else torch.bfloat16)
+    tied = llogos.parts.part_class("head", "linear_head")({"vocab_size": 301, "hidden_size": 72, "tied_to": "e.weight"}, "h.", env)
+    assert tied.tensors() == {}
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("window,qk_norm,bias", [(0, True, False), (50, False, True)])
+def test_attention_part_prompt_then_decode(llogos, ops, dtype, window, qk_norm, bias):
+    """The mixer alone with a cache of its own: a prompt step for two sequences, then single tokens."""
+    hidden, nh, nkv, hd = 72, 6, 2, 48
+    env = env_for(llogos, ops, dtype)
+    rope = llogos.parts.part_class("position", "rotary")({"head_dim": hd, "rotary_dim": hd, "theta": 3e4, "scaling": None, "pairing": "half"}, "", env)
+    rope.prepare(512)
+    env.encodings["r"] = rope
+    params = {"hidden_size": hidden, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd, "qkv_bias": bias,
+              "qk_norm": qk_norm, "qk_norm_eps": 1e-5, "window": window, "position": "r", "softmax_scale": None}
+    att = llogos.parts.part_class("mixer", "attention")(params, "a.", env)
+    decls = att.tensors()
+    t = {}
+    for i, (name, d) in enumerate(sorted(decls.items())):
+        t[name] = rnd(d.shape, 20 + i, dtype, 0.25) + (1 if d.role == "norm" else 0)
+    att.bind({k: v.to(DEV) for k, v in t.items()})
+    need = att.cache_need()
+    assert (need.num_kv_heads, need.head_dim, need.window) == (nkv, hd, window)
+    cache = llogos.cache.SequenceCache({0: need}, max_tokens=64 * 8, max_seq_len=64 * 4, n_slots=3, dtype=dtype, device=DEV)
+    xs = [rnd((n, hidden), 30 + i, dtype) for i, n in enumerate((90, 131))]
+
+    def plain(x):
+        n = x.shape[0]
+        q = P.linear(x, t["q_proj.weight"]).view(n, nh, hd)
+        k = P.linear(x, t["k_proj.weight"]).view(n, nkv, hd)
+        v = P.linear(x, t["v_proj.weight"]).view(n, nkv, hd)
+        if qk_norm:
+            q, k = P.per_head_rms_norm(q, t["q_norm.weight"], 1e-5), P.per_head_rms_norm(k, t["k_norm.weight"], 1e-5)
+        if bias:
+            q = q + t["q_proj.bias"].double().view(nh, hd)
+            k = k + t["k_proj.bias"].double().view(nkv, hd)
+            v = v + t["v_proj.bias"].double().view(nkv, hd)
+        inv = P.rope_inverse_frequencies(hd, 3e4, None)
+        q, k = P.rope_rotate(q, range(n), inv, "half"), P.rope_rotate(k, range(n), inv, "half")
+        o = P.attention(q, k, v, 1 / math.sqrt(hd), window).reshape(n, nh * hd)
+        return P.linear(o, t["o_proj.weight"])
+
+    refs = [plain(x) for x in xs]
+    slots = [cache.acquire(), cache.acquire()]
+    cut = [80, 120]
+    growth = list(zip(slots, cut))
+    for g, ups in cache.grow(growth):
+        if ups:
+            ops.scatter_i32(g.page_table, torch.tensor([u[0] for u in ups], dtype=torch.int32, device=DEV),
+                            torch.tensor([u[1] for u in ups], dtype=torch.int32, device=DEV))
+    ctx = prompt_ctx(llogos, ops, dtype, cut, [0, 0], slots)
+    out = att.forward(torch.cat([x[:c] for x, c in zip(xs, cut)]).to(DEV), ctx, cache.view(0)).data.sum(0)
+    cache.commit(growth)
+    check(out[:80], refs[0][:80], dtype, "prompt 0")
+    check(out[80:], refs[1][:120], dtype, "prompt 1")
+    pos = list(cut)
+    for step in range(10):
+        growth = [(s, 1) for s in slots]
+        for g, ups in cache.grow(growth):
+            if ups:
+                ops.scatter_i32(g.page_table, torch.tensor([u[0] for u in ups], dtype=torch.int32, device=DEV),
+                                torch.tensor([u[1] for u in ups], dtype=torch.int32, device=DEV))
+        ctx = prompt_ctx(llogos, ops, dtype, [1, 1], pos, slots)
+        x = torch.stack([xs[0][pos[0]], xs[1][pos[1]]]).to(DEV)
+        out = att.forward(x, ctx, cache.view(0)).data.sum(0)
+        cache.commit(growth)
+        check(out[0], refs[0][pos[0]], dtype, ("decode 0", pos[0]))
+        check(out[1], refs[1][pos[1]], dtype, ("decode 1", pos[1]))
+        pos = [p + 1 for p in pos]
+
+
+# ---- a toy mixer with state of its own ---------------------------------------------------------
+
+def _toy_parts(llogos):
+    Pt = llogos.parts
+
+    class DecayMixer(Pt.Mixer):
+        """out_t = s_t, s_t = decay * s_{t-1} + W x_t: a running state per sequence, no keys."""
+
+        def __init__(self, params, prefix, env):
+            super().__init__(params, prefix, env)
+            self.hidden, self.decay = int(params["hidden_size"]), float(params["decay"])
+
+        def tensors(self):
+            return {"mix.weight": Pt.TensorDecl((self.hidden, self.hidden))}
+
+        def bind(self, tensors):
+            self.w = tensors["mix.weight"].float()
+
+        def cache_need(self):
+            return Pt.StateNeed((self.hidden,), torch.float32)
+
+        def forward(self, x, ctx, cache):
+            u = x.float() @ self.w.t()
+            out = torch.empty_like(u)
+            slots = ctx.slots.long()
+            state = cache.state[slots]
+            start = 0
+            for b, c in enumerate(ctx.counts):
+                s = state[b]
+                for j in range(c):
+                    s = self.decay * s + u[start + j]
+                    out[start + j] = s
+                state[b] = s
+                start += c
+            cache.state[slots] = state
+            return Pt.Branch(out.unsqueeze(0))
+
+    return DecayMixer
+
+
+def _toy_spec_builder(llogos):
+    S = llogos.parts
+    C = llogos.config
+
+    def build(cfg):
+        spec = C.dense_decoder_spec(cfg)
+        layers = list(spec.layers)
+        for i in (1, 3):                                   # layers 1 and 3 mix by state, 0 and 2 by attention
+            parts = dict(layers[i].parts)
+            parts["mixer"] = S.PartSpec("toy_decay", {"hidden_size": cfg.hidden_size, "decay": 0.5 + 0.1 * i},
+                                        f"model.layers.{i}.toy.")
+            layers[i] = S.LayerSpec("prenorm", parts)
+        import dataclasses
+        return dataclasses.replace(spec, layers=tuple(layers))
+    return build
+
+
+def _toy_plain(weights, cfg, tokens):
+    """The toy model, whole sequence, in float64, from the plain parts."""
+    nh, nkv, hd, eps = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["rms_norm_eps"]
+    t = len(tokens)
+    inv = P.rope_inverse_frequencies(hd, cfg["rope_theta"], None)
+    h = P.embedding(weights["model.embed_tokens.weight"], tokens)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        x = P.rms_norm(h, weights[p + "input_layernorm.weight"], eps)
+        if i in (1, 3):
+            u = P.linear(x, weights[p + "toy.mix.weight"])
+            s = torch.zeros(cfg["hidden_size"], dtype=torch.float64)
+            rows = []
+            for j in range(t):
+                s = (0.5 + 0.1 * i) * s + u[j]
+                rows.append(s)
+            h = h + torch.stack(rows)
+        else:
+            a = p + "self_attn."
+            q = P.rope_rotate(P.linear(x, weights[a + "q_proj.weight"]).view(t, nh, hd), range(t), inv, "half")
+            k = P.rope_rotate(P.linear(x, weights[a + "k_proj.weight"]).view(t, nkv, hd), range(t), inv, "half")
+            v = P.linear(x, weights[a + "v_proj.weight"]).view(t, nkv, hd)
+            o = P.attention(q, k, v, 1 / math.sqrt(hd)).reshape(t, nh * hd)
+            h = h + P.linear(o, weights[a + "o_proj.weight"])
+        x = P.rms_norm(h, weights[p + "post_attention_layernorm.weight"], eps)
+        m = p + "mlp."
+        h = h + P.swiglu(x, weights[m + "gate_proj.weight"], weights[m + "up_proj.weight"], weights[m + "down_proj.weight"])
+    return P.linear(P.rms_norm(h, weights["model.norm.weight"], eps), weights["lm_head.weight"])
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(llogos, tmp_path):
+    from conftest import read_weights, random_tokens
+    reg = importlib.import_module("daisi-llogos_b200.config.registry")
+    llogos.parts.register_part("mixer", "toy_decay", _toy_parts(llogos))
+    llogos.config.register_architecture("ToyDecayForCausalLM", reg._dense_reader(qk_norm=False, force_bias=False),
+                                        _toy_spec_builder(llogos))
+    try:
+        cfg = {"architectures": ["ToyDecayForCausalLM"], "num_hidden_layers": 4, "hidden_size": 48,
+               "num_attention_heads": 3, "num_key_value_heads": 3, "head_dim": 16, "intermediate_size": 80,
+               "vocab_size": 99, "rope_theta": 777.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 256}
+        d = str(tmp_path / "toy")
+        llogos.weights.write_random_model(d, cfg, seed=9, std=0.2, norm_std=0.1)
+        w = read_weights(llogos, d)
+        assert "model.layers.1.toy.mix.weight" in w and "model.layers.1.self_attn.q_proj.weight" not in w
+        model = llogos.weights.load_model(d, dtype=torch.float32, device="cuda:0")
+        eng = llogos.engine.Engine(model, max_tokens=64 * 6, use_graphs=False)
+        assert sorted(eng.cache.state) == [1, 3] and len(eng.cache.kv_groups) == 1
+        assert eng.cache.kv_groups[0].units == [0, 2]
+        seqs = random_tokens(99, [50, 21, 70], 15)
+        refs = [_toy_plain(w, cfg, s) for s in seqs]
+        for rnd_ in range(2):                              # twice: slots and their state are used again
+            slots = [eng.open() for _ in seqs]
+            cut = [len(s) - 6 for s in seqs]
+            lg = eng.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)], [list(range(c)) for c in cut])
+            off = 0
+            for i, c in enumerate(cut):
+                assert float((lg[off:off + c].cpu().double() - refs[i][:c]).abs().max()) < 1e-4
+                off += c
+            for j in range(6):
+                lg = eng.step([(sl, [s[c + j]]) for sl, s, c in zip(slots, seqs, cut)])
+                for i, c in enumerate(cut):
+                    assert float((lg[i].cpu().double() - refs[i][c + j]).abs().max()) < 1e-4, (rnd_, i, j)
+            for sl in slots:
+                eng.close(sl)
+    finally:
+        llogos.parts.unregister_part("mixer", "toy_decay")
+        reg._ARCHITECTURES.pop("ToyDecayForCausalLM", None)
+
+
+def test_layer_run_twice_and_borrowed_cache(llogos, tmp_path):
+    """The run order is data: layer 0 runs twice (own cache each time), and a last entry reads the
+    cache of the first instead of keeping one."""
+    from conftest import read_weights, random_tokens
+    import dataclasses
+    reg = importlib.import_module("daisi-llogos_b200.config.registry")
+    S = llogos.parts
+
+    def build(cfg):
+        spec = llogos.config.dense_decoder_spec(cfg)
+        layers = list(spec.layers)
+        parts = dict(layers[2].parts)
+        params = dict(parts["mixer"].params, own_kv=False)
+        parts["mixer"] = S.PartSpec("attention", params, parts["mixer"].prefix)
+        layers[2] = S.LayerSpec("prenorm", parts)
+        sched = (S.ScheduleEntry(0), S.ScheduleEntry(1), S.ScheduleEntry(0), S.ScheduleEntry(2, cache_of=0))
+        return dataclasses.replace(spec, layers=tuple(layers), schedule=sched)
+
+    llogos.config.register_architecture("ToyLoopForCausalLM", reg._dense_reader(qk_norm=False, force_bias=False), build)
+    try:
+        cfg = {"architectures": ["ToyLoopForCausalLM"], "num_hidden_layers": 3, "hidden_size": 48,
+               "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16, "intermediate_size": 80,
+               "vocab_size": 99, "rope_theta": 777.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 256}
+        d = str(tmp_path / "loop")
+        llogos.weights.write_random_model(d, cfg, seed=10, std=0.2, norm_std=0.1)
+        w = read_weights(llogos, d)
+        assert "model.layers.2.self_attn.k_proj.weight" not in w
+
+        def plain(tokens):
+            t = len(tokens)
+            nh, nkv, hd, eps = 3, 1, 16, 1e-5
+            inv = P.rope_inverse_frequencies(hd, 777.0, None)
+            h = P.embedding(w["model.embed_tokens.weight"], tokens)
+            kept = {}
+            for e, (layer, borrow) in enumerate([(0, None), (1, None), (0, None), (2, 0)]):
+                p = f"model.layers.{layer}."
+                a = p + "self_attn."
+                x = P.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+                q = P.rope_rotate(P.linear(x, w[a + "q_proj.weight"]).view(t, nh, hd), range(t), inv, "half")
+                if borrow is None:
+                    k = P.rope_rotate(P.linear(x, w[a + "k_proj.weight"]).view(t, nkv, hd), range(t), inv, "half")
+                    v = P.linear(x, w[a + "v_proj.weight"]).view(t, nkv, hd)
+                    kept[e] = (k, v)
+                else:
+                    k, v = kept[borrow]
+                o = P.attention(q, k, v, 0.25).reshape(t, nh * hd)
+                h = h + P.linear(o, w[a + "o_proj.weight"])
+                x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+                m = p + "mlp."
+                h = h + P.swiglu(x, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+        model = llogos.weights.load_model(d, dtype=torch.float32, device="cuda:0")
+        eng = llogos.engine.Engine(model, max_tokens=64 * 6)
+        assert sorted(u for g in eng.cache.kv_groups for u in g.units) == [0, 1, 2]
+        seqs = random_tokens(99, [40, 75], 16)
+        refs = [plain(s) for s in seqs]
+        slots = [eng.open(), eng.open()]
+        lg = eng.step([(slots[0], seqs[0][:30]), (slots[1], seqs[1][:70])], [list(range(30)), list(range(70))])
+        assert float((lg[:30].cpu().double() - refs[0][:30]).abs().max()) < 1e-4
+        assert float((lg[30:].cpu().double() - refs[1][:70]).abs().max()) < 1e-4
+        for j in range(5):
+            lg = eng.step([(slots[0], [seqs[0][30 + j]]), (slots[1], [seqs[1][70 + j]])])
+            assert float((lg[0].cpu().double() - refs[0][30 + j]).abs().max()) < 1e-4
+            assert float((lg[1].cpu().double() - refs[1][70 + j]).abs().max()) < 1e-4
+    finally:
+        reg._ARCHITECTURES.pop("ToyLoopForCausalLM", None)
