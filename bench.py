@@ -1,0 +1,251 @@
+"""Decode and prefill throughput of the Llama-3.1-8B shape with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 with every sequence at
+the context length 8192 (one step = one decode step of the whole batch, timed with CUDA events
+around K steps after W warm-up steps).  ``e2e`` is the same batch through the Python entry point
+(``LlogosModel.generate``: host token ids in, host token ids out, sampling included, host clock).
+``prefill`` is one prompt of 2,048 tokens; ``roofline`` relates the decode step to the bytes it has
+to read; ``points`` holds decode at batch 1 and 64.  Every step reads far more than the 126 MB of
+L2 (16 GB of weights plus the cache), so no L2 flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_8B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 32, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336,
+    "vocab_size": 128256, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 131072,
+    "attention_bias": False, "tie_word_embeddings": False,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+}
+CONTEXT = 8192
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    """Measured peaks if the driver wrote them, else the pool's earlier measurement."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    if os.path.isfile(path):
+        try:
+            d = json.load(open(path))
+            if d.get("hbm_gbs") and d.get("bf16_tflops"):
+                out = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+                if d.get("bf16_tflops_sustained"):
+                    out["bf16_tflops_sustained"] = float(d["bf16_tflops_sustained"])
+        except (ValueError, OSError):
+            pass
+    return out
+
+
+class Clocks:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def model_numbers(cfg, n_layers):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = h * (q + 2 * kv) + q * h + 3 * h * i            # matrices only; norms are negligible
+    return {"layer_params": per_layer, "matrix_params": per_layer * n_layers, "head_params": v * h,
+            "kv_bytes_per_token": 2 * kv * 2 * n_layers}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=48)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LLAMA_8B["num_hidden_layers"],
+                    help="layers to build (the configuration has 32); both numbers are reported")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a .NET 10 / C# solution (no Python package, no dotnet SDK in this image): "
+                          "pip cannot install it and its CLI cannot be built here"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this library has no multi-GPU path (asked for {args.gpus})")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import importlib
+    import torch
+    L = importlib.import_module("llogos_b200")
+    ops = importlib.import_module("daisi-llogos_b200.kernels.ops")
+    pk = peaks()
+    cfg = dict(LLAMA_8B, num_hidden_layers=args.layers)
+    nums = model_numbers(cfg, args.layers)
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+
+    t0 = time.time()
+    model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
+    big = max(64, args.batch)
+    engine = L.engine.Engine(model, max_tokens=big * CONTEXT, max_seq_len=CONTEXT, n_slots=big)
+    for g in engine.cache.kv_groups:             # random keys and values: attention over real numbers
+        for t in list(g.k.values()) + list(g.v.values()):
+            t.normal_(0.0, 1.0)
+    torch.cuda.synchronize()
+    print(f"[bench] model and cache ready in {time.time() - t0:.1f} s "
+          f"(weights {(nums['matrix_params'] + 2 * nums['head_params']) * 2 / 1e9:.2f} GB, cache {engine.cache.bytes() / 1e9:.1f} GB)",
+          file=sys.stderr, flush=True)
+    gen = torch.Generator().manual_seed(1)
+
+    # ---- prefill of 2,048 tokens ------------------------------------------------------------
+    toks = torch.randint(0, cfg["vocab_size"], (PREFILL_TOKENS,), generator=gen).tolist()
+    times = []
+    for it in range(3 + 5):
+        slot = engine.open()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        engine.step([(slot, toks)])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            times.append(e0.elapsed_time(e1))
+        engine.close(slot)
+    pre_ms = sorted(times)[len(times) // 2]
+    t = PREFILL_TOKENS
+    attn_flops = args.layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * (t * (t + 1) / 2)
+    pre_flops = 2.0 * t * nums["matrix_params"] + 2.0 * nums["head_params"] + attn_flops
+    prefill = {"value": round(t / (pre_ms / 1e3), 1), "tokens": t, "ms": round(pre_ms, 3),
+               "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
+
+    # ---- decode steps at the context length --------------------------------------------------
+    def decode(batch, steps, warmup, clocks=None):
+        slots = [engine.open() for _ in range(batch)]
+        start = CONTEXT - (steps + warmup)
+        for s in slots:
+            engine.assume(s, start)
+        tok = torch.randint(0, cfg["vocab_size"], (steps + warmup, batch), generator=gen).tolist()
+        for i in range(warmup):
+            engine.step([(s, [tok[i][j]]) for j, s in enumerate(slots)])
+        torch.cuda.synchronize()
+        k0, l0 = engine.graph_kernels, ops.launches()
+        if clocks:
+            clocks.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warmup, warmup + steps):
+            engine.step([(s, [tok[i][j]]) for j, s in enumerate(slots)])
+        e1.record()
+        torch.cuda.synchronize()
+        if clocks:
+            clocks.stop()
+        ms = e0.elapsed_time(e1) / steps
+        launches = (engine.graph_kernels - k0) + (ops.launches() - l0)
+        mean_len = start + warmup + (steps + 1) / 2.0
+        for s in slots:
+            engine.close(s)
+        return ms, launches, mean_len
+
+    clocks = Clocks()
+    ms, launches, mean_len = decode(args.batch, args.steps, args.warmup, clocks)
+    value = args.batch / (ms / 1e3)
+    weight_bytes = (nums["matrix_params"] + nums["head_params"]) * 2 + args.batch * cfg["hidden_size"] * 2
+    step_bytes = weight_bytes + args.batch * mean_len * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]}
+    print(f"[bench] decode b{args.batch}: {ms:.3f} ms/step, {value:.1f} tok/s, {roofline}", file=sys.stderr, flush=True)
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _ = decode(b, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
+            print(f"[bench] decode b{b}: {pms:.3f} ms/step", file=sys.stderr, flush=True)
+
+    # ---- the same batch through the Python entry point ----------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        del engine
+        torch.cuda.empty_cache()
+        api = L.LlogosModel(model, max_context=CONTEXT, max_batch=args.batch)
+        n_new = args.steps
+        prompts = [torch.randint(0, cfg["vocab_size"], (CONTEXT - n_new - 1,), generator=gen).tolist() for _ in range(args.batch)]
+        params = L.GenerationParams.greedy_params(n_new, stop_tokens=())
+        api.generate([p[:64] for p in prompts], L.GenerationParams.greedy_params(args.warmup + 2, stop_tokens=()))   # warm-up: graph capture
+        r = api.generate(prompts, params)
+        e2e = {"value": round(r.decode_tokens_per_second, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": (6 * args.batch + 1) * 4, "d2h_bytes_per_step": args.batch * 4,
+               "prefill_tokens_per_s": round(r.prefill_tokens_per_second, 1), "decode_steps": r.decode_steps}
+        print(f"[bench] e2e {e2e}", file=sys.stderr, flush=True)
+
+    line = {
+        "metric": "decode tokens/s at batch 8, context 8192 (Llama-3.1-8B shape, bf16, random weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids, random cache contents",
+        "impl": "ours",
+        "config": {"model": "Llama-3.1-8B shape", "layers": args.layers, "layers_of_config": LLAMA_8B["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "rope_theta": cfg["rope_theta"], "rope_scaling": "llama3 factor 8 low 1 high 4 original 8192",
+                   "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+                   "l2": "every step reads more than L2 holds (weights + cache), no flush",
+                   "cache": "pages of 64 tokens, bf16", "decode": "CUDA graph per batch size"},
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "gpu_launches": int(launches), "clocks": clocks.summary(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
