@@ -403,3 +403,58 @@ LLG_API int llg_attn_decode_simt(const DecodeArgs* args, void* out, int dtype, c
   }
   return llg_check_launch("attn_decode");
 }
+
+// ---- the entry point that allocates nothing (see attention_noalloc.h) ---------------------------
+
+#include "attention_noalloc.h"
+
+// Scratch for the split partials of llg_attn_decode_noalloc.  In host code this name is only a
+// handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_noalloc_scratch[LLG_ATTN_NOALLOC_MAX_FLOATS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES];   // device address of the array, per device, once looked up
+}  // namespace
+
+int llg_attn_decode_noalloc(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
+                            int table_width, int ring_pages, const int* slots, const int* len_before, void* out,
+                            int dtype, int n_seqs, int n_heads, int n_kv_heads, int head_dim, int n_splits,
+                            float scale, int window, cudaStream_t stream) {
+  LLG_REQUIRE(n_seqs >= 0 && n_heads > 0 && head_dim > 0 && n_splits >= 1, "attn_decode_noalloc: bad sizes");
+  const long long need = (long long)n_seqs * n_heads * n_splits * (head_dim + 2);
+  LLG_REQUIRE(need <= (long long)LLG_ATTN_NOALLOC_MAX_FLOATS,
+              "attn_decode_noalloc: %d sequences x %d heads x %d splits x (%d + 2) = %lld floats of scratch, "
+              "the built-in array holds %d; use fewer splits or llg_attn_decode_simt with scratch of your own",
+              n_seqs, n_heads, n_splits, head_dim, need, (int)LLG_ATTN_NOALLOC_MAX_FLOATS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return llg_fail("attn_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  LLG_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "attn_decode_noalloc: device index %d is not supported", dev);
+  if (g_noalloc_ptr[dev] == nullptr) {   // set-up, once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return llg_fail("attn_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = p;
+  }
+  DecodeArgs a;
+  a.q = q;
+  a.k_pages = k_pages;
+  a.v_pages = v_pages;
+  a.page_table = page_table;
+  a.table_width = table_width;
+  a.ring_pages = ring_pages;
+  a.slots = slots;
+  a.len_before = len_before;
+  a.part_o = g_noalloc_ptr[dev];
+  a.part_ml = g_noalloc_ptr[dev] + (long long)n_seqs * n_heads * n_splits * head_dim;
+  a.n_seqs = n_seqs;
+  a.nh = n_heads;
+  a.nkv = n_kv_heads;
+  a.hd = head_dim;
+  a.n_splits = n_splits;
+  a.scale = scale;
+  a.window = window;
+  return llg_attn_decode_simt(&a, out, dtype, stream);
+}

@@ -30,7 +30,7 @@ SOURCES: Dict[str, List[str]] = {
     "elementwise": ["elementwise.cu", "common.cuh"],
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
     "gemm_tc": ["gemm_tc.cu", "common.cuh"],
-    "attention_simt": ["attention_simt.cu", "common.cuh"],
+    "attention_simt": ["attention_simt.cu", "common.cuh", "attention_noalloc.h"],
     "sampling": ["sampling.cu", "common.cuh"],
 }
 
