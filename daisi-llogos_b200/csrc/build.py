@@ -31,6 +31,7 @@ SOURCES: Dict[str, List[str]] = {
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
     "gemm_tc": ["gemm_tc.cu", "common.cuh"],
     "attention_simt": ["attention_simt.cu", "common.cuh", "attention_noalloc.h"],
+    "attention_mma": ["attention_mma.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
 }
 

@@ -54,7 +54,7 @@ class StepContext:
     slots: torch.Tensor               # [B]
     cu_tokens: torch.Tensor           # [B + 1]
     len_before: torch.Tensor          # [B] tokens each sequence held before this step
-    prefill_tiles: Optional[torch.Tensor]   # [n_tiles, 2] (sequence, first query) for prompt steps
+    prefill_tiles: Optional[Dict[int, torch.Tensor]]   # queries per tile -> [n_tiles, 2] (sequence, first query)
     dtype: torch.dtype = torch.float32
     device: torch.device = None
     ops: Any = None

@@ -24,7 +24,7 @@ from ..cache.store import PAGE, SequenceCache
 from .context import StepContext, Workspace
 from .model import DecoderModel
 
-_TILE_Q = 16   # queries per block of the prompt attention kernel
+_TILE_QS = (16, 64)   # queries per block of the prompt attention kernels (CUDA cores, tensor cores)
 
 
 class StepError(ValueError):
@@ -206,11 +206,11 @@ class Engine:
         token_ids = np.concatenate(toks).astype(np.int32)
         positions = np.concatenate([np.arange(lb, lb + c, dtype=np.int32) for lb, c in zip(len_before, counts)])
         seq_of = np.repeat(np.arange(b, dtype=np.int32), counts)
-        tiles = np.array([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, _TILE_Q)],
-                         dtype=np.int32).reshape(-1)
+        tiles = [np.array([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)],
+                          dtype=np.int32).reshape(-1) for tq in _TILE_QS]
         rows = np.array([cu[i] + int(w) for i in range(b) for w in want[i]], dtype=np.int32)
         host = [token_ids, positions, seq_of, np.asarray(slots, dtype=np.int32), cu,
-                np.asarray(len_before, dtype=np.int32), tiles, rows]
+                np.asarray(len_before, dtype=np.int32), *tiles, rows]
         plan = self._apply_updates(updates, host)
         block = np.concatenate(host)
         meta = self._ensure_meta(block.size)
@@ -226,7 +226,8 @@ class Engine:
         ctx = StepContext(
             n_tokens=n, n_seqs=b, decode=False, counts=counts, max_count=max(counts),
             token_ids=take(n), positions=take(n), seq_of_token=take(n), slots=take(b), cu_tokens=take(b + 1),
-            len_before=take(b), prefill_tiles=take(tiles.size).view(-1, 2), dtype=self.dtype, device=self.device,
+            len_before=take(b), prefill_tiles={tq: take(t.size).view(-1, 2) for tq, t in zip(_TILE_QS, tiles)},
+            dtype=self.dtype, device=self.device,
             ops=self.ops, workspace=self._workspace,
             max_len_after=max(lb + c for lb, c in zip(len_before, counts)))
         rows_dev = take(rows.size)

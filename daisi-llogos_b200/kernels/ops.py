@@ -149,6 +149,10 @@ def _lib(name: str):
         lib.llg_attn_decode_simt.argtypes = [POINTER(_DecodeArgs), c_void_p, c_int, c_void_p]
         lib.llg_attn_decode_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
         lib.llg_attn_decode_scratch_floats.restype = c_longlong
+    elif name == "attention_mma":
+        lib.llg_attn_mma_supported.argtypes = [c_int]
+        lib.llg_attn_prefill_mma.argtypes = [POINTER(_PrefillArgs), c_void_p]
+        lib.llg_attn_decode_mma.argtypes = [POINTER(_DecodeArgs), c_void_p, c_void_p]
     elif name == "sampling":
         lib.llg_argmax.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.llg_sample.argtypes = [POINTER(_SampleArgs), c_void_p]
@@ -323,13 +327,35 @@ def zero_rows(base: torch.Tensor, rows: torch.Tensor) -> None:
     _check(lib, lib.llg_zero_rows(_ptr(base), _ptr(rows, torch.int32), rows.numel(), row_bytes, _stream()))
 
 
+def _use_mma(dtype: torch.dtype, head_dim: int) -> bool:
+    """bfloat16 attention with a head size the tensor-core kernels take (multiples of 16 up to 128)."""
+    return dtype == torch.bfloat16 and 16 <= head_dim <= 128 and head_dim % 16 == 0
+
+
+def prefill_tile_queries(dtype: torch.dtype, head_dim: int) -> int:
+    """Queries per block of the prompt attention kernel that ``attn_prefill`` will run."""
+    return 64 if _use_mma(dtype, head_dim) else 16
+
+
 def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tiles, cu_tokens, len_before,
-                 slots, out, *, scale: float, window: int) -> None:
-    """Causal attention for a step with several tokens per sequence (see csrc/attention_simt.cu)."""
-    lib = _lib("attention_simt")
+                 slots, out, *, scale: float, window: int, tile_queries: int) -> None:
+    """Causal attention for a step with several tokens per sequence.
+
+    ``tiles`` is ``[n_tiles, 2]`` (sequence index, first query among its step tokens) cut every
+    ``tile_queries`` queries, which must be ``prefill_tile_queries(q.dtype, head_dim)``.  bfloat16 with
+    head sizes up to 128 runs on the tensor cores (csrc/attention_mma.cu), everything else on the
+    CUDA cores (csrc/attention_simt.cu).
+    """
     n, nh, hd = q.shape
     nkv = k_new.shape[1]
     assert out.shape == (n, nh * hd)
+    if tile_queries != prefill_tile_queries(q.dtype, hd):
+        raise KernelError(f"attn_prefill: tiles of {tile_queries} queries, the kernel works on "
+                          f"{prefill_tile_queries(q.dtype, hd)}")
+    if scale <= 0:
+        raise KernelError("attn_prefill: the softmax scale must be positive")
+    mma = _use_mma(q.dtype, hd)
+    lib = _lib("attention_mma" if mma else "attention_simt")
     a = _PrefillArgs()
     a.q, a.k_new, a.v_new = _ptr(q), _ptr(k_new, q.dtype), _ptr(v_new, q.dtype)
     a.k_pages, a.v_pages = _ptr(k_pages, q.dtype), _ptr(v_pages, q.dtype)
@@ -339,22 +365,26 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
     a.out = _ptr(out, q.dtype)
     a.n_tiles, a.nh, a.nkv, a.hd = tiles.shape[0], nh, nkv, hd
     a.scale, a.window = float(scale), int(window)
-    _check(lib, lib.llg_attn_prefill_simt(byref(a), _dt(q), _stream()))
-
-
-PREFILL_QUERIES_PER_TILE = 16
+    if mma:
+        _check(lib, lib.llg_attn_prefill_mma(byref(a), _stream()))
+    else:
+        _check(lib, lib.llg_attn_prefill_simt(byref(a), _dt(q), _stream()))
 
 
 def attn_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
-    return _lib("attention_simt").llg_attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits)
+    """Floats of scratch ``attn_decode`` needs for the partial results of its key splits."""
+    return n_seqs * n_heads * n_splits * (head_dim + 2)
 
 
 def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
                 n_splits: int, scale: float, window: int) -> None:
     """Attention of one new token per sequence over the cache; ``scratch`` holds the split partials."""
-    lib = _lib("attention_simt")
     b, nh, hd = q.shape
     nkv = k_pages.shape[1]
+    if scale <= 0:
+        raise KernelError("attn_decode: the softmax scale must be positive")
+    mma = _use_mma(q.dtype, hd)
+    lib = _lib("attention_mma" if mma else "attention_simt")
     need = b * nh * n_splits * (hd + 2)
     if scratch.numel() < need or scratch.dtype != torch.float32:
         raise KernelError(f"attn_decode: scratch of {scratch.numel()} floats, {need} needed")
@@ -367,7 +397,10 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
     a.part_ml = base + 4 * b * nh * n_splits * hd
     a.n_seqs, a.nh, a.nkv, a.hd, a.n_splits = b, nh, nkv, hd, n_splits
     a.scale, a.window = float(scale), int(window)
-    _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()), kernels=2)
+    if mma:
+        _check(lib, lib.llg_attn_decode_mma(byref(a), _ptr(out, q.dtype), _stream()), kernels=2)
+    else:
+        _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()), kernels=2)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

@@ -125,9 +125,10 @@ class Attention(Mixer):
             else:
                 ops.qk_prep(qkv, **common)
                 k_new, v_new = cache.shared["k_new"], cache.shared["v_new"]
+            tq = ops.prefill_tile_queries(q.dtype, self.hd)
             ops.attn_prefill(q, k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
-                             ctx.prefill_tiles, ctx.cu_tokens, ctx.len_before, ctx.slots, out,
-                             scale=self.scale, window=self.window)
+                             ctx.prefill_tiles[tq], ctx.cu_tokens, ctx.len_before, ctx.slots, out,
+                             scale=self.scale, window=self.window, tile_queries=tq)
             if self.own_kv:
                 ops.kv_write(k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
                              ctx.positions, ctx.seq_of_token, ctx.slots, ctx.cu_tokens, ctx.len_before)

@@ -9,7 +9,6 @@ from __future__ import annotations
 import torch
 
 PAGE = 64
-PREFILL_QUERIES_PER_TILE = 16
 
 
 def require_gpu():
@@ -134,8 +133,12 @@ def _gather(k_pages, v_pages, page_table, ring_pages, slot, positions, kvh):
     return ks, vs
 
 
+def prefill_tile_queries(dtype, head_dim):
+    return 16
+
+
 def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tiles, cu_tokens, len_before,
-                 slots, out, *, scale, window):
+                 slots, out, *, scale, window, tile_queries=16):
     n, nh, hd = q.shape
     nkv = k_new.shape[1]
     g = nh // nkv

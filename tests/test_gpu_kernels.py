@@ -191,7 +191,8 @@ def _paged(nkv, hd, dtype, lens, n_pages, ring_pages, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 0), (6, 3, 80, 0), (12, 1, 32, 0), (4, 2, 128, 100), (8, 4, 16, 70)])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 0), (6, 3, 80, 0), (12, 1, 32, 0), (4, 2, 128, 100), (8, 4, 16, 70),
+                                              (34, 2, 64, 0), (3, 3, 112, 0), (2, 1, 144, 0), (4, 2, 256, 130)])
 def test_attn_decode(ops, dtype, nh, nkv, hd, window):
     lens = [1, 64, 65, 300, 129]
     ring = 8 if window == 0 else (window + 63) // 64 + 1
@@ -212,7 +213,8 @@ def test_attn_decode(ops, dtype, nh, nkv, hd, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 0), (6, 3, 80, 0), (4, 2, 128, 100), (8, 4, 16, 40)])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 0), (6, 3, 80, 0), (4, 2, 128, 100), (8, 4, 16, 40), (3, 1, 112, 0),
+                                              (2, 2, 144, 0), (2, 1, 256, 90)])
 def test_attn_prefill_and_kv_write(ops, dtype, nh, nkv, hd, window):
     before = [0, 0, 70, 130, 64]           # tokens already in the cache
     counts = [1, 37, 16, 150, 3]           # tokens the step brings
@@ -231,15 +233,15 @@ def test_attn_prefill_and_kv_write(ops, dtype, nh, nkv, hd, window):
     q = rnd((n, nh, hd), 41, dtype)
     k_new = torch.cat([ks[b][before[b]:] for b in range(len(counts))])
     v_new = torch.cat([vs[b][before[b]:] for b in range(len(counts))])
-    tiles = torch.tensor([(b, q0) for b, c in enumerate(counts) for q0 in range(0, c, ops.PREFILL_QUERIES_PER_TILE)],
-                         dtype=torch.int32)
+    tq = ops.prefill_tile_queries(dtype, hd)
+    tiles = torch.tensor([(b, q0) for b, c in enumerate(counts) for q0 in range(0, c, tq)], dtype=torch.int32)
     out = torch.empty(n, nh * hd, dtype=dtype, device=DEV)
     scale = 0.37
     d = lambda t: t.to(DEV)
     kpd, vpd = d(kp0), d(vp0)
     lb = torch.tensor(before, dtype=torch.int32)
     ops.attn_prefill(d(q), d(k_new), d(v_new), kpd, vpd, d(table), ring, d(tiles), d(cu), d(lb), d(slots), out,
-                     scale=scale, window=window)
+                     scale=scale, window=window, tile_queries=tq)
     for b in range(len(counts)):
         qq = torch.zeros(total[b], nh, hd, dtype=dtype)
         qq[before[b]:] = q[int(cu[b]):int(cu[b + 1])]

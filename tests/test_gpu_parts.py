@@ -49,12 +49,12 @@ def prompt_ctx(llogos, ops, dtype, counts, before, slots):
         cu.append(cu[-1] + c)
     pos = [p for b, c in zip(before, counts) for p in range(b, b + c)]
     seq = [i for i, c in enumerate(counts) for _ in range(c)]
-    tiles = [(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, 16)]
+    tiles = {tq: i32([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)]).view(-1, 2) for tq in (16, 64)}
     decode = all(c == 1 for c in counts)
     return ctx_mod.StepContext(
         n_tokens=cu[-1], n_seqs=len(counts), decode=decode, counts=list(counts), max_count=max(counts),
         token_ids=i32([0] * cu[-1]), positions=i32(pos), seq_of_token=i32(seq), slots=i32(slots), cu_tokens=i32(cu),
-        len_before=i32(before), prefill_tiles=None if decode else i32(tiles).view(-1, 2), dtype=dtype, device=DEV, ops=ops,
+        len_before=i32(before), prefill_tiles=None if decode else tiles, dtype=dtype, device=DEV, ops=ops,
         workspace=ctx_mod.Workspace(DEV), max_len_after=max(b + c for b, c in zip(before, counts)))
 
 
