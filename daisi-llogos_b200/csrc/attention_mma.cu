@@ -130,28 +130,37 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
   const bf16* kp = (const bf16*)a.k_pages;
   const bf16* vp = (const bf16*)a.v_pages;
 
+  // Thread `tid` copies 16-byte chunk `ch0` of rows `row0, row0 + rstep, ...` when 128 is a multiple of
+  // the chunks per row (head sizes 16, 32, 64, 128); other head sizes take the general indexing.
+  const bool regular = (128 % cpr) == 0;
+  const int row0 = tid / cpr, ch0 = tid - row0 * cpr, rstep = regular ? 128 / cpr : 0;
   auto load_kv = [&](int tile, int stage) {
-    const int kt = k_begin + tile * TK;
+    const int kt = k_begin + tile * TK;           // a multiple of 64: the tile's old positions share one page
     unsigned char* kd = Ks + stage * 64 * rs;
     unsigned char* vd = Vs + stage * 64 * rs;
-    for (int c = tid; c < 64 * cpr; c += 128) {
-      const int row = c / cpr, ch = c - row * cpr;
-      const int pos = kt + row;
-      const bool valid = pos < k_end;
-      const bf16 *ks = kp, *vs = vp;
-      if (valid) {
-        if (pos >= lb) {
-          const long long off = ((long long)(tok0 + pos - lb) * a.nkv + kvh) * hd + ch * 8;
-          ks = kn + off;
-          vs = vn + off;
-        } else {
-          const long long off = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv) * hd + ch * 8;
-          ks = kp + off;
-          vs = vp + off;
-        }
+    const long long old_base = kt < lb ? kv_row(a.page_table, a.table_width, a.ring_pages, slot, kt, kvh, a.nkv) * hd : 0;
+    const long long new_base = ((long long)(tok0 + kt - lb) * a.nkv + kvh) * hd;    // row r adds r * nkv * hd
+    const long long new_step = (long long)a.nkv * hd;
+    if (regular) {
+      uint32_t kdst = smem_u32(kd + row0 * rs + ch0 * 16), vdst = smem_u32(vd + row0 * rs + ch0 * 16);
+      for (int row = row0; row < 64; row += rstep, kdst += rstep * rs, vdst += rstep * rs) {
+        const int pos = kt + row;
+        const bool valid = pos < k_end;
+        const bool fresh = pos >= lb;
+        const long long off = (fresh ? new_base + row * new_step : old_base + (long long)row * hd) + ch0 * 8;
+        cp_async16(kdst, (fresh ? kn : kp) + (valid ? off : 0), valid);
+        cp_async16(vdst, (fresh ? vn : vp) + (valid ? off : 0), valid);
       }
-      cp_async16(smem_u32(kd + row * rs + ch * 16), ks, valid);
-      cp_async16(smem_u32(vd + row * rs + ch * 16), vs, valid);
+    } else {
+      for (int c = tid; c < 64 * cpr; c += 128) {
+        const int row = c / cpr, ch = c - row * cpr;
+        const int pos = kt + row;
+        const bool valid = pos < k_end;
+        const bool fresh = pos >= lb;
+        const long long off = (fresh ? new_base + row * new_step : old_base + (long long)row * hd) + ch * 8;
+        cp_async16(smem_u32(kd + row * rs + ch * 16), (fresh ? kn : kp) + (valid ? off : 0), valid);
+        cp_async16(smem_u32(vd + row * rs + ch * 16), (fresh ? vn : vp) + (valid ? off : 0), valid);
+      }
     }
   };
 
@@ -296,8 +305,24 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
 }
 
 // ---- one new token per sequence ------------------------------------------------------------------
+//
+// The products are taken transposed so that no MMA row is padding: S^T = K Q^T has the warp's 16
+// keys as rows and (up to 8) query heads of the group as columns; O^T = V^T P^T has 16 head
+// dimensions as rows.  P^T reaches the operand layout of the second product by movmatrix.
 
 constexpr int DSTAGES = 3;
+constexpr int GH = 8;     // query heads per pass (one MMA n-tile)
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+// d (16x8) += a (16x16, row) * b (16x8, col)
+__device__ __forceinline__ void mma_16816_b2(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  mma_16816(d, a, b0, b1);
+}
 
 template <int HDMAX>
 __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
@@ -308,7 +333,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
   const int ksteps = hd / 16;
   unsigned char* Ks = smraw;                          // [DSTAGES][64][rs]
   unsigned char* Vs = Ks + DSTAGES * 64 * rs;         // [DSTAGES][64][rs]
-  float* merge = reinterpret_cast<float*>(smraw);     // after the key loop: [4 warps][16 rows][hd + 2]
+  float* merge = reinterpret_cast<float*>(smraw);     // after the key loop: [4 warps][GH heads][hd + 2]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -326,148 +351,158 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
   const bf16* qg = (const bf16*)a.q;
   const float sc = a.scale * LOG2E;
 
-  auto load_kv = [&](int tile, int stage) {
+  // The page of a tile is looked up one iteration before its copies are issued, so that the
+  // table read never sits between a finished tile and the next prefetch.
+  auto page_base = [&](int tile) -> long long {
     // positions 64 * tile .. + 63 lie in one page, contiguous for this key/value head
-    const long long base = kv_row(a.page_table, a.table_width, a.ring_pages, slot, tile * TK, kvh, a.nkv) * hd;
+    return kv_row(a.page_table, a.table_width, a.ring_pages, slot, tile * TK, kvh, a.nkv) * hd;
+  };
+  const bool regular = (128 % cpr) == 0;
+  const int row0 = tid / cpr, ch0 = tid - row0 * cpr, rstep = regular ? 128 / cpr : 0;
+  auto load_kv = [&](long long base, int stage) {
     unsigned char* kd = Ks + stage * 64 * rs;
     unsigned char* vd = Vs + stage * 64 * rs;
-    for (int c = tid; c < 64 * cpr; c += 128) {
-      const int row = c / cpr, ch = c - row * cpr;
-      const long long off = base + (long long)row * hd + ch * 8;
-      cp_async16(smem_u32(kd + row * rs + ch * 16), kp + off, true);
-      cp_async16(smem_u32(vd + row * rs + ch * 16), vp + off, true);
+    if (regular) {
+      uint32_t kdst = smem_u32(kd + row0 * rs + ch0 * 16), vdst = smem_u32(vd + row0 * rs + ch0 * 16);
+      const bf16* ksrc = kp + base + (long long)row0 * hd + ch0 * 8;
+      const bf16* vsrc = vp + base + (long long)row0 * hd + ch0 * 8;
+      const int gstep = rstep * hd, sstep = rstep * rs;
+      for (int row = row0; row < 64; row += rstep, kdst += sstep, vdst += sstep, ksrc += gstep, vsrc += gstep) {
+        cp_async16(kdst, ksrc, true);
+        cp_async16(vdst, vsrc, true);
+      }
+    } else {
+      for (int c = tid; c < 64 * cpr; c += 128) {
+        const int row = c / cpr, ch = c - row * cpr;
+        const long long off = base + (long long)row * hd + ch * 8;
+        cp_async16(smem_u32(kd + row * rs + ch * 16), kp + off, true);
+        cp_async16(smem_u32(vd + row * rs + ch * 16), vp + off, true);
+      }
     }
   };
 
-  for (int g0 = 0; g0 < G; g0 += 16) {
-    const int ng = min(16, G - g0);
+  for (int g0 = 0; g0 < G; g0 += GH) {
+    const int ng = min(GH, G - g0);
     __syncthreads();                                  // merge area of the previous pass is free again
-    // prologue of the pipeline
 #pragma unroll
     for (int s = 0; s < DSTAGES - 1; ++s) {
-      if (s < n_my) load_kv(my0 + s, s);
+      if (s < n_my) load_kv(page_base(my0 + s), s);
       cp_async_commit();
     }
-    // query fragments straight from global memory: rows = heads of this group
-    uint32_t qf[HDMAX / 16][4];
+    long long next_base = (DSTAGES - 1 < n_my) ? page_base(my0 + DSTAGES - 1) : 0;
+    // Q^T as the second operand: column g is head g0 + g, rows are head dimensions
+    uint32_t qf[HDMAX / 16][2];
 #pragma unroll
     for (int ks = 0; ks < HDMAX / 16; ++ks) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int row = g + (e & 1) * 8;
-        const int col = ks * 16 + 2 * t + (e >> 1) * 8;
+      for (int e = 0; e < 2; ++e) {
         uint32_t v = 0;
-        if (ks < ksteps && row < ng)
-          v = *reinterpret_cast<const uint32_t*>(qg + ((long long)b * a.nh + kvh * G + g0 + row) * hd + col);
+        if (ks < ksteps && g < ng)
+          v = *reinterpret_cast<const uint32_t*>(qg + ((long long)b * a.nh + kvh * G + g0 + g) * hd + ks * 16 + 2 * t + e * 8);
         qf[ks][e] = v;
       }
     }
-    float o[HDMAX / 8][4];
+    float o[HDMAX / 16][4];      // O^T: rows = 16 head dimensions per tile, columns = heads 2t, 2t + 1
 #pragma unroll
-    for (int j = 0; j < HDMAX / 8; ++j)
+    for (int j = 0; j < HDMAX / 16; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};   // per column (head 2t, 2t + 1)
 
     for (int i = 0; i < n_my; ++i) {
       const int stage = i % DSTAGES;
-      if (i + DSTAGES - 1 < n_my) load_kv(my0 + i + DSTAGES - 1, (i + DSTAGES - 1) % DSTAGES);
+      if (i + DSTAGES - 1 < n_my) load_kv(next_base, (i + DSTAGES - 1) % DSTAGES);
       cp_async_commit();
+      if (i + DSTAGES < n_my) next_base = page_base(my0 + i + DSTAGES);
       cp_async_wait<DSTAGES - 1>();
       __syncthreads();
       const unsigned char* kd = Ks + stage * 64 * rs;
       const unsigned char* vd = Vs + stage * 64 * rs;
       const int kt = (my0 + i) * TK + warp * 16;     // this warp's 16 keys of the page
 
-      float s[2][4];
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+      // S^T = K Q^T, two accumulators so that the chain of dependent MMAs is half as long
+      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t k_addr = smem_u32(kd + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * rs + (lane >> 4) * 16);
 #pragma unroll
       for (int ks = 0; ks < HDMAX / 16; ++ks) {
         if (ks < ksteps) {
-          uint32_t kb[4];
-          const int row = warp * 16 + (lane & 7) + (lane >> 4) * 8;
-          const int col = ks * 16 + ((lane >> 3) & 1) * 8;
-          ldmatrix_x4(kb, smem_u32(kd + row * rs + col * 2));
-          mma_16816(s[0], qf[ks], kb[0], kb[1]);
-          mma_16816(s[1], qf[ks], kb[2], kb[3]);
+          uint32_t ka[4];
+          ldmatrix_x4(ka, k_addr + ks * 32);
+          if (ks & 1) mma_16816(s1, ka, qf[ks][0], qf[ks][1]);
+          else mma_16816(s0, ka, qf[ks][0], qf[ks][1]);
         }
       }
-      float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int key = kt + j * 8 + 2 * t + (e & 1);
-          const bool valid = key >= lo && key < len;
-          s[j][e] = valid ? s[j][e] : -INFINITY;
-          mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
-        }
+      float sv[4];
+      const bool valid0 = (kt + g) >= lo && (kt + g) < len;
+      const bool valid1 = (kt + g + 8) >= lo && (kt + g + 8) < len;
+      sv[0] = valid0 ? s0[0] + s1[0] : -INFINITY;
+      sv[1] = valid0 ? s0[1] + s1[1] : -INFINITY;
+      sv[2] = valid1 ? s0[2] + s1[2] : -INFINITY;
+      sv[3] = valid1 ? s0[3] + s1[3] : -INFINITY;
+      // column maxima over the 16 keys: rows live in lanes that differ in g
+      float mx[2] = {fmaxf(sv[0], sv[2]), fmaxf(sv[1], sv[3])};
       float corr[2];
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m[r], mx[r]);
-        corr[r] = (m_new == -INFINITY) ? 1.f : exp2f((m[r] - m_new) * sc);
-        m[r] = m_new;
-        l[r] *= corr[r];
+      for (int c = 0; c < 2; ++c) {
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 4));
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
+        const float m_new = fmaxf(m[c], mx[c]);
+        corr[c] = (m_new == -INFINITY) ? 1.f : exp2f((m[c] - m_new) * sc);
+        m[c] = m_new;
       }
+      float pv[4];
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int e = 0; e < 4; ++e) {
+        const int c = e & 1;
+        pv[e] = (m[c] == -INFINITY) ? 0.f : exp2f((sv[e] - m[c]) * sc);
+      }
+      l[0] = l[0] * corr[0] + pv[0] + pv[2];
+      l[1] = l[1] * corr[1] + pv[1] + pv[3];
+      if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int r = e >> 1;
-          const float p = (m[r] == -INFINITY) ? 0.f : exp2f((s[j][e] - m[r]) * sc);
-          s[j][e] = p;
-          l[r] += p;
+        for (int j = 0; j < HDMAX / 16; ++j) {
+          o[j][0] *= corr[0];
+          o[j][1] *= corr[1];
+          o[j][2] *= corr[0];
+          o[j][3] *= corr[1];
         }
-#pragma unroll
-      for (int j = 0; j < HDMAX / 8; ++j) {
-        o[j][0] *= corr[0];
-        o[j][1] *= corr[0];
-        o[j][2] *= corr[1];
-        o[j][3] *= corr[1];
       }
-      uint32_t pa[4];
-      pa[0] = pack_bf16(s[0][0], s[0][1]);
-      pa[1] = pack_bf16(s[0][2], s[0][3]);
-      pa[2] = pack_bf16(s[1][0], s[1][1]);
-      pa[3] = pack_bf16(s[1][2], s[1][3]);
+      // P^T in the layout of the second operand: transpose the two 8x8 blocks of S^T
+      const uint32_t pb0 = movmatrix_trans(pack_bf16(pv[0], pv[1]));
+      const uint32_t pb1 = movmatrix_trans(pack_bf16(pv[2], pv[3]));
+      // O^T += V^T P^T, 16 head dimensions per MMA
+      const uint32_t v_addr = smem_u32(vd + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * rs + ((lane >> 3) & 1) * 16);
 #pragma unroll
-      for (int jp = 0; jp < HDMAX / 16; ++jp) {
-        if (jp < ksteps) {
-          uint32_t vb[4];
-          const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-          const int col = jp * 16 + (lane >> 4) * 8;
-          ldmatrix_x4_trans(vb, smem_u32(vd + row * rs + col * 2));
-          mma_16816(o[2 * jp], pa, vb[0], vb[1]);
-          mma_16816(o[2 * jp + 1], pa, vb[2], vb[3]);
+      for (int j = 0; j < HDMAX / 16; ++j) {
+        if (j < ksteps) {
+          uint32_t va[4];
+          ldmatrix_x4_trans(va, v_addr + j * 32);
+          mma_16816(o[j], va, pb0, pb1);
         }
       }
       __syncthreads();
     }
     cp_async_wait<0>();
     __syncthreads();
-    // each warp leaves its rows' (o, m, l); then the four are joined
+    // each warp leaves (o, m, l) of its heads; then the four are joined
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-      const int row = g + r * 8;
-      float* dst = merge + ((warp * 16 + row) * (hd + 2));
+    for (int c = 0; c < 2; ++c) {
+      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 4);
+      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 8);
+      l[c] += __shfl_xor_sync(0xffffffffu, l[c], 16);
+      const int head = 2 * t + c;
+      float* dst = merge + ((warp * GH + head) * (hd + 2));
 #pragma unroll
-      for (int j = 0; j < HDMAX / 8; ++j) {
-        if (j * 8 < hd) {
-          dst[j * 8 + 2 * t] = o[j][2 * r];
-          dst[j * 8 + 2 * t + 1] = o[j][2 * r + 1];
+      for (int j = 0; j < HDMAX / 16; ++j) {
+        if (j < ksteps) {
+          dst[j * 16 + g] = o[j][c];
+          dst[j * 16 + g + 8] = o[j][2 + c];
         }
       }
-      if (t == 0) {
-        dst[hd] = m[r];
-        dst[hd + 1] = l[r];
+      if (g == 0) {
+        dst[hd] = m[c];
+        dst[hd + 1] = l[c];
       }
     }
     __syncthreads();
@@ -475,21 +510,21 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
       float mw[4], M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        mw[w] = merge[(w * 16 + row) * (hd + 2) + hd];
+        mw[w] = merge[(w * GH + row) * (hd + 2) + hd];
         M = fmaxf(M, mw[w]);
       }
       float L = 0.f, scw[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         scw[w] = (mw[w] == -INFINITY) ? 0.f : exp2f((mw[w] - M) * sc);
-        L += scw[w] * merge[(w * 16 + row) * (hd + 2) + hd + 1];
+        L += scw[w] * merge[(w * GH + row) * (hd + 2) + hd + 1];
       }
       const int head = kvh * G + g0 + row;
       const long long pidx = ((long long)b * a.nh + head) * a.n_splits + split;
       for (int d = lane; d < hd; d += 32) {
         float acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) acc += scw[w] * merge[(w * 16 + row) * (hd + 2) + d];
+        for (int w = 0; w < 4; ++w) acc += scw[w] * merge[(w * GH + row) * (hd + 2) + d];
         a.part_o[pidx * hd + d] = acc;
       }
       if (lane == 0) {
@@ -566,7 +601,7 @@ LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, cudaStream_t 
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_decode_mma: bad cache geometry");
   if (a.n_seqs <= 0) return 0;
   size_t smem = (size_t)2 * DSTAGES * 64 * (a.hd * 2 + 16);
-  const size_t merge = (size_t)4 * 16 * (a.hd + 2) * sizeof(float);
+  const size_t merge = (size_t)4 * GH * (a.hd + 2) * sizeof(float);
   if (merge > smem) smem = merge;
   dim3 grid(a.n_splits, a.nkv, a.n_seqs);
   if (a.hd <= 64) {

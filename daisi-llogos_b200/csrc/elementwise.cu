@@ -72,6 +72,53 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     o[i] = from_f32<OT>(res[i] * inv * to_f32(weight[i]));
 }
 
+// The same for rows whose length is a multiple of 4: 16-byte accesses, and the partials of one
+// element are loaded four at a time so that their latencies overlap (a decode step has few rows
+// and nothing else to hide them behind).
+template <typename OT, typename WT>
+__global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const float* __restrict__ branch,
+                                        int n_partials, long long partial_stride, const WT* __restrict__ weight,
+                                        float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  __shared__ float red[32];
+  const int j = blockIdx.x;
+  const int r = rows ? rows[j] : j;
+  float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
+  const int nv = hidden >> 2;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float4 v = res[i];
+    if (branch) {
+      const float4* b = reinterpret_cast<const float4*>(branch + (long long)r * hidden) + i;
+      const long long ps = partial_stride >> 2;
+      int s = 0;
+      for (; s + 4 <= n_partials; s += 4) {
+        const float4 b0 = b[(s + 0) * ps], b1 = b[(s + 1) * ps], b2 = b[(s + 2) * ps], b3 = b[(s + 3) * ps];
+        v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+        v.x += b1.x; v.y += b1.y; v.z += b1.z; v.w += b1.w;
+        v.x += b2.x; v.y += b2.y; v.z += b2.z; v.w += b2.w;
+        v.x += b3.x; v.y += b3.y; v.z += b3.z; v.w += b3.w;
+      }
+      for (; s < n_partials; ++s) {
+        const float4 b0 = b[s * ps];
+        v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+      }
+      res[i] = v;
+    }
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  OT* o = out + (long long)j * hidden;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const float4 v = res[i];
+    const WT* w = weight + 4 * i;
+    o[4 * i + 0] = from_f32<OT>(v.x * inv * to_f32(w[0]));
+    o[4 * i + 1] = from_f32<OT>(v.y * inv * to_f32(w[1]));
+    o[4 * i + 2] = from_f32<OT>(v.z * inv * to_f32(w[2]));
+    o[4 * i + 3] = from_f32<OT>(v.w * inv * to_f32(w[3]));
+  }
+}
+
 LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials, long long partial_stride,
                             const void* weight, int weight_dtype, float eps, void* out, int out_dtype,
                             const int* rows, int n_out, int hidden, cudaStream_t stream) {
@@ -79,10 +126,19 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
   LLG_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
   LLG_REQUIRE(!branch || n_partials >= 1, "add_rmsnorm: a branch needs n_partials >= 1");
   if (n_out == 0) return 0;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-#define LAUNCH(OT, WT)                                                                              \
-  add_rmsnorm_kernel<OT, WT><<<n_out, threads, 0, stream>>>(residual, branch, n_partials, partial_stride, \
-                                                            (const WT*)weight, eps, (OT*)out, rows, hidden)
+  const bool vec = hidden % 4 == 0 && partial_stride % 4 == 0 && ((uintptr_t)residual % 16) == 0 &&
+                   ((uintptr_t)branch % 16) == 0;
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (vec) threads = hidden >= 4096 ? 1024 : (hidden >= 1024 ? 256 : 128);
+#define LAUNCH(OT, WT)                                                                                         \
+  do {                                                                                                         \
+    if (vec)                                                                                                   \
+      add_rmsnorm_vec4_kernel<OT, WT><<<n_out, threads, 0, stream>>>(residual, branch, n_partials, partial_stride, \
+                                                                     (const WT*)weight, eps, (OT*)out, rows, hidden); \
+    else                                                                                                       \
+      add_rmsnorm_kernel<OT, WT><<<n_out, threads, 0, stream>>>(residual, branch, n_partials, partial_stride,     \
+                                                                (const WT*)weight, eps, (OT*)out, rows, hidden);  \
+  } while (0)
   if (out_dtype == LLG_F32 && weight_dtype == LLG_F32) LAUNCH(float, float);
   else if (out_dtype == LLG_F32 && weight_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
   else if (out_dtype == LLG_BF16 && weight_dtype == LLG_F32) LAUNCH(__nv_bfloat16, float);

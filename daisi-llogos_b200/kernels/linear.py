@@ -13,12 +13,24 @@ _SMS = 148
 
 
 def plan_splits(n: int, o: int, k: int) -> int:
-    """Split-K wish for a product with few rows: two blocks per SM, at least 256 k per split."""
-    tile_n = 16 if n <= 16 else 32 if n <= 32 else 64 if n <= 64 else 128 if n <= 128 else 256
-    tiles = -(-o // 128) * -(-n // tile_n)
-    if tiles >= 2 * _SMS:
+    """Split-K wish for a product with few rows.
+
+    ``tiles`` output tiles, each with ``nkb`` k-blocks of 64, are cut into ``s`` splits; the blocks run
+    in ``ceil(tiles * s / resident)`` rounds (two blocks are resident per SM for token tiles up to 64)
+    of ``ceil(nkb / s)`` k-blocks plus a fixed cost each.  The cheapest ``s`` wins, the smallest on
+    ties: a last round with a few stragglers costs as much as a full one."""
+    if n > 64:
         return 1
-    return max(1, min(-(-2 * _SMS // tiles), k // 256, 32))
+    tile_n = 16 if n <= 16 else 32 if n <= 32 else 64
+    tiles = -(-o // 128) * -(-n // tile_n)
+    nkb = -(-k // 64)
+    resident = 2 * _SMS
+    best, best_cost = 1, None
+    for s in range(1, max(1, min(nkb // 4, 32)) + 1):
+        cost = -(-tiles * s // resident) * (-(-nkb // s) + 3)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dtype,

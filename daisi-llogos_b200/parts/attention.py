@@ -18,12 +18,22 @@ from ..kernels.linear import linear
 from .base import Branch, KvNeed, Mixer, TensorDecl, register_part
 
 
-def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
-    """How many blocks share one (sequence, key/value head): enough to fill the GPU twice,
-    never less than 256 keys per block."""
-    want = -(-2 * 148 // max(1, n_seqs * n_kv_heads))
-    by_len = max(1, -(-max_len // 256))
-    return max(1, min(want, by_len, 64))
+def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int, blocks_per_sm: int = 2, n_sms: int = 148) -> int:
+    """How many blocks share one (sequence, key/value head) in decode attention.
+
+    With ``pairs = n_seqs * n_kv_heads`` and ``tiles`` 64-key tiles per sequence, ``s`` splits run in
+    ``ceil(pairs * s / resident blocks)`` rounds of ``ceil(tiles / s)`` tiles each; the ``s`` with
+    the least rounds x tiles wins (the smallest on ties), so that no nearly empty last round of
+    blocks doubles the time."""
+    pairs = max(1, n_seqs * n_kv_heads)
+    tiles = max(1, -(-max_len // 64))
+    resident = blocks_per_sm * n_sms
+    best, best_cost = 1, None
+    for s in range(1, min(64, tiles) + 1):
+        cost = -(-pairs * s // resident) * (-(-tiles // s) + 3)     # + 3: prologue and join of a block
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
 
 
 class Attention(Mixer):
