@@ -250,6 +250,89 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
   }
 }
 
+// The same for the common geometry (head size 64, 128 or 256; rotation by halves over the whole
+// head, or none): lane l keeps elements l, l + 32, ... in
+// registers, a rotation pair (i, i + rotary_dim / 2) lies in one lane, nothing goes through shared
+// memory, and all loads of a head are issued before the first use.
+template <typename IT, typename OT, typename WT, int MAXE>
+__global__ void __launch_bounds__(256) qk_prep_lane_kernel(QkPrepArgs a) {
+  const int warps = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = a.nh + 2 * a.nkv;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)a.n_tokens * heads) return;
+  const int n = (int)(item / heads);
+  const int h = (int)(item % heads);
+  constexpr int hd = 32 * MAXE, ne = MAXE;
+  const int kind = h < a.nh ? 0 : (h < a.nh + a.nkv ? 1 : 2);
+  const IT* src = (const IT*)a.qkv + (long long)n * heads * hd + (long long)h * hd + lane;
+  float x[MAXE];
+#pragma unroll
+  for (int k = 0; k < MAXE; ++k) x[k] = 0.f;
+  for (int s = 0; s < a.n_partials; ++s) {
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k)
+      if (k < ne) x[k] += to_f32(src[s * a.partial_stride + 32 * k]);
+  }
+  const WT* nw = kind == 0 ? (const WT*)a.q_norm_w : (kind == 1 ? (const WT*)a.k_norm_w : nullptr);
+  if (nw) {
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k) ss += x[k] * x[k];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hd + a.norm_eps);
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k)
+      if (k < ne) x[k] = x[k] * inv * to_f32(nw[lane + 32 * k]);
+  }
+  if (a.bias) {
+    const WT* b = (const WT*)a.bias + (long long)h * hd + lane;
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k)
+      if (k < ne) x[k] += to_f32(b[32 * k]);
+  }
+  const int pos = a.positions[n];
+  if (kind != 2 && a.cos_table) {
+    constexpr int half = hd / 2, nh2 = MAXE / 2;             // pairs per lane (rotation over the whole head)
+    const int p = pos < a.table_positions ? pos : a.table_positions - 1;
+    const float* c = a.cos_table + (long long)p * half + lane;
+    const float* sn = a.sin_table + (long long)p * half + lane;
+#pragma unroll
+    for (int k = 0; k < MAXE / 2; ++k) {
+      if (k < nh2) {
+        const float cs = c[32 * k], si = sn[32 * k];
+        const float x0 = x[k], x1 = x[k + nh2];
+        x[k] = x0 * cs - x1 * si;
+        x[k + nh2] = x0 * si + x1 * cs;
+      }
+    }
+  }
+  if (kind == 0) {
+    OT* o = (OT*)a.q_out + ((long long)n * a.nh + h) * hd + lane;
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k)
+      if (k < ne) o[32 * k] = from_f32<OT>(x[k]);
+    return;
+  }
+  const int kvh = kind == 1 ? h - a.nh : h - a.nh - a.nkv;
+  void* packed = kind == 1 ? a.k_new : a.v_new;
+  if (packed) {
+    OT* o = (OT*)packed + ((long long)n * a.nkv + kvh) * hd + lane;
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k)
+      if (k < ne) o[32 * k] = from_f32<OT>(x[k]);
+  }
+  void* pages = kind == 1 ? a.k_pages : a.v_pages;
+  if (pages) {
+    const int slot = a.slots[a.seq_of_token[n]];
+    const long long row = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv);
+    OT* o = (OT*)pages + row * hd + lane;
+#pragma unroll
+    for (int k = 0; k < MAXE; ++k)
+      if (k < ne) o[32 * k] = from_f32<OT>(x[k]);
+  }
+}
+
 LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stream) {
   const QkPrepArgs& a = *args;
   LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.nkv >= 0 && a.hd > 0, "qk_prep: bad sizes");
@@ -260,15 +343,23 @@ LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stre
   LLG_REQUIRE(!a.k_pages || (a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
               "qk_prep: a cache write needs page_table, slots and seq_of_token");
   if (a.n_tokens == 0) return 0;
-  const int warps = 4;
+  const bool lane_ok = (a.hd == 64 || a.hd == 128 || a.hd == 256) &&
+                       (!a.cos_table || (a.pairing == 0 && a.rotary_dim == a.hd));
+  const int warps = lane_ok ? 8 : 4;
   const long long items = (long long)a.n_tokens * (a.nh + 2 * a.nkv);
   const unsigned grid = (unsigned)((items + warps - 1) / warps);
-  const size_t smem = (size_t)warps * a.hd * sizeof(float);
+  const size_t smem = lane_ok ? 0 : (size_t)warps * a.hd * sizeof(float);
   const bool w_bf16 = (a.q_norm_w || a.k_norm_w) ? a.norm_w_dtype == LLG_BF16
                                                  : (a.bias ? a.bias_dtype == LLG_BF16 : false);
   if ((a.q_norm_w || a.k_norm_w) && a.bias)
     LLG_REQUIRE(a.norm_w_dtype == a.bias_dtype, "qk_prep: norm weights and bias must share a dtype");
-#define LAUNCH(IT, OT, WT) qk_prep_kernel<IT, OT, WT><<<grid, warps * 32, smem, stream>>>(a)
+#define LAUNCH(IT, OT, WT)                                                        \
+  do {                                                                            \
+    if (lane_ok && a.hd == 64) qk_prep_lane_kernel<IT, OT, WT, 2><<<grid, warps * 32, 0, stream>>>(a);        \
+    else if (lane_ok && a.hd == 128) qk_prep_lane_kernel<IT, OT, WT, 4><<<grid, warps * 32, 0, stream>>>(a);  \
+    else if (lane_ok) qk_prep_lane_kernel<IT, OT, WT, 8><<<grid, warps * 32, 0, stream>>>(a);                 \
+    else qk_prep_kernel<IT, OT, WT><<<grid, warps * 32, smem, stream>>>(a);         \
+  } while (0)
   if (out_dtype == LLG_F32) {
     LLG_REQUIRE(a.qkv_dtype == LLG_F32, "qk_prep: float32 output needs float32 input");
     if (w_bf16) LAUNCH(float, float, __nv_bfloat16); else LAUNCH(float, float, float);
@@ -343,20 +434,23 @@ LLG_API int llg_kv_write(const void* k_new, const void* v_new, void* k_pages, vo
 
 // ---- SiLU gating --------------------------------------------------------------------
 
-// out[n][i] = silu(g) * u with g = sum_s gu[s][n][i], u = sum_s gu[s][n][inter + i];
-// silu(g) = g / (1 + exp(-g))  (Daisi.Llogos.Cpu/Silu.cs:9-16).
+// The gate and up projections are stored as one matrix in blocks of 256 rows: the gate rows of 128
+// features, then the up rows of the same features (the layout the tensor-core product's gated
+// epilogue wants).  A product's output row therefore holds, for feature i, g at
+// (i / 128) * 256 + i % 128 and u 128 further:
+// out[n][i] = silu(g) * u, silu(g) = g / (1 + exp(-g))  (Daisi.Llogos.Cpu/Silu.cs:9-16).
 template <typename IT, typename OT>
 __global__ void silu_mul_kernel(const IT* __restrict__ gu, int n_partials, long long partial_stride,
-                                OT* __restrict__ out, long long total, int inter) {
+                                OT* __restrict__ out, long long total, int inter, int width) {
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long n = idx / inter;
-    const int i = (int)(idx % inter);
-    const IT* p = gu + n * 2 * inter + i;
+    const int i = (int)(idx - n * inter);
+    const IT* p = gu + n * width + (i >> 7) * 256 + (i & 127);
     float g = 0.f, u = 0.f;
     for (int s = 0; s < n_partials; ++s) {
       g += to_f32(p[s * partial_stride]);
-      u += to_f32(p[s * partial_stride + inter]);
+      u += to_f32(p[s * partial_stride + 128]);
     }
     out[idx] = from_f32<OT>(g / (1.0f + expf(-g)) * u);
   }
@@ -367,11 +461,13 @@ LLG_API int llg_silu_mul(const void* gu, int in_dtype, int n_partials, long long
   LLG_REQUIRE(n_tokens >= 0 && inter > 0 && n_partials >= 1, "silu_mul: bad sizes");
   const long long total = (long long)n_tokens * inter;
   if (total == 0) return 0;
+  const int width = ((inter + 127) / 128) * 256;
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;
   if (blocks > 148 * 16) blocks = 148 * 16;
-#define LAUNCH(IT, OT) \
-  silu_mul_kernel<IT, OT><<<(unsigned)blocks, threads, 0, stream>>>((const IT*)gu, n_partials, partial_stride, (OT*)out, total, inter)
+#define LAUNCH(IT, OT)                                                                                          \
+  silu_mul_kernel<IT, OT><<<(unsigned)blocks, threads, 0, stream>>>((const IT*)gu, n_partials, partial_stride, \
+                                                                     (OT*)out, total, inter, width)
   if (in_dtype == LLG_F32 && out_dtype == LLG_F32) LAUNCH(float, float);
   else if (in_dtype == LLG_F32 && out_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
   else if (in_dtype == LLG_BF16 && out_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);

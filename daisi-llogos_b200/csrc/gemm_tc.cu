@@ -118,19 +118,25 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 
 struct GemmParams {
-  void* out;        // [splits][n][o]
+  void* out;        // [splits][n][o], or [n][gated_features] with the gated epilogue
   int n, o, k;
   int kb_per_split; // k-blocks of 64 per split
+  int gated_features;
 };
 
-template <int TN, int STAGES, typename OT>
+// MT: weight tiles of 128 rows per block (1 or 2; two tiles share every activation tile, which halves
+// the shared-memory traffic per flop of a large product).  EPI 1 (MT = 2): the first tile holds gate
+// rows and the second the up rows of the same 128 features; the block writes silu(gate) * up.
+template <int TN, int STAGES, typename OT, int MT, int EPI>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, GemmParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int A_TILE = BM * BK * 2;
+  constexpr int A_BYTES = MT * A_TILE;
   constexpr int B_BYTES = TN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int TMEM_COLS = TN < 32 ? 32 : TN;
+  constexpr int TMEM_COLS = MT * TN < 32 ? 32 : MT * TN;
+  static_assert(EPI == 0 || MT == 2, "the gated epilogue needs a gate tile and an up tile");
   // 1024-byte alignment of the operand tiles is what the swizzle pattern of TMA and of the MMA assume
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], done_bar;
@@ -138,7 +144,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int o0 = blockIdx.x * BM, n0 = blockIdx.y * TN, split = blockIdx.z;
+  const int o0 = blockIdx.x * (BM * MT), n0 = blockIdx.y * TN, split = blockIdx.z;
   const int nkb_total = (p.k + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, nkb_total - kb0);   // >= 1 by construction of the grid
@@ -176,7 +182,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       }
       mbar_expect_tx(&full_bar[s], STAGE_BYTES);
       unsigned char* a = smem + s * STAGE_BYTES;
-      tma_load_2d(a, &map_w, (kb0 + i) * BK, o0, &full_bar[s]);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * A_TILE, &map_w, (kb0 + i) * BK, o0 + mt * BM, &full_bar[s]);
       tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * BK, n0, &full_bar[s]);
       issued = i + 1;
     }
@@ -202,18 +209,20 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-      const uint64_t da = umma_desc(a_addr), db = umma_desc(a_addr + A_BYTES);
+      const uint64_t db = umma_desc(a_addr + A_BYTES);
 #pragma unroll
       for (int kk = 0; kk < BK / UMMA_K; ++kk) {
         // 16 k = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
-        umma_bf16(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, (i | kk) != 0);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+          umma_bf16(tmem_d + mt * TN, umma_desc(a_addr + mt * A_TILE) + 2 * kk, db + 2 * kk, IDESC, (i | kk) != 0);
       }
       umma_commit(&empty_bar[s]);       // arrives when the MMAs above have read the stage
     }
     umma_commit(&done_bar);             // arrives when every MMA issued so far has finished
   }
 
-  // ---- epilogue: tensor memory -> registers -> out[n][o] -----------------------------------
+  // ---- epilogue: tensor memory -> registers -> out --------------------------------------------
   __syncwarp();
   bool have = mbar_wait(&done_bar, 0, abortp);
   if (!have && !*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
@@ -221,19 +230,47 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const bool aborted = *abortp != 0;
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   if (!aborted) {
-    const int o = o0 + warp * 32 + lane;
-    OT* out = (OT*)p.out + (long long)split * p.n * p.o;
+    const uint32_t lane_base = tmem_d + ((uint32_t)(warp * 32) << 16);
+    if (EPI == 0) {
+      OT* out = (OT*)p.out + (long long)split * p.n * p.o;
 #pragma unroll
-    for (int c0 = 0; c0 < TN; c0 += 16) {
-      if (n0 + c0 >= p.n) break;       // uniform over the block: the tile's tail holds no tokens
-      uint32_t r[16];
-      tmem_ld16(tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (o < p.o) {
+      for (int mt = 0; mt < MT; ++mt) {
+        const int o = o0 + mt * BM + warp * 32 + lane;
+        if (o0 + mt * BM >= p.o) break;     // uniform: the second tile lies past the matrix
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int n = n0 + c0 + c;
-          if (n < p.n) out[(long long)n * p.o + o] = from_f32<OT>(__uint_as_float(r[c]));
+        for (int c0 = 0; c0 < TN; c0 += 16) {
+          if (n0 + c0 >= p.n) break;        // uniform over the block: the tile's tail holds no tokens
+          uint32_t r[16];
+          tmem_ld16(lane_base + (uint32_t)(mt * TN + c0), r);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (o < p.o) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int n = n0 + c0 + c;
+              if (n < p.n) out[(long long)n * p.o + o] = from_f32<OT>(__uint_as_float(r[c]));
+            }
+          }
+        }
+      }
+    } else {
+      // accumulator 0 holds gate, accumulator 1 up, of feature blockIdx.x * 128 + lane row
+      OT* out = (OT*)p.out;
+      const int inter = p.gated_features;
+      const int f = blockIdx.x * BM + warp * 32 + lane;
+#pragma unroll
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        if (n0 + c0 >= p.n) break;
+        uint32_t rg[16], ru[16];
+        tmem_ld16(lane_base + (uint32_t)c0, rg);
+        tmem_ld16(lane_base + (uint32_t)(TN + c0), ru);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (f < inter) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int n = n0 + c0 + c;
+            const float g = __uint_as_float(rg[c]), u = __uint_as_float(ru[c]);
+            if (n < p.n) out[(long long)n * inter + f] = from_f32<OT>(__fdividef(g, 1.0f + __expf(-g)) * u);
+          }
         }
       }
     }
@@ -293,17 +330,18 @@ bool tensor_map(const void* base, int rows, int k, int box_rows, CUtensorMap* re
   return true;
 }
 
-template <int TN, int STAGES, typename OT>
+template <int TN, int STAGES, typename OT, int MT, int EPI>
 int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, int splits, cudaStream_t stream) {
-  constexpr int smem = STAGES * (BM * BK * 2 + TN * BK * 2) + 1024;
+  constexpr int smem = STAGES * (MT * BM * BK * 2 + TN * BK * 2) + 1024;
+  static_assert(smem <= 232448, "stage ring does not fit shared memory");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN, STAGES, OT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN, STAGES, OT, MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return llg_fail("gemm_tc: cannot have %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((p.o + BM - 1) / BM, (p.n + TN - 1) / TN, splits);
-  gemm_tc_kernel<TN, STAGES, OT><<<grid, 128, smem, stream>>>(*mw, *mx, p);
+  dim3 grid((p.o + BM * MT - 1) / (BM * MT), (p.n + TN - 1) / TN, splits);
+  gemm_tc_kernel<TN, STAGES, OT, MT, EPI><<<grid, 128, smem, stream>>>(*mw, *mx, p);
   return llg_check_launch("gemm_tc");
 }
 
@@ -325,29 +363,44 @@ LLG_API int llg_gemm_tc_splits(int k, int splits) {
 }
 
 // out[s][n][o] for s < llg_gemm_tc_splits(k, splits); out_dtype float32, or bfloat16 when there is one split.
+// gated_features > 0 (one split only): w has ceil(F / 128) blocks of 256 rows, each block the gate rows of 128
+// features followed by their up rows (rows past F are zero), and out is [n][F] = silu(gate) * up.
 LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int splits,
-                        int tile_n, cudaStream_t stream) {
+                        int tile_n, int gated_features, cudaStream_t stream) {
   LLG_REQUIRE(llg_gemm_tc_supported(x, w, n, o, k), "gemm_tc: needs k %% 8 == 0 and 16-byte aligned operands (n=%d o=%d k=%d)",
               n, o, k);
   splits = llg_gemm_tc_splits(k, splits);
   LLG_REQUIRE(out_dtype == LLG_F32 || (out_dtype == LLG_BF16 && splits == 1), "gemm_tc: bfloat16 output needs one split");
+  const bool gated = gated_features > 0;
+  LLG_REQUIRE(!gated || (splits == 1 && o == ((gated_features + BM - 1) / BM) * 2 * BM),
+              "gemm_tc: the gated epilogue needs one split and ceil(features / 128) * 256 rows of w (features=%d rows=%d splits=%d)",
+              gated_features, o, splits);
   const int nkb = (k + BK - 1) / BK;
-  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits};
+  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features};
   if (tile_n <= 0) tile_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
-  LLG_REQUIRE((o + BM - 1) / BM <= 2147483647 && (n + tile_n - 1) / tile_n <= 65535 && splits <= 65535, "gemm_tc: grid too large");
+  LLG_REQUIRE((n + tile_n - 1) / tile_n <= 65535 && splits <= 65535, "gemm_tc: grid too large");
   CUtensorMap map_w, map_x;
   LLG_REQUIRE(tensor_map(w, o, k, BM, &map_w) && tensor_map(x, n, k, tile_n, &map_x),
               "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
   const CUtensorMap *mw = &map_w, *mx = &map_x;
-#define GO(TN, ST)                                                             \
-  return out_dtype == LLG_F32 ? launch<TN, ST, float>(mw, mx, p, splits, stream) \
-                              : launch<TN, ST, __nv_bfloat16>(mw, mx, p, splits, stream)
+  // two weight tiles per block when the product is large enough to fill the GPU that way
+  const bool wide = !gated && tile_n >= 128 && (long long)((o + 2 * BM - 1) / (2 * BM)) * ((n + tile_n - 1) / tile_n) >= 148;
+#define GO(TN, ST1, ST2)                                                                              \
+  if (gated)                                                                                          \
+    return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 1>(mw, mx, p, splits, stream)               \
+                                : launch<TN, ST2, __nv_bfloat16, 2, 1>(mw, mx, p, splits, stream);      \
+  else if (wide)                                                                                      \
+    return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 0>(mw, mx, p, splits, stream)               \
+                                : launch<TN, ST2, __nv_bfloat16, 2, 0>(mw, mx, p, splits, stream);      \
+  else                                                                                                \
+    return out_dtype == LLG_F32 ? launch<TN, ST1, float, 1, 0>(mw, mx, p, splits, stream)               \
+                                : launch<TN, ST1, __nv_bfloat16, 1, 0>(mw, mx, p, splits, stream)
   switch (tile_n) {
-    case 16: GO(16, 5);
-    case 32: GO(32, 5);
-    case 64: GO(64, 4);
-    case 128: GO(128, 6);
-    case 256: GO(256, 4);
+    case 16: GO(16, 5, 5);
+    case 32: GO(32, 5, 5);
+    case 64: GO(64, 4, 4);
+    case 128: GO(128, 6, 4);
+    case 256: GO(256, 4, 3);
     default: return llg_fail("gemm_tc: tile_n %d is not one of 16, 32, 64, 128, 256", tile_n);
   }
 #undef GO

@@ -52,3 +52,44 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dt
         out = ctx.buffer(name, (1, n, o), out_dtype)
     ops.gemm_simt(x, w, out[0])
     return out
+
+
+_GATED_CHUNK = 16384   # rows per pass of the two-kernel path, bounds its [rows, 2I] scratch
+
+
+def gated_layout(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """One matrix of blocks of 256 rows: the gate rows of 128 features, then their up rows; the last
+    block is filled with zero rows."""
+    inter, hidden = gate.shape
+    nb = -(-inter // 128)
+    out = torch.zeros((nb, 2, 128, hidden), dtype=gate.dtype, device=gate.device)
+    flat = out.view(nb, 2, 128 * hidden)
+    full = inter // 128
+    if full:
+        out[:full, 0] = gate[:full * 128].view(full, 128, hidden)
+        out[:full, 1] = up[:full * 128].view(full, 128, hidden)
+    rest = inter - full * 128
+    if rest:
+        out[full, 0, :rest] = gate[full * 128:]
+        out[full, 1, :rest] = up[full * 128:]
+    del flat
+    return out.view(nb * 256, hidden)
+
+
+def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, i] = silu(x . gate_i) * (x . up_i) for a gate/up matrix in ``gated_layout``.
+
+    On the tensor cores the gating is the epilogue of the product; otherwise the product writes
+    gate and up values and the gating kernel follows."""
+    ops = ctx.ops
+    n = x.shape[0]
+    rows = w_gated.shape[0]
+    tc = getattr(ops, "gemm_tc_supported", None)
+    if tc is not None and tc(x, w_gated) and out.dtype == torch.bfloat16:
+        ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1])
+        return
+    for r0 in range(0, n, _GATED_CHUNK):
+        r1 = min(n, r0 + _GATED_CHUNK)
+        gu = ctx.buffer("ffn.gate_up", (1, r1 - r0, rows), x.dtype)
+        ops.gemm_simt(x[r0:r1], w_gated, gu[0])
+        ops.silu_mul(gu, out[r0:r1])

@@ -143,7 +143,7 @@ def _lib(name: str):
     elif name == "gemm_tc":
         lib.llg_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
         lib.llg_gemm_tc_splits.argtypes = [c_int, c_int]
-        lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     elif name == "attention_simt":
         lib.llg_attn_prefill_simt.argtypes = [POINTER(_PrefillArgs), c_int, c_void_p]
         lib.llg_attn_decode_simt.argtypes = [POINTER(_DecodeArgs), c_void_p, c_int, c_void_p]
@@ -224,20 +224,27 @@ def gemm_tc_splits(k: int, wish: int) -> int:
     return _lib("gemm_tc").llg_gemm_tc_splits(k, wish)
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int = 0) -> None:
+def gated_rows(features: int) -> int:
+    """Rows of a gate/up matrix in the gated layout: blocks of 128 gate rows + 128 up rows."""
+    return -(-features // 128) * 256
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int = 0, gated_features: int = 0) -> None:
     """out[s, n, o] = split-K partials of x[n, k] w[o, k] on the tensor cores (tcgen05, TMA).
 
     ``out`` is ``[S, N, O]`` float32 with S = ``gemm_tc_splits(k, wish)``, or ``[1, N, O]`` bfloat16.
+    With ``gated_features = F`` the matrix ``w`` is in the gated layout (``gated_rows(F)`` rows) and
+    ``out`` is ``[1, N, F]`` holding ``silu(gate) * up``.
     """
     lib = _lib("gemm_tc")
     n, k = x.shape
     o, k2 = w.shape
     s = out.shape[0]
-    assert k == k2 and out.shape == (s, n, o), (x.shape, w.shape, out.shape)
+    assert k == k2 and out.shape == (s, n, gated_features if gated_features else o), (x.shape, w.shape, out.shape)
     if lib.llg_gemm_tc_splits(k, s) != s:
         raise KernelError(f"gemm_tc: {s} splits cannot be had for k = {k}")
     _check(lib, lib.llg_gemm_tc(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k, s,
-                                tile_n, _stream()))
+                                tile_n, gated_features, _stream()))
 
 
 def gemm_tc_status() -> int:
@@ -304,11 +311,12 @@ def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, 
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n, i] = silu(g) * u, g and u the two halves of the summed partials ``[S, N, 2I]``."""
+    """out[n, i] = silu(g) * u; the summed partials ``[S, N, gated_rows(I)]`` hold g and u in the gated
+    layout (blocks of 128 gate values followed by the 128 up values of the same features)."""
     lib = _lib("elementwise")
     s, n, two_i = gate_up.shape
-    inter = two_i // 2
-    assert out.shape == (n, inter) and two_i == 2 * inter
+    inter = out.shape[1]
+    assert out.shape == (n, inter) and two_i == gated_rows(inter)
     _check(lib, lib.llg_silu_mul(_ptr(gate_up), _dt(gate_up), s, n * two_i, _ptr(out), _dt(out), n, inter, _stream()))
 
 

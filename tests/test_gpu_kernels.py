@@ -84,7 +84,8 @@ def test_gemm_simt(ops, xd, wd, od, n, o, k):
 
 
 @pytest.mark.parametrize("n,o,k", [(1, 128, 64), (3, 200, 72), (16, 129, 128), (17, 384, 1000), (33, 100, 8),
-                                   (70, 130, 336), (129, 65, 16), (300, 1000, 520), (2, 301, 4104)])
+                                   (70, 130, 336), (129, 65, 16), (300, 1000, 520), (2, 301, 4104),
+                                   (1100, 9000, 72), (2050, 4700, 136)])
 def test_gemm_tc(ops, n, o, k):
     """The tcgen05 product at ragged sizes: rows, features and k that fill no tile."""
     x, w = rnd((n, k), 5, torch.bfloat16), rnd((o, k), 6, torch.bfloat16, 0.1)
@@ -106,6 +107,29 @@ def test_gemm_tc(ops, n, o, k):
     assert ops.gemm_tc_status() == 0
 
 
+def _gated(gate, up):
+    lin = importlib.import_module("daisi-llogos_b200.kernels.linear")
+    return lin.gated_layout(gate, up)
+
+
+@pytest.mark.parametrize("n,feat,k", [(1, 128, 64), (5, 101, 72), (70, 300, 336), (300, 500, 520), (2100, 176, 64)])
+def test_gemm_tc_gated_epilogue(ops, n, feat, k):
+    """A gate/up matrix in the gated layout; the epilogue writes silu(gate) * up."""
+    x = rnd((n, k), 5, torch.bfloat16)
+    gate, up = rnd((feat, k), 6, torch.bfloat16, 0.2), rnd((feat, k), 7, torch.bfloat16, 0.2)
+    w = _gated(gate, up)
+    assert w.shape == (ops.gated_rows(feat), k)
+    g, u = P.linear(x, gate), P.linear(x, up)
+    ref = g / (1 + torch.exp(-g)) * u
+    for dt in (torch.bfloat16, torch.float32):
+        out = torch.full((1, n, feat), float("nan"), dtype=dt, device=DEV)
+        ops.gemm_tc(x.to(DEV), w.to(DEV), out, gated_features=feat)
+        check(out[0], ref, torch.bfloat16 if dt == torch.bfloat16 else torch.float32, dt)
+    with pytest.raises(ops.KernelError, match="gated epilogue"):
+        ops.gemm_tc(x.to(DEV), w[:128].contiguous().to(DEV), torch.empty(1, n, feat, device=DEV), gated_features=feat)
+    assert ops.gemm_tc_status() == 0
+
+
 def test_gemm_tc_refuses_what_tma_cannot_address(ops):
     x, w = rnd((4, 36), 5, torch.bfloat16).to(DEV), rnd((8, 36), 6, torch.bfloat16).to(DEV)
     assert not ops.gemm_tc_supported(x, w)                       # 72-byte rows
@@ -119,11 +143,13 @@ def test_gemm_tc_refuses_what_tma_cannot_address(ops):
 def test_silu_mul(ops, dtype, partials):
     n, inter = 5, 333
     in_dtype = torch.float32 if partials > 1 else dtype
-    gu = rnd((partials, n, 2 * inter), 7, in_dtype, 2.0)
+    gu = rnd((partials, n, ops.gated_rows(inter)), 7, in_dtype, 2.0)
     out = torch.empty(n, inter, dtype=dtype, device=DEV)
     ops.silu_mul(gu.to(DEV), out)
     s = gu.double().sum(0)
-    g, u = s[:, :inter], s[:, inter:]
+    i = torch.arange(inter)
+    at = (i // 128) * 256 + i % 128
+    g, u = s[:, at], s[:, at + 128]
     check(out, g / (1 + torch.exp(-g)) * u, dtype)
 
 
@@ -136,7 +162,8 @@ def _rope_tables(hd, rd, theta, n_pos):
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("nh,nkv,hd,rd,pairing,norm,bias", [
     (5, 1, 48, 48, "half", True, True), (6, 3, 80, 32, "adjacent", False, True),
-    (4, 4, 16, 16, "half", True, False), (9, 3, 128, 128, "half", False, False)])
+    (4, 4, 16, 16, "half", True, False), (9, 3, 128, 128, "half", False, False), (3, 1, 64, 64, "half", True, True),
+    (2, 2, 256, 256, "half", True, False), (2, 1, 128, 64, "half", False, False), (4, 2, 128, 128, "adjacent", True, False)])
 def test_qk_prep(ops, dtype, nh, nkv, hd, rd, pairing, norm, bias):
     n, eps = 11, 2e-6
     width = (nh + 2 * nkv) * hd
