@@ -133,7 +133,7 @@ def main():
 
     t0 = time.time()
     model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
-    big = max(64, args.batch)
+    big = args.batch if args.no_points else max(64, args.batch)
     engine = L.engine.Engine(model, max_tokens=big * CONTEXT, max_seq_len=CONTEXT, n_slots=big)
     for g in engine.cache.kv_groups:             # random keys and values: attention over real numbers
         for t in list(g.k.values()) + list(g.v.values()):

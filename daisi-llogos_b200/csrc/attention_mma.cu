@@ -104,6 +104,8 @@ constexpr float LOG2E = 1.4426950408889634f;
 template <int HDMAX>
 __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
   extern __shared__ __align__(16) unsigned char smraw[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int hd = a.hd;
   const int rs = hd * 2 + 16;                 // bytes per shared-memory row
   const int cpr = hd / 8;                     // 16-byte chunks per row
@@ -319,14 +321,14 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
-// d (16x8) += a (16x16, row) * b (16x8, col)
-__device__ __forceinline__ void mma_16816_b2(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  mma_16816(d, a, b0, b1);
-}
-
 template <int HDMAX>
 __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smraw[];
+  pdl_launch_dependents();
+  // Lengths, slots and page tables were written before this step's first kernel started.  The
+  // kernel just before this one writes only the newest position (in the sequence's last page) and
+  // the queries: tiles before the last page may be requested before waiting for it.
+  bool waited = false;
   const int hd = a.hd;
   const int rs = hd * 2 + 16;
   const int cpr = hd / 8;
@@ -386,8 +388,18 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
     __syncthreads();                                  // merge area of the previous pass is free again
 #pragma unroll
     for (int s = 0; s < DSTAGES - 1; ++s) {
-      if (s < n_my) load_kv(page_base(my0 + s), s);
+      if (s < n_my) {
+        if (!waited && my0 + s >= t_end - 1) {
+          pdl_wait();
+          waited = true;
+        }
+        load_kv(page_base(my0 + s), s);
+      }
       cp_async_commit();
+    }
+    if (!waited) {
+      pdl_wait();
+      waited = true;
     }
     long long next_base = (DSTAGES - 1 < n_my) ? page_base(my0 + DSTAGES - 1) : 0;
     // Q^T as the second operand: column g is head g0 + g, rows are head dimensions
@@ -540,6 +552,8 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
 // joins the partials of the splits: out = sum_s exp(m_s - M) o_s / sum_s exp(m_s - M) l_s
 __global__ void attn_decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           bf16* __restrict__ out, int nh, int hd, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int h = blockIdx.x, b = blockIdx.y;
   const long long base = ((long long)b * nh + h) * n_splits;
   float M = -INFINITY;
@@ -584,10 +598,10 @@ LLG_API int llg_attn_prefill_mma(const PrefillArgs* args, cudaStream_t stream) {
   dim3 grid(a.n_tiles, a.nh);
   if (a.hd <= 64) {
     if (set_smem(attn_prefill_mma_kernel<64>, smem, "attn_prefill_mma")) return 1;
-    attn_prefill_mma_kernel<64><<<grid, 128, smem, stream>>>(a);
+    llg_launch(attn_prefill_mma_kernel<64>, grid, dim3(128), smem, stream, a);
   } else {
     if (set_smem(attn_prefill_mma_kernel<128>, smem, "attn_prefill_mma")) return 1;
-    attn_prefill_mma_kernel<128><<<grid, 128, smem, stream>>>(a);
+    llg_launch(attn_prefill_mma_kernel<128>, grid, dim3(128), smem, stream, a);
   }
   return llg_check_launch("attn_prefill_mma");
 }
@@ -606,11 +620,12 @@ LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, cudaStream_t 
   dim3 grid(a.n_splits, a.nkv, a.n_seqs);
   if (a.hd <= 64) {
     if (set_smem(attn_decode_mma_kernel<64>, smem, "attn_decode_mma")) return 1;
-    attn_decode_mma_kernel<64><<<grid, 128, smem, stream>>>(a);
+    llg_launch(attn_decode_mma_kernel<64>, grid, dim3(128), smem, stream, a);
   } else {
     if (set_smem(attn_decode_mma_kernel<128>, smem, "attn_decode_mma")) return 1;
-    attn_decode_mma_kernel<128><<<grid, 128, smem, stream>>>(a);
+    llg_launch(attn_decode_mma_kernel<128>, grid, dim3(128), smem, stream, a);
   }
-  attn_decode_reduce_kernel<<<dim3(a.nh, a.n_seqs), 64, 0, stream>>>(a.part_o, a.part_ml, (bf16*)out, a.nh, a.hd, a.n_splits);
+  llg_launch(attn_decode_reduce_kernel, dim3(a.nh, a.n_seqs), dim3(64), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)out,
+             a.nh, a.hd, a.n_splits);
   return llg_check_launch("attn_decode_mma");
 }

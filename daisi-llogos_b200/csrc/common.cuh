@@ -41,6 +41,45 @@ static inline int llg_check_launch(const char* what) {
     if (!(cond)) return llg_fail(__VA_ARGS__); \
   } while (0)
 
+// ---- programmatic dependent launch -----------------------------------------------------
+//
+// Kernels of a step run back to back on one stream, each consuming what the one before wrote.
+// A kernel launched with llg_launch() may start while its predecessor is still running: it runs
+// its own set-up (shared memory, barriers, tensor memory), calls pdl_wait() before it touches any
+// memory that another kernel writes or reads, and calls pdl_launch_dependents() at its start so
+// that its successor may do the same.  Without the launch attribute both calls do nothing.
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+
+static inline bool llg_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LLOGOS_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+// Launches `kernel` so that it may overlap the tail of the previous kernel on the stream (see above).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t llg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = llg_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // ---- element access ---------------------------------------------------------------
 
 __device__ __forceinline__ float to_f32(float v) { return v; }

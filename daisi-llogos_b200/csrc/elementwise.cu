@@ -17,6 +17,8 @@ LLG_API int llg_page_size() { return LLG_PAGE; }
 template <typename TT>
 __global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int hidden, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int n = blockIdx.x;
   int id = ids[n];
   if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of range
@@ -33,10 +35,9 @@ LLG_API int llg_embed_rows(const void* table, int table_dtype, const int* ids, f
   if (n_tokens == 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == LLG_F32)
-    embed_rows_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+    llg_launch(embed_rows_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab);
   else if (table_dtype == LLG_BF16)
-    embed_rows_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out,
-                                                                       hidden, vocab);
+    llg_launch(embed_rows_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
   else
     return llg_fail("embed_rows: unknown table dtype %d", table_dtype);
   return llg_check_launch("embed_rows");
@@ -51,6 +52,8 @@ template <typename OT, typename WT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ branch,
                                    int n_partials, long long partial_stride, const WT* __restrict__ weight,
                                    float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int j = blockIdx.x;
   const int r = rows ? rows[j] : j;
@@ -79,6 +82,8 @@ template <typename OT, typename WT>
 __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const float* __restrict__ branch,
                                         int n_partials, long long partial_stride, const WT* __restrict__ weight,
                                         float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[32];
   const int j = blockIdx.x;
   const int r = rows ? rows[j] : j;
@@ -133,11 +138,11 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
 #define LAUNCH(OT, WT)                                                                                         \
   do {                                                                                                         \
     if (vec)                                                                                                   \
-      add_rmsnorm_vec4_kernel<OT, WT><<<n_out, threads, 0, stream>>>(residual, branch, n_partials, partial_stride, \
-                                                                     (const WT*)weight, eps, (OT*)out, rows, hidden); \
+      llg_launch(add_rmsnorm_vec4_kernel<OT, WT>, n_out, threads, 0, stream, residual, branch, n_partials,       \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
     else                                                                                                       \
-      add_rmsnorm_kernel<OT, WT><<<n_out, threads, 0, stream>>>(residual, branch, n_partials, partial_stride,     \
-                                                                (const WT*)weight, eps, (OT*)out, rows, hidden);  \
+      llg_launch(add_rmsnorm_kernel<OT, WT>, n_out, threads, 0, stream, residual, branch, n_partials,            \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
   } while (0)
   if (out_dtype == LLG_F32 && weight_dtype == LLG_F32) LAUNCH(float, float);
   else if (out_dtype == LLG_F32 && weight_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
@@ -182,6 +187,8 @@ struct QkPrepArgs {
 
 template <typename IT, typename OT, typename WT>
 __global__ void qk_prep_kernel(QkPrepArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float sm[];
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -256,6 +263,8 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
 // memory, and all loads of a head are issued before the first use.
 template <typename IT, typename OT, typename WT, int MAXE>
 __global__ void __launch_bounds__(256) qk_prep_lane_kernel(QkPrepArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = a.nh + 2 * a.nkv;
@@ -355,10 +364,10 @@ LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stre
     LLG_REQUIRE(a.norm_w_dtype == a.bias_dtype, "qk_prep: norm weights and bias must share a dtype");
 #define LAUNCH(IT, OT, WT)                                                        \
   do {                                                                            \
-    if (lane_ok && a.hd == 64) qk_prep_lane_kernel<IT, OT, WT, 2><<<grid, warps * 32, 0, stream>>>(a);        \
-    else if (lane_ok && a.hd == 128) qk_prep_lane_kernel<IT, OT, WT, 4><<<grid, warps * 32, 0, stream>>>(a);  \
-    else if (lane_ok) qk_prep_lane_kernel<IT, OT, WT, 8><<<grid, warps * 32, 0, stream>>>(a);                 \
-    else qk_prep_kernel<IT, OT, WT><<<grid, warps * 32, smem, stream>>>(a);         \
+    if (lane_ok && a.hd == 64) llg_launch(qk_prep_lane_kernel<IT, OT, WT, 2>, grid, warps * 32, 0, stream, a);        \
+    else if (lane_ok && a.hd == 128) llg_launch(qk_prep_lane_kernel<IT, OT, WT, 4>, grid, warps * 32, 0, stream, a);  \
+    else if (lane_ok) llg_launch(qk_prep_lane_kernel<IT, OT, WT, 8>, grid, warps * 32, 0, stream, a);                 \
+    else llg_launch(qk_prep_kernel<IT, OT, WT>, grid, warps * 32, smem, stream, a);         \
   } while (0)
   if (out_dtype == LLG_F32) {
     LLG_REQUIRE(a.qkv_dtype == LLG_F32, "qk_prep: float32 output needs float32 input");
@@ -388,6 +397,8 @@ __global__ void kv_write_kernel(const T* __restrict__ k_new, const T* __restrict
                                 const int* __restrict__ seq_of_token, const int* __restrict__ slots,
                                 const int* __restrict__ cu_tokens, const int* __restrict__ len_before,
                                 int n_tokens, int nkv, int hd) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * warps + warp;
@@ -442,6 +453,8 @@ LLG_API int llg_kv_write(const void* k_new, const void* v_new, void* k_pages, vo
 template <typename IT, typename OT>
 __global__ void silu_mul_kernel(const IT* __restrict__ gu, int n_partials, long long partial_stride,
                                 OT* __restrict__ out, long long total, int inter, int width) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long n = idx / inter;
@@ -480,6 +493,8 @@ LLG_API int llg_silu_mul(const void* gu, int in_dtype, int n_partials, long long
 
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx,
                                    const int* __restrict__ val, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[idx[i]] = val[i];
 }
@@ -493,6 +508,8 @@ LLG_API int llg_scatter_i32(int* dst, const int* idx, const int* val, int n, cud
 
 __global__ void zero_rows_kernel(unsigned char* __restrict__ base, const int* __restrict__ rows,
                                  long long row_bytes) {
+  pdl_launch_dependents();
+  pdl_wait();
   unsigned char* p = base + (long long)rows[blockIdx.x] * row_bytes;
   for (long long i = threadIdx.x; i < row_bytes; i += blockDim.x) p[i] = 0;
 }

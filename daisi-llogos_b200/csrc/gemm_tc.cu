@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  pdl_launch_dependents();      // the next kernel may set itself up while this one runs
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int o0 = blockIdx.x * (BM * MT), n0 = blockIdx.y * TN, split = blockIdx.z;
   const int nkb_total = (p.k + BK - 1) / BK;
@@ -172,8 +173,19 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 
   if (tid == 0) {
     // ---- producer: TMA loads into the ring ------------------------------------------------
-    int issued = 0;
-    for (int i = 0; i < nkb; ++i) {
+    // The weights do not depend on the previous kernel: the first ring of weight tiles is requested
+    // before this kernel waits for its predecessor, the activation tiles right after.
+    const int pre = min(nkb, STAGES);
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+        tma_load_2d(smem + i * STAGE_BYTES + mt * A_TILE, &map_w, (kb0 + i) * BK, o0 + mt * BM, &full_bar[i]);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i) tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_x, (kb0 + i) * BK, n0, &full_bar[i]);
+    int issued = pre;
+    for (int i = pre; i < nkb; ++i) {
       const int s = i % STAGES;
       const uint32_t parity = ((i / STAGES) & 1) ^ 1;     // a fresh barrier passes a wait on parity 1
       if (!mbar_wait(&empty_bar[s], parity, abortp)) {
@@ -196,7 +208,10 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         }
       }
     }
-  } else if (tid == 32) {
+  } else {
+    pdl_wait();                 // every other thread: before anything of the previous kernel is read or overwritten
+  }
+  if (tid == 32) {
     // ---- consumer: one thread issues every MMA ----------------------------------------------
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     bool ok = true;
@@ -341,7 +356,8 @@ int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, in
     configured = true;
   }
   dim3 grid((p.o + BM * MT - 1) / (BM * MT), (p.n + TN - 1) / TN, splits);
-  gemm_tc_kernel<TN, STAGES, OT, MT, EPI><<<grid, 128, smem, stream>>>(*mw, *mx, p);
+  cudaError_t le = llg_launch(gemm_tc_kernel<TN, STAGES, OT, MT, EPI>, grid, dim3(128), (size_t)smem, stream, *mw, *mx, p);
+  if (le != cudaSuccess) return llg_fail("gemm_tc: launch: %s", cudaGetErrorString(le));
   return llg_check_launch("gemm_tc");
 }
 
