@@ -115,7 +115,9 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
   unsigned char* Vs = Ks + 2 * 64 * rs;       // [2][64][rs]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int b = a.tiles[2 * blockIdx.x], q_off = a.tiles[2 * blockIdx.x + 1];
+  // later tiles of a sequence see more keys: run the list backwards so that long blocks start first
+  const int tile_id = a.n_tiles - 1 - (int)blockIdx.x;
+  const int b = a.tiles[2 * tile_id], q_off = a.tiles[2 * tile_id + 1];
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
   const int tok0 = a.cu_tokens[b];
   const int nq = min(64, a.cu_tokens[b + 1] - tok0 - q_off);
@@ -225,19 +227,25 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
         }
       }
     }
-    // mask, running maximum, exponentials
+    // mask (only tiles that touch the diagonal or the window's edge need one), running maximum, exponentials
     float mx[2] = {-INFINITY, -INFINITY};
+    const bool need_mask = (kt + TK - 1 > pos0 + warp * 16) || (a.window > 0 && kt <= pos0 + warp * 16 + 15 - a.window);
+    if (need_mask) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = e >> 1;
+          const int key = kt + j * 8 + 2 * t + (e & 1);
+          const int qp = qpos0 + r * 8;
+          const bool valid = key <= qp && (a.window == 0 || key > qp - a.window);
+          s[j][e] = valid ? s[j][e] : -INFINITY;
+        }
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = e >> 1;
-        const int key = kt + j * 8 + 2 * t + (e & 1);
-        const int qp = qpos0 + r * 8;
-        const bool valid = key <= qp && (a.window == 0 || key > qp - a.window);
-        s[j][e] = valid ? s[j][e] : -INFINITY;
-        mx[r] = fmaxf(mx[r], s[j][e]);
-      }
+      for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
     float corr[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -248,21 +256,24 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
       m[r] = m_new;
       l[r] *= corr[r];
     }
+    const float ms0 = (m[0] == -INFINITY) ? 0.f : m[0] * sc, ms1 = (m[1] == -INFINITY) ? 0.f : m[1] * sc;
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        const float p = (m[r] == -INFINITY) ? 0.f : exp2f((s[j][e] - m[r]) * sc);
+        const float p = exp2f(fmaf(s[j][e], sc, r ? -ms1 : -ms0));     // exp2(-inf) = 0 for masked keys
         s[j][e] = p;
         l[r] += p;
       }
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-    for (int j = 0; j < HDMAX / 8; ++j) {
-      o[j][0] *= corr[0];
-      o[j][1] *= corr[0];
-      o[j][2] *= corr[1];
-      o[j][3] *= corr[1];
+      for (int j = 0; j < HDMAX / 8; ++j) {
+        o[j][0] *= corr[0];
+        o[j][1] *= corr[0];
+        o[j][2] *= corr[1];
+        o[j][3] *= corr[1];
+      }
     }
     // o += p v
 #pragma unroll
