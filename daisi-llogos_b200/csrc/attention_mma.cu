@@ -101,12 +101,13 @@ constexpr float LOG2E = 1.4426950408889634f;
 
 // ---- prompt steps --------------------------------------------------------------------------------
 
-template <int HDMAX>
+// EXACT: the head size is HDMAX itself, known at compile time (all offsets become constants)
+template <int HDMAX, bool EXACT>
 __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
   extern __shared__ __align__(16) unsigned char smraw[];
   pdl_launch_dependents();
   pdl_wait();
-  const int hd = a.hd;
+  const int hd = EXACT ? HDMAX : a.hd;
   const int rs = hd * 2 + 16;                 // bytes per shared-memory row
   const int cpr = hd / 8;                     // 16-byte chunks per row
   const int ksteps = hd / 16;
@@ -332,7 +333,7 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
-template <int HDMAX>
+template <int HDMAX, bool EXACT>
 __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smraw[];
   pdl_launch_dependents();
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
   // kernel just before this one writes only the newest position (in the sequence's last page) and
   // the queries: tiles before the last page may be requested before waiting for it.
   bool waited = false;
-  const int hd = a.hd;
+  const int hd = EXACT ? HDMAX : a.hd;
   const int rs = hd * 2 + 16;
   const int cpr = hd / 8;
   const int ksteps = hd / 16;
@@ -607,13 +608,16 @@ LLG_API int llg_attn_prefill_mma(const PrefillArgs* args, cudaStream_t stream) {
   if (a.n_tiles <= 0) return 0;
   const size_t smem = (size_t)5 * 64 * (a.hd * 2 + 16);
   dim3 grid(a.n_tiles, a.nh);
-  if (a.hd <= 64) {
-    if (set_smem(attn_prefill_mma_kernel<64>, smem, "attn_prefill_mma")) return 1;
-    llg_launch(attn_prefill_mma_kernel<64>, grid, dim3(128), smem, stream, a);
-  } else {
-    if (set_smem(attn_prefill_mma_kernel<128>, smem, "attn_prefill_mma")) return 1;
-    llg_launch(attn_prefill_mma_kernel<128>, grid, dim3(128), smem, stream, a);
-  }
+#define GO(HDM, EX)                                                                        \
+  do {                                                                                     \
+    if (set_smem(attn_prefill_mma_kernel<HDM, EX>, smem, "attn_prefill_mma")) return 1;      \
+    llg_launch(attn_prefill_mma_kernel<HDM, EX>, grid, dim3(128), smem, stream, a);          \
+  } while (0)
+  if (a.hd == 64) GO(64, true);
+  else if (a.hd == 128) GO(128, true);
+  else if (a.hd < 64) GO(64, false);
+  else GO(128, false);
+#undef GO
   return llg_check_launch("attn_prefill_mma");
 }
 
@@ -629,13 +633,16 @@ LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, cudaStream_t 
   const size_t merge = (size_t)4 * GH * (a.hd + 2) * sizeof(float);
   if (merge > smem) smem = merge;
   dim3 grid(a.n_splits, a.nkv, a.n_seqs);
-  if (a.hd <= 64) {
-    if (set_smem(attn_decode_mma_kernel<64>, smem, "attn_decode_mma")) return 1;
-    llg_launch(attn_decode_mma_kernel<64>, grid, dim3(128), smem, stream, a);
-  } else {
-    if (set_smem(attn_decode_mma_kernel<128>, smem, "attn_decode_mma")) return 1;
-    llg_launch(attn_decode_mma_kernel<128>, grid, dim3(128), smem, stream, a);
-  }
+#define GO(HDM, EX)                                                                       \
+  do {                                                                                    \
+    if (set_smem(attn_decode_mma_kernel<HDM, EX>, smem, "attn_decode_mma")) return 1;       \
+    llg_launch(attn_decode_mma_kernel<HDM, EX>, grid, dim3(128), smem, stream, a);          \
+  } while (0)
+  if (a.hd == 64) GO(64, true);
+  else if (a.hd == 128) GO(128, true);
+  else if (a.hd < 64) GO(64, false);
+  else GO(128, false);
+#undef GO
   llg_launch(attn_decode_reduce_kernel, dim3(a.nh, a.n_seqs), dim3(64), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)out,
              a.nh, a.hd, a.n_splits);
   return llg_check_launch("attn_decode_mma");
