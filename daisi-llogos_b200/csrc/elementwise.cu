@@ -75,52 +75,64 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     o[i] = from_f32<OT>(res[i] * inv * to_f32(weight[i]));
 }
 
-// The same for rows whose length is a multiple of 4: 16-byte accesses, and the partials of one
-// element are loaded four at a time so that their latencies overlap (a decode step has few rows
-// and nothing else to hide them behind).
-template <typename OT, typename WT>
+// The same for rows whose length is a multiple of 4: 16-byte accesses, the row stays in registers
+// between the two passes (VPT float4 per thread), and the partials of one element are loaded four
+// at a time so that their latencies overlap (a decode step has few rows and nothing else to hide
+// them behind).
+template <typename OT, typename WT, int VPT>
 __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const float* __restrict__ branch,
                                         int n_partials, long long partial_stride, const WT* __restrict__ weight,
                                         float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float red[32];
   const int j = blockIdx.x;
   const int r = rows ? rows[j] : j;
   float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
   const int nv = hidden >> 2;
+  float4 keep[VPT];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    float4 v = res[i];
-    if (branch) {
-      const float4* b = reinterpret_cast<const float4*>(branch + (long long)r * hidden) + i;
-      const long long ps = partial_stride >> 2;
-      int s = 0;
-      for (; s + 4 <= n_partials; s += 4) {
-        const float4 b0 = b[(s + 0) * ps], b1 = b[(s + 1) * ps], b2 = b[(s + 2) * ps], b3 = b[(s + 3) * ps];
-        v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
-        v.x += b1.x; v.y += b1.y; v.z += b1.z; v.w += b1.w;
-        v.x += b2.x; v.y += b2.y; v.z += b2.z; v.w += b2.w;
-        v.x += b3.x; v.y += b3.y; v.z += b3.z; v.w += b3.w;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < nv) {
+      v = res[i];
+      if (branch) {
+        const float4* b = reinterpret_cast<const float4*>(branch + (long long)r * hidden) + i;
+        const long long ps = partial_stride >> 2;
+        int s = 0;
+        for (; s + 4 <= n_partials; s += 4) {
+          const float4 b0 = b[(s + 0) * ps], b1 = b[(s + 1) * ps], b2 = b[(s + 2) * ps], b3 = b[(s + 3) * ps];
+          v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+          v.x += b1.x; v.y += b1.y; v.z += b1.z; v.w += b1.w;
+          v.x += b2.x; v.y += b2.y; v.z += b2.z; v.w += b2.w;
+          v.x += b3.x; v.y += b3.y; v.z += b3.z; v.w += b3.w;
+        }
+        for (; s < n_partials; ++s) {
+          const float4 b0 = b[s * ps];
+          v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+        }
+        res[i] = v;
       }
-      for (; s < n_partials; ++s) {
-        const float4 b0 = b[s * ps];
-        v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
-      }
-      res[i] = v;
     }
+    keep[k] = v;
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
   OT* o = out + (long long)j * hidden;
-  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-    const float4 v = res[i];
-    const WT* w = weight + 4 * i;
-    o[4 * i + 0] = from_f32<OT>(v.x * inv * to_f32(w[0]));
-    o[4 * i + 1] = from_f32<OT>(v.y * inv * to_f32(w[1]));
-    o[4 * i + 2] = from_f32<OT>(v.z * inv * to_f32(w[2]));
-    o[4 * i + 3] = from_f32<OT>(v.w * inv * to_f32(w[3]));
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nv) {
+      const float4 v = keep[k];
+      const WT* w = weight + 4 * i;
+      o[4 * i + 0] = from_f32<OT>(v.x * inv * to_f32(w[0]));
+      o[4 * i + 1] = from_f32<OT>(v.y * inv * to_f32(w[1]));
+      o[4 * i + 2] = from_f32<OT>(v.z * inv * to_f32(w[2]));
+      o[4 * i + 3] = from_f32<OT>(v.w * inv * to_f32(w[3]));
+    }
   }
 }
 
@@ -134,11 +146,35 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
   const bool vec = hidden % 4 == 0 && partial_stride % 4 == 0 && ((uintptr_t)residual % 16) == 0 &&
                    ((uintptr_t)branch % 16) == 0;
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  if (vec) threads = hidden >= 4096 ? 1024 : (hidden >= 1024 ? 256 : 128);
+  // vector path: few rows (decode) want many threads per row, many rows want the row in registers
+  int vpt = 1;
+  if (vec) {
+    const int nv = hidden / 4;
+    if (n_out <= 256) {
+      threads = nv >= 1024 ? 1024 : (nv >= 256 ? 256 : 128);
+    } else {
+      threads = 256;
+    }
+    vpt = (nv + threads - 1) / threads;
+    if (vpt > 8) {                     // rows longer than 8 float4 per thread: more threads
+      threads = 1024;
+      vpt = (nv + threads - 1) / threads;
+    }
+  }
+  const bool vec_ok = vec && vpt <= 8;
 #define LAUNCH(OT, WT)                                                                                         \
   do {                                                                                                         \
-    if (vec)                                                                                                   \
-      llg_launch(add_rmsnorm_vec4_kernel<OT, WT>, n_out, threads, 0, stream, residual, branch, n_partials,       \
+    if (vec_ok && vpt <= 1)                                                                                    \
+      llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 1>, n_out, threads, 0, stream, residual, branch, n_partials,    \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+    else if (vec_ok && vpt <= 2)                                                                               \
+      llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 2>, n_out, threads, 0, stream, residual, branch, n_partials,    \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+    else if (vec_ok && vpt <= 4)                                                                               \
+      llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 4>, n_out, threads, 0, stream, residual, branch, n_partials,    \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+    else if (vec_ok)                                                                                           \
+      llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 8>, n_out, threads, 0, stream, residual, branch, n_partials,    \
                  partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
     else                                                                                                       \
       llg_launch(add_rmsnorm_kernel<OT, WT>, n_out, threads, 0, stream, residual, branch, n_partials,            \
@@ -491,9 +527,10 @@ LLG_API int llg_silu_mul(const void* gu, int in_dtype, int n_partials, long long
 
 // ---- small index updates ------------------------------------------------------------
 
+// (No early launch of dependents here: kernels further down the step read the page table before
+// they wait for their predecessor, so this kernel must be complete before any of them starts.)
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx,
                                    const int* __restrict__ val, int n) {
-  pdl_launch_dependents();
   pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) dst[idx[i]] = val[i];
@@ -508,7 +545,6 @@ LLG_API int llg_scatter_i32(int* dst, const int* idx, const int* val, int n, cud
 
 __global__ void zero_rows_kernel(unsigned char* __restrict__ base, const int* __restrict__ rows,
                                  long long row_bytes) {
-  pdl_launch_dependents();
   pdl_wait();
   unsigned char* p = base + (long long)rows[blockIdx.x] * row_bytes;
   for (long long i = threadIdx.x; i < row_bytes; i += blockDim.x) p[i] = 0;
