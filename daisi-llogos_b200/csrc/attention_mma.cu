@@ -103,7 +103,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 
 // EXACT: the head size is HDMAX itself, known at compile time (all offsets become constants)
 template <int HDMAX, bool EXACT>
-__global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a) {
   extern __shared__ __align__(16) unsigned char smraw[];
   pdl_launch_dependents();
   pdl_wait();
@@ -111,9 +111,10 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
   const int rs = hd * 2 + 16;                 // bytes per shared-memory row
   const int cpr = hd / 8;                     // 16-byte chunks per row
   const int ksteps = hd / 16;
-  unsigned char* Qs = smraw;                  // [64][rs]
-  unsigned char* Ks = Qs + 64 * rs;           // [2][64][rs]
+  unsigned char* Ks = smraw;                  // [2][64][rs]
   unsigned char* Vs = Ks + 2 * 64 * rs;       // [2][64][rs]
+  unsigned char* Qs = Vs + 64 * rs;           // [64][rs]: the queries pass through the second value stage,
+                                              // which is first needed after they are in registers
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   // later tiles of a sequence see more keys: run the list backwards so that long blocks start first
@@ -190,6 +191,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(PrefillArgs a) {
       ldmatrix_x4(qf[ks], smem_u32(Qs + row * rs + col * 2));
     }
   }
+  __syncthreads();                             // every warp has its queries: their staging area may be overwritten
   float o[HDMAX / 8][4];
 #pragma unroll
   for (int j = 0; j < HDMAX / 8; ++j)
@@ -606,7 +608,7 @@ LLG_API int llg_attn_prefill_mma(const PrefillArgs* args, cudaStream_t stream) {
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages && a.nh <= 65535,
               "attn_prefill_mma: bad cache geometry");
   if (a.n_tiles <= 0) return 0;
-  const size_t smem = (size_t)5 * 64 * (a.hd * 2 + 16);
+  const size_t smem = (size_t)4 * 64 * (a.hd * 2 + 16);
   dim3 grid(a.n_tiles, a.nh);
 #define GO(HDM, EX)                                                                        \
   do {                                                                                     \
