@@ -1,0 +1,433 @@
+// Causal attention for prompt steps on the 5th-generation tensor cores (tcgen05), bfloat16, head
+// sizes 64 and 128.  One block of 128 threads owns 128 queries of one head; thread r owns query row
+// r, which is lane r of tensor memory, so the softmax of a row needs no exchange between threads:
+//
+//   per 64-key tile (one cache page):   S = Q K^T      tcgen05.mma, accumulator S[128 x 64] in TMEM
+//                                       each thread reads its row of S (tcgen05.ld), masks, updates the
+//                                       running maximum and sum, writes P (bfloat16) to shared memory
+//                                       O += P V       tcgen05.mma, accumulator O[128 x head] in TMEM
+//
+// Q, K and P are K-major operands with the 128-byte swizzle; V is stored as it lies in memory
+// ([key][dim], dim contiguous), which makes it the MN-major second operand of the second product.
+// Key and value tiles are copied by all threads with cp.async (rows come from the step's packed
+// buffer or from cache pages, as in attn_prefill_simt), two stages deep.  When a row's maximum
+// grows, its accumulator row is rescaled in place (tcgen05.ld / tcgen05.st), warp by warp and only
+// when some row of the warp needs it.
+//
+// Every mbarrier wait is bounded; on expiry the block records an error (llg_attn_tc_status), stops
+// issuing work, waits for its copies in flight, frees its tensor memory and returns.
+#include "common.cuh"
+
+LLG_API const char* llg_last_error() { return g_llg_error; }
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int BQ = 128;      // queries per block
+constexpr int TK = 64;       // keys per tile = one cache page
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ int g_error = 0;  // 0 ok; 1 score wait, 2 output wait, 3 shared memory not aligned to 1024 bytes
+
+struct PrefillArgs {         // same layout as in attention_simt.cu
+  const void* q;
+  const void* k_new;
+  const void* v_new;
+  const void* k_pages;
+  const void* v_pages;
+  const int* page_table;
+  int table_width;
+  int ring_pages;
+  const int* tiles;          // [n_tiles][2]: (sequence, first query), 128 queries per tile
+  const int* cu_tokens;
+  const int* len_before;
+  const int* slots;
+  void* out;
+  int n_tiles, nh, nkv, hd;
+  float scale;
+  int window;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 1023) == 0) {
+      if (*abort_flag) return false;
+      if (now_ns() - t0 > WAIT_LIMIT_NS) return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// shared memory written by threads (cp.async, st.shared) becomes visible to the tensor core's reads
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// K-major operand, rows of 128 bytes with the 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// MN-major operand: 64 elements of the MN dimension are contiguous (one swizzled 128-byte row per k),
+// 8-k groups 1024 bytes apart, the next 64 MN elements `lbo_bytes` further
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo_bytes) {
+  return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a tile of 128-byte rows with the 128-byte swizzle
+__device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+template <int HD>
+__global__ void __launch_bounds__(128) attn_prefill_tc_kernel(PrefillArgs a) {
+  constexpr int KB = HD / 64;                 // 64-wide blocks of the head dimension
+  constexpr int Q_BYTES = KB * BQ * 128;      // [KB][128 rows][128 bytes]
+  constexpr int KV_BYTES = KB * TK * 128;     // [KB][64 keys][128 bytes]
+  constexpr int TMEM_COLS = HD == 64 ? 128 : 256;   // S: 64 columns, O: HD columns
+  constexpr uint32_t S_COL = 0, O_COL = 64;
+  // The tiles need 1024-byte alignment (swizzle); the declaration asks for it and the kernel checks it.
+  // No slack is added: 112 KB + the barriers' kilobyte lets two blocks share an SM.
+  extern __shared__ __align__(1024) unsigned char smem[];
+  unsigned char* Qs = smem;
+  unsigned char* Ks = Qs + Q_BYTES;           // [2 stages]
+  unsigned char* Vs = Ks + 2 * KV_BYTES;      // [2 stages]
+  unsigned char* Ps = Vs + 2 * KV_BYTES;      // [128 rows][64 keys]
+  __shared__ uint64_t bar_s, bar_o;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  pdl_launch_dependents();
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if ((smem_u32(smem) & 1023u) != 0) {          // uniform over the block
+    if (tid == 0) atomicCAS(&g_error, 0, 3);
+    return;
+  }
+  if (tid == 0) {
+    mbar_init(&bar_s, 1);
+    mbar_init(&bar_o, 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = tmem_base_slot;
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  volatile int* abortp = &abort_flag;
+  pdl_wait();
+
+  // later tiles of a sequence see more keys: run the list backwards so that long blocks start first
+  const int tile_id = a.n_tiles - 1 - (int)blockIdx.x;
+  const int b = a.tiles[2 * tile_id], q_off = a.tiles[2 * tile_id + 1];
+  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int tok0 = a.cu_tokens[b];
+  const int nq = min(BQ, a.cu_tokens[b + 1] - tok0 - q_off);
+  const int lb = a.len_before[b];
+  const int slot = a.slots[b];
+  const int pos0 = lb + q_off;
+  const int k_end = pos0 + nq;
+  int k_begin = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  k_begin = (k_begin / TK) * TK;
+  const int n_tiles = (k_end - k_begin + TK - 1) / TK;
+  const bf16* qg = (const bf16*)a.q;
+  const bf16* kn = (const bf16*)a.k_new;
+  const bf16* vn = (const bf16*)a.v_new;
+  const bf16* kp = (const bf16*)a.k_pages;
+  const bf16* vp = (const bf16*)a.v_pages;
+  constexpr int CPR = HD / 8;                 // 16-byte chunks per row of the head
+
+  // copies one 64-key tile of K and V: chunk c of the head goes to block c / 8, swizzled chunk c % 8
+  auto load_kv = [&](int tile, int stage) {
+    const int kt = k_begin + tile * TK;
+    unsigned char* kd = Ks + stage * KV_BYTES;
+    unsigned char* vd = Vs + stage * KV_BYTES;
+    const long long old_base = kt < lb ? kv_row(a.page_table, a.table_width, a.ring_pages, slot, kt, kvh, a.nkv) * HD : 0;
+    const long long new_base = ((long long)(tok0 + kt - lb) * a.nkv + kvh) * HD;
+    const long long new_step = (long long)a.nkv * HD;
+    constexpr int RSTEP = 128 / CPR;
+    const int ch = tid % CPR;
+    for (int row = tid / CPR; row < TK; row += RSTEP) {
+      const int pos = kt + row;
+      const bool valid = pos < k_end;
+      const bool fresh = pos >= lb;
+      const long long off = (fresh ? new_base + row * new_step : old_base + (long long)row * HD) + ch * 8;
+      const uint32_t so = (uint32_t)((ch >> 3) * (TK * 128)) + swz(row, ch & 7);
+      cp_async16(smem_u32(kd) + so, (fresh ? kn : kp) + (valid ? off : 0), valid);
+      cp_async16(smem_u32(vd) + so, (fresh ? vn : vp) + (valid ? off : 0), valid);
+    }
+  };
+
+  // queries: row r of the tile, block c / 8 of the head
+  {
+    constexpr int RSTEP = 128 / CPR;
+    const int ch = tid % CPR;
+    for (int row = tid / CPR; row < BQ; row += RSTEP) {
+      const bool valid = row < nq;
+      const bf16* src = qg + ((long long)(tok0 + q_off + (valid ? row : 0)) * a.nh + h) * HD + ch * 8;
+      cp_async16(smem_u32(Qs) + (uint32_t)((ch >> 3) * (BQ * 128)) + swz(row, ch & 7), src, valid);
+    }
+  }
+  load_kv(0, 0);
+  cp_async_commit();
+
+  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+  const float sc = a.scale * LOG2E;
+  const int qpos = pos0 + tid;                 // this thread's query position
+  float m_run = -INFINITY, l_run = 0.f;
+  bool ok = true;
+
+  for (int tile = 0; tile < n_tiles && ok; ++tile) {
+    const int stage = tile & 1;
+    // the other stage and P were last read by the second product of the previous tile
+    if (tile > 0) {
+      if (!mbar_wait(&bar_o, (tile - 1) & 1, abortp)) {
+        if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+      }
+    }
+    __syncthreads();
+    if (*abortp) { ok = false; break; }
+    if (tile + 1 < n_tiles) load_kv(tile + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();                        // this tile's (and, the first time, the queries') copies are done
+    fence_async_smem();
+    __syncthreads();
+    const int kt = k_begin + tile * TK;
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + stage * KV_BYTES);
+#pragma unroll
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        const uint32_t blk = ks >> 2, kk = ks & 3;      // 64-wide block, 16-wide step inside it (32 bytes)
+        umma_bf16(tmem + S_COL, desc_kmajor(qa + blk * (BQ * 128) + kk * 32), desc_kmajor(ka + blk * (TK * 128) + kk * 32),
+                  IDESC_S, ks != 0);
+      }
+      umma_commit(&bar_s);
+    }
+    if (!mbar_wait(&bar_s, tile & 1, abortp)) {
+      if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
+    }
+    __syncthreads();
+    if (*abortp) { ok = false; break; }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+
+    // this thread's row of scores: maximum, then exponentials straight into P
+    float sv[TK];
+#pragma unroll
+    for (int c0 = 0; c0 < TK; c0 += 16) {
+      uint32_t r[16];
+      tmem_ld16(lane_base + S_COL + c0, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int c = 0; c < 16; ++c) sv[c0 + c] = __uint_as_float(r[c]);
+    }
+    const bool need_mask = (kt + TK - 1 > pos0 + warp * 32) || (a.window > 0 && kt <= pos0 + warp * 32 + 31 - a.window);
+    float mx = -INFINITY;
+    if (need_mask) {
+#pragma unroll
+      for (int c = 0; c < TK; ++c) {
+        const int key = kt + c;
+        const bool valid = key <= qpos && (a.window == 0 || key > qpos - a.window);
+        sv[c] = valid ? sv[c] : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < TK; ++c) mx = fmaxf(mx, sv[c]);
+    const float m_new = fmaxf(m_run, mx);
+    const float corr = (m_new == -INFINITY) ? 1.f : exp2f((m_run - m_new) * sc);
+    const float ms = (m_new == -INFINITY) ? 0.f : m_new * sc;
+    m_run = m_new;
+    float psum = 0.f;
+    unsigned char* prow = Ps;
+#pragma unroll
+    for (int c8 = 0; c8 < TK / 8; ++c8) {
+      float p[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        p[e] = exp2f(fmaf(sv[c8 * 8 + e], sc, -ms));
+        psum += p[e];
+      }
+      uint4 v;
+      v.x = pack_bf16(p[0], p[1]);
+      v.y = pack_bf16(p[2], p[3]);
+      v.z = pack_bf16(p[4], p[5]);
+      v.w = pack_bf16(p[6], p[7]);
+      *reinterpret_cast<uint4*>(prow + swz(tid, c8)) = v;
+    }
+    l_run = l_run * corr + psum;
+    // rescale the accumulator row when some row of this warp moved its maximum (never for the first tile:
+    // the first product overwrites the accumulator)
+    if (tile > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_base + O_COL + c0, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+        tmem_st16(lane_base + O_COL + c0, r);
+      }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs + stage * KV_BYTES);
+#pragma unroll
+      for (int kk = 0; kk < TK / 16; ++kk) {
+        // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
+        umma_bf16(tmem + O_COL, desc_kmajor(pa + kk * 32), desc_mnmajor(va + kk * 2048, TK * 128), IDESC_O, (tile | kk) != 0);
+      }
+      umma_commit(&bar_o);
+    }
+  }
+
+  if (ok && n_tiles > 0) {
+    if (!mbar_wait(&bar_o, (n_tiles - 1) & 1, abortp)) {
+      if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (!*abortp) {
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    bf16* dst = (bf16*)a.out + ((long long)(tok0 + q_off + tid) * a.nh + h) * HD;
+#pragma unroll
+    for (int c0 = 0; c0 < HD; c0 += 16) {
+      uint32_t r[16];
+      tmem_ld16(lane_base + O_COL + c0, r);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (tid < nq) {
+        uint4 v0, v1;
+        v0.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+        v0.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+        v0.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+        v0.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+        v1.x = pack_bf16(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+        v1.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+        v1.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+        v1.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+        *reinterpret_cast<uint4*>(dst + c0) = v0;
+        *reinterpret_cast<uint4*>(dst + c0 + 8) = v1;
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+  }
+}
+
+template <int HD>
+int launch(const PrefillArgs& a, cudaStream_t stream) {
+  constexpr int smem = (HD / 64) * BQ * 128 + 4 * (HD / 64) * TK * 128 + BQ * 128;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return llg_fail("attn_prefill_tc: shared memory %d: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.n_tiles, a.nh), dim3(128), (size_t)smem, stream, a);
+  if (le != cudaSuccess) return llg_fail("attn_prefill_tc: launch: %s", cudaGetErrorString(le));
+  return llg_check_launch("attn_prefill_tc");
+}
+
+}  // namespace
+
+// 1 when this kernel takes the head size (bfloat16 only): 64 or 128.
+LLG_API int llg_attn_tc_supported(int hd) { return hd == 64 || hd == 128; }
+
+LLG_API int llg_attn_prefill_tc(const PrefillArgs* args, cudaStream_t stream) {
+  const PrefillArgs& a = *args;
+  LLG_REQUIRE(llg_attn_tc_supported(a.hd), "attn_prefill_tc: head_dim %d is neither 64 nor 128", a.hd);
+  LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_prefill_tc: %d heads are no multiple of %d key/value heads",
+              a.nh, a.nkv);
+  LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages && a.nh <= 65535,
+              "attn_prefill_tc: bad cache geometry");
+  LLG_REQUIRE(a.scale > 0.f, "attn_prefill_tc: the softmax scale must be positive");
+  if (a.n_tiles <= 0) return 0;
+  return a.hd == 64 ? launch<64>(a, stream) : launch<128>(a, stream);
+}
+
+// Error code recorded when a wait ran out (0 = none); clears it.  Synchronises the device.
+LLG_API int llg_attn_tc_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_error, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) cudaMemcpyToSymbol(g_error, &zero, sizeof(int));
+  return v;
+}

@@ -32,6 +32,7 @@ SOURCES: Dict[str, List[str]] = {
     "gemm_tc": ["gemm_tc.cu", "common.cuh"],
     "attention_simt": ["attention_simt.cu", "common.cuh", "attention_noalloc.h"],
     "attention_mma": ["attention_mma.cu", "common.cuh"],
+    "attention_tc": ["attention_tc.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
 }
 

@@ -153,6 +153,10 @@ def _lib(name: str):
         lib.llg_attn_mma_supported.argtypes = [c_int]
         lib.llg_attn_prefill_mma.argtypes = [POINTER(_PrefillArgs), c_void_p]
         lib.llg_attn_decode_mma.argtypes = [POINTER(_DecodeArgs), c_void_p, c_void_p]
+    elif name == "attention_tc":
+        lib.llg_attn_tc_supported.argtypes = [c_int]
+        lib.llg_attn_prefill_tc.argtypes = [POINTER(_PrefillArgs), c_void_p]
+        lib.llg_attn_tc_status.restype = c_int
     elif name == "sampling":
         lib.llg_argmax.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.llg_sample.argtypes = [POINTER(_SampleArgs), c_void_p]
@@ -340,9 +344,24 @@ def _use_mma(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and 16 <= head_dim <= 128 and head_dim % 16 == 0
 
 
+USE_TC_PROMPT_ATTENTION = True     # tests switch it off to reach the mma.sync kernel at head sizes 64 and 128
+
+
+def _use_tc_attn(dtype: torch.dtype, head_dim: int) -> bool:
+    """bfloat16 prompt attention with a head size the tcgen05 kernel takes (64 or 128)."""
+    return USE_TC_PROMPT_ATTENTION and dtype == torch.bfloat16 and head_dim in (64, 128)
+
+
 def prefill_tile_queries(dtype: torch.dtype, head_dim: int) -> int:
     """Queries per block of the prompt attention kernel that ``attn_prefill`` will run."""
+    if _use_tc_attn(dtype, head_dim):
+        return 128
     return 64 if _use_mma(dtype, head_dim) else 16
+
+
+def attn_tc_status() -> int:
+    """Error code the tcgen05 prompt attention recorded when a wait ran out (0 = none); synchronises."""
+    return _lib("attention_tc").llg_attn_tc_status()
 
 
 def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tiles, cu_tokens, len_before,
@@ -350,9 +369,10 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
     """Causal attention for a step with several tokens per sequence.
 
     ``tiles`` is ``[n_tiles, 2]`` (sequence index, first query among its step tokens) cut every
-    ``tile_queries`` queries, which must be ``prefill_tile_queries(q.dtype, head_dim)``.  bfloat16 with
-    head sizes up to 128 runs on the tensor cores (csrc/attention_mma.cu), everything else on the
-    CUDA cores (csrc/attention_simt.cu).
+    ``tile_queries`` queries, which must be ``prefill_tile_queries(q.dtype, head_dim)``.  bfloat16 runs on
+    the tensor cores: head sizes 64 and 128 with tcgen05 (csrc/attention_tc.cu), other multiples of 16 up
+    to 128 with mma.sync (csrc/attention_mma.cu); everything else on the CUDA cores
+    (csrc/attention_simt.cu).
     """
     n, nh, hd = q.shape
     nkv = k_new.shape[1]
@@ -362,8 +382,9 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
                           f"{prefill_tile_queries(q.dtype, hd)}")
     if scale <= 0:
         raise KernelError("attn_prefill: the softmax scale must be positive")
+    tc = _use_tc_attn(q.dtype, hd)
     mma = _use_mma(q.dtype, hd)
-    lib = _lib("attention_mma" if mma else "attention_simt")
+    lib = _lib("attention_tc" if tc else "attention_mma" if mma else "attention_simt")
     a = _PrefillArgs()
     a.q, a.k_new, a.v_new = _ptr(q), _ptr(k_new, q.dtype), _ptr(v_new, q.dtype)
     a.k_pages, a.v_pages = _ptr(k_pages, q.dtype), _ptr(v_pages, q.dtype)
@@ -373,7 +394,9 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
     a.out = _ptr(out, q.dtype)
     a.n_tiles, a.nh, a.nkv, a.hd = tiles.shape[0], nh, nkv, hd
     a.scale, a.window = float(scale), int(window)
-    if mma:
+    if tc:
+        _check(lib, lib.llg_attn_prefill_tc(byref(a), _stream()))
+    elif mma:
         _check(lib, lib.llg_attn_prefill_mma(byref(a), _stream()))
     else:
         _check(lib, lib.llg_attn_prefill_simt(byref(a), _dt(q), _stream()))

@@ -239,10 +239,14 @@ def test_attn_decode(ops, dtype, nh, nkv, hd, window):
             check(out[b], ref, dtype, (b, n, splits))
 
 
+@pytest.mark.parametrize("tc", [True, False], ids=["tcgen05", "mma"])
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
 @pytest.mark.parametrize("nh,nkv,hd,window", [(5, 1, 48, 0), (6, 3, 80, 0), (4, 2, 128, 100), (8, 4, 16, 40), (3, 1, 112, 0),
-                                              (2, 2, 144, 0), (2, 1, 256, 90)])
-def test_attn_prefill_and_kv_write(ops, dtype, nh, nkv, hd, window):
+                                              (2, 2, 144, 0), (2, 1, 256, 90), (6, 2, 64, 0), (3, 3, 128, 0), (4, 1, 64, 70)])
+def test_attn_prefill_and_kv_write(ops, dtype, nh, nkv, hd, window, tc, monkeypatch):
+    if not tc and not (dtype == torch.bfloat16 and hd in (64, 128)):
+        pytest.skip("only head sizes 64 and 128 in bfloat16 have two tensor-core kernels")
+    monkeypatch.setattr(ops, "USE_TC_PROMPT_ATTENTION", tc)
     before = [0, 0, 70, 130, 64]           # tokens already in the cache
     counts = [1, 37, 16, 150, 3]           # tokens the step brings
     ring = 8 if window == 0 else (window + 63) // 64 + 1
@@ -286,6 +290,8 @@ def test_attn_prefill_and_kv_write(ops, dtype, nh, nkv, hd, window):
         for p in range(max(0, t - ring * 64), t):
             pg = int(table[slots[b], (p // 64) % ring])
             assert torch.equal(kpd[pg, :, p % 64].cpu(), ks[b][p]) and torch.equal(vpd[pg, :, p % 64].cpu(), vs[b][p]), (b, p)
+    if dtype == torch.bfloat16 and hd in (64, 128) and tc:
+        assert ops.attn_tc_status() == 0
 
 
 def test_kernels_refuse_what_they_cannot_do(ops):

@@ -49,7 +49,7 @@ def prompt_ctx(llogos, ops, dtype, counts, before, slots):
         cu.append(cu[-1] + c)
     pos = [p for b, c in zip(before, counts) for p in range(b, b + c)]
     seq = [i for i, c in enumerate(counts) for _ in range(c)]
-    tiles = {tq: i32([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)]).view(-1, 2) for tq in (16, 64)}
+    tiles = {tq: i32([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)]).view(-1, 2) for tq in (16, 64, 128)}
     decode = all(c == 1 for c in counts)
     return ctx_mod.StepContext(
         n_tokens=cu[-1], n_seqs=len(counts), decode=decode, counts=list(counts), max_count=max(counts),
