@@ -127,7 +127,11 @@ struct GemmParams {
 // MT: weight tiles of 128 rows per block (1 or 2; two tiles share every activation tile, which halves
 // the shared-memory traffic per flop of a large product).  EPI 1 (MT = 2): the first tile holds gate
 // rows and the second the up rows of the same 128 features; the block writes silu(gate) * up.
-template <int TN, int STAGES, typename OT, int MT, int EPI>
+// SWAP 0: the first operand (MMA rows, accumulator lanes) is the weight matrix, the second the activations:
+// out[n][o] with o along the lanes (decode steps: the token tile can be as small as 16).
+// SWAP 1: the first operand is the activations (128 tokens per tile), the second the weights (TN features):
+// a thread owns a token and writes runs of consecutive features with 16-byte stores (prompt steps).
+template <int TN, int STAGES, typename OT, int MT, int EPI, int SWAP>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, GemmParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -136,7 +140,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   constexpr int B_BYTES = TN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = MT * TN < 32 ? 32 : MT * TN;
-  static_assert(EPI == 0 || MT == 2, "the gated epilogue needs a gate tile and an up tile");
+  static_assert(EPI == 0 || (SWAP ? TN == 256 : MT == 2), "the gated epilogue needs a gate tile and an up tile");
   // 1024-byte alignment of the operand tiles is what the swizzle pattern of TMA and of the MMA assume
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], done_bar;
@@ -182,7 +186,10 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   bool first = true;
   int preloaded = 0;            // k-blocks of the coming tile that are already requested
   for (int tile = blockIdx.x, round = 0; tile < total_tiles; tile += gridDim.x, ++round) {
-    const int o0 = (tile / n_tiles_n) * (BM * MT), n0 = (tile % n_tiles_n) * TN;
+    // the operand that is shared by neighbouring blocks is the weight tile in both orientations
+    const int m_tiles = total_tiles / n_tiles_n;
+    const int o0 = (SWAP ? tile % m_tiles : tile / n_tiles_n) * (BM * MT);
+    const int n0 = (SWAP ? tile / m_tiles : tile % n_tiles_n) * TN;
 
     if (tid == 0) {
       // ---- producer: TMA loads into the ring ------------------------------------------------
@@ -252,7 +259,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     preloaded = 0;
     if (tid == 0 && tile + (int)gridDim.x < total_tiles) {
       const int nt = tile + gridDim.x;
-      const int no0 = (nt / n_tiles_n) * (BM * MT), nn0 = (nt % n_tiles_n) * TN;
+      const int no0 = (SWAP ? nt % m_tiles : nt / n_tiles_n) * (BM * MT);
+      const int nn0 = (SWAP ? nt / m_tiles : nt % n_tiles_n) * TN;
       const int pre = min(nkb, STAGES);
       for (int i = 0; i < pre; ++i, ++it_issue) {
         const int s = it_issue % STAGES;
@@ -267,7 +275,67 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     {
       const uint32_t lane_base = tmem_d + ((uint32_t)(warp * 32) << 16);
-      if (EPI == 0) {
+      if (SWAP) {
+        // lanes are tokens (p.o of them), columns are features (p.n, or gate|up blocks of 128 + 128)
+        constexpr int VEC = 16 / (int)sizeof(OT);      // outputs per 16-byte store
+        const int width = EPI ? p.gated_features : p.n;
+        const bool vec_ok = width % VEC == 0;
+        OT* out = (OT*)p.out + (long long)split * p.n * p.o;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          if (o0 + mt * BM >= p.o) break;
+          const int tok = o0 + mt * BM + warp * 32 + lane;
+          OT* row = out + (long long)tok * width;
+          constexpr int COLS = EPI ? TN / 2 : TN;
+#pragma unroll
+          for (int c0 = 0; c0 < COLS; c0 += 16) {
+            const int f0 = EPI ? (n0 / 256) * 128 + c0 : n0 + c0;      // first feature of this run
+            if (f0 >= width) break;
+            float v[16];
+            uint32_t r[16];
+            tmem_ld16(lane_base + (uint32_t)(mt * TN + c0), r);
+            if (EPI) {
+              uint32_t ru[16];
+              tmem_ld16(lane_base + (uint32_t)(mt * TN + TN / 2 + c0), ru);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                const float g = __uint_as_float(r[c]);
+                v[c] = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(ru[c]);
+              }
+            } else {
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+            }
+            if (tok < p.o) {
+              if (vec_ok && f0 + 16 <= width) {
+                if (sizeof(OT) == 4) {
+#pragma unroll
+                  for (int q = 0; q < 4; ++q)
+                    *reinterpret_cast<float4*>((float*)row + f0 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else {
+#pragma unroll
+                  for (int q = 0; q < 2; ++q) {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]), h1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]), h3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+                    uint4 u;
+                    u.x = *reinterpret_cast<uint32_t*>(&h0);
+                    u.y = *reinterpret_cast<uint32_t*>(&h1);
+                    u.z = *reinterpret_cast<uint32_t*>(&h2);
+                    u.w = *reinterpret_cast<uint32_t*>(&h3);
+                    *reinterpret_cast<uint4*>((__nv_bfloat16*)row + f0 + 8 * q) = u;
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                  if (f0 + c < width) row[f0 + c] = from_f32<OT>(v[c]);
+              }
+            }
+          }
+        }
+      } else if (EPI == 0) {
         OT* out = (OT*)p.out + (long long)split * p.n * p.o;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
@@ -380,13 +448,13 @@ bool tensor_map(const void* base, int rows, int k, int box_rows, CUtensorMap* re
   return true;
 }
 
-template <int TN, int STAGES, typename OT, int MT, int EPI>
+template <int TN, int STAGES, typename OT, int MT, int EPI, int SWAP>
 int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, int splits, cudaStream_t stream) {
   constexpr int smem = STAGES * (MT * BM * BK * 2 + TN * BK * 2) + 1024;
   static_assert(smem <= 232448, "stage ring does not fit shared memory");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN, STAGES, OT, MT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TN, STAGES, OT, MT, EPI, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return llg_fail("gemm_tc: cannot have %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
@@ -400,7 +468,7 @@ int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, in
   }
   if (blocks > 2147483647LL) return llg_fail("gemm_tc: too many tiles");
   dim3 grid((unsigned)blocks, 1, splits);
-  cudaError_t le = llg_launch(gemm_tc_kernel<TN, STAGES, OT, MT, EPI>, grid, dim3(128), (size_t)smem, stream, *mw, *mx, p);
+  cudaError_t le = llg_launch(gemm_tc_kernel<TN, STAGES, OT, MT, EPI, SWAP>, grid, dim3(128), (size_t)smem, stream, *mw, *mx, p);
   if (le != cudaSuccess) return llg_fail("gemm_tc: launch: %s", cudaGetErrorString(le));
   return llg_check_launch("gemm_tc");
 }
@@ -436,10 +504,30 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
               "gemm_tc: the gated epilogue needs one split and ceil(features / 128) * 256 rows of w (features=%d rows=%d splits=%d)",
               gated_features, o, splits);
   const int nkb = (k + BK - 1) / BK;
+  CUtensorMap map_w, map_x;
+  if (n >= 256 && tile_n <= 0) {
+    // ---- prompt steps: activations are the first operand (128 tokens per tile), 256 features per tile ----
+    // in this orientation the kernel's first-operand rows (field o) are the tokens, the second's (field n) the features
+    GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features};
+    LLG_REQUIRE(tensor_map(x, n, k, BM, &map_x) && tensor_map(w, o, k, 256, &map_w),
+                "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
+    const long long nt = (o + 255) / 256;
+    const long long t1 = (long long)((n + BM - 1) / BM) * nt, t2 = (long long)((n + 2 * BM - 1) / (2 * BM)) * nt;
+    // two token tiles per block halve the weight traffic per flop (worth about 15 %) but double the tile
+    const bool two = ((t2 + 147) / 148) * 2 * 0.85 < (double)((t1 + 147) / 148);
+#define GOS(OTT, EP)                                                                       \
+  return two ? launch<256, 3, OTT, 2, EP, 1>(&map_x, &map_w, ps, splits, stream)             \
+             : launch<256, 4, OTT, 1, EP, 1>(&map_x, &map_w, ps, splits, stream)
+    if (gated) {
+      if (out_dtype == LLG_F32) GOS(float, 1); else GOS(__nv_bfloat16, 1);
+    } else {
+      if (out_dtype == LLG_F32) GOS(float, 0); else GOS(__nv_bfloat16, 0);
+    }
+#undef GOS
+  }
   GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features};
   if (tile_n <= 0) tile_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
   LLG_REQUIRE(splits <= 65535, "gemm_tc: grid too large");
-  CUtensorMap map_w, map_x;
   LLG_REQUIRE(tensor_map(w, o, k, BM, &map_w) && tensor_map(x, n, k, tile_n, &map_x),
               "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
   const CUtensorMap *mw = &map_w, *mx = &map_x;
@@ -450,14 +538,14 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   const bool wide = !gated && tile_n >= 128 && ((t2 + 147) / 148) * 2 * 0.85 < (double)((t1 + 147) / 148);
 #define GO(TN, ST1, ST2)                                                                              \
   if (gated)                                                                                          \
-    return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 1>(mw, mx, p, splits, stream)               \
-                                : launch<TN, ST2, __nv_bfloat16, 2, 1>(mw, mx, p, splits, stream);      \
+    return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 1, 0>(mw, mx, p, splits, stream)            \
+                                : launch<TN, ST2, __nv_bfloat16, 2, 1, 0>(mw, mx, p, splits, stream);   \
   else if (wide)                                                                                      \
-    return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 0>(mw, mx, p, splits, stream)               \
-                                : launch<TN, ST2, __nv_bfloat16, 2, 0>(mw, mx, p, splits, stream);      \
+    return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 0, 0>(mw, mx, p, splits, stream)            \
+                                : launch<TN, ST2, __nv_bfloat16, 2, 0, 0>(mw, mx, p, splits, stream);   \
   else                                                                                                \
-    return out_dtype == LLG_F32 ? launch<TN, ST1, float, 1, 0>(mw, mx, p, splits, stream)               \
-                                : launch<TN, ST1, __nv_bfloat16, 1, 0>(mw, mx, p, splits, stream)
+    return out_dtype == LLG_F32 ? launch<TN, ST1, float, 1, 0, 0>(mw, mx, p, splits, stream)            \
+                                : launch<TN, ST1, __nv_bfloat16, 1, 0, 0>(mw, mx, p, splits, stream)
   switch (tile_n) {
     case 16: GO(16, 5, 5);
     case 32: GO(32, 5, 5);
