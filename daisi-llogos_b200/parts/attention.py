@@ -126,11 +126,20 @@ class Attention(Mixer):
             ops.attn_decode(q, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages, ctx.slots,
                             ctx.len_before, out, scratch, n_splits=splits, scale=self.scale, window=self.window)
         else:
+            # A group that keeps every key can take the step's keys and values into its pages right away
+            # (the step reads them from the packed buffer, never from the pages).  A ring must wait until
+            # the attention has read the old keys that the new ones overwrite.
+            write_now = self.own_kv and self.window == 0
             if self.own_kv:
                 suffix = f".{cache.unit}" if cache.keep_step_kv else ""
                 k_new = ctx.buffer("attn.k_new" + suffix, (n, self.nkv, self.hd))
                 v_new = ctx.buffer("attn.v_new" + suffix, (n, self.nkv, self.hd))
-                ops.qk_prep(qkv, **common, k_new=k_new, v_new=v_new)
+                if write_now:
+                    ops.qk_prep(qkv, **common, k_new=k_new, v_new=v_new, k_pages=cache.k_pages, v_pages=cache.v_pages,
+                                page_table=cache.page_table, ring_pages=cache.ring_pages,
+                                seq_of_token=ctx.seq_of_token, slots=ctx.slots)
+                else:
+                    ops.qk_prep(qkv, **common, k_new=k_new, v_new=v_new)
                 cache.shared["k_new"], cache.shared["v_new"] = k_new, v_new
             else:
                 ops.qk_prep(qkv, **common)
@@ -139,7 +148,7 @@ class Attention(Mixer):
             ops.attn_prefill(q, k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
                              ctx.prefill_tiles[tq], ctx.cu_tokens, ctx.len_before, ctx.slots, out,
                              scale=self.scale, window=self.window, tile_queries=tq)
-            if self.own_kv:
+            if self.own_kv and not write_now:
                 ops.kv_write(k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
                              ctx.positions, ctx.seq_of_token, ctx.slots, ctx.cu_tokens, ctx.len_before)
         return Branch(linear(ctx, out, self.w_o, "attn.proj", torch.float32))

@@ -52,7 +52,15 @@ TINY_QWEN2 = {
     "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 64},
 }
-TINY = {"llama": TINY_LLAMA, "qwen3": TINY_QWEN3, "qwen2": TINY_QWEN2}
+# head size 128: the geometry the tcgen05 attention and the register-resident q/k kernel are written for
+TINY_WIDE = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 192,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 320,
+    "vocab_size": 500, "rope_theta": 20000.0, "rms_norm_eps": 2e-6, "max_position_embeddings": 1024,
+    "tie_word_embeddings": False, "sliding_window": 90,
+    "layer_types": ["sliding_attention", "full_attention"],
+}
+TINY = {"llama": TINY_LLAMA, "qwen3": TINY_QWEN3, "qwen2": TINY_QWEN2, "wide": TINY_WIDE}
 INIT = dict(std=0.15, norm_std=0.1, bias_std=0.1)
 
 
