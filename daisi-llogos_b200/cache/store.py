@@ -65,8 +65,11 @@ class KvGroup:
         self.table_width = self.ring_pages
         self.pool = FreeList(n_pages, "page")
         self.pages_of: Dict[int, List[int]] = {}
-        self.page_table = torch.zeros((n_slots, self.table_width), dtype=torch.int32, device=device)
-        shape = (max(n_pages, 1), need.num_kv_heads, PAGE, need.head_dim)
+        # One row and one page beyond what sequences can get: the padding slot (row n_slots) owns page
+        # n_pages for good.  Steps that are padded up to a graph's batch size park their extra rows there.
+        self.page_table = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32, device=device)
+        self.page_table[n_slots, :] = n_pages
+        shape = (n_pages + 1, need.num_kv_heads, PAGE, need.head_dim)
         self.k = {u: torch.zeros(shape, dtype=dtype, device=device) for u in units}
         self.v = {u: torch.zeros(shape, dtype=dtype, device=device) for u in units}
 
@@ -115,6 +118,7 @@ class SequenceCache:
         self.n_pages = pages_for(max_tokens)
         self.max_seq_len = min(max_seq_len, self.n_pages * PAGE)
         self.slots = SlotTable(n_slots)
+        self.pad_slot = n_slots          # never handed out; see KvGroup
         self.kv_groups: List[KvGroup] = []
         self._group_of_unit: Dict[int, KvGroup] = {}
         self.state: Dict[int, torch.Tensor] = {}
@@ -125,7 +129,7 @@ class SequenceCache:
             if isinstance(need, KvNeed):
                 by_need.setdefault(need, []).append(unit)
             elif isinstance(need, StateNeed):
-                self.state[unit] = torch.zeros((n_slots, *need.shape), dtype=need.dtype, device=device)
+                self.state[unit] = torch.zeros((n_slots + 1, *need.shape), dtype=need.dtype, device=device)
             else:
                 raise TypeError(f"cache unit {unit}: unknown need {need!r}")
         for need, units in by_need.items():

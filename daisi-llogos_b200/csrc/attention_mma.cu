@@ -99,6 +99,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x by the special-function unit alone (float32, about 2 ulp, denormal results flushed to zero);
+// exp2f() adds range handling that the softmax does not need: its arguments are <= 0 or -inf.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---- prompt steps --------------------------------------------------------------------------------
 
 // EXACT: the head size is HDMAX itself, known at compile time (all offsets become constants)
@@ -255,7 +263,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float m_new = fmaxf(m[r], mx[r]);
-      corr[r] = (m_new == -INFINITY) ? 1.f : exp2f((m[r] - m_new) * sc);
+      corr[r] = (m_new == -INFINITY) ? 1.f : fast_exp2((m[r] - m_new) * sc);
       m[r] = m_new;
       l[r] *= corr[r];
     }
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1;
-        const float p = exp2f(fmaf(s[j][e], sc, r ? -ms1 : -ms0));     // exp2(-inf) = 0 for masked keys
+        const float p = fast_exp2(fmaf(s[j][e], sc, r ? -ms1 : -ms0));     // exp2(-inf) = 0 for masked keys
         s[j][e] = p;
         l[r] += p;
       }
@@ -474,14 +482,14 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
         const float m_new = fmaxf(m[c], mx[c]);
-        corr[c] = (m_new == -INFINITY) ? 1.f : exp2f((m[c] - m_new) * sc);
+        corr[c] = (m_new == -INFINITY) ? 1.f : fast_exp2((m[c] - m_new) * sc);
         m[c] = m_new;
       }
       float pv[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int c = e & 1;
-        pv[e] = (m[c] == -INFINITY) ? 0.f : exp2f((sv[e] - m[c]) * sc);
+        pv[e] = (m[c] == -INFINITY) ? 0.f : fast_exp2((sv[e] - m[c]) * sc);
       }
       l[0] = l[0] * corr[0] + pv[0] + pv[2];
       l[1] = l[1] * corr[1] + pv[1] + pv[3];
@@ -542,7 +550,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
       float L = 0.f, scw[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        scw[w] = (mw[w] == -INFINITY) ? 0.f : exp2f((mw[w] - M) * sc);
+        scw[w] = (mw[w] == -INFINITY) ? 0.f : fast_exp2((mw[w] - M) * sc);
         L += scw[w] * merge[(w * GH + row) * (hd + 2) + hd + 1];
       }
       const int head = kvh * G + g0 + row;

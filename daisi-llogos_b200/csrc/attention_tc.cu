@@ -28,6 +28,14 @@ constexpr int TK = 64;       // keys per tile = one cache page
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 constexpr float LOG2E = 1.4426950408889634f;
 
+// 2^x by the special-function unit alone (float32, about 2 ulp, denormal results flushed to zero);
+// exp2f() adds range handling that the softmax does not need: its arguments are <= 0 or -inf.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ int g_error = 0;  // 0 ok; 1 score wait, 2 output wait, 3 shared memory not aligned to 1024 bytes
 
 struct PrefillArgs {         // same layout as in attention_simt.cu
@@ -305,7 +313,7 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(PrefillArgs a) {
 #pragma unroll
     for (int c = 0; c < TK; ++c) mx = fmaxf(mx, sv[c]);
     const float m_new = fmaxf(m_run, mx);
-    const float corr = (m_new == -INFINITY) ? 1.f : exp2f((m_run - m_new) * sc);
+    const float corr = (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * sc);
     const float ms = (m_new == -INFINITY) ? 0.f : m_new * sc;
     m_run = m_new;
     float psum = 0.f;
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(PrefillArgs a) {
       float p[8];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        p[e] = exp2f(fmaf(sv[c8 * 8 + e], sc, -ms));
+        p[e] = fast_exp2(fmaf(sv[c8 * 8 + e], sc, -ms));
         psum += p[e];
       }
       uint4 v;

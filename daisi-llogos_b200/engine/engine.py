@@ -58,6 +58,19 @@ class _Staging:
             self.events[self.i] = ev
 
 
+_BUCKETS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024)
+
+
+def decode_bucket(b: int) -> int:
+    """Batch size a decode step of ``b`` sequences runs at: the next of a short list of sizes (at most a
+    third more rows), so that a batch that shrinks as sequences end reuses a few CUDA graphs instead of
+    recording one per size.  The extra rows are parked on the cache's padding slot."""
+    for x in _BUCKETS:
+        if x >= b:
+            return x
+    return -(-b // 256) * 256
+
+
 class _DecodeState:
     """Static buffers (and later the CUDA graph) of decode steps of one batch size."""
 
@@ -236,15 +249,19 @@ class Engine:
         return self.model.forward(ctx, self.cache, rows_dev)
 
     # ---- decode step -----------------------------------------------------------------------
-    def _decode_step(self, b, slots, toks, len_before, updates, want) -> torch.Tensor:
+    def _decode_step(self, n_real, slots, toks, len_before, updates, want) -> torch.Tensor:
+        b = decode_bucket(n_real) if self.use_graphs else n_real
         st = self._decode.get(b)
         if st is None:
             st = self._decode[b] = _DecodeState(b, self.device)
-        token_ids = np.concatenate(toks).astype(np.int32)
+        pad = b - n_real
+        token_ids = np.concatenate(toks + [np.zeros(pad, dtype=np.int64)]).astype(np.int32)
         ar = np.arange(b, dtype=np.int32)
-        lb = np.asarray(len_before, dtype=np.int32)
+        # padding rows: token 0 at position 0 of the padding slot (its one page is never anyone else's)
+        lb = np.asarray(list(len_before) + [0] * pad, dtype=np.int32)
+        all_slots = np.asarray(list(slots) + [self.cache.pad_slot] * pad, dtype=np.int32)
         # layout: token_ids | positions | seq_of_token | slots | cu_tokens (b + 1) | len_before
-        host = [token_ids, lb, ar, np.asarray(slots, dtype=np.int32), np.arange(b + 1, dtype=np.int32), lb]
+        host = [token_ids, lb, ar, all_slots, np.arange(b + 1, dtype=np.int32), lb]
         fixed = 6 * b + 1
         plan = self._apply_updates(updates, host)
         block = np.concatenate(host)
@@ -284,9 +301,9 @@ class Engine:
             else:
                 logits = self.model.forward(ctx, self.cache, st.rows)
                 st.eager_runs += 1
-        flat_want = [(i, int(w)) for i in range(b) for w in want[i]]
-        if len(flat_want) == b and all(i == j for j, (i, _) in enumerate(flat_want)):
-            return logits
+        flat_want = [(i, int(w)) for i in range(n_real) for w in want[i]]
+        if len(flat_want) == n_real and all(i == j for j, (i, _) in enumerate(flat_want)):
+            return logits[:n_real]
         if not flat_want:
             return logits[:0]
         idx = torch.tensor([i for i, _ in flat_want], dtype=torch.long, device=self.device)

@@ -62,7 +62,9 @@ def test_groups_by_need(C, P):
     ring = [g for g in c.kv_groups if g.window == 100][0]
     assert full.units == [0, 2] and ring.units == [1]
     assert full.ring_pages == 6 and ring.ring_pages == 3          # ceil(100 / 64) + 1
-    assert full.k[0].shape == (10, 2, 64, 16) and ring.page_table.shape == (4, 3)
+    # one page and one table row more than sequences can get: the padding slot's
+    assert full.k[0].shape == (11, 2, 64, 16) and ring.page_table.shape == (5, 3)
+    assert c.pad_slot == 4 and ring.page_table[4].tolist() == [10, 10, 10]
     assert c.view(1).window == 100 and c.view(0).ring_pages == 6
 
 
@@ -107,7 +109,7 @@ def test_state_is_zeroed_for_a_new_sequence(C, P):
     c = make(C, P, extra_state=True)
     s = c.acquire()
     v = c.view(3)
-    assert v.state.shape == (4, 3, 5)
+    assert v.state.shape == (5, 3, 5)
     v.state[s] += 7
     c.release(s)
     s2 = c.acquire()

@@ -201,3 +201,37 @@ def test_a_far_key_among_hundreds(llogos, tmp_path, dtype):
     lg = eng.step([(s, [toks[-1]])])
     ok, err = close(lg[0], ref[-1], dtype, float(ref.abs().max()))
     assert ok, ("decode", err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_padded_decode_batches_change_nothing(llogos, model_dirs, dtype):
+    """Decode steps run at a few fixed batch sizes (CUDA graphs); a batch of 5 or 7 is filled up with
+    rows on the cache's padding slot.  The real rows must come out as without padding, and the padding
+    must leave no trace in the cache's books."""
+    name = "qwen3"
+    cfg = TINY[name]
+    w = read_weights(llogos, model_dirs[name])
+    seqs = random_tokens(cfg["vocab_size"], [30, 41, 52, 63, 74, 85, 96], 17)
+    refs = [P.forward(w, cfg, s) for s in seqs]
+    model = llogos.weights.load_model(model_dirs[name], dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 16, n_slots=8)
+    eng_mod = __import__("importlib").import_module("daisi-llogos_b200.engine.engine")
+    assert [eng_mod.decode_bucket(b) for b in (1, 2, 3, 5, 7, 9, 65)] == [1, 2, 3, 6, 8, 12, 96]
+    slots = [eng.open() for _ in seqs]
+    cut = [len(s) - 12 for s in seqs]
+    eng.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)], [[] for _ in seqs])
+    live = list(range(7))
+    for j in range(12):
+        if j == 4:
+            live = [0, 2, 3, 5, 6]              # 7 -> 5 rows (runs as 6)
+            eng.close(slots[1])
+            eng.close(slots[4])
+        lg = eng.step([(slots[i], [seqs[i][cut[i] + j]]) for i in live])
+        assert lg.shape[0] == len(live)
+        for k, i in enumerate(live):
+            ok, err = close(lg[k], refs[i][cut[i] + j], dtype, float(refs[i].abs().max()))
+            assert ok, (j, i, err)
+    for i in live:
+        eng.close(slots[i])
+    eng.cache.audit()
+    assert eng.cache.slots.free_count == 8
