@@ -343,9 +343,13 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
   return y;
 }
 
+// `counters` ([n_seqs][nkv] ints, zero before the first launch) let the block that finishes last for a
+// (sequence, key/value head) join the partials of all splits and write `out`; it leaves the counter at
+// zero again.  No second kernel is needed.
 template <int HDMAX, bool EXACT>
-__global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16* __restrict__ out, int* __restrict__ counters) {
   extern __shared__ __align__(16) unsigned char smraw[];
+  __shared__ int is_last;
   pdl_launch_dependents();
   // Lengths, slots and page tables were written before this step's first kernel started.  The
   // kernel just before this one writes only the newest position (in the sequence's last page) and
@@ -569,6 +573,67 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a) {
       }
     }
   }
+  // ---- the last block of this (sequence, key/value head) joins the splits ---------------------------
+  __threadfence();                     // this block's partials are visible to the whole device ...
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(&counters[b * a.nkv + kvh], 1);   // ... before its ticket is
+    is_last = ticket == a.n_splits - 1;
+    if (is_last) counters[b * a.nkv + kvh] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // one warp per head; the splits' weights exp(m_s - M) are worked out by the lanes side by side and kept
+  // in shared memory (64 at a time), then every lane sums its head dimensions over the splits with
+  // independent loads
+  float* wsm = reinterpret_cast<float*>(smraw) + warp * 64;
+  for (int head = kvh * G + warp; head < (kvh + 1) * G; head += 4) {
+    const long long base = ((long long)b * a.nh + head) * a.n_splits;
+    float M = -INFINITY;
+    for (int s = lane; s < a.n_splits; s += 32) M = fmaxf(M, __ldcg(&a.part_ml[(base + s) * 2]));
+    M = warp_max(M);
+    float L = 0.f;
+    for (int s = lane; s < a.n_splits; s += 32) {
+      const float ms = __ldcg(&a.part_ml[(base + s) * 2]);
+      if (ms != -INFINITY) L += expf(ms - M) * __ldcg(&a.part_ml[(base + s) * 2 + 1]);
+    }
+    L = warp_sum(L);
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    float oacc[HDMAX / 32];
+#pragma unroll
+    for (int dd = 0; dd < HDMAX / 32; ++dd) oacc[dd] = 0.f;
+    for (int s0 = 0; s0 < a.n_splits; s0 += 64) {
+      const int ns = min(64, a.n_splits - s0);
+      __syncwarp();
+      for (int s = lane; s < ns; s += 32) {
+        const float ms = __ldcg(&a.part_ml[(base + s0 + s) * 2]);
+        wsm[s] = (ms == -INFINITY) ? 0.f : expf(ms - M);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int dd = 0; dd < HDMAX / 32; ++dd) {
+        const int d = lane + 32 * dd;
+        if (d < hd) {
+          const float* po = a.part_o + (base + s0) * hd + d;
+          float o = 0.f;
+          int s = 0;
+          for (; s + 4 <= ns; s += 4) {
+            const float p0 = __ldcg(po + (long long)(s + 0) * hd), p1 = __ldcg(po + (long long)(s + 1) * hd);
+            const float p2 = __ldcg(po + (long long)(s + 2) * hd), p3 = __ldcg(po + (long long)(s + 3) * hd);
+            o += wsm[s] * p0 + wsm[s + 1] * p1 + wsm[s + 2] * p2 + wsm[s + 3] * p3;
+          }
+          for (; s < ns; ++s) o += wsm[s] * __ldcg(po + (long long)s * hd);
+          oacc[dd] += o;
+        }
+      }
+    }
+#pragma unroll
+    for (int dd = 0; dd < HDMAX / 32; ++dd) {
+      const int d = lane + 32 * dd;
+      if (d < hd) out[((long long)b * a.nh + head) * hd + d] = __float2bfloat16_rn(oacc[dd] * inv);
+    }
+  }
 }
 
 // joins the partials of the splits: out = sum_s exp(m_s - M) o_s / sum_s exp(m_s - M) l_s
@@ -631,13 +696,14 @@ LLG_API int llg_attn_prefill_mma(const PrefillArgs* args, cudaStream_t stream) {
   return llg_check_launch("attn_prefill_mma");
 }
 
-LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, cudaStream_t stream) {
+LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, int* counters, cudaStream_t stream) {
   const DecodeArgs& a = *args;
   LLG_REQUIRE(llg_attn_mma_supported(a.hd), "attn_decode_mma: head_dim %d is not a multiple of 16 up to 128", a.hd);
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_decode_mma: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
   LLG_REQUIRE(a.n_splits >= 1 && a.n_splits <= 65535 && a.nkv <= 65535 && a.n_seqs <= 65535, "attn_decode_mma: grid too large");
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_decode_mma: bad cache geometry");
+  LLG_REQUIRE(counters != nullptr, "attn_decode_mma: needs n_seqs * nkv zeroed counters");
   if (a.n_seqs <= 0) return 0;
   size_t smem = (size_t)2 * DSTAGES * 64 * (a.hd * 2 + 16);
   const size_t merge = (size_t)4 * GH * (a.hd + 2) * sizeof(float);
@@ -646,14 +712,12 @@ LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, cudaStream_t 
 #define GO(HDM, EX)                                                                       \
   do {                                                                                    \
     if (set_smem(attn_decode_mma_kernel<HDM, EX>, smem, "attn_decode_mma")) return 1;       \
-    llg_launch(attn_decode_mma_kernel<HDM, EX>, grid, dim3(128), smem, stream, a);          \
+    llg_launch(attn_decode_mma_kernel<HDM, EX>, grid, dim3(128), smem, stream, a, (bf16*)out, counters);  \
   } while (0)
   if (a.hd == 64) GO(64, true);
   else if (a.hd == 128) GO(128, true);
   else if (a.hd < 64) GO(64, false);
   else GO(128, false);
 #undef GO
-  llg_launch(attn_decode_reduce_kernel, dim3(a.nh, a.n_seqs), dim3(64), 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (bf16*)out,
-             a.nh, a.hd, a.n_splits);
   return llg_check_launch("attn_decode_mma");
 }

@@ -536,25 +536,28 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   const long long nt = (n + tile_n - 1) / tile_n;
   const long long t1 = (long long)((o + BM - 1) / BM) * nt, t2 = (long long)((o + 2 * BM - 1) / (2 * BM)) * nt;
   const bool wide = !gated && tile_n >= 128 && ((t2 + 147) / 148) * 2 * 0.85 < (double)((t1 + 147) / 148);
-#define GO(TN, ST1, ST2)                                                                              \
+#define GATED(TN, ST2)                                                                               \
   if (gated)                                                                                          \
     return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 1, 0>(mw, mx, p, splits, stream)            \
-                                : launch<TN, ST2, __nv_bfloat16, 2, 1, 0>(mw, mx, p, splits, stream);   \
-  else if (wide)                                                                                      \
+                                : launch<TN, ST2, __nv_bfloat16, 2, 1, 0>(mw, mx, p, splits, stream)
+#define PLAIN(TN, ST1)                                                                               \
+  return out_dtype == LLG_F32 ? launch<TN, ST1, float, 1, 0, 0>(mw, mx, p, splits, stream)              \
+                              : launch<TN, ST1, __nv_bfloat16, 1, 0, 0>(mw, mx, p, splits, stream)
+#define WIDE(TN, ST2)                                                                                \
+  if (wide)                                                                                           \
     return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 0, 0>(mw, mx, p, splits, stream)            \
-                                : launch<TN, ST2, __nv_bfloat16, 2, 0, 0>(mw, mx, p, splits, stream);   \
-  else                                                                                                \
-    return out_dtype == LLG_F32 ? launch<TN, ST1, float, 1, 0, 0>(mw, mx, p, splits, stream)            \
-                                : launch<TN, ST1, __nv_bfloat16, 1, 0, 0>(mw, mx, p, splits, stream)
+                                : launch<TN, ST2, __nv_bfloat16, 2, 0, 0>(mw, mx, p, splits, stream)
   switch (tile_n) {
-    case 16: GO(16, 5, 5);
-    case 32: GO(32, 5, 5);
-    case 64: GO(64, 4, 4);
-    case 128: GO(128, 6, 4);
-    case 256: GO(256, 4, 3);
+    case 16: GATED(16, 5); PLAIN(16, 5);
+    case 32: GATED(32, 5); PLAIN(32, 5);
+    case 64: GATED(64, 4); PLAIN(64, 4);
+    case 128: GATED(128, 4); WIDE(128, 4); PLAIN(128, 6);
+    case 256: GATED(256, 3); WIDE(256, 3); PLAIN(256, 4);
     default: return llg_fail("gemm_tc: tile_n %d is not one of 16, 32, 64, 128, 256", tile_n);
   }
-#undef GO
+#undef GATED
+#undef PLAIN
+#undef WIDE
 }
 
 // Error code that a block recorded when one of its waits ran out (0 = none); clears it.  Synchronises the device.

@@ -23,7 +23,8 @@ class Workspace:
         self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self.frozen = False   # set while a CUDA graph that uses these buffers exists
 
-    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """``zero``: the buffer is zero when it is first handed out (and whenever it had to grow)."""
         n = 1
         for s in shape:
             n *= int(s)
@@ -32,7 +33,7 @@ class Workspace:
         if flat is None or flat.numel() < n:
             if self.frozen:
                 raise RuntimeError(f"workspace buffer '{name}' would have to grow after graph capture")
-            flat = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            flat = (torch.zeros if zero else torch.empty)(max(n, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
         return flat[:n].view(shape)
 
@@ -62,5 +63,5 @@ class StepContext:
     max_len_after: int = 0            # host upper bound of len_before + count over the batch
     extras: Dict[str, Any] = field(default_factory=dict)
 
-    def buffer(self, name: str, shape, dtype=None) -> torch.Tensor:
-        return self.workspace.get(name, tuple(shape), dtype or self.dtype)
+    def buffer(self, name: str, shape, dtype=None, zero: bool = False) -> torch.Tensor:
+        return self.workspace.get(name, tuple(shape), dtype or self.dtype, zero)

@@ -152,7 +152,7 @@ def _lib(name: str):
     elif name == "attention_mma":
         lib.llg_attn_mma_supported.argtypes = [c_int]
         lib.llg_attn_prefill_mma.argtypes = [POINTER(_PrefillArgs), c_void_p]
-        lib.llg_attn_decode_mma.argtypes = [POINTER(_DecodeArgs), c_void_p, c_void_p]
+        lib.llg_attn_decode_mma.argtypes = [POINTER(_DecodeArgs), c_void_p, c_void_p, c_void_p]
     elif name == "attention_tc":
         lib.llg_attn_tc_supported.argtypes = [c_int]
         lib.llg_attn_prefill_tc.argtypes = [POINTER(_PrefillArgs), c_void_p]
@@ -407,9 +407,17 @@ def attn_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_split
     return n_seqs * n_heads * n_splits * (head_dim + 2)
 
 
+def attn_decode_uses_counters(dtype: torch.dtype, head_dim: int) -> bool:
+    """Whether ``attn_decode`` wants ``counters`` (the tensor-core kernel joins its splits itself)."""
+    return _use_mma(dtype, head_dim)
+
+
 def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
-                n_splits: int, scale: float, window: int) -> None:
-    """Attention of one new token per sequence over the cache; ``scratch`` holds the split partials."""
+                n_splits: int, scale: float, window: int, counters: Optional[torch.Tensor] = None) -> None:
+    """Attention of one new token per sequence over the cache; ``scratch`` holds the split partials.
+
+    The tensor-core kernel also needs ``counters``: ``n_seqs * n_kv_heads`` int32, zero when first used
+    (the kernel leaves them zero), through which the last block of a sequence joins the splits."""
     b, nh, hd = q.shape
     nkv = k_pages.shape[1]
     if scale <= 0:
@@ -429,7 +437,9 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
     a.n_seqs, a.nh, a.nkv, a.hd, a.n_splits = b, nh, nkv, hd, n_splits
     a.scale, a.window = float(scale), int(window)
     if mma:
-        _check(lib, lib.llg_attn_decode_mma(byref(a), _ptr(out, q.dtype), _stream()), kernels=2)
+        if counters is None or counters.numel() < b * nkv:
+            raise KernelError(f"attn_decode: needs {b * nkv} zeroed int32 counters")
+        _check(lib, lib.llg_attn_decode_mma(byref(a), _ptr(out, q.dtype), _ptr(counters, torch.int32), _stream()))
     else:
         _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()), kernels=2)
 

@@ -123,8 +123,12 @@ class Attention(Mixer):
             splits = decode_splits(ctx.n_seqs, self.nkv, ctx.max_len_after)
             scratch = ctx.buffer("attn.scratch", (ops.attn_decode_scratch_floats(n, self.nh, self.hd, splits),),
                                  torch.float32)
+            counters = None
+            if ops.attn_decode_uses_counters(q.dtype, self.hd):
+                counters = ctx.buffer("attn.counters", (n * self.nkv,), torch.int32, zero=True)
             ops.attn_decode(q, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages, ctx.slots,
-                            ctx.len_before, out, scratch, n_splits=splits, scale=self.scale, window=self.window)
+                            ctx.len_before, out, scratch, n_splits=splits, scale=self.scale, window=self.window,
+                            counters=counters)
         else:
             # A group that keeps every key can take the step's keys and values into its pages right away
             # (the step reads them from the packed buffer, never from the pages).  A ring must wait until

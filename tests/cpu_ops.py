@@ -166,8 +166,12 @@ def attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits):
     return n_seqs * n_heads * n_splits * (head_dim + 2)
 
 
+def attn_decode_uses_counters(dtype, head_dim):
+    return False
+
+
 def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *, n_splits,
-                scale, window):
+                scale, window, counters=None):
     b_n, nh, hd = q.shape
     nkv = k_pages.shape[1]
     g = nh // nkv

@@ -121,3 +121,53 @@ def test_padding_free_layout(llogos, setup):
     assert seen["n"] == 27
     eng.step([(s1, [1]), (s3, [3])])
     assert seen["n"] == 2
+
+
+@pytest.mark.parametrize("name", ["qwen3", "qwen2"])
+def test_random_cuts_and_batches(llogos, setup, name):
+    """Requests cut into steps at random (several tokens, one token, mixed in one step), joined in
+    random batches, closed at random: every wanted logit equals the whole-sequence reference."""
+    import random
+    rng = random.Random(7)
+    model, w = setup[name]
+    cfg = TINY[name]
+    eng = engine_for(llogos, model, max_tokens=64 * 10, n_slots=4)
+    seqs = random_tokens(cfg["vocab_size"], [9, 70, 33, 140, 65, 128, 20, 5], 9)
+    refs = [P.forward(w, cfg, s) for s in seqs]
+    waiting = list(range(len(seqs)))
+    live = {}                                   # request -> (slot, tokens done)
+    while waiting or live:
+        while waiting and eng.cache.slots.free_count and rng.random() < 0.7:
+            i = waiting.pop(0)
+            live[i] = [eng.open(), 0]
+        if not live:
+            continue
+        batch = rng.sample(sorted(live), rng.randint(1, len(live)))
+        entries, want, expect = [], [], []
+        for i in batch:
+            slot, done = live[i]
+            left = len(seqs[i]) - done
+            take = min(left, rng.choice([1, 1, 1, 2, 7, 40, 64, 200]))
+            ws = sorted(rng.sample(range(take), rng.randint(0, min(take, 3))))
+            entries.append((slot, seqs[i][done:done + take]))
+            want.append(ws)
+            expect += [(i, done + x) for x in ws]
+            live[i][1] = done + take
+        try:
+            lg = eng.step(entries, want)
+        except llogos.engine.StepError as e:
+            assert "cache full" in str(e)           # too many long requests alive at once: end one and go on
+            for i in batch:
+                live[i][1] -= len(entries[batch.index(i)][1])
+            victim = max(live, key=lambda i: live[i][1])
+            eng.close(live.pop(victim)[0])
+            waiting.append(victim)
+            continue
+        assert lg.shape[0] == len(expect)
+        for row, (i, pos) in enumerate(expect):
+            assert float((lg[row].double() - refs[i][pos]).abs().max()) < 2e-4, (i, pos)
+        for i in batch:
+            if live[i][1] == len(seqs[i]):
+                eng.close(live.pop(i)[0])
+        eng.cache.audit()
+    assert eng.cache.slots.free_count == 4

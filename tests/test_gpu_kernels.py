@@ -231,7 +231,8 @@ def test_attn_decode(ops, dtype, nh, nkv, hd, window):
         scratch = torch.empty(ops.attn_decode_scratch_floats(len(lens), nh, hd, splits), device=DEV)
         lb = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
         ops.attn_decode(q.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV), ring, slots.to(DEV), lb.to(DEV), out,
-                        scratch, n_splits=splits, scale=scale, window=window)
+                        scratch, n_splits=splits, scale=scale, window=window,
+                        counters=torch.zeros(len(lens) * nkv, dtype=torch.int32, device=DEV))
         for b, n in enumerate(lens):
             qq = torch.zeros(n, nh, hd, dtype=dtype)
             qq[-1] = q[b]

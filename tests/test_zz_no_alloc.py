@@ -57,7 +57,8 @@ def test_matches_the_ordinary_entry_point_twice_in_a_row(dtype):
         scale = 1 / math.sqrt(hd)
         want = torch.empty(len(lens), nh * hd, dtype=dtype, device=DEV)
         scratch = torch.empty(ops.attn_decode_scratch_floats(len(lens), nh, hd, splits), device=DEV)
-        ops.attn_decode(q, kp, vp, table, table.shape[1], slots, lb, want, scratch, n_splits=splits, scale=scale, window=window)
+        ops.attn_decode(q, kp, vp, table, table.shape[1], slots, lb, want, scratch, n_splits=splits, scale=scale, window=window,
+                        counters=torch.zeros(len(lens) * nkv, dtype=torch.int32, device=DEV))
         got = torch.full_like(want, float("nan"))
         rc = fn(q.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), table.shape[1], table.shape[1],
                 slots.data_ptr(), lb.data_ptr(), got.data_ptr(), code, len(lens), nh, nkv, hd, splits, scale, window,
