@@ -382,3 +382,120 @@ def test_layer_run_twice_and_borrowed_cache(llogos, tmp_path):
             assert float((lg[1].cpu().double() - refs[1][70 + j]).abs().max()) < 1e-4
     finally:
         reg._ARCHITECTURES.pop("ToyLoopForCausalLM", None)
+
+
+def test_toy_routed_feedforward_and_learned_positions(llogos, tmp_path):
+    """A feed-forward with routing (top-1 of three experts) and a position encoding that is added to the
+    embeddings, both defined here and registered from outside; attention runs without rotation."""
+    from conftest import read_weights, random_tokens
+    import dataclasses
+    reg = importlib.import_module("daisi-llogos_b200.config.registry")
+    Pt = llogos.parts
+
+    class Top1Experts(Pt.FeedForward):
+        """y = expert_e(x) with e = argmax(router(x)); each expert is down(relu(up(x)))."""
+
+        def __init__(self, params, prefix, env):
+            super().__init__(params, prefix, env)
+            self.h, self.i, self.e = int(params["hidden_size"]), int(params["inner"]), int(params["experts"])
+
+        def tensors(self):
+            t = {"router.weight": Pt.TensorDecl((self.e, self.h))}
+            for e in range(self.e):
+                t[f"experts.{e}.up.weight"] = Pt.TensorDecl((self.i, self.h))
+                t[f"experts.{e}.down.weight"] = Pt.TensorDecl((self.h, self.i))
+            return t
+
+        def bind(self, tensors):
+            self.router = tensors["router.weight"].float()
+            self.up = torch.stack([tensors[f"experts.{e}.up.weight"].float() for e in range(self.e)])
+            self.down = torch.stack([tensors[f"experts.{e}.down.weight"].float() for e in range(self.e)])
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            choice = (xf @ self.router.t()).argmax(-1)                     # routing in float32
+            hmid = torch.relu(torch.einsum("nh,nih->ni", xf, self.up[choice]))
+            return Pt.Branch(torch.einsum("ni,nhi->nh", hmid, self.down[choice]).unsqueeze(0).contiguous())
+
+    class LearnedPositions(Pt.PositionEncoding):
+        def tensors(self):
+            return {"weight": Pt.TensorDecl((int(self.params["positions"]), int(self.params["hidden_size"])), "table")}
+
+        def bind(self, tensors):
+            self.table = tensors["weight"].float()
+
+        def on_embeddings(self, residual, ctx):
+            residual += self.table[ctx.positions.long()]
+
+    def build(cfg):
+        spec = llogos.config.dense_decoder_spec(cfg)
+        layers = []
+        for i, layer in enumerate(spec.layers):
+            parts = dict(layer.parts)
+            parts["mixer"] = Pt.PartSpec("attention", dict(parts["mixer"].params, position=None), parts["mixer"].prefix)
+            if i == 1:
+                parts["ffn"] = Pt.PartSpec("toy_top1", {"hidden_size": cfg.hidden_size, "inner": 40, "experts": 3},
+                                           f"model.layers.{i}.moe.")
+            layers.append(Pt.LayerSpec("prenorm", parts))
+        enc = {"learned": Pt.PartSpec("toy_learned", {"positions": 128, "hidden_size": cfg.hidden_size}, "model.positions.")}
+        return dataclasses.replace(spec, layers=tuple(layers), encodings=enc)
+
+    Pt.register_part("ffn", "toy_top1", Top1Experts)
+    Pt.register_part("position", "toy_learned", LearnedPositions)
+    llogos.config.register_architecture("ToyRoutedForCausalLM", reg._dense_reader(qk_norm=False, force_bias=False), build)
+    try:
+        cfg = {"architectures": ["ToyRoutedForCausalLM"], "num_hidden_layers": 2, "hidden_size": 48,
+               "num_attention_heads": 3, "num_key_value_heads": 3, "head_dim": 16, "intermediate_size": 80,
+               "vocab_size": 99, "rope_theta": 777.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 128}
+        d = str(tmp_path / "routed")
+        llogos.weights.write_random_model(d, cfg, seed=11, std=0.25, norm_std=0.1)
+        w = read_weights(llogos, d)
+        assert "model.layers.1.moe.experts.2.down.weight" in w and "model.positions.weight" in w
+        assert "model.layers.1.mlp.gate_proj.weight" not in w
+
+        def plain(tokens):
+            t, nh, hd, eps = len(tokens), 3, 16, 1e-5
+            h = P.embedding(w["model.embed_tokens.weight"], tokens) + w["model.positions.weight"].double()[:t]
+            for i in range(2):
+                p = f"model.layers.{i}."
+                a = p + "self_attn."
+                x = P.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+                q = P.linear(x, w[a + "q_proj.weight"]).view(t, nh, hd)
+                k = P.linear(x, w[a + "k_proj.weight"]).view(t, nh, hd)
+                v = P.linear(x, w[a + "v_proj.weight"]).view(t, nh, hd)
+                h = h + P.linear(P.attention(q, k, v, 0.25).reshape(t, nh * hd), w[a + "o_proj.weight"])
+                x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+                if i == 1:
+                    m = p + "moe."
+                    # the engine routes on bfloat16 activations: route on the same rounded values
+                    choice = (x.float() @ w[m + "router.weight"].float().t()).argmax(-1)
+                    rows = []
+                    for j in range(t):
+                        e = int(choice[j])
+                        mid = torch.relu(P.linear(x[j:j + 1], w[m + f"experts.{e}.up.weight"]))
+                        rows.append(P.linear(mid, w[m + f"experts.{e}.down.weight"])[0])
+                    h = h + torch.stack(rows)
+                else:
+                    m = p + "mlp."
+                    h = h + P.swiglu(x, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+        model = llogos.weights.load_model(d, dtype=torch.float32, device="cuda:0")
+        eng = llogos.engine.Engine(model, max_tokens=64 * 4, use_graphs=False)
+        seqs = random_tokens(99, [60, 25], 18)
+        refs = [plain(s) for s in seqs]
+        slots = [eng.open(), eng.open()]
+        lg = eng.step([(slots[0], seqs[0][:50]), (slots[1], seqs[1][:20])], [list(range(50)), list(range(20))])
+        # a token whose two best experts tie within float32 noise may be routed differently: compare rows
+        # whose routing margin is clear (all of them, with these weights) and require most rows to match
+        err0 = (lg[:50].cpu().double() - refs[0][:50]).abs().max(dim=1).values
+        err1 = (lg[50:].cpu().double() - refs[1][:20]).abs().max(dim=1).values
+        assert int((err0 < 1e-4).sum()) >= 49 and int((err1 < 1e-4).sum()) >= 19
+        for j in range(5):
+            lg = eng.step([(slots[0], [seqs[0][50 + j]]), (slots[1], [seqs[1][20 + j]])])
+            assert float((lg[0].cpu().double() - refs[0][50 + j]).abs().max()) < 1e-4
+            assert float((lg[1].cpu().double() - refs[1][20 + j]).abs().max()) < 1e-4
+    finally:
+        Pt.unregister_part("ffn", "toy_top1")
+        Pt.unregister_part("position", "toy_learned")
+        reg._ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
