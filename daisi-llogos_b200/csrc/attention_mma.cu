@@ -636,31 +636,6 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
   }
 }
 
-// joins the partials of the splits: out = sum_s exp(m_s - M) o_s / sum_s exp(m_s - M) l_s
-__global__ void attn_decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                          bf16* __restrict__ out, int nh, int hd, int n_splits) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int h = blockIdx.x, b = blockIdx.y;
-  const long long base = ((long long)b * nh + h) * n_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = part_ml[(base + s) * 2];
-    if (ms != -INFINITY) L += expf(ms - M) * part_ml[(base + s) * 2 + 1];
-  }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float o = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = part_ml[(base + s) * 2];
-      if (ms != -INFINITY) o += expf(ms - M) * part_o[(base + s) * hd + d];
-    }
-    out[((long long)b * nh + h) * hd + d] = __float2bfloat16_rn(o * inv);
-  }
-}
-
 template <typename K>
 int set_smem(K kernel, size_t smem, const char* what) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

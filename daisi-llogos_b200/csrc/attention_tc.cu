@@ -1,6 +1,7 @@
 // Causal attention for prompt steps on the 5th-generation tensor cores (tcgen05), bfloat16, head
-// sizes 64 and 128.  One block of 128 threads owns 128 queries of one head; thread r owns query row
-// r, which is lane r of tensor memory, so the softmax of a row needs no exchange between threads:
+// sizes 64 and 128.  One block owns 128 queries of one head; thread r of its first four warps owns
+// query row r, which is lane r of tensor memory, so the softmax of a row needs no exchange between
+// threads; one elected lane of the first warp issues the products:
 //
 //   per 64-key tile (one cache page):   S = Q K^T      tcgen05.mma, accumulator S[128 x 64] in TMEM
 //                                       each thread reads its row of S (tcgen05.ld), masks, updates the
@@ -10,9 +11,11 @@
 // Q, K and P are K-major operands with the 128-byte swizzle; V is stored as it lies in memory
 // ([key][dim], dim contiguous), which makes it the MN-major second operand of the second product.
 // Key and value tiles are copied by all threads with cp.async (rows come from the step's packed
-// buffer or from cache pages, as in attn_prefill_simt), two stages deep.  When a row's maximum
-// grows, its accumulator row is rescaled in place (tcgen05.ld / tcgen05.st), warp by warp and only
-// when some row of the warp needs it.
+// buffer or from cache pages, as in attn_prefill_simt), two stages deep.  The
+// scores have two buffers in tensor memory, so that the tensor core computes the next tile's scores
+// and the previous tile's O += P V while the threads run the softmax of the current one.  A row's
+// accumulator is rescaled in place (tcgen05.ld / tcgen05.st) only when its maximum grows by more
+// than a factor of 2^8 in the weights, warp by warp and only when some row of the warp needs it.
 //
 // Every mbarrier wait is bounded; on expiry the block records an error (llg_attn_tc_status), stops
 // issuing work, waits for its copies in flight, frees its tensor memory and returns.
@@ -143,6 +146,17 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+// true in one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -152,31 +166,36 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
 template <int HD>
-__global__ void __launch_bounds__(128) attn_prefill_tc_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(PrefillArgs a) {
   constexpr int KB = HD / 64;                 // 64-wide blocks of the head dimension
   constexpr int Q_BYTES = KB * BQ * 128;      // [KB][128 rows][128 bytes]
   constexpr int KV_BYTES = KB * TK * 128;     // [KB][64 keys][128 bytes]
-  constexpr int TMEM_COLS = HD == 64 ? 128 : 256;   // S: 64 columns, O: HD columns
-  constexpr uint32_t S_COL = 0, O_COL = 64;
+  constexpr int KST = 2, VST = 2;             // stages of keys and of values
+  constexpr int TMEM_COLS = 256;              // S: 2 x 64 columns, O: HD columns
+  constexpr uint32_t S_COL = 0, O_COL = 128;
   // The tiles need 1024-byte alignment (swizzle); the declaration asks for it and the kernel checks it.
   // No slack is added: 112 KB + the barriers' kilobyte lets two blocks share an SM.
   extern __shared__ __align__(1024) unsigned char smem[];
   unsigned char* Qs = smem;
-  unsigned char* Ks = Qs + Q_BYTES;           // [2 stages]
-  unsigned char* Vs = Ks + 2 * KV_BYTES;      // [2 stages]
-  unsigned char* Ps = Vs + 2 * KV_BYTES;      // [128 rows][64 keys]
-  __shared__ uint64_t bar_s, bar_o;
+  unsigned char* Ks = Qs + Q_BYTES;           // [KST]
+  unsigned char* Vs = Ks + KST * KV_BYTES;    // [VST]
+  unsigned char* Ps = Vs + VST * KV_BYTES;
+  __shared__ uint64_t bar_s[2], bar_o;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool issue_warp = __shfl_sync(0xffffffffu, warp, 0) == 0;   // uniform over the warp
+  //               // first thread of the fifth warp: issues the products
+  const bool worker = tid < BQ;                 // thread r owns query row r
   if ((smem_u32(smem) & 1023u) != 0) {          // uniform over the block
     if (tid == 0) atomicCAS(&g_error, 0, 3);
     return;
   }
   if (tid == 0) {
-    mbar_init(&bar_s, 1);
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
     mbar_init(&bar_o, 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -191,7 +210,7 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(PrefillArgs a) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_base_slot;
-  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   volatile int* abortp = &abort_flag;
   pdl_wait();
 
@@ -214,156 +233,205 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(PrefillArgs a) {
   const bf16* kp = (const bf16*)a.k_pages;
   const bf16* vp = (const bf16*)a.v_pages;
   constexpr int CPR = HD / 8;                 // 16-byte chunks per row of the head
+  constexpr int RSTEP = 128 / CPR;            // rows that the block copies in one pass (a multiple of 8)
+  const int ch = tid % CPR, r0 = tid / CPR;
+  // chunk `ch` of row r0 + i * RSTEP lies i * RSTEP * 128 bytes after this offset (the swizzle depends on row % 8)
+  const uint32_t tile_off = (uint32_t)((ch >> 3) * (TK * 128)) + swz(r0, ch & 7);
 
-  // copies one 64-key tile of K and V: chunk c of the head goes to block c / 8, swizzled chunk c % 8
-  auto load_kv = [&](int tile, int stage) {
+  // Copies the 64 keys (or values) of key tile `tile` to `dst`.  A tile lies in one cache page, or in this
+  // step's packed rows, or (at most once per sequence) partly in each.
+  auto load_tile = [&](unsigned char* dst, int tile, const bf16* fresh_src, const bf16* page_src) {
     const int kt = k_begin + tile * TK;
-    unsigned char* kd = Ks + stage * KV_BYTES;
-    unsigned char* vd = Vs + stage * KV_BYTES;
-    const long long old_base = kt < lb ? kv_row(a.page_table, a.table_width, a.ring_pages, slot, kt, kvh, a.nkv) * HD : 0;
-    const long long new_base = ((long long)(tok0 + kt - lb) * a.nkv + kvh) * HD;
-    const long long new_step = (long long)a.nkv * HD;
-    constexpr int RSTEP = 128 / CPR;
-    const int ch = tid % CPR;
-    for (int row = tid / CPR; row < TK; row += RSTEP) {
-      const int pos = kt + row;
-      const bool valid = pos < k_end;
-      const bool fresh = pos >= lb;
-      const long long off = (fresh ? new_base + row * new_step : old_base + (long long)row * HD) + ch * 8;
-      const uint32_t so = (uint32_t)((ch >> 3) * (TK * 128)) + swz(row, ch & 7);
-      cp_async16(smem_u32(kd) + so, (fresh ? kn : kp) + (valid ? off : 0), valid);
-      cp_async16(smem_u32(vd) + so, (fresh ? vn : vp) + (valid ? off : 0), valid);
+    const uint32_t d0 = smem_u32(dst) + tile_off;
+    if (kt >= lb) {
+      const bf16* src = fresh_src + ((long long)(tok0 + kt - lb + r0) * a.nkv + kvh) * HD + ch * 8;
+      const long long step = (long long)RSTEP * a.nkv * HD;
+      if (kt + TK <= k_end) {
+#pragma unroll
+        for (int i = 0; i < TK / RSTEP; ++i) cp_async16(d0 + i * (RSTEP * 128), src + i * step, true);
+      } else {
+#pragma unroll
+        for (int i = 0; i < TK / RSTEP; ++i) {
+          const bool valid = kt + r0 + i * RSTEP < k_end;
+          cp_async16(d0 + i * (RSTEP * 128), valid ? src + i * step : fresh_src, valid);
+        }
+      }
+    } else if (kt + TK <= lb) {
+      const bf16* src = page_src + (kv_row(a.page_table, a.table_width, a.ring_pages, slot, kt, kvh, a.nkv) + r0) * HD + ch * 8;
+#pragma unroll
+      for (int i = 0; i < TK / RSTEP; ++i) cp_async16(d0 + i * (RSTEP * 128), src + i * (RSTEP * HD), true);
+    } else {
+      const long long old_base = kv_row(a.page_table, a.table_width, a.ring_pages, slot, kt, kvh, a.nkv) * HD;
+      const long long new_base = ((long long)(tok0 + kt - lb) * a.nkv + kvh) * HD;
+#pragma unroll
+      for (int i = 0; i < TK / RSTEP; ++i) {
+        const int row = r0 + i * RSTEP, pos = kt + row;
+        const bool valid = pos < k_end, fresh = pos >= lb;
+        const long long off = (fresh ? new_base + (long long)row * a.nkv * HD : old_base + (long long)row * HD) + ch * 8;
+        cp_async16(d0 + i * (RSTEP * 128), (fresh ? fresh_src : page_src) + (valid ? off : 0), valid);
+      }
     }
   };
 
-  // queries: row r of the tile, block c / 8 of the head
-  {
-    constexpr int RSTEP = 128 / CPR;
-    const int ch = tid % CPR;
-    for (int row = tid / CPR; row < BQ; row += RSTEP) {
+  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+  // scores of key tile t into score buffer t % 2 (one thread calls this)
+  auto issue_scores = [&](int t) {
+    const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + (t % KST) * KV_BYTES);
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+      const uint32_t blk = ks >> 2, kk = ks & 3;      // 64-wide block, 16-wide step inside it (32 bytes)
+      umma_bf16(tmem + S_COL + (uint32_t)(t & 1) * TK, desc_kmajor(qa + blk * (BQ * 128) + kk * 32),
+                desc_kmajor(ka + blk * (TK * 128) + kk * 32), IDESC_S, ks != 0);
+    }
+    umma_commit(&bar_s[t & 1]);
+  };
+
+  // Copies are committed in groups: {Q, K0}, {K1, V0}, then two groups per tile j: {K(j+2)} at its start and
+  // {V(j+1)} near its end.  Before the products of tile j are issued, all groups but the newest are complete.
+  if (worker) {
+    for (int row = r0; row < BQ; row += RSTEP) {
       const bool valid = row < nq;
       const bf16* src = qg + ((long long)(tok0 + q_off + (valid ? row : 0)) * a.nh + h) * HD + ch * 8;
       cp_async16(smem_u32(Qs) + (uint32_t)((ch >> 3) * (BQ * 128)) + swz(row, ch & 7), src, valid);
     }
+    load_tile(Ks, 0, kn, kp);
+    cp_async_commit();
+    if (n_tiles > 1) load_tile(Ks + KV_BYTES, 1, kn, kp);
+    load_tile(Vs, 0, vn, vp);
+    cp_async_commit();
+    cp_async_wait<1>();
+    fence_async_smem();
   }
-  load_kv(0, 0);
-  cp_async_commit();
+  __syncthreads();
+  if (issue_warp && elect_one()) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    issue_scores(0);
+  }
+  if (worker) {
+    cp_async_wait<0>();
+    fence_async_smem();
+  }
+  __syncthreads();
+  if (issue_warp && n_tiles > 1 && elect_one()) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    issue_scores(1);
+  }
 
-  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
-  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
   const float sc = a.scale * LOG2E;
+  // A row's exponentials use its maximum so far, which is raised only when a tile exceeds it by more than
+  // 2^RAISE in the exponent: the weights stay below 2^RAISE and the accumulator is rescaled rarely.  The
+  // common factor cancels in the final division.
+  const float raise_by = 8.0f / sc;
   const int qpos = pos0 + tid;                 // this thread's query position
   float m_run = -INFINITY, l_run = 0.f;
   bool ok = true;
 
-  for (int tile = 0; tile < n_tiles && ok; ++tile) {
-    const int stage = tile & 1;
-    // the other stage and P were last read by the second product of the previous tile
-    if (tile > 0) {
-      if (!mbar_wait(&bar_o, (tile - 1) & 1, abortp)) {
-        if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+  // Tile j: the scores S(j) were issued a tile earlier.  While the threads turn them into weights P(j), the
+  // tensor core runs O += P(j-1) V(j-1) and S(j+1); at the end of the tile one thread issues O += P(j) V(j)
+  // and S(j+2).
+  for (int j = 0; j < n_tiles; ++j) {
+    if (worker) {
+      if (!mbar_wait(&bar_s[j & 1], (j >> 1) & 1, abortp)) {
+        if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
       }
-    }
-    __syncthreads();
-    if (*abortp) { ok = false; break; }
-    if (tile + 1 < n_tiles) load_kv(tile + 1, stage ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();                        // this tile's (and, the first time, the queries') copies are done
-    fence_async_smem();
-    __syncthreads();
-    const int kt = k_begin + tile * TK;
-    if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + stage * KV_BYTES);
-#pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
-        const uint32_t blk = ks >> 2, kk = ks & 3;      // 64-wide block, 16-wide step inside it (32 bytes)
-        umma_bf16(tmem + S_COL, desc_kmajor(qa + blk * (BQ * 128) + kk * 32), desc_kmajor(ka + blk * (TK * 128) + kk * 32),
-                  IDESC_S, ks != 0);
-      }
-      umma_commit(&bar_s);
-    }
-    if (!mbar_wait(&bar_s, tile & 1, abortp)) {
-      if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
-    }
-    __syncthreads();
-    if (*abortp) { ok = false; break; }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int kt = k_begin + j * TK;
+      if (j + 2 < n_tiles) load_tile(Ks + (j % KST) * KV_BYTES, j + 2, kn, kp);   // S(j) has finished with this stage
+      cp_async_commit();
 
-    // this thread's row of scores: maximum, then exponentials straight into P
-    float sv[TK];
-#pragma unroll
-    for (int c0 = 0; c0 < TK; c0 += 16) {
-      uint32_t r[16];
-      tmem_ld16(lane_base + S_COL + c0, r);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < 16; ++c) sv[c0 + c] = __uint_as_float(r[c]);
-    }
-    const bool need_mask = (kt + TK - 1 > pos0 + warp * 32) || (a.window > 0 && kt <= pos0 + warp * 32 + 31 - a.window);
-    float mx = -INFINITY;
-    if (need_mask) {
-#pragma unroll
-      for (int c = 0; c < TK; ++c) {
-        const int key = kt + c;
-        const bool valid = key <= qpos && (a.window == 0 || key > qpos - a.window);
-        sv[c] = valid ? sv[c] : -INFINITY;
-      }
-    }
-#pragma unroll
-    for (int c = 0; c < TK; ++c) mx = fmaxf(mx, sv[c]);
-    const float m_new = fmaxf(m_run, mx);
-    const float corr = (m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * sc);
-    const float ms = (m_new == -INFINITY) ? 0.f : m_new * sc;
-    m_run = m_new;
-    float psum = 0.f;
-    unsigned char* prow = Ps;
-#pragma unroll
-    for (int c8 = 0; c8 < TK / 8; ++c8) {
-      float p[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        p[e] = fast_exp2(fmaf(sv[c8 * 8 + e], sc, -ms));
-        psum += p[e];
-      }
-      uint4 v;
-      v.x = pack_bf16(p[0], p[1]);
-      v.y = pack_bf16(p[2], p[3]);
-      v.z = pack_bf16(p[4], p[5]);
-      v.w = pack_bf16(p[6], p[7]);
-      *reinterpret_cast<uint4*>(prow + swz(tid, c8)) = v;
-    }
-    l_run = l_run * corr + psum;
-    // rescale the accumulator row when some row of this warp moved its maximum (never for the first tile:
-    // the first product overwrites the accumulator)
-    if (tile > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld16(lane_base + O_COL + c0, r);
+      // this thread's row of scores: maximum, then the weights P, kept in registers until P's buffer is free
+      float sv[TK];
+      {
+        uint32_t r0_[16], r1_[16], r2_[16], r3_[16];
+        const uint32_t sa = lane_base + S_COL + (uint32_t)(j & 1) * TK;
+        tmem_ld16(sa, r0_);
+        tmem_ld16(sa + 16, r1_);
+        tmem_ld16(sa + 32, r2_);
+        tmem_ld16(sa + 48, r3_);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-        for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
-        tmem_st16(lane_base + O_COL + c0, r);
+        for (int c = 0; c < 16; ++c) {
+          sv[c] = __uint_as_float(r0_[c]);
+          sv[16 + c] = __uint_as_float(r1_[c]);
+          sv[32 + c] = __uint_as_float(r2_[c]);
+          sv[48 + c] = __uint_as_float(r3_[c]);
+        }
       }
-      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      const bool need_mask = (kt + TK - 1 > pos0 + warp * 32) || (a.window > 0 && kt <= pos0 + warp * 32 + 31 - a.window);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < TK; ++c) {
+          const int key = kt + c;
+          const bool valid = key <= qpos && (a.window == 0 || key > qpos - a.window);
+          sv[c] = valid ? sv[c] : -INFINITY;
+        }
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < TK; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], sv[c]);
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const bool raise = mx > m_run + raise_by || m_run == -INFINITY;
+      const float m_new = raise ? fmaxf(m_run, mx) : m_run;
+      const float corr = (!raise || m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * sc);
+      const float ms = (m_new == -INFINITY) ? 0.f : m_new * sc;
+      m_run = m_new;
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[TK / 2];
+#pragma unroll
+      for (int c2 = 0; c2 < TK / 2; ++c2) {
+        const float p0 = fast_exp2(fmaf(sv[2 * c2], sc, -ms));
+        const float p1 = fast_exp2(fmaf(sv[2 * c2 + 1], sc, -ms));
+        ps4[(2 * c2) & 3] += p0;
+        ps4[(2 * c2 + 1) & 3] += p1;
+        pk[c2] = pack_bf16(p0, p1);
+      }
+      l_run = l_run * corr + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+
+      if (j > 0) {
+        // O += P(j-1) V(j-1) has finished: the accumulator may be rescaled, and V(j-1)'s stage reused
+        if (!mbar_wait(&bar_o, (j - 1) & 1, abortp)) {
+          if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(lane_base + O_COL + c0, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
+            tmem_st16(lane_base + O_COL + c0, r);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+      }
+#pragma unroll
+      for (int c8 = 0; c8 < TK / 8; ++c8)
+        *reinterpret_cast<uint4*>(Ps + swz(tid, c8)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
+      if (j + 1 < n_tiles) load_tile(Vs + ((j + 1) % VST) * KV_BYTES, j + 1, vn, vp);
+      cp_async_commit();
+      cp_async_wait<1>();                        // V(j) and K(j+2) have arrived
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      fence_async_smem();
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    fence_async_smem();
     __syncthreads();
-    if (tid == 0) {
+    if (*abortp) { ok = false; break; }
+    if (issue_warp && elect_one()) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs + stage * KV_BYTES);
+      const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs + (j % VST) * KV_BYTES);
 #pragma unroll
       for (int kk = 0; kk < TK / 16; ++kk) {
         // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-        umma_bf16(tmem + O_COL, desc_kmajor(pa + kk * 32), desc_mnmajor(va + kk * 2048, TK * 128), IDESC_O, (tile | kk) != 0);
+        umma_bf16(tmem + O_COL, desc_kmajor(pa + kk * 32), desc_mnmajor(va + kk * 2048, TK * 128), IDESC_O, (j | kk) != 0);
       }
       umma_commit(&bar_o);
+      if (j + 2 < n_tiles) issue_scores(j + 2);
     }
   }
 
-  if (ok && n_tiles > 0) {
+  if (ok && worker) {
     if (!mbar_wait(&bar_o, (n_tiles - 1) & 1, abortp)) {
       if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
     }
@@ -371,7 +439,7 @@ __global__ void __launch_bounds__(128) attn_prefill_tc_kernel(PrefillArgs a) {
   cp_async_wait<0>();
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (!*abortp) {
+  if (!*abortp && worker) {
     const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
     bf16* dst = (bf16*)a.out + ((long long)(tok0 + q_off + tid) * a.nh + h) * HD;
 #pragma unroll
@@ -408,6 +476,8 @@ int launch(const PrefillArgs& a, cudaStream_t stream) {
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return llg_fail("attn_prefill_tc: shared memory %d: %s", smem, cudaGetErrorString(e));
+    // two blocks share an SM only if the SM's memory is configured for the largest shared part
+    cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
   cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.n_tiles, a.nh), dim3(128), (size_t)smem, stream, a);

@@ -295,6 +295,49 @@ def test_attn_prefill_and_kv_write(ops, dtype, nh, nkv, hd, window, tc, monkeypa
         assert ops.attn_tc_status() == 0
 
 
+@pytest.mark.parametrize("tc", [True, False], ids=["tcgen05", "mma"])
+@pytest.mark.parametrize("shape", ["slow", "steps"])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attn_prefill_scores_that_rise_along_the_keys(ops, hd, shape, tc, monkeypatch):
+    """Scores that grow with the key's position move every row's maximum again and again: slowly (a few
+    units per tile, which the tcgen05 kernel absorbs without rescaling its accumulator) or in steps of
+    twenty units (which force a rescale in the middle of a sequence).  Eleven key tiles, a prompt that
+    continues 70 cached tokens."""
+    monkeypatch.setattr(ops, "USE_TC_PROMPT_ATTENTION", tc)
+    dtype, nh, nkv, before, count = torch.bfloat16, 4, 2, 70, 640
+    total = before + count
+    g = torch.Generator().manual_seed(77 + hd)
+    u = torch.randn(hd, generator=g)
+    u = u / u.norm()
+    pos = torch.arange(total, dtype=torch.float32)
+    rise = pos * (40.0 / total) if shape == "slow" else 20.0 * ((pos >= 100).float() + (pos >= 333).float() + (pos >= 600).float())
+    k = (0.3 * torch.randn(total, nkv, hd, generator=g) + rise[:, None, None] * u).to(dtype)
+    v = torch.randn(total, nkv, hd, generator=g).to(dtype)
+    q = (0.3 * torch.randn(count, nh, hd, generator=g) + u).to(dtype)
+    ring = 12
+    table = torch.zeros(3, ring, dtype=torch.int32)
+    table[1] = torch.tensor([11, 3, 7, 0, 9, 1, 5, 10, 2, 8, 4, 6], dtype=torch.int32)
+    kp = torch.zeros(12, nkv, 64, hd, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    for p_ in range(before):
+        kp[int(table[1, p_ // 64]), :, p_ % 64] = k[p_]
+        vp[int(table[1, p_ // 64]), :, p_ % 64] = v[p_]
+    tq = ops.prefill_tile_queries(dtype, hd)
+    tiles = torch.tensor([(0, q0) for q0 in range(0, count, tq)], dtype=torch.int32)
+    cu = torch.tensor([0, count], dtype=torch.int32)
+    out = torch.empty(count, nh * hd, dtype=dtype, device=DEV)
+    d = lambda t: t.to(DEV)
+    ops.attn_prefill(d(q), d(k[before:].contiguous()), d(v[before:].contiguous()), d(kp), d(vp), d(table), ring, d(tiles), d(cu),
+                     d(torch.tensor([before], dtype=torch.int32)), d(torch.tensor([1], dtype=torch.int32)), out,
+                     scale=1.0, window=0, tile_queries=tq)
+    qq = torch.zeros(total, nh, hd, dtype=dtype)
+    qq[before:] = q
+    ref = P.attention(qq, k, v, 1.0, 0)[before:].reshape(count, -1)
+    check(out, ref, dtype, shape)
+    if tc:
+        assert ops.attn_tc_status() == 0
+
+
 def test_kernels_refuse_what_they_cannot_do(ops):
     q = torch.zeros(1, 2, 272, device=DEV)
     kp = torch.zeros(1, 1, 64, 272, device=DEV)
