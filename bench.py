@@ -159,11 +159,23 @@ def main():
             times.append(e0.elapsed_time(e1))
         engine.close(slot)
     pre_ms = sorted(times)[len(times) // 2]
+    # prompt steps back to back run into the power cap; one more after half a second of idle shows the
+    # step as a lone request meets it (reported beside the back-to-back median, which stays the headline)
+    time.sleep(0.5)
+    slot = engine.open()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    engine.step([(slot, toks)])
+    e1.record()
+    torch.cuda.synchronize()
+    idle_ms = e0.elapsed_time(e1)
+    engine.close(slot)
     t = PREFILL_TOKENS
     attn_flops = args.layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * (t * (t + 1) / 2)
     pre_flops = 2.0 * t * nums["matrix_params"] + 2.0 * nums["head_params"] + attn_flops
     prefill = {"value": round(t / (pre_ms / 1e3), 1), "tokens": t, "ms": round(pre_ms, 3),
-               "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+               "ms_after_idle": round(idle_ms, 3)}
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---- decode steps at the context length --------------------------------------------------

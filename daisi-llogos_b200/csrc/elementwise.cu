@@ -293,88 +293,120 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
   }
 }
 
+// four consecutive elements, as float32
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&t.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const uint32_t*>(&lo);
+  t.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
 // The same for the common geometry (head size 64, 128 or 256; rotation by halves over the whole
-// head, or none): lane l keeps elements l, l + 32, ... in
-// registers, a rotation pair (i, i + rotary_dim / 2) lies in one lane, nothing goes through shared
-// memory, and all loads of a head are issued before the first use.
-template <typename IT, typename OT, typename WT, int MAXE>
-__global__ void __launch_bounds__(256) qk_prep_lane_kernel(QkPrepArgs a) {
+// head, or none): HD / 8 lanes share a head; a lane keeps elements 4l .. 4l+3 of each half in
+// registers, so a rotation pair (i, i + HD / 2) lies in one lane, every access moves four elements,
+// nothing goes through shared memory, and all loads of a head are issued before the first use.
+template <typename IT, typename OT, typename WT, int HD>
+__global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  const int warps = blockDim.x >> 5;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int LPH = HD / 8, HALF = HD / 2;      // lanes per head
   const int heads = a.nh + 2 * a.nkv;
-  const long long item = (long long)blockIdx.x * warps + warp;
-  if (item >= (long long)a.n_tokens * heads) return;
-  const int n = (int)(item / heads);
-  const int h = (int)(item % heads);
-  constexpr int hd = 32 * MAXE, ne = MAXE;
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPH;
+  const int l = threadIdx.x % LPH;
+  // lanes past the last head still take part in the shuffles below
+  const bool live = item < (long long)a.n_tokens * heads;
+  const int n = live ? (int)(item / heads) : 0;
+  const int h = live ? (int)(item % heads) : 0;
   const int kind = h < a.nh ? 0 : (h < a.nh + a.nkv ? 1 : 2);
-  const IT* src = (const IT*)a.qkv + (long long)n * heads * hd + (long long)h * hd + lane;
-  float x[MAXE];
-#pragma unroll
-  for (int k = 0; k < MAXE; ++k) x[k] = 0.f;
+  const IT* src = (const IT*)a.qkv + (long long)n * heads * HD + (long long)h * HD + 4 * l;
+  float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f};   // elements 4l.. of the first and second half
   for (int s = 0; s < a.n_partials; ++s) {
+    float t0[4], t1[4];
+    load4(src + s * a.partial_stride, t0);
+    load4(src + s * a.partial_stride + HALF, t1);
 #pragma unroll
-    for (int k = 0; k < MAXE; ++k)
-      if (k < ne) x[k] += to_f32(src[s * a.partial_stride + 32 * k]);
+    for (int k = 0; k < 4; ++k) {
+      x0[k] += t0[k];
+      x1[k] += t1[k];
+    }
   }
   const WT* nw = kind == 0 ? (const WT*)a.q_norm_w : (kind == 1 ? (const WT*)a.k_norm_w : nullptr);
-  if (nw) {
+  if (a.q_norm_w || a.k_norm_w) {                  // uniform over the block: the shuffles need every lane
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < MAXE; ++k) ss += x[k] * x[k];
-    ss = warp_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / (float)hd + a.norm_eps);
+    for (int k = 0; k < 4; ++k) ss += x0[k] * x0[k] + x1[k] * x1[k];
 #pragma unroll
-    for (int k = 0; k < MAXE; ++k)
-      if (k < ne) x[k] = x[k] * inv * to_f32(nw[lane + 32 * k]);
-  }
-  if (a.bias) {
-    const WT* b = (const WT*)a.bias + (long long)h * hd + lane;
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (nw) {
+      const float inv = 1.0f / sqrtf(ss / (float)HD + a.norm_eps);
+      float w0[4], w1[4];
+      load4(nw + 4 * l, w0);
+      load4(nw + 4 * l + HALF, w1);
 #pragma unroll
-    for (int k = 0; k < MAXE; ++k)
-      if (k < ne) x[k] += to_f32(b[32 * k]);
-  }
-  const int pos = a.positions[n];
-  if (kind != 2 && a.cos_table) {
-    constexpr int half = hd / 2, nh2 = MAXE / 2;             // pairs per lane (rotation over the whole head)
-    const int p = pos < a.table_positions ? pos : a.table_positions - 1;
-    const float* c = a.cos_table + (long long)p * half + lane;
-    const float* sn = a.sin_table + (long long)p * half + lane;
-#pragma unroll
-    for (int k = 0; k < MAXE / 2; ++k) {
-      if (k < nh2) {
-        const float cs = c[32 * k], si = sn[32 * k];
-        const float x0 = x[k], x1 = x[k + nh2];
-        x[k] = x0 * cs - x1 * si;
-        x[k + nh2] = x0 * si + x1 * cs;
+      for (int k = 0; k < 4; ++k) {
+        x0[k] = x0[k] * inv * w0[k];
+        x1[k] = x1[k] * inv * w1[k];
       }
     }
   }
-  if (kind == 0) {
-    OT* o = (OT*)a.q_out + ((long long)n * a.nh + h) * hd + lane;
+  if (!live) return;
+  if (a.bias) {
+    const WT* bsrc = (const WT*)a.bias + (long long)h * HD + 4 * l;
+    float b0[4], b1[4];
+    load4(bsrc, b0);
+    load4(bsrc + HALF, b1);
 #pragma unroll
-    for (int k = 0; k < MAXE; ++k)
-      if (k < ne) o[32 * k] = from_f32<OT>(x[k]);
+    for (int k = 0; k < 4; ++k) {
+      x0[k] += b0[k];
+      x1[k] += b1[k];
+    }
+  }
+  const int pos = a.positions[n];
+  if (kind != 2 && a.cos_table) {
+    const int p = pos < a.table_positions ? pos : a.table_positions - 1;
+    float cs[4], si[4];
+    load4(a.cos_table + (long long)p * HALF + 4 * l, cs);
+    load4(a.sin_table + (long long)p * HALF + 4 * l, si);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float u = x0[k], v = x1[k];
+      x0[k] = u * cs[k] - v * si[k];
+      x1[k] = u * si[k] + v * cs[k];
+    }
+  }
+  if (kind == 0) {
+    OT* o = (OT*)a.q_out + ((long long)n * a.nh + h) * HD + 4 * l;
+    store4(o, x0);
+    store4(o + HALF, x1);
     return;
   }
   const int kvh = kind == 1 ? h - a.nh : h - a.nh - a.nkv;
   void* packed = kind == 1 ? a.k_new : a.v_new;
   if (packed) {
-    OT* o = (OT*)packed + ((long long)n * a.nkv + kvh) * hd + lane;
-#pragma unroll
-    for (int k = 0; k < MAXE; ++k)
-      if (k < ne) o[32 * k] = from_f32<OT>(x[k]);
+    OT* o = (OT*)packed + ((long long)n * a.nkv + kvh) * HD + 4 * l;
+    store4(o, x0);
+    store4(o + HALF, x1);
   }
   void* pages = kind == 1 ? a.k_pages : a.v_pages;
   if (pages) {
     const int slot = a.slots[a.seq_of_token[n]];
     const long long row = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv);
-    OT* o = (OT*)pages + row * hd + lane;
-#pragma unroll
-    for (int k = 0; k < MAXE; ++k)
-      if (k < ne) o[32 * k] = from_f32<OT>(x[k]);
+    OT* o = (OT*)pages + row * HD + 4 * l;
+    store4(o, x0);
+    store4(o + HALF, x1);
   }
 }
 
@@ -388,11 +420,18 @@ LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stre
   LLG_REQUIRE(!a.k_pages || (a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
               "qk_prep: a cache write needs page_table, slots and seq_of_token");
   if (a.n_tokens == 0) return 0;
+  // the vector kernel moves four elements at a time: every pointer must be 16-byte aligned
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
   const bool lane_ok = (a.hd == 64 || a.hd == 128 || a.hd == 256) &&
-                       (!a.cos_table || (a.pairing == 0 && a.rotary_dim == a.hd));
+                       (!a.cos_table || (a.pairing == 0 && a.rotary_dim == a.hd)) && a.partial_stride % 4 == 0 &&
+                       aligned(a.qkv) && aligned(a.q_norm_w) && aligned(a.k_norm_w) && aligned(a.bias) &&
+                       aligned(a.cos_table) && aligned(a.sin_table) && aligned(a.q_out) && aligned(a.k_new) &&
+                       aligned(a.v_new) && aligned(a.k_pages) && aligned(a.v_pages);
   const int warps = lane_ok ? 8 : 4;
   const long long items = (long long)a.n_tokens * (a.nh + 2 * a.nkv);
-  const unsigned grid = (unsigned)((items + warps - 1) / warps);
+  // the vector kernel gives a head to head_dim / 8 lanes, the general one to a warp
+  const long long per_block = lane_ok ? (long long)warps * 32 / (a.hd / 8) : warps;
+  const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
   const size_t smem = lane_ok ? 0 : (size_t)warps * a.hd * sizeof(float);
   const bool w_bf16 = (a.q_norm_w || a.k_norm_w) ? a.norm_w_dtype == LLG_BF16
                                                  : (a.bias ? a.bias_dtype == LLG_BF16 : false);
@@ -400,9 +439,9 @@ LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stre
     LLG_REQUIRE(a.norm_w_dtype == a.bias_dtype, "qk_prep: norm weights and bias must share a dtype");
 #define LAUNCH(IT, OT, WT)                                                        \
   do {                                                                            \
-    if (lane_ok && a.hd == 64) llg_launch(qk_prep_lane_kernel<IT, OT, WT, 2>, grid, warps * 32, 0, stream, a);        \
-    else if (lane_ok && a.hd == 128) llg_launch(qk_prep_lane_kernel<IT, OT, WT, 4>, grid, warps * 32, 0, stream, a);  \
-    else if (lane_ok) llg_launch(qk_prep_lane_kernel<IT, OT, WT, 8>, grid, warps * 32, 0, stream, a);                 \
+    if (lane_ok && a.hd == 64) llg_launch(qk_prep_vec_kernel<IT, OT, WT, 64>, grid, warps * 32, 0, stream, a);        \
+    else if (lane_ok && a.hd == 128) llg_launch(qk_prep_vec_kernel<IT, OT, WT, 128>, grid, warps * 32, 0, stream, a);  \
+    else if (lane_ok) llg_launch(qk_prep_vec_kernel<IT, OT, WT, 256>, grid, warps * 32, 0, stream, a);                 \
     else llg_launch(qk_prep_kernel<IT, OT, WT>, grid, warps * 32, smem, stream, a);         \
   } while (0)
   if (out_dtype == LLG_F32) {
