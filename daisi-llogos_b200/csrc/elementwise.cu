@@ -43,6 +43,27 @@ LLG_API int llg_embed_rows(const void* table, int table_dtype, const int* ids, f
   return llg_check_launch("embed_rows");
 }
 
+// four consecutive elements as float32 (the address is a multiple of 4 elements)
+__device__ __forceinline__ void vec_load4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void vec_load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&t.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+__device__ __forceinline__ void vec_store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void vec_store4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const uint32_t*>(&lo);
+  t.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
 // ---- residual add + RMSNorm ---------------------------------------------------------
 
 // For output row j (token r = rows ? rows[j] : j):
@@ -85,11 +106,18 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const floa
                                         float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
   __shared__ float red[32];
   pdl_launch_dependents();
+  const int nv = hidden >> 2;
+  // the norm's weight is no result of an earlier kernel: fetch it while the predecessor still runs
+  float wv[VPT][4];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nv) vec_load4(weight + 4 * i, wv[k]);
+  }
   pdl_wait();
   const int j = blockIdx.x;
   const int r = rows ? rows[j] : j;
   float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
-  const int nv = hidden >> 2;
   float4 keep[VPT];
   float ss = 0.f;
 #pragma unroll
@@ -127,11 +155,8 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const floa
     const int i = threadIdx.x + k * blockDim.x;
     if (i < nv) {
       const float4 v = keep[k];
-      const WT* w = weight + 4 * i;
-      o[4 * i + 0] = from_f32<OT>(v.x * inv * to_f32(w[0]));
-      o[4 * i + 1] = from_f32<OT>(v.y * inv * to_f32(w[1]));
-      o[4 * i + 2] = from_f32<OT>(v.z * inv * to_f32(w[2]));
-      o[4 * i + 3] = from_f32<OT>(v.w * inv * to_f32(w[3]));
+      const float y[4] = {v.x * inv * wv[k][0], v.y * inv * wv[k][1], v.z * inv * wv[k][2], v.w * inv * wv[k][3]};
+      vec_store4(o + 4 * i, y);
     }
   }
 }
@@ -144,7 +169,7 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
   LLG_REQUIRE(!branch || n_partials >= 1, "add_rmsnorm: a branch needs n_partials >= 1");
   if (n_out == 0) return 0;
   const bool vec = hidden % 4 == 0 && partial_stride % 4 == 0 && ((uintptr_t)residual % 16) == 0 &&
-                   ((uintptr_t)branch % 16) == 0;
+                   ((uintptr_t)branch % 16) == 0 && ((uintptr_t)weight % 16) == 0 && ((uintptr_t)out % 16) == 0;
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   // vector path: few rows (decode) want many threads per row, many rows want the row in registers
   int vpt = 1;
@@ -293,27 +318,6 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
   }
 }
 
-// four consecutive elements, as float32
-__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
-  const float4 t = *reinterpret_cast<const float4*>(p);
-  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-}
-__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
-  const uint2 t = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&t.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
-  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
-}
-__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
-  const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
-  uint2 t;
-  t.x = *reinterpret_cast<const uint32_t*>(&lo);
-  t.y = *reinterpret_cast<const uint32_t*>(&hi);
-  *reinterpret_cast<uint2*>(p) = t;
-}
-
 // The same for the common geometry (head size 64, 128 or 256; rotation by halves over the whole
 // head, or none): HD / 8 lanes share a head; a lane keeps elements 4l .. 4l+3 of each half in
 // registers, so a rotation pair (i, i + HD / 2) lies in one lane, every access moves four elements,
@@ -335,8 +339,8 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f};   // elements 4l.. of the first and second half
   for (int s = 0; s < a.n_partials; ++s) {
     float t0[4], t1[4];
-    load4(src + s * a.partial_stride, t0);
-    load4(src + s * a.partial_stride + HALF, t1);
+    vec_load4(src + s * a.partial_stride, t0);
+    vec_load4(src + s * a.partial_stride + HALF, t1);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       x0[k] += t0[k];
@@ -353,8 +357,8 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
     if (nw) {
       const float inv = 1.0f / sqrtf(ss / (float)HD + a.norm_eps);
       float w0[4], w1[4];
-      load4(nw + 4 * l, w0);
-      load4(nw + 4 * l + HALF, w1);
+      vec_load4(nw + 4 * l, w0);
+      vec_load4(nw + 4 * l + HALF, w1);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         x0[k] = x0[k] * inv * w0[k];
@@ -366,8 +370,8 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   if (a.bias) {
     const WT* bsrc = (const WT*)a.bias + (long long)h * HD + 4 * l;
     float b0[4], b1[4];
-    load4(bsrc, b0);
-    load4(bsrc + HALF, b1);
+    vec_load4(bsrc, b0);
+    vec_load4(bsrc + HALF, b1);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       x0[k] += b0[k];
@@ -378,8 +382,8 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   if (kind != 2 && a.cos_table) {
     const int p = pos < a.table_positions ? pos : a.table_positions - 1;
     float cs[4], si[4];
-    load4(a.cos_table + (long long)p * HALF + 4 * l, cs);
-    load4(a.sin_table + (long long)p * HALF + 4 * l, si);
+    vec_load4(a.cos_table + (long long)p * HALF + 4 * l, cs);
+    vec_load4(a.sin_table + (long long)p * HALF + 4 * l, si);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float u = x0[k], v = x1[k];
@@ -389,24 +393,24 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   }
   if (kind == 0) {
     OT* o = (OT*)a.q_out + ((long long)n * a.nh + h) * HD + 4 * l;
-    store4(o, x0);
-    store4(o + HALF, x1);
+    vec_store4(o, x0);
+    vec_store4(o + HALF, x1);
     return;
   }
   const int kvh = kind == 1 ? h - a.nh : h - a.nh - a.nkv;
   void* packed = kind == 1 ? a.k_new : a.v_new;
   if (packed) {
     OT* o = (OT*)packed + ((long long)n * a.nkv + kvh) * HD + 4 * l;
-    store4(o, x0);
-    store4(o + HALF, x1);
+    vec_store4(o, x0);
+    vec_store4(o + HALF, x1);
   }
   void* pages = kind == 1 ? a.k_pages : a.v_pages;
   if (pages) {
     const int slot = a.slots[a.seq_of_token[n]];
     const long long row = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv);
     OT* o = (OT*)pages + row * HD + 4 * l;
-    store4(o, x0);
-    store4(o + HALF, x1);
+    vec_store4(o, x0);
+    vec_store4(o + HALF, x1);
   }
 }
 
