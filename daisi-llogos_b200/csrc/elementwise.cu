@@ -586,6 +586,19 @@ LLG_API int llg_scatter_i32(int* dst, const int* idx, const int* val, int n, cud
   return llg_check_launch("scatter_i32");
 }
 
+__global__ void gather_i32_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ idx, int n) {
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = src[idx[i]];
+}
+
+// dst[i] = src[idx[i]]: the tokens that a sampler left on the device become the next step's input.
+LLG_API int llg_gather_i32(int* dst, const int* src, const int* idx, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  gather_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, src, idx, n);
+  return llg_check_launch("gather_i32");
+}
+
 __global__ void zero_rows_kernel(unsigned char* __restrict__ base, const int* __restrict__ rows,
                                  long long row_bytes) {
   pdl_wait();

@@ -173,6 +173,36 @@ class Engine:
             for w in want[i]:
                 if not 0 <= int(w) < c:
                     raise StepError(f"entry {i} (slot {slots[i]}): wanted position {w} is outside its {c} tokens")
+        return self._run(slots, toks, counts, want, None)
+
+    def step_fed(self, slots: Sequence[int], source: torch.Tensor, rows: Sequence[int],
+                 want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """A step of one token per sequence whose ids are still on the device: sequence ``slots[i]`` gets
+        ``source[rows[i]]`` (``source``: int32, what a sampler wrote).  The host never sees the ids, so the
+        step can be queued before the sampler's result has been read; an id outside the vocabulary is read
+        as token 0.  Everything else is as in ``step``."""
+        if len(slots) == 0:
+            raise StepError("a step needs at least one sequence")
+        if len(rows) != len(slots):
+            raise StepError("step_fed needs one source row per slot")
+        if source.dtype != torch.int32 or source.device != self.device:
+            raise StepError("step_fed: the token source must be an int32 tensor on the engine's device")
+        for r in rows:
+            if not 0 <= int(r) < source.numel():
+                raise StepError(f"step_fed: source row {r} is outside the source's {source.numel()} entries")
+        slots = [int(s) for s in slots]
+        if want is None:
+            want = [[0]] * len(slots)
+        if len(want) != len(slots):
+            raise StepError("want must have one list per entry")
+        for i, w_ in enumerate(want):
+            for w in w_:
+                if int(w) != 0:
+                    raise StepError(f"entry {i} (slot {slots[i]}): wanted position {w} is outside its 1 tokens")
+        toks = [np.zeros(1, dtype=np.int64) for _ in slots]
+        return self._run(slots, toks, [1] * len(slots), want, (source, [int(r) for r in rows]))
+
+    def _run(self, slots, toks, counts, want, fed) -> torch.Tensor:
         growth = list(zip(slots, counts))
         try:
             self.cache.check_room(growth)
@@ -181,10 +211,10 @@ class Engine:
 
         len_before = [self.cache.length(s) for s in slots]
         updates = self.cache.grow(growth)
-        b = len(entries)
+        b = len(slots)
         decode = all(c == 1 for c in counts)
         if decode:
-            logits = self._decode_step(b, slots, toks, len_before, updates, want)
+            logits = self._decode_step(b, slots, toks, len_before, updates, want, fed)
         else:
             logits = self._prompt_step(b, slots, toks, counts, len_before, updates, want)
         self.cache.commit(growth)
@@ -249,7 +279,7 @@ class Engine:
         return self.model.forward(ctx, self.cache, rows_dev)
 
     # ---- decode step -----------------------------------------------------------------------
-    def _decode_step(self, n_real, slots, toks, len_before, updates, want) -> torch.Tensor:
+    def _decode_step(self, n_real, slots, toks, len_before, updates, want, fed=None) -> torch.Tensor:
         b = decode_bucket(n_real) if self.use_graphs else n_real
         st = self._decode.get(b)
         if st is None:
@@ -263,15 +293,19 @@ class Engine:
         # layout: token_ids | positions | seq_of_token | slots | cu_tokens (b + 1) | len_before
         host = [token_ids, lb, ar, all_slots, np.arange(b + 1, dtype=np.int32), lb]
         fixed = 6 * b + 1
+        if fed is not None:
+            host.append(np.asarray(fed[1], dtype=np.int32))      # source rows, right after the fixed part
         plan = self._apply_updates(updates, host)
         block = np.concatenate(host)
-        if plan:
-            # page-table updates travel through the general buffer, the fixed part through the static one
+        if plan or fed is not None:
+            # page-table updates and source rows travel through the general buffer, the fixed part through the static one
             meta2 = self._ensure_meta(block.size)
             self._staging.upload(block, meta2)
             for g, off, k in plan:
                 self.ops.scatter_i32(g.page_table, meta2[off:off + k], meta2[off + k:off + 2 * k])
             st.meta.copy_(meta2[:fixed], non_blocking=True)
+            if fed is not None:
+                self.ops.gather_i32(st.meta[:n_real], fed[0], meta2[fixed:fixed + n_real])
         else:
             self._staging.upload(block, st.meta)
         m = st.meta

@@ -137,6 +137,7 @@ def _lib(name: str):
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
         lib.llg_silu_mul.argtypes = [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.llg_scatter_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        lib.llg_gather_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.llg_zero_rows.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
     elif name == "gemm_simt":
         lib.llg_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
@@ -330,6 +331,14 @@ def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None
     assert idx.numel() == val.numel()
     _check(lib, lib.llg_scatter_i32(_ptr(dst, torch.int32), _ptr(idx, torch.int32), _ptr(val, torch.int32),
                                     idx.numel(), _stream()))
+
+
+def gather_i32(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor) -> None:
+    """dst[i] = src.flat[idx[i]]."""
+    lib = _lib("elementwise")
+    assert dst.numel() == idx.numel()
+    _check(lib, lib.llg_gather_i32(_ptr(dst, torch.int32), _ptr(src, torch.int32), _ptr(idx, torch.int32),
+                                   idx.numel(), _stream()))
 
 
 def zero_rows(base: torch.Tensor, rows: torch.Tensor) -> None:

@@ -7,6 +7,12 @@ A sequence ends at a stop token (which is not emitted, Inference/TextGenerator.c
 batch, which goes on smaller.  When the batch is over, its slots go back to the cache and the
 next batch uses them again.  The loop decides; the engine and the sampler do the arithmetic, so
 the decisions can be tested with stand-ins for both.
+
+When the sampler can leave its tokens on the device and the engine can take them from there
+(``sample_device`` / ``fetch`` / ``step_fed``) and the sampling needs no token history, the loop runs
+one step ahead of what it has read: it queues the step that consumes the tokens of sample k before it
+reads them, and reads them while that step runs.  A stop token is then seen one step late; the
+sequence has run one step too many, whose token is thrown away.  The tokens that come out are the same.
 """
 from __future__ import annotations
 
@@ -70,7 +76,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: Generati
              stop_tokens: Optional[Sequence[int]] = None, max_batch: int = 64,
              on_token: Optional[Callable[[int, int], None]] = None,
              clock: Callable[[], float] = time.perf_counter,
-             sync: Optional[Callable[[], None]] = None) -> GenerationResult:
+             sync: Optional[Callable[[], None]] = None, run_ahead: bool = True) -> GenerationResult:
     """Generates for every prompt; ``on_token(request index, token)`` is called as tokens appear.
 
     ``engine`` needs ``open()``, ``close(slot)``, ``step(entries, want=None)`` and a ``cache`` with
@@ -105,6 +111,11 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: Generati
             result.prompt_tokens += sum(len(prompts[i]) for i in active)
             t0 = clock()
             step_no = 0
+            if (run_ahead and params.max_tokens > 0 and not params.uses_history and hasattr(sampler, "sample_device")
+                    and hasattr(sampler, "fetch") and hasattr(engine, "step_fed")):
+                _decode_ahead(engine, sampler, params, seed, sorted(stop), stop, slots, histories, active, logits,
+                              result, on_token, cache.max_seq_len)
+                active = []
             while active and params.max_tokens > 0:
                 picked = sampler.sample(logits, params, seed=seed, step=step_no, seq_ids=active,
                                         histories=[histories[i] for i in active], stop_tokens=sorted(stop))
@@ -137,3 +148,54 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: Generati
             for s in slots.values():
                 engine.close(s)
     return result
+
+
+def _decode_ahead(engine, sampler, params, seed, stop_list, stop, slots, histories, active, logits, result,
+                  on_token, max_seq_len) -> None:
+    """The decode loop of one batch, one step ahead of the tokens it has read (see the module's text)."""
+    alive = {i: True for i in active}
+    length = {i: len(histories[i]) for i in active}      # tokens of the sequence counting samples not yet read
+    unread = []                                         # (pending tokens, their sequences), oldest first
+
+    def read(pending, seqs):
+        for i, tok in zip(seqs, pending.result()):
+            if not alive[i]:
+                continue                                # the step too many of a sequence that had stopped
+            tok = int(tok)
+            if tok in stop:
+                result.finish_reasons[i] = "stop"
+                alive[i] = False
+                continue
+            result.tokens[i].append(tok)
+            histories[i].append(tok)
+            result.generated_tokens += 1
+            if on_token is not None:
+                on_token(i, tok)
+            if len(result.tokens[i]) >= params.max_tokens:
+                result.finish_reasons[i] = "length"
+                alive[i] = False
+            elif len(histories[i]) >= max_seq_len:
+                result.finish_reasons[i] = "context"
+                alive[i] = False
+
+    rows = list(active)
+    step_no = 0
+    while rows:
+        picked = sampler.sample_device(logits, params, seed=seed, step=step_no, seq_ids=rows, stop_tokens=stop_list)
+        unread.append((sampler.fetch(picked), rows))
+        for i in rows:
+            length[i] += 1
+        while len(unread) > 1:                          # everything but the sample just queued
+            read(*unread.pop(0))
+        # who goes on: not known to have ended, and not ending by count or context with the sample just queued
+        nxt = [(r, i) for r, i in enumerate(rows)
+               if alive[i] and length[i] - len(histories[i]) + len(result.tokens[i]) < params.max_tokens
+               and length[i] < max_seq_len]
+        step_no += 1
+        if not nxt:
+            break
+        logits = engine.step_fed([slots[i] for _, i in nxt], picked, [r for r, _ in nxt])
+        result.decode_steps += 1
+        rows = [i for _, i in nxt]
+    while unread:
+        read(*unread.pop(0))

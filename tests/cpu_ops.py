@@ -116,6 +116,10 @@ def scatter_i32(dst, idx, val):
     dst.view(-1)[idx.long()] = val
 
 
+def gather_i32(dst, src, idx):
+    dst.copy_(src.view(-1)[idx.long()])
+
+
 def zero_rows(base, rows):
     base[rows.long()] = 0
 

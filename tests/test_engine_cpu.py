@@ -171,3 +171,31 @@ def test_random_cuts_and_batches(llogos, setup, name):
                 eng.close(live.pop(i)[0])
         eng.cache.audit()
     assert eng.cache.slots.free_count == 4
+
+
+def test_tokens_fed_from_the_device_side(llogos, setup):
+    """step_fed takes one token per sequence out of a tensor by row: the same logits as step with the ids."""
+    model, w = setup["qwen3"]
+    cfg = TINY["qwen3"]
+    eng = engine_for(llogos, model)
+    seqs = random_tokens(cfg["vocab_size"], [20, 9, 31], 8)
+    refs = [P.forward(w, cfg, s) for s in seqs]
+    slots = [eng.open() for _ in seqs]
+    eng.step([(sl, s[:5]) for sl, s in zip(slots, seqs)])
+    source = torch.tensor([seqs[2][5], 0, seqs[0][5], seqs[1][5]], dtype=torch.int32)
+    lg = eng.step_fed(slots, source, [2, 3, 0])
+    for i in range(3):
+        assert float((lg[i].double() - refs[i][5]).abs().max()) < 2e-4
+    lg = eng.step_fed([slots[1]], torch.tensor([seqs[1][6]], dtype=torch.int32), [0])
+    assert float((lg[0].double() - refs[1][6]).abs().max()) < 2e-4
+    before = [eng.length(s) for s in slots]
+    with pytest.raises(llogos.engine.StepError, match="source row"):
+        eng.step_fed(slots, source, [0, 1, 4])
+    with pytest.raises(llogos.engine.StepError, match="int32"):
+        eng.step_fed(slots, source.long(), [0, 1, 2])
+    with pytest.raises(llogos.engine.StepError, match="one source row"):
+        eng.step_fed(slots, source, [0, 1])
+    assert [eng.length(s) for s in slots] == before
+    for s in slots:
+        eng.close(s)
+    eng.cache.audit()

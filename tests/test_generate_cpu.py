@@ -158,3 +158,55 @@ def test_params(G):
     assert not p.greedy and p.uses_history and Params.greedy_params().greedy
     with pytest.raises(ValueError):
         Params(temperature=-1).validate()
+
+
+class AheadEngine(FakeEngine):
+    """FakeEngine that can also take its tokens from a 'device' tensor the host has not read."""
+
+    def step_fed(self, slots, source, rows, want=None):
+        return self.step([(s, [int(source[r])]) for s, r in zip(slots, rows)])
+
+
+class AheadSampler(ArgmaxSampler):
+    """Hands tokens out only through result(), and records when each was read."""
+
+    def __init__(self):
+        super().__init__()
+        self.reads = []
+
+    def sample_device(self, logits, params, *, seed, step, seq_ids, histories=None, stop_tokens=()):
+        self.calls.append(dict(step=step, seq_ids=list(seq_ids), seed=seed, hist=None))
+        return logits.argmax(-1).to(torch.int32)
+
+    def fetch(self, picked):
+        sampler, n_calls = self, len(self.calls)
+
+        class Pending:
+            def result(self):
+                sampler.reads.append((n_calls, len(sampler.calls)))     # (sample number, samples queued when read)
+                return picked.tolist()
+        return Pending()
+
+
+@pytest.mark.parametrize("stop_tokens,max_new,max_seq_len", [((), 4, 512), ([4, 8, 23], 6, 512), ([9], 30, 14), ([2], 3, 512)])
+def test_running_one_step_ahead_gives_the_same_tokens(G, stop_tokens, max_new, max_seq_len):
+    gen, Params = G
+    prompts = [[1], [6, 7], [20], [40, 41, 42, 43, 44]]
+    params = Params.greedy_params(max_new, seed=1)
+    e0, s0 = FakeEngine(max_seq_len=max_seq_len), ArgmaxSampler()
+    r0 = gen.generate(e0, s0, prompts, params, stop_tokens=stop_tokens)
+    e1, s1 = AheadEngine(max_seq_len=max_seq_len), AheadSampler()
+    r1 = gen.generate(e1, s1, prompts, params, stop_tokens=stop_tokens)
+    assert r1.tokens == r0.tokens and r1.finish_reasons == r0.finish_reasons
+    assert r1.generated_tokens == r0.generated_tokens
+    assert not e1.cache.slots.live and sorted(e1.closed) == sorted(e0.closed)
+    # every sample but the last of a batch was read only after the next one had been queued
+    assert s1.reads and all(at > n for n, at in s1.reads[:-1])
+    # a sequence runs at most one step more than in the loop that reads every token at once
+    for s in e0.length:
+        assert e0.length[s] <= e1.length[s] <= e0.length[s] + 1
+    assert max(e1.length.values()) <= max_seq_len
+    # and with the switch off the same objects take the ordinary loop
+    e2, s2 = AheadEngine(max_seq_len=max_seq_len), AheadSampler()
+    r2 = gen.generate(e2, s2, prompts, params, stop_tokens=stop_tokens, run_ahead=False)
+    assert r2.tokens == r0.tokens and not s2.reads

@@ -94,6 +94,31 @@ def test_seeded_sampling_matches_plain_and_ignores_batch_mates(llogos, model_dir
     assert sum(int(a == b) for a, b in zip(rf.tokens, wantf)) >= 1
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_one_step_ahead_changes_no_token(llogos, model_dirs, dtype):
+    """Greedy and seeded sampling without penalties run one step ahead of the tokens the host has read
+    (the next step takes them from the device); with the switch off the host reads every token first.
+    Stop tokens that really occur, unequal prompts, two batches."""
+    name = "qwen2"
+    cfg = TINY[name]
+    prompts = random_tokens(cfg["vocab_size"], [5, 9, 13, 1, 30, 64, 3], 41)
+    model = L.LlogosModel.load(model_dirs[name], dtype=dtype, max_context=256, max_batch=4)
+    free = L.GenerationParams.greedy_params(24, stop_tokens=())
+    base = model.generate(prompts, free, run_ahead=False)
+    # stop at tokens that the free run produced in its middle, so that sequences end at different steps
+    stop = sorted({t[len(t) // 2] for t in base.tokens[:3]})
+    for params in (L.GenerationParams.greedy_params(24, stop_tokens=stop),
+                   L.GenerationParams(max_tokens=17, temperature=0.9, top_k=20, top_p=0.9, repetition_penalty=1.0,
+                                      seed=77, stop_tokens=stop)):
+        slow = model.generate(prompts, params, run_ahead=False)
+        fast = model.generate(prompts, params)
+        assert fast.tokens == slow.tokens and fast.finish_reasons == slow.finish_reasons
+        assert "stop" in slow.finish_reasons and "length" in slow.finish_reasons
+        assert fast.decode_steps >= slow.decode_steps
+        assert not model.engine.cache.slots.live()
+        model.engine.cache.audit()
+
+
 def test_bfloat16_generation_runs_and_is_deterministic(model_dirs):
     cfg = TINY["llama"]
     prompts = random_tokens(cfg["vocab_size"], [5, 9, 13], 33)
