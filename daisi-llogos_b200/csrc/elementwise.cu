@@ -524,10 +524,9 @@ LLG_API int llg_kv_write(const void* k_new, const void* v_new, void* k_pages, vo
 
 // ---- SiLU gating --------------------------------------------------------------------
 
-// The gate and up projections are stored as one matrix in blocks of 256 rows: the gate rows of 128
-// features, then the up rows of the same features (the layout the tensor-core product's gated
-// epilogue wants).  A product's output row therefore holds, for feature i, g at
-// (i / 128) * 256 + i % 128 and u 128 further:
+// The gate and up projections are stored as one matrix: the gate rows of all features, zero rows up
+// to a multiple P of 128, then the up rows in the same way (the layout the tensor-core product's
+// gated epilogue wants).  A product's output row therefore holds, for feature i, g at i and u at P + i:
 // out[n][i] = silu(g) * u, silu(g) = g / (1 + exp(-g))  (Daisi.Llogos.Cpu/Silu.cs:9-16).
 template <typename IT, typename OT>
 __global__ void silu_mul_kernel(const IT* __restrict__ gu, int n_partials, long long partial_stride,
@@ -538,11 +537,11 @@ __global__ void silu_mul_kernel(const IT* __restrict__ gu, int n_partials, long 
        idx += (long long)gridDim.x * blockDim.x) {
     const long long n = idx / inter;
     const int i = (int)(idx - n * inter);
-    const IT* p = gu + n * width + (i >> 7) * 256 + (i & 127);
+    const IT* p = gu + n * width + i;
     float g = 0.f, u = 0.f;
     for (int s = 0; s < n_partials; ++s) {
       g += to_f32(p[s * partial_stride]);
-      u += to_f32(p[s * partial_stride + 128]);
+      u += to_f32(p[s * partial_stride + width / 2]);
     }
     out[idx] = from_f32<OT>(g / (1.0f + expf(-g)) * u);
   }

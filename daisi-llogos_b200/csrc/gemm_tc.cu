@@ -122,11 +122,15 @@ struct GemmParams {
   int n, o, k;
   int kb_per_split; // k-blocks of 64 per split
   int gated_features;
+  int up_offset;    // gated: row of w that holds the up row of feature 0 (gate rows come first)
+  int gate_rows;    // gated, weights as first operand: features per block (at most 128)
 };
 
 // MT: weight tiles of 128 rows per block (1 or 2; two tiles share every activation tile, which halves
 // the shared-memory traffic per flop of a large product).  EPI 1 (MT = 2): the first tile holds gate
-// rows and the second the up rows of the same 128 features; the block writes silu(gate) * up.
+// rows and the second the up rows of the same features; the block writes silu(gate) * up.  A block
+// takes `gate_rows` features (TMA boxes of that many rows; the accumulator lanes past them are not
+// read), chosen on the host so that the blocks of a decode step are as many as the SMs.
 // SWAP 0: the first operand (MMA rows, accumulator lanes) is the weight matrix, the second the activations:
 // out[n][o] with o along the lanes (decode steps: the token tile can be as small as 16).
 // SWAP 1: the first operand is the activations (128 tokens per tile), the second the weights (TN features):
@@ -151,7 +155,21 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.z;
   const int n_tiles_n = (p.n + TN - 1) / TN;
-  const int total_tiles = ((p.o + BM * MT - 1) / (BM * MT)) * n_tiles_n;
+  constexpr bool GATED_ROWS = EPI == 1 && SWAP == 0;       // gate and up tiles fetched separately, gate_rows each
+  const int total_tiles = (GATED_ROWS ? (p.gated_features + p.gate_rows - 1) / p.gate_rows
+                                      : (p.o + BM * MT - 1) / (BM * MT)) * n_tiles_n;
+  const uint32_t stage_tx = GATED_ROWS ? (uint32_t)(2 * p.gate_rows * BK * 2 + B_BYTES) : (uint32_t)STAGE_BYTES;
+  // row of w that the weight tile `mt` of the block at first-operand offset o0 starts at
+  auto w_row = [&](int o0, int mt) { return GATED_ROWS ? mt * p.up_offset + o0 : o0 + mt * BM; };
+  // second operand: one box of TN rows, or (gated, tokens first) the gate half and the up half of the features
+  auto load_second = [&](unsigned char* dst, int kb, int n0, uint64_t* bar) {
+    if (EPI == 1 && SWAP == 1) {
+      tma_load_2d(dst, &map_x, kb * BK, n0 / 2, bar);
+      tma_load_2d(dst + (TN / 2) * BK * 2, &map_x, kb * BK, p.up_offset + n0 / 2, bar);
+    } else {
+      tma_load_2d(dst, &map_x, kb * BK, n0, bar);
+    }
+  };
   const int nkb_total = (p.k + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, nkb_total - kb0);   // >= 1 by construction of the grid
@@ -188,7 +206,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   for (int tile = blockIdx.x, round = 0; tile < total_tiles; tile += gridDim.x, ++round) {
     // the operand that is shared by neighbouring blocks is the weight tile in both orientations
     const int m_tiles = total_tiles / n_tiles_n;
-    const int o0 = (SWAP ? tile % m_tiles : tile / n_tiles_n) * (BM * MT);
+    const int o0 = (SWAP ? tile % m_tiles : tile / n_tiles_n) * (GATED_ROWS ? p.gate_rows : BM * MT);
     const int n0 = (SWAP ? tile / m_tiles : tile % n_tiles_n) * TN;
 
     if (tid == 0) {
@@ -198,13 +216,13 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         // before this kernel waits for its predecessor, the activation tiles right after.
         const int pre = min(nkb, STAGES);
         for (int i = 0; i < pre; ++i) {
-          mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+          mbar_expect_tx(&full_bar[i], stage_tx);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
-            tma_load_2d(smem + i * STAGE_BYTES + mt * A_TILE, &map_w, (kb0 + i) * BK, o0 + mt * BM, &full_bar[i]);
+            tma_load_2d(smem + i * STAGE_BYTES + mt * A_TILE, &map_w, (kb0 + i) * BK, w_row(o0, mt), &full_bar[i]);
         }
         pdl_wait();
-        for (int i = 0; i < pre; ++i) tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_x, (kb0 + i) * BK, n0, &full_bar[i]);
+        for (int i = 0; i < pre; ++i) load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
         it_issue = pre;
         preloaded = pre;
       }
@@ -215,11 +233,11 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
           if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
           break;
         }
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], stage_tx);
         unsigned char* a = smem + s * STAGE_BYTES;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * A_TILE, &map_w, (kb0 + i) * BK, o0 + mt * BM, &full_bar[s]);
-        tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * BK, n0, &full_bar[s]);
+        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * A_TILE, &map_w, (kb0 + i) * BK, w_row(o0, mt), &full_bar[s]);
+        load_second(a + A_BYTES, kb0 + i, n0, &full_bar[s]);
       }
     } else if (first) {
       pdl_wait();               // every other thread: before anything of the previous kernel is read or overwritten
@@ -259,16 +277,16 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     preloaded = 0;
     if (tid == 0 && tile + (int)gridDim.x < total_tiles) {
       const int nt = tile + gridDim.x;
-      const int no0 = (SWAP ? nt % m_tiles : nt / n_tiles_n) * (BM * MT);
+      const int no0 = (SWAP ? nt % m_tiles : nt / n_tiles_n) * (GATED_ROWS ? p.gate_rows : BM * MT);
       const int nn0 = (SWAP ? nt / m_tiles : nt % n_tiles_n) * TN;
       const int pre = min(nkb, STAGES);
       for (int i = 0; i < pre; ++i, ++it_issue) {
         const int s = it_issue % STAGES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], stage_tx);
         unsigned char* a = smem + s * STAGE_BYTES;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * A_TILE, &map_w, (kb0 + i) * BK, no0 + mt * BM, &full_bar[s]);
-        tma_load_2d(a + A_BYTES, &map_x, (kb0 + i) * BK, nn0, &full_bar[s]);
+        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * A_TILE, &map_w, (kb0 + i) * BK, w_row(no0, mt), &full_bar[s]);
+        load_second(a + A_BYTES, kb0 + i, nn0, &full_bar[s]);
       }
       preloaded = pre;
     }
@@ -357,10 +375,11 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
           }
         }
       } else {
-        // accumulator 0 holds gate, accumulator 1 up, of feature (weight tile) * 128 + lane row
+        // accumulator 0 holds gate, accumulator 1 up, of feature o0 + lane row (the first gate_rows lanes)
         OT* out = (OT*)p.out;
-        const int inter = p.gated_features;
-        const int f = (tile / n_tiles_n) * BM + warp * 32 + lane;
+        const int row = warp * 32 + lane;
+        const int inter = row < p.gate_rows ? p.gated_features : 0;
+        const int f = o0 + row;
 #pragma unroll
         for (int c0 = 0; c0 < TN; c0 += 16) {
           if (n0 + c0 >= p.n) break;
@@ -460,7 +479,8 @@ int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, in
   }
   // one block per tile for the small token tiles of a decode step; for the large ones as many blocks as
   // fit the GPU at once, each working through several tiles
-  const long long tiles = (long long)((p.o + BM * MT - 1) / (BM * MT)) * ((p.n + TN - 1) / TN);
+  const long long m_tiles = (EPI == 1 && SWAP == 0) ? (p.gated_features + p.gate_rows - 1) / p.gate_rows : (p.o + BM * MT - 1) / (BM * MT);
+  const long long tiles = m_tiles * ((p.n + TN - 1) / TN);
   long long blocks = tiles;
   if (TN >= 128) {
     const long long resident = 148LL * (smem <= 113 * 1024 ? 2 : 1);
@@ -491,8 +511,8 @@ LLG_API int llg_gemm_tc_splits(int k, int splits) {
 }
 
 // out[s][n][o] for s < llg_gemm_tc_splits(k, splits); out_dtype float32, or bfloat16 when there is one split.
-// gated_features > 0 (one split only): w has ceil(F / 128) blocks of 256 rows, each block the gate rows of 128
-// features followed by their up rows (rows past F are zero), and out is [n][F] = silu(gate) * up.
+// gated_features > 0 (one split only): w has 2 * P rows with P = F rounded up to a multiple of 128: the gate rows of
+// all features, zero rows up to P, then the up rows in the same way; out is [n][F] = silu(gate) * up.
 LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int splits,
                         int tile_n, int gated_features, cudaStream_t stream) {
   LLG_REQUIRE(llg_gemm_tc_supported(x, w, n, o, k), "gemm_tc: needs k %% 8 == 0 and 16-byte aligned operands (n=%d o=%d k=%d)",
@@ -508,8 +528,9 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   if (n >= 256 && tile_n <= 0) {
     // ---- prompt steps: activations are the first operand (128 tokens per tile), 256 features per tile ----
     // in this orientation the kernel's first-operand rows (field o) are the tokens, the second's (field n) the features
-    GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features};
-    LLG_REQUIRE(tensor_map(x, n, k, BM, &map_x) && tensor_map(w, o, k, 256, &map_w),
+    GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features, o / 2, BM};
+    // the gated product fetches the gate half and the up half of a feature tile with a box of 128 rows each
+    LLG_REQUIRE(tensor_map(x, n, k, BM, &map_x) && tensor_map(w, o, k, gated ? 128 : 256, &map_w),
                 "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
     const long long nt = (o + 255) / 256;
     const long long t1 = (long long)((n + BM - 1) / BM) * nt, t2 = (long long)((n + 2 * BM - 1) / (2 * BM)) * nt;
@@ -525,10 +546,19 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
     }
 #undef GOS
   }
-  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features};
+  // Features per block of a gated product: with one token tile the blocks should be as many as the SMs (or a
+  // multiple), whatever the feature count; 128 per block would leave a quarter of the SMs idle at 14336 features.
+  int gate_rows = BM;
   if (tile_n <= 0) tile_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
+  if (gated && n <= tile_n) {
+    const int rounds = ((gated_features + BM - 1) / BM + 147) / 148;
+    gate_rows = (gated_features + 148 * rounds - 1) / (148 * rounds);
+    if (gate_rows < 16) gate_rows = 16;
+    if (gate_rows > BM) gate_rows = BM;
+  }
+  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features, o / 2, gate_rows};
   LLG_REQUIRE(splits <= 65535, "gemm_tc: grid too large");
-  LLG_REQUIRE(tensor_map(w, o, k, BM, &map_w) && tensor_map(x, n, k, tile_n, &map_x),
+  LLG_REQUIRE(tensor_map(w, o, k, gated ? gate_rows : BM, &map_w) && tensor_map(x, n, k, tile_n, &map_x),
               "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
   const CUtensorMap *mw = &map_w, *mx = &map_x;
   // Two weight tiles per block halve the activation traffic per flop (worth about 15 %) but double the

@@ -58,22 +58,14 @@ _GATED_CHUNK = 16384   # rows per pass of the two-kernel path, bounds its [rows,
 
 
 def gated_layout(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
-    """One matrix of blocks of 256 rows: the gate rows of 128 features, then their up rows; the last
-    block is filled with zero rows."""
+    """One matrix ``[2 P, hidden]``, P = the feature count rounded up to a multiple of 128: the gate rows,
+    zero rows up to P, then the up rows in the same way."""
     inter, hidden = gate.shape
-    nb = -(-inter // 128)
-    out = torch.zeros((nb, 2, 128, hidden), dtype=gate.dtype, device=gate.device)
-    flat = out.view(nb, 2, 128 * hidden)
-    full = inter // 128
-    if full:
-        out[:full, 0] = gate[:full * 128].view(full, 128, hidden)
-        out[:full, 1] = up[:full * 128].view(full, 128, hidden)
-    rest = inter - full * 128
-    if rest:
-        out[full, 0, :rest] = gate[full * 128:]
-        out[full, 1, :rest] = up[full * 128:]
-    del flat
-    return out.view(nb * 256, hidden)
+    pad = -(-inter // 128) * 128
+    out = torch.zeros((2, pad, hidden), dtype=gate.dtype, device=gate.device)
+    out[0, :inter] = gate
+    out[1, :inter] = up
+    return out.view(2 * pad, hidden)
 
 
 def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor) -> None:

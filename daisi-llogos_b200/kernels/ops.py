@@ -230,7 +230,8 @@ def gemm_tc_splits(k: int, wish: int) -> int:
 
 
 def gated_rows(features: int) -> int:
-    """Rows of a gate/up matrix in the gated layout: blocks of 128 gate rows + 128 up rows."""
+    """Rows of a gate/up matrix in the gated layout: the gate rows, filled up to a multiple of 128, then
+    the up rows in the same way."""
     return -(-features // 128) * 256
 
 
@@ -317,7 +318,7 @@ def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """out[n, i] = silu(g) * u; the summed partials ``[S, N, gated_rows(I)]`` hold g and u in the gated
-    layout (blocks of 128 gate values followed by the 128 up values of the same features)."""
+    layout (g of feature i at i, u at ``gated_rows(I) / 2 + i``)."""
     lib = _lib("elementwise")
     s, n, two_i = gate_up.shape
     inter = out.shape[1]

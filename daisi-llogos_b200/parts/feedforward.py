@@ -2,8 +2,8 @@
 
 ``SwiGLU``: ``down( silu(gate(x)) * up(x) )`` without biases
 (Inference/ForwardPass.cs:242-246; silu(g) = g / (1 + exp(-g)), Daisi.Llogos.Cpu/Silu.cs:9-16).
-The gate and up matrices are stored as one matrix in blocks of 256 rows (128 gate rows, then the up
-rows of the same features), so that the gating is the epilogue of one product.
+The gate and up matrices are stored as one matrix (gate rows, then up rows, each part filled up to a
+multiple of 128 rows), so that the gating is the epilogue of one product.
 """
 from __future__ import annotations
 

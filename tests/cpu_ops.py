@@ -106,9 +106,8 @@ def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, 
 def silu_mul(gate_up, out):
     x = gate_up.float().sum(0)
     inter = out.shape[1]
-    i = torch.arange(inter)
-    at = (i // 128) * 256 + i % 128
-    g, u = x[:, at], x[:, at + 128]
+    half = x.shape[1] // 2
+    g, u = x[:, :inter], x[:, half:half + inter]
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 

@@ -147,9 +147,8 @@ def test_silu_mul(ops, dtype, partials):
     out = torch.empty(n, inter, dtype=dtype, device=DEV)
     ops.silu_mul(gu.to(DEV), out)
     s = gu.double().sum(0)
-    i = torch.arange(inter)
-    at = (i // 128) * 256 + i % 128
-    g, u = s[:, at], s[:, at + 128]
+    half = ops.gated_rows(inter) // 2
+    g, u = s[:, :inter], s[:, half:half + inter]
     check(out, g / (1 + torch.exp(-g)) * u, dtype)
 
 

@@ -80,12 +80,13 @@ def test_loader_binds_and_keeps_types(llogos, model_dirs):
     m = llogos.weights.load_model(model_dirs["llama"], dtype=torch.bfloat16, device="cpu", ops=cpu_ops)
     att = m.blocks[0].parts["mixer"]
     assert att.w_qkv.shape == ((4 + 2 * 2) * 16, 64) and att.w_qkv.dtype == torch.bfloat16
-    gu = m.blocks[1].parts["ffn"].w_gate_up          # blocks of 128 gate rows + 128 up rows, zero filled
+    gu = m.blocks[1].parts["ffn"].w_gate_up          # 176 gate rows, zero rows up to 256, then the up rows likewise
     assert gu.shape == (512, 64)
     w = read_weights(llogos, model_dirs["llama"])
     g, u = w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"]
-    assert torch.equal(gu[0:128], g[:128]) and torch.equal(gu[128:256], u[:128])
-    assert torch.equal(gu[256:304], g[128:]) and torch.equal(gu[384:432], u[128:]) and float(gu[304:384].abs().sum()) == 0
+    assert g.shape[0] == 176
+    assert torch.equal(gu[0:176], g) and torch.equal(gu[256:432], u)
+    assert float(gu[176:256].abs().sum()) == 0 and float(gu[432:512].abs().sum()) == 0
     m32 = llogos.weights.load_model(model_dirs["llama"], dtype=torch.float32, device="cpu", ops=cpu_ops)
     assert m32.blocks[0].parts["mixer"].w_qkv.dtype == torch.float32
     assert torch.equal(m32.blocks[0].parts["mixer"].w_qkv, att.w_qkv.float())
