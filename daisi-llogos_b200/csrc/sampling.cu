@@ -11,6 +11,15 @@
 //
 // The uniform number of (seed, sequence id, step) comes from a counter-based generator, so a
 // sequence's tokens do not depend on what else is in its batch.
+//
+// Two ways through the pipeline.  The general one works on the whole vocabulary in global memory,
+// one block per sequence (some seventy passes).  With top-k up to 64, the common case, the
+// vocabulary is first cut into slices of 8192 logits, one block per (slice, sequence): a block
+// keeps its logits in registers, finds its own k-th largest and passes on what reaches it, in index
+// order.  No slice can hold k logits above the k-th largest of the whole row, so every token that
+// top-k keeps is among these candidates; a second kernel runs the same filters and the same draw
+// on the candidates alone (a few thousand at most, in shared memory).  A slice with more than 64
+// candidates (ties) sends its row through the general way.
 #include "common.cuh"
 
 LLG_API const char* llg_last_error() { return g_llg_error; }
@@ -128,7 +137,18 @@ struct SampleArgs {
   int step;
   const int* banned;       // [n_banned] tokens whose logit becomes -inf (PreventEOS), or null
   int n_banned;
+  float* cand_val;         // [B][n_slices][CAND_CAP] scaled logits of the candidates, or null
+  int* cand_idx;           // [B][n_slices][CAND_CAP] their tokens
+  int* cand_count;         // [B][n_slices] candidates found (more than CAND_CAP: the row takes the general way)
+  int n_slices;
 };
+
+constexpr int SLICE_PER = 8;                       // logits per thread of a slice's block
+constexpr int SLICE_LEN = THREADS * SLICE_PER;     // logits per slice
+constexpr int CAND_CAP = 64;                       // candidates a slice may pass on (and largest top-k of this way)
+constexpr int MAX_SLICES = 64;
+constexpr int HIST_MAX = 256;                      // recent tokens the slice kernel takes
+constexpr int BANNED_MAX = 64;
 
 // k-th largest value (k >= 1) of key(x[i]) over elements with keep(i); bisection over the 32 key bits.
 template <typename KeyFn>
@@ -144,70 +164,24 @@ __device__ unsigned kth_largest_key(int n, int k, KeyFn key, int* is) {
   return lo;
 }
 
-__global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
-  __shared__ float fs[32];
-  __shared__ int is[32];
-  __shared__ int chosen;
-  const int b = blockIdx.x, n = a.vocab, tid = threadIdx.x;
-  const float* logits = a.logits + (long long)b * n;
-  float* w = a.work + (long long)b * n;
+// New value of token t's logit `v` that occurs `count` times among the recent tokens.
+__device__ __forceinline__ float penalised(const SampleArgs& a, float v, int count) {
+  if (a.repetition_penalty != 1.0f) {
+    // applied once per occurrence in the window, as the reference's loop does
+    for (int c = 0; c < count; ++c) v = v > 0.f ? v / a.repetition_penalty : v * a.repetition_penalty;
+  }
+  if (a.frequency_penalty != 0.f || a.presence_penalty != 0.f)
+    v -= a.frequency_penalty * (float)count + a.presence_penalty;
+  return v;
+}
 
-  // 1. copy, penalties over the recent tokens, banned tokens
-  for (int i = tid; i < n; i += THREADS) w[i] = logits[i];
-  __syncthreads();
-  const bool penal = a.history && (a.repetition_penalty != 1.0f || a.frequency_penalty != 0.f ||
-                                   a.presence_penalty != 0.f);
-  if (penal) {
-    const int hl = a.history_len[b];
-    const int* hist = a.history + (long long)b * a.history_stride;
-    // One thread per distinct recent token: the first occurrence owns the token.
-    for (int j = tid; j < hl; j += THREADS) {
-      const int t = hist[j];
-      if (t < 0 || t >= n) continue;
-      if (!a.penalize_newline && (t == 10 || t == 13)) continue;
-      int count = 0;
-      bool first = true;
-      for (int q = 0; q < hl; ++q)
-        if (hist[q] == t) {
-          if (q < j) first = false;
-          ++count;
-        }
-      if (!first) continue;
-      float v = w[t];
-      if (a.repetition_penalty != 1.0f) {
-        // applied once per occurrence in the window, as the reference's loop does
-        for (int c = 0; c < count; ++c) v = v > 0.f ? v / a.repetition_penalty : v * a.repetition_penalty;
-      }
-      if (a.frequency_penalty != 0.f || a.presence_penalty != 0.f)
-        v -= a.frequency_penalty * (float)count + a.presence_penalty;
-      w[t] = v;
-    }
-    __syncthreads();
-  }
-  for (int j = tid; j < a.n_banned; j += THREADS) {
-    const int t = a.banned[j];
-    if (t >= 0 && t < n) w[t] = -INFINITY;
-  }
-  __syncthreads();
+// Filters and draw for sequence b over w[0..n): scaled logits in, probabilities left behind.  `map` (or null)
+// gives the token of entry i; entries are in the order of their tokens.  mx = the largest scaled logit.
+__device__ void filter_and_draw(const SampleArgs& a, int b, float* w, int n, const int* map, float mx,
+                                float* fs, int* is, int* chosen_slot, float* scan) {
+  const int tid = threadIdx.x;
+  int& chosen = *chosen_slot;
 
-  // 2. greedy
-  if (a.temperature == 0.f) {
-    const int r = block_argmax(w, n, fs, is);
-    if (tid == 0) a.out[b] = r;
-    if (a.probs_out)
-      for (int i = tid; i < n; i += THREADS) a.probs_out[(long long)b * n + i] = i == r ? 1.f : 0.f;
-    return;
-  }
-
-  // 3. temperature
-  const float inv_t = 1.0f / a.temperature;
-  float mx = -INFINITY;
-  for (int i = tid; i < n; i += THREADS) {
-    const float v = w[i] * inv_t;
-    w[i] = v;
-    mx = fmaxf(mx, v);
-  }
-  mx = block_max(mx, fs);
   const int min_keep = a.min_keep > 1 ? a.min_keep : 1;
 
   // 4. top-k and min-p as one lower bound on the scaled logit
@@ -311,8 +285,16 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
     }
     __syncthreads();
   }
-  if (a.probs_out)
-    for (int i = tid; i < n; i += THREADS) a.probs_out[(long long)b * n + i] = w[i];
+  if (a.probs_out) {
+    float* po = a.probs_out + (long long)b * a.vocab;
+    if (map) {
+      for (int i = tid; i < a.vocab; i += THREADS) po[i] = 0.f;
+      __syncthreads();
+      for (int i = tid; i < n; i += THREADS) po[map[i]] = w[i];
+    } else {
+      for (int i = tid; i < n; i += THREADS) po[i] = w[i];
+    }
+  }
 
   // 8. draw: first index whose cumulative probability exceeds u * total
   const int seq = a.seq_ids ? a.seq_ids[b] : b;
@@ -322,7 +304,6 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
   float mine = 0.f;
   for (int i = i0; i < i1; ++i) mine += w[i];
   // inclusive scan of the per-thread sums
-  __shared__ float scan[THREADS];
   scan[tid] = mine;
   __syncthreads();
   for (int o = 1; o < THREADS; o <<= 1) {
@@ -361,8 +342,222 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
     if (tid == 0) chosen = r;
     __syncthreads();
   }
-  if (tid == 0) a.out[b] = chosen;
+  if (tid == 0) a.out[b] = map ? map[chosen] : chosen;
 }
+
+// The general way: the whole vocabulary of sequence b, in global memory.
+__device__ void sample_full(const SampleArgs& a, int b, float* fs, int* is, int* chosen_slot, float* scan) {
+  const int n = a.vocab, tid = threadIdx.x;
+  const float* logits = a.logits + (long long)b * n;
+  float* w = a.work + (long long)b * n;
+
+  // 1. copy, penalties over the recent tokens, banned tokens
+  for (int i = tid; i < n; i += THREADS) w[i] = logits[i];
+  __syncthreads();
+  const bool penal = a.history && (a.repetition_penalty != 1.0f || a.frequency_penalty != 0.f ||
+                                   a.presence_penalty != 0.f);
+  if (penal) {
+    const int hl = a.history_len[b];
+    const int* hist = a.history + (long long)b * a.history_stride;
+    // One thread per distinct recent token: the first occurrence owns the token.
+    for (int j = tid; j < hl; j += THREADS) {
+      const int t = hist[j];
+      if (t < 0 || t >= n) continue;
+      if (!a.penalize_newline && (t == 10 || t == 13)) continue;
+      int count = 0;
+      bool first = true;
+      for (int q = 0; q < hl; ++q)
+        if (hist[q] == t) {
+          if (q < j) first = false;
+          ++count;
+        }
+      if (!first) continue;
+      w[t] = penalised(a, w[t], count);
+    }
+    __syncthreads();
+  }
+  for (int j = tid; j < a.n_banned; j += THREADS) {
+    const int t = a.banned[j];
+    if (t >= 0 && t < n) w[t] = -INFINITY;
+  }
+  __syncthreads();
+
+  // 2. greedy
+  if (a.temperature == 0.f) {
+    const int r = block_argmax(w, n, fs, is);
+    if (tid == 0) a.out[b] = r;
+    if (a.probs_out)
+      for (int i = tid; i < n; i += THREADS) a.probs_out[(long long)b * n + i] = i == r ? 1.f : 0.f;
+    return;
+  }
+
+  // 3. temperature
+  const float inv_t = 1.0f / a.temperature;
+  float mx = -INFINITY;
+  for (int i = tid; i < n; i += THREADS) {
+    const float v = w[i] * inv_t;
+    w[i] = v;
+    mx = fmaxf(mx, v);
+  }
+  mx = block_max(mx, fs);
+  filter_and_draw(a, b, w, n, nullptr, mx, fs, is, chosen_slot, scan);
+}
+
+__global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
+  __shared__ float fs[32];
+  __shared__ int is[32];
+  __shared__ int chosen;
+  __shared__ float scan[THREADS];
+  sample_full(a, blockIdx.x, fs, is, &chosen, scan);
+}
+
+// Exclusive prefix sum of v over the block's threads; *total gets the sum.
+__device__ int block_exclusive_scan_int(int v, int* scratch, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  int wsum = lane < (THREADS >> 5) ? scratch[lane] : 0;
+  int wincl = wsum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, wincl, o);
+    if (lane >= o) wincl += t;
+  }
+  *total = __shfl_sync(0xffffffffu, wincl, 31);
+  const int before_warp = __shfl_sync(0xffffffffu, wincl - wsum, warp);
+  return before_warp + incl - v;
+}
+
+// First stage of the candidate way: block (slice, sequence) keeps SLICE_LEN scaled logits in registers and
+// passes on those that reach its own top_k-th largest, in index order.
+__global__ void __launch_bounds__(THREADS) sample_candidates_kernel(SampleArgs a) {
+  __shared__ int is[32];
+  __shared__ int pen_tok[HIST_MAX];
+  __shared__ float pen_val[HIST_MAX];
+  const int s = blockIdx.x, b = blockIdx.y, n = a.vocab, tid = threadIdx.x;
+  const float* logits = a.logits + (long long)b * n;
+  const int i0 = s * SLICE_LEN + tid * SLICE_PER;
+  float v[SLICE_PER];
+#pragma unroll
+  for (int e = 0; e < SLICE_PER; ++e) v[e] = i0 + e < n ? logits[i0 + e] : -INFINITY;
+  const bool penal = a.history && (a.repetition_penalty != 1.0f || a.frequency_penalty != 0.f ||
+                                   a.presence_penalty != 0.f);
+  if (penal) {
+    const int hl = min(a.history_len[b], HIST_MAX);
+    const int* hist = a.history + (long long)b * a.history_stride;
+    for (int j = tid; j < hl; j += THREADS) {      // the first occurrence of a token owns it
+      const int t = hist[j];
+      int owner = t;
+      int count = 0;
+      if (t < 0 || t >= n || (!a.penalize_newline && (t == 10 || t == 13))) owner = -1;
+      for (int q = 0; q < hl; ++q)
+        if (hist[q] == t) {
+          if (q < j) owner = -1;
+          ++count;
+        }
+      pen_tok[j] = owner;
+      pen_val[j] = owner >= 0 ? penalised(a, logits[t], count) : 0.f;
+    }
+    __syncthreads();
+    for (int j = 0; j < hl; ++j) {
+      const int d = pen_tok[j] - i0;
+      if (pen_tok[j] >= 0 && d >= 0 && d < SLICE_PER) {
+#pragma unroll
+        for (int e = 0; e < SLICE_PER; ++e)
+          if (e == d) v[e] = pen_val[j];
+      }
+    }
+  }
+  for (int j = 0; j < a.n_banned; ++j) {
+    const int d = a.banned[j] - i0;
+    if (d >= 0 && d < SLICE_PER) {
+#pragma unroll
+      for (int e = 0; e < SLICE_PER; ++e)
+        if (e == d) v[e] = -INFINITY;
+    }
+  }
+  const float inv_t = 1.0f / a.temperature;
+#pragma unroll
+  for (int e = 0; e < SLICE_PER; ++e) v[e] *= inv_t;
+  // the slice's top_k-th largest (bisection over the key bits, counts from registers)
+  unsigned lo = 0u;
+  for (int bit = 31; bit >= 0; --bit) {
+    const unsigned t = lo | (1u << bit);
+    int c = 0;
+#pragma unroll
+    for (int e = 0; e < SLICE_PER; ++e) c += f2key(v[e]) >= t ? 1 : 0;
+    c = block_sum_int(c, is);
+    if (c >= a.top_k) lo = t;
+  }
+  const float thr = key2f(lo);
+  int cnt = 0;
+#pragma unroll
+  for (int e = 0; e < SLICE_PER; ++e) cnt += (v[e] >= thr && v[e] > -INFINITY) ? 1 : 0;
+  int total;
+  int pos = block_exclusive_scan_int(cnt, is, &total);
+  const long long base = ((long long)b * a.n_slices + s) * CAND_CAP;
+#pragma unroll
+  for (int e = 0; e < SLICE_PER; ++e) {
+    if (v[e] >= thr && v[e] > -INFINITY) {
+      if (pos < CAND_CAP) {
+        a.cand_val[base + pos] = v[e];
+        a.cand_idx[base + pos] = i0 + e;
+      }
+      ++pos;
+    }
+  }
+  if (tid == 0) a.cand_count[(long long)b * a.n_slices + s] = total;
+}
+
+// Second stage: the candidates of sequence b, gathered in index order, go through the filters and the draw.
+__global__ void __launch_bounds__(THREADS) sample_from_candidates_kernel(SampleArgs a) {
+  __shared__ float fs[32];
+  __shared__ int is[32];
+  __shared__ int chosen;
+  __shared__ float scan[THREADS];
+  __shared__ float cw[MAX_SLICES * CAND_CAP];
+  __shared__ int cidx[MAX_SLICES * CAND_CAP];
+  __shared__ int offs[MAX_SLICES + 1];
+  __shared__ int overflow;
+  const int b = blockIdx.x, tid = threadIdx.x, ns = a.n_slices;
+  if (tid == 0) {
+    int o = 0, ov = 0;
+    for (int s = 0; s < ns; ++s) {
+      const int c = a.cand_count[(long long)b * ns + s];
+      if (c > CAND_CAP) ov = 1;
+      offs[s] = o;
+      o += min(c, CAND_CAP);
+    }
+    offs[ns] = o;
+    overflow = ov;
+  }
+  __syncthreads();
+  if (overflow) {                                  // uniform over the block
+    sample_full(a, b, fs, is, &chosen, scan);
+    return;
+  }
+  const int n_c = offs[ns];
+  for (int g = tid; g < ns * CAND_CAP; g += THREADS) {
+    const int s = g / CAND_CAP, j = g % CAND_CAP;
+    if (j < offs[s + 1] - offs[s]) {
+      cw[offs[s] + j] = a.cand_val[((long long)b * ns + s) * CAND_CAP + j];
+      cidx[offs[s] + j] = a.cand_idx[((long long)b * ns + s) * CAND_CAP + j];
+    }
+  }
+  __syncthreads();
+  float mx = -INFINITY;
+  for (int i = tid; i < n_c; i += THREADS) mx = fmaxf(mx, cw[i]);
+  mx = block_max(mx, fs);
+  filter_and_draw(a, b, cw, n_c, cidx, mx, fs, is, &chosen, scan);
+}
+
 
 }  // namespace
 
@@ -374,6 +569,11 @@ LLG_API int llg_argmax(const float* logits, int n_seqs, int vocab, int* out, cud
   return llg_check_launch("argmax");
 }
 
+// Slices that the candidate way cuts a vocabulary into, and the candidates a slice may pass on: the caller
+// gives cand_val / cand_idx as [n_seqs][slices][cap] and cand_count as [n_seqs][slices] (or leaves them null).
+LLG_API int llg_sample_slices(int vocab) { return (vocab + SLICE_LEN - 1) / SLICE_LEN; }
+LLG_API int llg_sample_candidate_cap() { return CAND_CAP; }
+
 LLG_API int llg_sample(const SampleArgs* args, cudaStream_t stream) {
   const SampleArgs& a = *args;
   LLG_REQUIRE(a.n_seqs >= 0 && a.vocab > 0, "sample: bad sizes");
@@ -382,6 +582,17 @@ LLG_API int llg_sample(const SampleArgs* args, cudaStream_t stream) {
   LLG_REQUIRE(!(a.history) || (a.history_len && a.history_stride > 0), "sample: history needs lengths and a stride");
   LLG_REQUIRE(a.repetition_penalty > 0.f, "sample: repetition penalty must be positive");
   if (a.n_seqs == 0) return 0;
-  sample_kernel<<<a.n_seqs, THREADS, 0, stream>>>(a);
+  const int slices = (a.vocab + SLICE_LEN - 1) / SLICE_LEN;
+  const bool by_candidates = a.cand_val && a.cand_idx && a.cand_count && a.n_slices == slices && slices <= MAX_SLICES &&
+                             a.temperature > 0.f && a.top_k > 0 && a.top_k <= CAND_CAP && a.top_k < a.vocab &&
+                             a.min_keep <= a.top_k && (!a.history || a.history_stride <= HIST_MAX) &&
+                             a.n_banned <= BANNED_MAX && a.n_seqs <= 65535;
+  if (by_candidates) {
+    sample_candidates_kernel<<<dim3(slices, a.n_seqs), THREADS, 0, stream>>>(a);
+    if (llg_check_launch("sample (candidates)")) return 1;
+    sample_from_candidates_kernel<<<a.n_seqs, THREADS, 0, stream>>>(a);
+  } else {
+    sample_kernel<<<a.n_seqs, THREADS, 0, stream>>>(a);
+  }
   return llg_check_launch("sample");
 }

@@ -115,6 +115,7 @@ class _SampleArgs(Structure):
         ("repetition_penalty", c_float), ("frequency_penalty", c_float), ("presence_penalty", c_float),
         ("penalize_newline", c_int), ("seed", c_ulonglong), ("step", c_int),
         ("banned", c_void_p), ("n_banned", c_int),
+        ("cand_val", c_void_p), ("cand_idx", c_void_p), ("cand_count", c_void_p), ("n_slices", c_int),
     ]
 
 
@@ -161,6 +162,7 @@ def _lib(name: str):
     elif name == "sampling":
         lib.llg_argmax.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.llg_sample.argtypes = [POINTER(_SampleArgs), c_void_p]
+        lib.llg_sample_slices.argtypes = [c_int]
     _protos_done.add(name)
     return lib
 
@@ -466,8 +468,11 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
            penalize_newline: bool = False, seed: int = 0, step: int = 0,
            seq_ids: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None,
            history_len: Optional[torch.Tensor] = None, banned: Optional[torch.Tensor] = None,
-           probs_out: Optional[torch.Tensor] = None) -> None:
-    """One token per row of ``logits`` by the sampling pipeline of csrc/sampling.cu."""
+           probs_out: Optional[torch.Tensor] = None, candidates: bool = True) -> None:
+    """One token per row of ``logits`` by the sampling pipeline of csrc/sampling.cu.
+
+    ``candidates=False`` keeps the kernels on the general way over the whole vocabulary (tests compare the
+    two ways)."""
     lib = _lib("sampling")
     b, v = logits.shape
     assert work.numel() >= b * v and work.dtype == torch.float32
@@ -487,4 +492,17 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
     a.seed, a.step = int(seed) & 0xFFFFFFFFFFFFFFFF, int(step)
     if banned is not None and banned.numel():
         a.banned, a.n_banned = _ptr(banned, torch.int32), banned.numel()
+    if candidates:
+        # scratch of the two-stage way (top-k up to the candidate cap): the kernels decide whether they take it
+        slices, cap = lib.llg_sample_slices(v), lib.llg_sample_candidate_cap()
+        key = (logits.device, b, slices)
+        ws = _sample_scratch.get(key)
+        if ws is None:
+            ws = _sample_scratch[key] = (torch.empty(b * slices * cap, dtype=torch.float32, device=logits.device),
+                                         torch.empty(b * slices * cap, dtype=torch.int32, device=logits.device),
+                                         torch.empty(b * slices, dtype=torch.int32, device=logits.device))
+        a.cand_val, a.cand_idx, a.cand_count, a.n_slices = _ptr(ws[0]), _ptr(ws[1]), _ptr(ws[2]), slices
     _check(lib, lib.llg_sample(byref(a), _stream()))
+
+
+_sample_scratch = {}

@@ -400,6 +400,46 @@ def test_sampler_distribution_and_draw(ops, case):
         assert int(out[i]) == P.draw(got, P.uniform_of(11, int(seq_ids[i]), 5))
 
 
+@pytest.mark.parametrize("case", [dict(temperature=0.7, top_k=40, top_p=0.9, repetition_penalty=1.1),
+                                  dict(temperature=1.0, top_k=64, min_p=0.02, typical_p=0.8, frequency_penalty=0.3),
+                                  dict(temperature=1.4, top_k=1), dict(temperature=0.9, top_k=7, min_keep=5, top_p=0.3),
+                                  dict(temperature=0.8, top_k=33, banned=[5, 9000, 20010])])
+def test_sampler_by_candidates_equals_the_general_way(ops, case):
+    """With top-k up to 64 the vocabulary is cut into slices whose best tokens alone reach the filters: the
+    distribution and the draw are those of the general way over the whole vocabulary, also when the recent
+    tokens and the banned ones lie in different slices, and when ties at a slice's k-th value overflow its
+    64 candidates (that row then takes the general way)."""
+    c = dict(case)
+    banned = c.pop("banned", None)
+    vocab, b = 20011, 5                       # three slices of 8192, the last one short
+    logits = rnd((b, vocab), 70, scale=3.0)
+    logits[1, 100:400] = 9.5                  # 300 equal logits at the top of a slice: more ties than candidates fit
+    logits[2, 8190:8194] = 12.0               # the best tokens straddle a slice boundary
+    logits[3, 19000:] = -50.0                 # a short last slice with nothing worth keeping
+    g = torch.Generator().manual_seed(71)
+    hist = torch.randint(0, vocab, (b, 64), generator=g, dtype=torch.int32)
+    hist[:, 7] = hist[:, 3]
+    hist[2, 0], hist[2, 1], hist[2, 2] = 8191, 8192, 8193
+    hl = torch.tensor([64, 20, 64, 0, 33], dtype=torch.int32)
+    seq_ids = torch.tensor([3, 1, 4, 1, 5], dtype=torch.int32)
+    res = []
+    for cand in (True, False):
+        work = torch.empty(b * vocab, device=DEV)
+        out = torch.empty(b, dtype=torch.int32, device=DEV)
+        probs = torch.full((b, vocab), float("nan"), device=DEV)
+        ops.sample(logits.to(DEV), work, out, seed=13, step=2, history=hist.to(DEV), history_len=hl.to(DEV),
+                   probs_out=probs, seq_ids=seq_ids.to(DEV), candidates=cand,
+                   banned=None if banned is None else torch.tensor(banned, dtype=torch.int32, device=DEV), **c)
+        res.append((out.cpu(), probs.cpu()))
+    assert torch.equal(res[0][0], res[1][0])
+    assert ((res[0][1] > 0) == (res[1][1] > 0)).all()
+    assert float((res[0][1] - res[1][1]).abs().max()) < 1e-6
+    for i in (0, 2):
+        ref = P.sampling_distribution(logits[i].tolist(), previous=hist[i, :hl[i]].tolist(), banned=banned or (), **c)
+        assert float((res[0][1][i].double() - ref).abs().max()) < 2e-6
+        assert int(res[0][0][i]) == P.draw(res[0][1][i].double(), P.uniform_of(13, int(seq_ids[i]), 2))
+
+
 def test_sampler_draws_follow_the_distribution(ops):
     vocab = 37
     logits = rnd((1, vocab), 62, scale=1.5).repeat(512, 1)
