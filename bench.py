@@ -31,6 +31,21 @@ LLAMA_8B = {
     "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                      "original_max_position_embeddings": 8192},
 }
+# The other two shapes that the reference's numbers are quoted on; the default run keeps the first.
+QWEN3_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 36, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+    "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 40960,
+    "attention_bias": False, "tie_word_embeddings": False,
+}
+QWEN25_14B = {
+    "architectures": ["Qwen2ForCausalLM"], "num_hidden_layers": 48, "hidden_size": 5120,
+    "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 13824,
+    "vocab_size": 152064, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 131072,
+    "tie_word_embeddings": False,
+}
+SHAPES = {"llama-3.1-8b": ("Llama-3.1-8B shape", LLAMA_8B), "qwen3-8b": ("Qwen3-8B shape", QWEN3_8B),
+          "qwen2.5-14b": ("Qwen2.5-14B shape", QWEN25_14B)}
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
 
@@ -105,8 +120,10 @@ def main():
     ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=LLAMA_8B["num_hidden_layers"],
-                    help="layers to build (the configuration has 32); both numbers are reported")
+    ap.add_argument("--shape", default="llama-3.1-8b", choices=sorted(SHAPES), help="layer sizes (default: the headline shape)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="context length of the decode steps (default 8192)")
+    ap.add_argument("--layers", type=int, default=0,
+                    help="layers to build (default: all of the shape's); both numbers are reported")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
@@ -128,7 +145,11 @@ def main():
     L = importlib.import_module("llogos_b200")
     ops = importlib.import_module("daisi-llogos_b200.kernels.ops")
     pk = peaks()
-    cfg = dict(LLAMA_8B, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    if args.layers <= 0:
+        args.layers = shape["num_hidden_layers"]
+    context = args.context
+    cfg = dict(shape, num_hidden_layers=args.layers)
     nums = model_numbers(cfg, args.layers)
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
@@ -136,7 +157,11 @@ def main():
     t0 = time.time()
     model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
     big = args.batch if args.no_points else max(64, args.batch)
-    engine = L.engine.Engine(model, max_tokens=big * CONTEXT, max_seq_len=CONTEXT, n_slots=big)
+    weight_gb = (nums["matrix_params"] + 2 * nums["head_params"]) * 2 / 1e9
+    if weight_gb + big * context * nums["kv_bytes_per_token"] / 1e9 > 165.0:
+        # the cache of 64 sequences at this context does not fit beside the weights: no batch-64 point
+        big = args.batch
+    engine = L.engine.Engine(model, max_tokens=big * context, max_seq_len=context, n_slots=big)
     for g in engine.cache.kv_groups:             # random keys and values: attention over real numbers
         for t in list(g.k.values()) + list(g.v.values()):
             t.normal_(0.0, 1.0)
@@ -183,7 +208,7 @@ def main():
     # ---- decode steps at the context length --------------------------------------------------
     def decode(batch, steps, warmup, clocks=None):
         slots = [engine.open() for _ in range(batch)]
-        start = CONTEXT - (steps + warmup)
+        start = context - (steps + warmup)
         for s in slots:
             engine.assume(s, start)
         tok = torch.randint(0, cfg["vocab_size"], (steps + warmup, batch), generator=gen).tolist()
@@ -221,6 +246,9 @@ def main():
     points = {}
     if not args.no_points:
         for b in (1, 64):
+            if b > big:
+                points[f"decode_b{b}"] = None
+                continue
             pms, _, _ = decode(b, max(8, args.steps // 2), args.warmup)
             points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
             print(f"[bench] decode b{b}: {pms:.3f} ms/step", file=sys.stderr, flush=True)
@@ -230,13 +258,13 @@ def main():
     if not args.no_e2e:
         del engine
         torch.cuda.empty_cache()
-        api = L.LlogosModel(model, max_context=CONTEXT, max_batch=args.batch)
+        api = L.LlogosModel(model, max_context=context, max_batch=args.batch)
         # A request's own prompt (8 x 8k tokens, most of a second at the power cap) leaves the SM clock
         # throttled for the first twenty or so decode steps; they are run untimed, as warm-up steps are,
         # and the K steps after them are timed on the host from the moments their tokens arrive.
         untimed = max(args.warmup, 32)
         n_new = untimed + args.steps
-        prompts = [torch.randint(0, cfg["vocab_size"], (CONTEXT - n_new - 1,), generator=gen).tolist() for _ in range(args.batch)]
+        prompts = [torch.randint(0, cfg["vocab_size"], (context - n_new - 1,), generator=gen).tolist() for _ in range(args.batch)]
         params = L.GenerationParams.greedy_params(n_new, stop_tokens=())
         api.generate([p[:64] for p in prompts], L.GenerationParams.greedy_params(args.warmup + 2, stop_tokens=()))   # warm-up: graph capture
         stamps = []
@@ -256,16 +284,17 @@ def main():
         print(f"[bench] e2e {e2e}", file=sys.stderr, flush=True)
 
     line = {
-        "metric": "decode tokens/s at batch 8, context 8192 (Llama-3.1-8B shape, bf16, random weights)",
+        "metric": f"decode tokens/s at batch {args.batch}, context {context} ({shape_name}, bf16, random weights)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids, random cache contents",
         "impl": "ours",
-        "config": {"model": "Llama-3.1-8B shape", "layers": args.layers, "layers_of_config": LLAMA_8B["num_hidden_layers"],
+        "config": {"model": shape_name, "layers": args.layers, "layers_of_config": shape["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "rope_theta": cfg["rope_theta"], "rope_scaling": "llama3 factor 8 low 1 high 4 original 8192",
-                   "global_batch": args.batch, "seq_len": CONTEXT, "parallelism": "single GPU",
+                   "rope_theta": cfg["rope_theta"],
+                   "rope_scaling": "llama3 factor 8 low 1 high 4 original 8192" if cfg.get("rope_scaling") else "none",
+                   "global_batch": args.batch, "seq_len": context, "parallelism": "single GPU",
                    "l2": "every step reads more than L2 holds (weights + cache), no flush",
                    "cache": "pages of 64 tokens, bf16", "decode": "CUDA graph per batch size"},
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
