@@ -123,8 +123,8 @@ struct SampleArgs {
   int* out;                // [B]
   float* probs_out;        // [B][V] or null: the distribution drawn from (for tests)
   const int* seq_ids;      // [B] or null (then the row index)
-  const int* history;      // [B][history_stride] recent tokens, or null
-  const int* history_len;  // [B]
+  int* history;            // [rows][history_stride] recent tokens, or null; row of sequence b: history_rows[b], else b
+  int* history_len;        // [rows] tokens seen so far (the row holds the last min(len, stride) of them, as a ring)
   int history_stride;
   int n_seqs, vocab;
   float temperature;
@@ -141,7 +141,21 @@ struct SampleArgs {
   int* cand_idx;           // [B][n_slices][CAND_CAP] their tokens
   int* cand_count;         // [B][n_slices] candidates found (more than CAND_CAP: the row takes the general way)
   int n_slices;
+  const int* history_rows; // [B] or null
+  int history_append;      // 1: the drawn token is written into the sequence's ring and its count goes up
 };
+
+__device__ __forceinline__ int history_row(const SampleArgs& a, int b) { return a.history_rows ? a.history_rows[b] : b; }
+
+// The kernel that has drawn `token` for sequence b keeps the ring of recent tokens up to date, so that the host
+// need not send the history again (one thread calls this, after every read of the ring in this launch).
+__device__ __forceinline__ void history_push(const SampleArgs& a, int b, int token) {
+  if (!a.history || !a.history_append) return;
+  const int row = history_row(a, b);
+  const int len = a.history_len[row];
+  a.history[(long long)row * a.history_stride + len % a.history_stride] = token;
+  a.history_len[row] = len + 1;
+}
 
 constexpr int SLICE_PER = 8;                       // logits per thread of a slice's block
 constexpr int SLICE_LEN = THREADS * SLICE_PER;     // logits per slice
@@ -342,7 +356,11 @@ __device__ void filter_and_draw(const SampleArgs& a, int b, float* w, int n, con
     if (tid == 0) chosen = r;
     __syncthreads();
   }
-  if (tid == 0) a.out[b] = map ? map[chosen] : chosen;
+  if (tid == 0) {
+    const int token = map ? map[chosen] : chosen;
+    a.out[b] = token;
+    history_push(a, b, token);
+  }
 }
 
 // The general way: the whole vocabulary of sequence b, in global memory.
@@ -357,8 +375,8 @@ __device__ void sample_full(const SampleArgs& a, int b, float* fs, int* is, int*
   const bool penal = a.history && (a.repetition_penalty != 1.0f || a.frequency_penalty != 0.f ||
                                    a.presence_penalty != 0.f);
   if (penal) {
-    const int hl = a.history_len[b];
-    const int* hist = a.history + (long long)b * a.history_stride;
+    const int hl = min(a.history_len[history_row(a, b)], a.history_stride);
+    const int* hist = a.history + (long long)history_row(a, b) * a.history_stride;
     // One thread per distinct recent token: the first occurrence owns the token.
     for (int j = tid; j < hl; j += THREADS) {
       const int t = hist[j];
@@ -385,7 +403,10 @@ __device__ void sample_full(const SampleArgs& a, int b, float* fs, int* is, int*
   // 2. greedy
   if (a.temperature == 0.f) {
     const int r = block_argmax(w, n, fs, is);
-    if (tid == 0) a.out[b] = r;
+    if (tid == 0) {
+      a.out[b] = r;
+      history_push(a, b, r);
+    }
     if (a.probs_out)
       for (int i = tid; i < n; i += THREADS) a.probs_out[(long long)b * n + i] = i == r ? 1.f : 0.f;
     return;
@@ -450,8 +471,8 @@ __global__ void __launch_bounds__(THREADS) sample_candidates_kernel(SampleArgs a
   const bool penal = a.history && (a.repetition_penalty != 1.0f || a.frequency_penalty != 0.f ||
                                    a.presence_penalty != 0.f);
   if (penal) {
-    const int hl = min(a.history_len[b], HIST_MAX);
-    const int* hist = a.history + (long long)b * a.history_stride;
+    const int hl = min(min(a.history_len[history_row(a, b)], a.history_stride), HIST_MAX);
+    const int* hist = a.history + (long long)history_row(a, b) * a.history_stride;
     for (int j = tid; j < hl; j += THREADS) {      // the first occurrence of a token owns it
       const int t = hist[j];
       int owner = t;

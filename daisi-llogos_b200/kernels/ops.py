@@ -116,6 +116,7 @@ class _SampleArgs(Structure):
         ("penalize_newline", c_int), ("seed", c_ulonglong), ("step", c_int),
         ("banned", c_void_p), ("n_banned", c_int),
         ("cand_val", c_void_p), ("cand_idx", c_void_p), ("cand_count", c_void_p), ("n_slices", c_int),
+        ("history_rows", c_void_p), ("history_append", c_int),
     ]
 
 
@@ -468,8 +469,14 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
            penalize_newline: bool = False, seed: int = 0, step: int = 0,
            seq_ids: Optional[torch.Tensor] = None, history: Optional[torch.Tensor] = None,
            history_len: Optional[torch.Tensor] = None, banned: Optional[torch.Tensor] = None,
-           probs_out: Optional[torch.Tensor] = None, candidates: bool = True) -> None:
+           probs_out: Optional[torch.Tensor] = None, candidates: bool = True,
+           history_rows: Optional[torch.Tensor] = None, history_append: bool = False) -> None:
     """One token per row of ``logits`` by the sampling pipeline of csrc/sampling.cu.
+
+    ``history`` holds recent tokens per sequence, ``history_len`` how many each has seen: a row is a ring of
+    ``history.shape[1]`` entries of which the last ``min(len, width)`` count.  Row of sequence b:
+    ``history_rows[b]`` (default b).  With ``history_append`` the kernel writes the token it drew into the
+    ring and raises the count, so that the next step needs nothing from the host.
 
     ``candidates=False`` keeps the kernels on the general way over the whole vocabulary (tests compare the
     two ways)."""
@@ -483,6 +490,8 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
     if history is not None:
         a.history, a.history_len = _ptr(history, torch.int32), _ptr(history_len, torch.int32)
         a.history_stride = history.shape[1]
+        a.history_rows = _ptr(history_rows, torch.int32)
+        a.history_append = int(bool(history_append))
     a.n_seqs, a.vocab = b, v
     a.temperature, a.top_k = float(temperature), int(top_k)
     a.top_p, a.min_p, a.typical_p, a.min_keep = float(top_p), float(min_p), float(typical_p), int(min_keep)

@@ -9,8 +9,9 @@ next batch uses them again.  The loop decides; the engine and the sampler do the
 the decisions can be tested with stand-ins for both.
 
 When the sampler can leave its tokens on the device and the engine can take them from there
-(``sample_device`` / ``fetch`` / ``step_fed``) and the sampling needs no token history, the loop runs
-one step ahead of what it has read: it queues the step that consumes the tokens of sample k before it
+(``sample_device`` / ``fetch`` / ``step_fed``; with penalties also ``begin``, which puts the recent
+tokens on the device where the sampler extends them itself), the loop runs one step ahead of what it
+has read: it queues the step that consumes the tokens of sample k before it
 reads them, and reads them while that step runs.  A stop token is then seen one step late; the
 sequence has run one step too many, whose token is thrown away.  The tokens that come out are the same.
 """
@@ -111,8 +112,10 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: Generati
             result.prompt_tokens += sum(len(prompts[i]) for i in active)
             t0 = clock()
             step_no = 0
-            if (run_ahead and params.max_tokens > 0 and not params.uses_history and hasattr(sampler, "sample_device")
-                    and hasattr(sampler, "fetch") and hasattr(engine, "step_fed")):
+            if (run_ahead and params.max_tokens > 0 and hasattr(sampler, "sample_device")
+                    and hasattr(sampler, "fetch") and hasattr(engine, "step_fed")
+                    and (not params.uses_history
+                         or (hasattr(sampler, "begin") and sampler.begin([histories[i] for i in active], params)))):
                 _decode_ahead(engine, sampler, params, seed, sorted(stop), stop, slots, histories, active, logits,
                               result, on_token, cache.max_seq_len)
                 active = []
@@ -179,9 +182,14 @@ def _decode_ahead(engine, sampler, params, seed, stop_list, stop, slots, histori
                 alive[i] = False
 
     rows = list(active)
+    ring_row = {i: r for r, i in enumerate(active)}     # where the sampler keeps a sequence's recent tokens
+    extra = {"ring_rows": None} if params.uses_history else {}
     step_no = 0
     while rows:
-        picked = sampler.sample_device(logits, params, seed=seed, step=step_no, seq_ids=rows, stop_tokens=stop_list)
+        if params.uses_history:
+            extra["ring_rows"] = [ring_row[i] for i in rows]
+        picked = sampler.sample_device(logits, params, seed=seed, step=step_no, seq_ids=rows, stop_tokens=stop_list,
+                                       **extra)
         unread.append((sampler.fetch(picked), rows))
         for i in rows:
             length[i] += 1
