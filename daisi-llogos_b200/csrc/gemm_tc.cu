@@ -153,6 +153,11 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 
   pdl_launch_dependents();      // the next kernel may set itself up while this one runs
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    // the first copies need the two descriptors: fetch them while the barriers and the tensor memory are set up
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+  }
   const int split = blockIdx.z;
   const int n_tiles_n = (p.n + TN - 1) / TN;
   constexpr bool GATED_ROWS = EPI == 1 && SWAP == 0;       // gate and up tiles fetched separately, gate_rows each
