@@ -21,10 +21,14 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._flat: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: Dict[Tuple[str, torch.dtype, Tuple[int, ...]], torch.Tensor] = {}
         self.frozen = False   # set while a CUDA graph that uses these buffers exists
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """``zero``: the buffer is zero when it is first handed out (and whenever it had to grow)."""
+        view = self._views.get((name, dtype, shape))
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -35,7 +39,12 @@ class Workspace:
                 raise RuntimeError(f"workspace buffer '{name}' would have to grow after graph capture")
             flat = (torch.zeros if zero else torch.empty)(max(n, 1), dtype=dtype, device=self.device)
             self._flat[key] = flat
-        return flat[:n].view(shape)
+            for k in [k for k in self._views if k[0] == name and k[1] == dtype]:
+                del self._views[k]          # views of the buffer that was replaced
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = self._views[(name, dtype, shape)] = flat[:n].view(shape)
+        return view
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._flat.values())

@@ -12,7 +12,17 @@ import torch
 _SMS = 148
 
 
+_plan_cache = {}
+
+
 def plan_splits(n: int, o: int, k: int) -> int:
+    s = _plan_cache.get((n, o, k))
+    if s is None:
+        s = _plan_cache[(n, o, k)] = _plan_splits(n, o, k)
+    return s
+
+
+def _plan_splits(n: int, o: int, k: int) -> int:
     """Split-K wish for a product with few rows.
 
     ``tiles`` output tiles, each with ``nkb`` k-blocks of 64, are cut into ``s`` splits; the blocks run

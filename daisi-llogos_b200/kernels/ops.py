@@ -48,7 +48,14 @@ def _ptr(t: Optional[torch.Tensor], dtype=None) -> Optional[int]:
     return t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    """Handle of the current stream of the current device (the raw query: this runs once per launch)."""
+    if _raw_stream is not None and _raw_device is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -123,7 +130,19 @@ class _SampleArgs(Structure):
 _protos_done = set()
 
 
+_libs = {}
+
+
 def _lib(name: str):
+    lib = _libs.get(name)
+    if lib is not None:
+        return lib
+    lib = _load_lib(name)
+    _libs[name] = lib
+    return lib
+
+
+def _load_lib(name: str):
     lib = load_library(name)
     if name in _protos_done:
         return lib
@@ -223,13 +242,20 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
     """Whether the tensor-core kernel takes this product (bfloat16 operands, k a multiple of 8)."""
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not (x.is_cuda and w.is_cuda):
         return False
-    lib = _lib("gemm_tc")
-    return bool(lib.llg_gemm_tc_supported(x.data_ptr(), w.data_ptr(), x.shape[0], w.shape[0], x.shape[1]))
+    # the library's rule (llg_gemm_tc_supported), kept here because this runs before every product
+    return x.shape[0] > 0 and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
+_splits_cache = {}
 
 
 def gemm_tc_splits(k: int, wish: int) -> int:
     """The number of split-K partials the kernel writes when asked for ``wish``."""
-    return _lib("gemm_tc").llg_gemm_tc_splits(k, wish)
+    key = (k, wish)
+    s = _splits_cache.get(key)
+    if s is None:
+        s = _splits_cache[key] = _lib("gemm_tc").llg_gemm_tc_splits(k, wish)
+    return s
 
 
 def gated_rows(features: int) -> int:
@@ -250,7 +276,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int 
     o, k2 = w.shape
     s = out.shape[0]
     assert k == k2 and out.shape == (s, n, gated_features if gated_features else o), (x.shape, w.shape, out.shape)
-    if lib.llg_gemm_tc_splits(k, s) != s:
+    if gemm_tc_splits(k, s) != s:
         raise KernelError(f"gemm_tc: {s} splits cannot be had for k = {k}")
     _check(lib, lib.llg_gemm_tc(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k, s,
                                 tile_n, gated_features, _stream()))
