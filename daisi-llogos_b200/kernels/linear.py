@@ -23,24 +23,34 @@ def plan_splits(n: int, o: int, k: int) -> int:
 
 
 def _plan_splits(n: int, o: int, k: int) -> int:
-    """Split-K wish for a product with few rows.
+    """Split-K wish for a product with few enough rows that streaming the weights is what takes the time.
 
     ``tiles`` output tiles, each with ``nkb`` k-blocks of 64, are cut into ``s`` splits; the blocks run
-    in ``ceil(tiles * s / resident)`` rounds (two blocks are resident per SM for token tiles up to 64)
-    of ``ceil(nkb / s)`` k-blocks plus a fixed cost each.  The cheapest ``s`` wins, the smallest on
-    ties: a last round with a few stragglers costs as much as a full one."""
-    if n > 64:
+    in ``ceil(tiles * s / resident)`` rounds of ``ceil(nkb / s)`` k-blocks plus a fixed cost each, and
+    the ``s`` partial results are written and read once more.  The cheapest ``s`` wins, the smallest on
+    ties: a last round with a few stragglers costs as much as a full one.  The tile shapes and the
+    blocks per SM are those the kernel takes for ``n`` rows (csrc/gemm_tc.cu)."""
+    if n > SPLIT_ROWS_MAX:
         return 1
-    tile_n = 16 if n <= 16 else 32 if n <= 32 else 64
-    tiles = -(-o // 128) * -(-n // tile_n)
     nkb = -(-k // 64)
-    resident = 2 * _SMS
+    if n >= 256:                  # tokens are the MMA rows: 128 tokens x 256 features per tile, one block per SM
+        tiles, tile_bytes, resident = -(-n // 128) * -(-o // 256), (128 + 256) * 128, _SMS
+    else:                         # weights are the MMA rows: 128 features x a token tile
+        tile_n = 16 if n <= 16 else 32 if n <= 32 else 64 if n <= 64 else 128 if n <= 128 else 256
+        tiles, tile_bytes = -(-o // 128) * -(-n // tile_n), (128 + tile_n) * 128
+        resident = 2 * _SMS if tile_n <= 64 else _SMS
+    unit_us = tile_bytes / 45e3   # a block streams about 45 GB/s
     best, best_cost = 1, None
     for s in range(1, max(1, min(nkb // 4, 32)) + 1):
-        cost = -(-tiles * s // resident) * (-(-nkb // s) + 3)
+        cost = -(-tiles * s // resident) * (-(-nkb // s) + 3) * unit_us
+        if s > 1:
+            cost += s * n * o * 8 / 4e6          # the partials, out and in again, at about 4 TB/s
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
+
+
+SPLIT_ROWS_MAX = 512    # with more rows the products are bound by arithmetic and one split is right
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dtype,
