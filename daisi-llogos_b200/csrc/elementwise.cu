@@ -178,7 +178,7 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
     if (n_out <= 256) {
       threads = nv >= 1024 ? 1024 : (nv >= 256 ? 256 : 128);
     } else {
-      threads = 256;
+      threads = nv >= 1024 ? 512 : 256;
     }
     vpt = (nv + threads - 1) / threads;
     if (vpt > 8) {                     // rows longer than 8 float4 per thread: more threads
