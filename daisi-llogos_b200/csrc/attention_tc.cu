@@ -39,6 +39,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// the largest of three (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 __device__ int g_error = 0;  // 0 ok; 1 score wait, 2 output wait, 3 shared memory not aligned to 1024 bytes
 
 struct PrefillArgs {         // same layout as in attention_simt.cu
@@ -369,24 +376,28 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(PrefillArgs a) 
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < TK; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], sv[c]);
+      for (int c = 0; c < TK; c += 8) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], sv[c + 2 * k], sv[c + 2 * k + 1]);
+      }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const bool raise = mx > m_run + raise_by || m_run == -INFINITY;
       const float m_new = raise ? fmaxf(m_run, mx) : m_run;
       const float corr = (!raise || m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * sc);
       const float ms = (m_new == -INFINITY) ? 0.f : m_new * sc;
       m_run = m_new;
-      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      // two elements per instruction where the arithmetic allows it (fma.rn.f32x2, add.rn.f32x2)
+      const float2 sc2 = make_float2(sc, sc), nms2 = make_float2(-ms, -ms);
+      float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pk[TK / 2];
 #pragma unroll
       for (int c2 = 0; c2 < TK / 2; ++c2) {
-        const float p0 = fast_exp2(fmaf(sv[2 * c2], sc, -ms));
-        const float p1 = fast_exp2(fmaf(sv[2 * c2 + 1], sc, -ms));
-        ps4[(2 * c2) & 3] += p0;
-        ps4[(2 * c2 + 1) & 3] += p1;
-        pk[c2] = pack_bf16(p0, p1);
+        const float2 x = __ffma2_rn(make_float2(sv[2 * c2], sv[2 * c2 + 1]), sc2, nms2);
+        const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+        ps2[c2 & 1] = __fadd2_rn(ps2[c2 & 1], p);
+        pk[c2] = pack_bf16(p.x, p.y);
       }
-      l_run = l_run * corr + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
+      l_run = l_run * corr + ((ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y));
 
       if (j > 0) {
         // O += P(j-1) V(j-1) has finished: the accumulator may be rescaled, and V(j-1)'s stage reused
