@@ -1,24 +1,29 @@
 // Causal attention for prompt steps on the 5th-generation tensor cores (tcgen05), bfloat16, head
-// sizes 64 and 128.  One block owns 128 queries of one head; thread r of its first four warps owns
-// query row r, which is lane r of tensor memory, so the softmax of a row needs no exchange between
-// threads; one elected lane of the first warp issues the products:
+// sizes 64 and 128.
 //
 //   per 64-key tile (one cache page):   S = Q K^T      tcgen05.mma, accumulator S[128 x 64] in TMEM
 //                                       each thread reads its row of S (tcgen05.ld), masks, updates the
 //                                       running maximum and sum, writes P (bfloat16) to shared memory
 //                                       O += P V       tcgen05.mma, accumulator O[128 x head] in TMEM
 //
+// A block owns 256 queries of one head as two tiles of 128.  Each tile has a group of four softmax
+// warps: thread r of a group owns query row r of its tile, which is lane r of tensor memory, so the
+// softmax of a row needs no exchange between threads.  Three more warps serve both groups: one lane
+// issues every product, one warp copies the key tiles and one the value tiles (cp.async; rows come
+// from the step's packed buffer or from cache pages, as in attn_prefill_simt; three stages each).
+// The roles meet only at mbarriers: tiles full / free between the copying warps and the issuing lane,
+// scores ready, weights ready and accumulator updated between the issuing lane and a group.  Each
+// group has two score buffers in tensor memory, so that the tensor core computes the next tile's
+// scores and the previous tile's O += P V while the group runs the softmax of the current one.
+//
 // Q, K and P are K-major operands with the 128-byte swizzle; V is stored as it lies in memory
 // ([key][dim], dim contiguous), which makes it the MN-major second operand of the second product.
-// Key and value tiles are copied by all threads with cp.async (rows come from the step's packed
-// buffer or from cache pages, as in attn_prefill_simt), two stages deep.  The
-// scores have two buffers in tensor memory, so that the tensor core computes the next tile's scores
-// and the previous tile's O += P V while the threads run the softmax of the current one.  A row's
-// accumulator is rescaled in place (tcgen05.ld / tcgen05.st) only when its maximum grows by more
-// than a factor of 2^8 in the weights, warp by warp and only when some row of the warp needs it.
+// A row's accumulator is rescaled in place (tcgen05.ld / tcgen05.st) only when its maximum grows by
+// more than a factor of 2^8 in the weights, warp by warp and only when some row of the warp needs it.
 //
-// Every mbarrier wait is bounded; on expiry the block records an error (llg_attn_tc_status), stops
-// issuing work, waits for its copies in flight, frees its tensor memory and returns.
+// Every mbarrier wait is bounded; on expiry the thread records an error (llg_attn_tc_status) and
+// raises a flag that ends the other roles' waits; every role waits for its own copies in flight,
+// and the block frees its tensor memory and returns.
 #include "common.cuh"
 
 LLG_API const char* llg_last_error() { return g_llg_error; }
@@ -26,7 +31,7 @@ LLG_API const char* llg_last_error() { return g_llg_error; }
 namespace {
 
 typedef __nv_bfloat16 bf16;
-constexpr int BQ = 128;      // queries per block
+constexpr int BQ = 128;      // queries per tile (rows of a product, lanes of tensor memory)
 constexpr int TK = 64;       // keys per tile = one cache page
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -46,7 +51,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-__device__ int g_error = 0;  // 0 ok; 1 score wait, 2 output wait, 3 shared memory not aligned to 1024 bytes
+__device__ int g_error = 0;  // 0 ok; waits that ran out: 1 scores, 2 accumulator, 4 free stage, 5 tile copied, 6 weights; 3 shared memory not aligned to 1024 bytes
 
 struct PrefillArgs {         // same layout as in attention_simt.cu
   const void* q;
@@ -57,7 +62,7 @@ struct PrefillArgs {         // same layout as in attention_simt.cu
   const int* page_table;
   int table_width;
   int ring_pages;
-  const int* tiles;          // [n_tiles][2]: (sequence, first query), 128 queries per tile
+  const int* tiles;          // [n_tiles][2]: (sequence, first query), 256 queries per tile
   const int* cu_tokens;
   const int* len_before;
   const int* slots;
@@ -172,38 +177,66 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` in a tile of 128-byte rows with the 128-byte swizzle
 __device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
+constexpr int GROUPS = 2;                     // query tiles of 128 rows per block, each with its own softmax warps
+constexpr int KST = 3, VST = 3;               // stages of keys and of values
+constexpr int WORKERS = GROUPS * BQ;          // softmax threads: thread r of group g owns query row r of tile g
+constexpr int ISSUE_WARP = WORKERS / 32;      // one lane of this warp issues every product
+constexpr int K_LOAD_WARP = ISSUE_WARP + 1;   // copies key tiles
+constexpr int V_LOAD_WARP = ISSUE_WARP + 2;   // copies value tiles
+constexpr int THREADS = (V_LOAD_WARP + 1) * 32;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// What a block knows about its two query tiles and the key tiles they need.
+struct TileInfo {
+  int b, tok0, lb, slot, k_begin;
+  int nq[GROUPS], pos0[GROUPS], n_tiles[GROUPS], n_max;
+};
+
 template <int HD>
-__global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) {
   constexpr int KB = HD / 64;                 // 64-wide blocks of the head dimension
   constexpr int Q_BYTES = KB * BQ * 128;      // [KB][128 rows][128 bytes]
   constexpr int KV_BYTES = KB * TK * 128;     // [KB][64 keys][128 bytes]
-  constexpr int KST = 2, VST = 2;             // stages of keys and of values
-  constexpr int TMEM_COLS = 256;              // S: 2 x 64 columns, O: HD columns
-  constexpr uint32_t S_COL = 0, O_COL = 128;
+  constexpr int P_BYTES = BQ * 128;           // [128 rows][64 keys]
+  constexpr int TMEM_COLS = 512;              // per group 256: S 2 x 64 columns, O HD columns from column 128
+  constexpr uint32_t G_COLS = 256, O_COL = 128;
+  constexpr int CPR = HD / 8;                 // 16-byte chunks per row of the head
   // The tiles need 1024-byte alignment (swizzle); the declaration asks for it and the kernel checks it.
-  // No slack is added: 112 KB + the barriers' kilobyte lets two blocks share an SM.
   extern __shared__ __align__(1024) unsigned char smem[];
-  unsigned char* Qs = smem;
-  unsigned char* Ks = Qs + Q_BYTES;           // [KST]
-  unsigned char* Vs = Ks + KST * KV_BYTES;    // [VST]
-  unsigned char* Ps = Vs + VST * KV_BYTES;
-  __shared__ uint64_t bar_s[2], bar_o;
+  unsigned char* Qs = smem;                          // [GROUPS]
+  unsigned char* Ks = Qs + GROUPS * Q_BYTES;         // [KST]
+  unsigned char* Vs = Ks + KST * KV_BYTES;           // [VST]
+  unsigned char* Ps = Vs + VST * KV_BYTES;           // [GROUPS][2]
+  __shared__ uint64_t k_full[KST], k_free[KST], v_full[VST], v_free[VST];
+  __shared__ uint64_t s_full[GROUPS][2], p_ready[GROUPS][2], o_done[GROUPS];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
   pdl_launch_dependents();
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const bool issue_warp = __shfl_sync(0xffffffffu, warp, 0) == 0;   // uniform over the warp
-  //               // first thread of the fifth warp: issues the products
-  const bool worker = tid < BQ;                 // thread r owns query row r
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if ((smem_u32(smem) & 1023u) != 0) {          // uniform over the block
     if (tid == 0) atomicCAS(&g_error, 0, 3);
     return;
   }
   if (tid == 0) {
-    mbar_init(&bar_s[0], 1);
-    mbar_init(&bar_s[1], 1);
-    mbar_init(&bar_o, 1);
+    for (int s = 0; s < KST; ++s) {
+      mbar_init(&k_full[s], 32);
+      mbar_init(&k_free[s], 1);
+    }
+    for (int s = 0; s < VST; ++s) {
+      mbar_init(&v_full[s], 32);
+      mbar_init(&v_free[s], 1);
+    }
+    for (int g = 0; g < GROUPS; ++g) {
+      mbar_init(&s_full[g][0], 1);
+      mbar_init(&s_full[g][1], 1);
+      mbar_init(&p_ready[g][0], BQ);
+      mbar_init(&p_ready[g][1], BQ);
+      mbar_init(&o_done[g], 1);
+    }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -217,141 +250,188 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(PrefillArgs a) 
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = tmem_base_slot;
-  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   volatile int* abortp = &abort_flag;
   pdl_wait();
 
   // later tiles of a sequence see more keys: run the list backwards so that long blocks start first
-  const int tile_id = a.n_tiles - 1 - (int)blockIdx.x;
-  const int b = a.tiles[2 * tile_id], q_off = a.tiles[2 * tile_id + 1];
+  TileInfo ti;
+  {
+    const int tile_id = a.n_tiles - 1 - (int)blockIdx.x;
+    ti.b = a.tiles[2 * tile_id];
+    const int q_off = a.tiles[2 * tile_id + 1];
+    ti.tok0 = a.cu_tokens[ti.b];
+    const int total = a.cu_tokens[ti.b + 1] - ti.tok0;
+    ti.lb = a.len_before[ti.b];
+    ti.slot = a.slots[ti.b];
+    ti.n_max = 0;
+    for (int g = 0; g < GROUPS; ++g) {
+      ti.nq[g] = max(0, min(BQ, total - q_off - g * BQ));
+      ti.pos0[g] = ti.lb + q_off + g * BQ;
+    }
+    // the first group's window starts earliest; the second masks the tiles that lie before its own
+    int kb = a.window > 0 ? max(0, ti.pos0[0] - a.window + 1) : 0;
+    ti.k_begin = (kb / TK) * TK;
+    for (int g = 0; g < GROUPS; ++g) {
+      ti.n_tiles[g] = ti.nq[g] > 0 ? (ti.pos0[g] + ti.nq[g] - ti.k_begin + TK - 1) / TK : 0;
+      ti.n_max = max(ti.n_max, ti.n_tiles[g]);
+    }
+  }
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
-  const int tok0 = a.cu_tokens[b];
-  const int nq = min(BQ, a.cu_tokens[b + 1] - tok0 - q_off);
-  const int lb = a.len_before[b];
-  const int slot = a.slots[b];
-  const int pos0 = lb + q_off;
-  const int k_end = pos0 + nq;
-  int k_begin = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-  k_begin = (k_begin / TK) * TK;
-  const int n_tiles = (k_end - k_begin + TK - 1) / TK;
-  const bf16* qg = (const bf16*)a.q;
-  const bf16* kn = (const bf16*)a.k_new;
-  const bf16* vn = (const bf16*)a.v_new;
-  const bf16* kp = (const bf16*)a.k_pages;
-  const bf16* vp = (const bf16*)a.v_pages;
-  constexpr int CPR = HD / 8;                 // 16-byte chunks per row of the head
-  constexpr int RSTEP = 128 / CPR;            // rows that the block copies in one pass (a multiple of 8)
-  const int ch = tid % CPR, r0 = tid / CPR;
-  // chunk `ch` of row r0 + i * RSTEP lies i * RSTEP * 128 bytes after this offset (the swizzle depends on row % 8)
-  const uint32_t tile_off = (uint32_t)((ch >> 3) * (TK * 128)) + swz(r0, ch & 7);
+  const int k_end = ti.pos0[0] + (ti.nq[1] > 0 ? BQ + ti.nq[1] : ti.nq[0]);   // keys past it are never copied
+  const int q_tok0 = ti.tok0 + ti.pos0[0] - ti.lb;                              // first token of the first query tile
 
-  // Copies the 64 keys (or values) of key tile `tile` to `dst`.  A tile lies in one cache page, or in this
-  // step's packed rows, or (at most once per sequence) partly in each.
-  auto load_tile = [&](unsigned char* dst, int tile, const bf16* fresh_src, const bf16* page_src) {
-    const int kt = k_begin + tile * TK;
-    const uint32_t d0 = smem_u32(dst) + tile_off;
-    if (kt >= lb) {
-      const bf16* src = fresh_src + ((long long)(tok0 + kt - lb + r0) * a.nkv + kvh) * HD + ch * 8;
-      const long long step = (long long)RSTEP * a.nkv * HD;
-      if (kt + TK <= k_end) {
-#pragma unroll
-        for (int i = 0; i < TK / RSTEP; ++i) cp_async16(d0 + i * (RSTEP * 128), src + i * step, true);
-      } else {
-#pragma unroll
-        for (int i = 0; i < TK / RSTEP; ++i) {
-          const bool valid = kt + r0 + i * RSTEP < k_end;
-          cp_async16(d0 + i * (RSTEP * 128), valid ? src + i * step : fresh_src, valid);
-        }
-      }
-    } else if (kt + TK <= lb) {
-      const bf16* src = page_src + (kv_row(a.page_table, a.table_width, a.ring_pages, slot, kt, kvh, a.nkv) + r0) * HD + ch * 8;
-#pragma unroll
-      for (int i = 0; i < TK / RSTEP; ++i) cp_async16(d0 + i * (RSTEP * 128), src + i * (RSTEP * HD), true);
-    } else {
-      const long long old_base = kv_row(a.page_table, a.table_width, a.ring_pages, slot, kt, kvh, a.nkv) * HD;
-      const long long new_base = ((long long)(tok0 + kt - lb) * a.nkv + kvh) * HD;
-#pragma unroll
-      for (int i = 0; i < TK / RSTEP; ++i) {
-        const int row = r0 + i * RSTEP, pos = kt + row;
-        const bool valid = pos < k_end, fresh = pos >= lb;
-        const long long off = (fresh ? new_base + (long long)row * a.nkv * HD : old_base + (long long)row * HD) + ch * 8;
-        cp_async16(d0 + i * (RSTEP * 128), (fresh ? fresh_src : page_src) + (valid ? off : 0), valid);
-      }
+  // queries: thread r of group g copies its part of tile g
+  if (tid < WORKERS) {
+    const int g = tid / BQ, r = tid % BQ;
+    const int ch = r % CPR;
+    for (int row = r / CPR; row < BQ; row += BQ / CPR) {
+      const bool valid = row < ti.nq[g];
+      const bf16* src = (const bf16*)a.q + ((long long)(q_tok0 + g * BQ + (valid ? row : 0)) * a.nh + h) * HD + ch * 8;
+      cp_async16(smem_u32(Qs + g * Q_BYTES) + (uint32_t)((ch >> 3) * (BQ * 128)) + swz(row, ch & 7), src, valid);
     }
-  };
-
-  constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
-  constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
-  // scores of key tile t into score buffer t % 2 (one thread calls this)
-  auto issue_scores = [&](int t) {
-    const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + (t % KST) * KV_BYTES);
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-      const uint32_t blk = ks >> 2, kk = ks & 3;      // 64-wide block, 16-wide step inside it (32 bytes)
-      umma_bf16(tmem + S_COL + (uint32_t)(t & 1) * TK, desc_kmajor(qa + blk * (BQ * 128) + kk * 32),
-                desc_kmajor(ka + blk * (TK * 128) + kk * 32), IDESC_S, ks != 0);
-    }
-    umma_commit(&bar_s[t & 1]);
-  };
-
-  // Copies are committed in groups: {Q, K0}, {K1, V0}, then two groups per tile j: {K(j+2)} at its start and
-  // {V(j+1)} near its end.  Before the products of tile j are issued, all groups but the newest are complete.
-  if (worker) {
-    for (int row = r0; row < BQ; row += RSTEP) {
-      const bool valid = row < nq;
-      const bf16* src = qg + ((long long)(tok0 + q_off + (valid ? row : 0)) * a.nh + h) * HD + ch * 8;
-      cp_async16(smem_u32(Qs) + (uint32_t)((ch >> 3) * (BQ * 128)) + swz(row, ch & 7), src, valid);
-    }
-    load_tile(Ks, 0, kn, kp);
     cp_async_commit();
-    if (n_tiles > 1) load_tile(Ks + KV_BYTES, 1, kn, kp);
-    load_tile(Vs, 0, vn, vp);
-    cp_async_commit();
-    cp_async_wait<1>();
-    fence_async_smem();
-  }
-  __syncthreads();
-  if (issue_warp && elect_one()) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    issue_scores(0);
-  }
-  if (worker) {
     cp_async_wait<0>();
     fence_async_smem();
   }
   __syncthreads();
-  if (issue_warp && n_tiles > 1 && elect_one()) {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    issue_scores(1);
-  }
 
-  const float sc = a.scale * LOG2E;
-  // A row's exponentials use its maximum so far, which is raised only when a tile exceeds it by more than
-  // 2^RAISE in the exponent: the weights stay below 2^RAISE and the accumulator is rescaled rarely.  The
-  // common factor cancels in the final division.
-  const float raise_by = 8.0f / sc;
-  const int qpos = pos0 + tid;                 // this thread's query position
-  float m_run = -INFINITY, l_run = 0.f;
-  bool ok = true;
-
-  // Tile j: the scores S(j) were issued a tile earlier.  While the threads turn them into weights P(j), the
-  // tensor core runs O += P(j-1) V(j-1) and S(j+1); at the end of the tile one thread issues O += P(j) V(j)
-  // and S(j+2).
-  for (int j = 0; j < n_tiles; ++j) {
-    if (worker) {
-      if (!mbar_wait(&bar_s[j & 1], (j >> 1) & 1, abortp)) {
+  if (warp == K_LOAD_WARP || warp == V_LOAD_WARP) {
+    // ---- copies: one warp per operand, a tile ahead of the one whose arrival it announces -----------
+    const bool keys = warp == K_LOAD_WARP;
+    const int stages = keys ? KST : VST;
+    unsigned char* base = keys ? Ks : Vs;
+    uint64_t* full = keys ? k_full : v_full;
+    uint64_t* freeb = keys ? k_free : v_free;
+    const bf16* fresh_src = (const bf16*)(keys ? a.k_new : a.v_new);
+    const bf16* page_src = (const bf16*)(keys ? a.k_pages : a.v_pages);
+    const int ch = lane % CPR, r0 = lane / CPR;
+    constexpr int RSTEP = 32 / CPR;             // rows per pass: 2 (head size 128) or 4 (64)
+    constexpr int PASSES = TK / RSTEP;
+    bool ok = true;
+    for (int t = 0; t < ti.n_max && ok; ++t) {
+      if (t >= 1) {
+        // the tile copied in the last round has arrived: say so before waiting for room for the next one
+        cp_async_wait<0>();
+        fence_async_smem();
+        mbar_arrive(&full[(t - 1) % stages]);
+      }
+      const int st = t % stages;
+      if (t >= stages && !mbar_wait(&freeb[st], (t / stages - 1) & 1, abortp)) {
+        if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 4); }
+        ok = false;
+        break;
+      }
+      // A tile lies in one cache page, or in this step's packed rows, or (at most once per sequence) partly in each.
+      const int kt = ti.k_begin + t * TK;
+      const uint32_t dst = smem_u32(base + st * KV_BYTES) + (uint32_t)((ch >> 3) * (TK * 128));
+      if (kt >= ti.lb && kt + TK <= k_end) {
+        const bf16* src = fresh_src + ((long long)(ti.tok0 + kt - ti.lb + r0) * a.nkv + kvh) * HD + ch * 8;
+        const long long step = (long long)RSTEP * a.nkv * HD;
+#pragma unroll 8
+        for (int i = 0; i < PASSES; ++i) cp_async16(dst + swz(r0 + i * RSTEP, ch & 7), src + i * step, true);
+      } else if (kt + TK <= ti.lb) {
+        const bf16* src = page_src + (kv_row(a.page_table, a.table_width, a.ring_pages, ti.slot, kt, kvh, a.nkv) + r0) * HD + ch * 8;
+#pragma unroll 8
+        for (int i = 0; i < PASSES; ++i) cp_async16(dst + swz(r0 + i * RSTEP, ch & 7), src + i * (RSTEP * HD), true);
+      } else {
+        const long long old_base = kt < ti.lb ? kv_row(a.page_table, a.table_width, a.ring_pages, ti.slot, kt, kvh, a.nkv) * HD : 0;
+        const long long new_base = ((long long)(ti.tok0 + kt - ti.lb) * a.nkv + kvh) * HD;
+        for (int row = r0; row < TK; row += RSTEP) {
+          const int pos = kt + row;
+          const bool valid = pos < k_end, fresh = pos >= ti.lb;
+          const long long off = (fresh ? new_base + (long long)row * a.nkv * HD : old_base + (long long)row * HD) + ch * 8;
+          cp_async16(dst + swz(row, ch & 7), (fresh ? fresh_src : page_src) + (valid ? off : 0), valid);
+        }
+      }
+      cp_async_commit();
+    }
+    cp_async_wait<0>();
+    if (ok && ti.n_max > 0) {
+      fence_async_smem();
+      mbar_arrive(&full[(ti.n_max - 1) % stages]);
+    }
+  } else if (warp == ISSUE_WARP) {
+    // ---- products: one lane issues them all.  The tensor core takes them one after the other, and a
+    // lane that issues is held up while its queue is full, which is why no softmax warp does this. ------
+    if (elect_one()) {
+      constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+      constexpr uint32_t IDESC_O = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+      // scores of key tile t for group g into the group's score buffer t % 2
+      auto issue_scores = [&](int g, int t) {
+        const uint32_t qa = smem_u32(Qs + g * Q_BYTES), ka = smem_u32(Ks + (t % KST) * KV_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t blk = ks >> 2, kk = ks & 3;      // 64-wide block, 16-wide step inside it (32 bytes)
+          umma_bf16(tmem + g * G_COLS + (uint32_t)(t & 1) * TK, desc_kmajor(qa + blk * (BQ * 128) + kk * 32),
+                    desc_kmajor(ka + blk * (TK * 128) + kk * 32), IDESC_S, ks != 0);
+        }
+        umma_commit(&s_full[g][t & 1]);
+      };
+      bool ok = true;
+      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int code) {
+        if (!ok) return;
+        if (!mbar_wait(bar, parity, abortp)) {
+          if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, code); }
+          ok = false;
+        }
+      };
+      for (int t = 0; t < 2 && t < ti.n_max; ++t) {
+        wait_or_fail(&k_full[t % KST], 0, 5);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int g = 0; g < GROUPS; ++g)
+          if (t < ti.n_tiles[g]) issue_scores(g, t);
+        umma_commit(&k_free[t % KST]);
+      }
+      for (int j = 0; j < ti.n_max && ok; ++j) {
+        wait_or_fail(&v_full[j % VST], (j / VST) & 1, 5);
+        if (j + 2 < ti.n_max) wait_or_fail(&k_full[(j + 2) % KST], ((j + 2) / KST) & 1, 5);
+        for (int g = 0; g < GROUPS && ok; ++g) {
+          if (j >= ti.n_tiles[g]) continue;
+          // the group has turned S(j) into P(j) and, where needed, rescaled its accumulator
+          wait_or_fail(&p_ready[g][j & 1], (j >> 1) & 1, 6);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t pa = smem_u32(Ps + (g * 2 + (j & 1)) * P_BYTES), va = smem_u32(Vs + (j % VST) * KV_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < TK / 16; ++kk) {
+            // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
+            umma_bf16(tmem + g * G_COLS + O_COL, desc_kmajor(pa + kk * 32), desc_mnmajor(va + kk * 2048, TK * 128), IDESC_O,
+                      (j | kk) != 0);
+          }
+          umma_commit(&o_done[g]);
+          if (j + 2 < ti.n_tiles[g]) issue_scores(g, j + 2);      // its score buffer j % 2 has been read
+        }
+        if (!ok) break;
+        umma_commit(&v_free[j % VST]);
+        if (j + 2 < ti.n_max) umma_commit(&k_free[(j + 2) % KST]);
+      }
+    }
+  } else if (tid < WORKERS && ti.nq[tid / BQ] > 0) {
+    // ---- softmax: thread r of group g owns query row r of tile g ------------------------------------
+    const int g = tid / BQ, r = tid % BQ, gw = (tid % BQ) >> 5;       // gw: warp inside the group = its lane quarter
+    const uint32_t lane_base = tmem + g * G_COLS + ((uint32_t)(gw * 32) << 16);
+    const int n_tiles = ti.n_tiles[g], pos0 = ti.pos0[g];
+    const float sc = a.scale * LOG2E;
+    // A row's exponentials use its maximum so far, which is raised only when a tile exceeds it by more than
+    // 2^8 in the weights: the weights stay below 2^8 and the accumulator is rescaled rarely.  The common
+    // factor cancels in the final division.
+    const float raise_by = 8.0f / sc;
+    const int qpos = pos0 + r;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait(&s_full[g][j & 1], (j >> 1) & 1, abortp)) {
         if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
+        ok = false;
+        break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int kt = k_begin + j * TK;
-      if (j + 2 < n_tiles) load_tile(Ks + (j % KST) * KV_BYTES, j + 2, kn, kp);   // S(j) has finished with this stage
-      cp_async_commit();
-
-      // this thread's row of scores: maximum, then the weights P, kept in registers until P's buffer is free
+      const int kt = ti.k_begin + j * TK;
       float sv[TK];
       {
         uint32_t r0_[16], r1_[16], r2_[16], r3_[16];
-        const uint32_t sa = lane_base + S_COL + (uint32_t)(j & 1) * TK;
+        const uint32_t sa = lane_base + (uint32_t)(j & 1) * TK;
         tmem_ld16(sa, r0_);
         tmem_ld16(sa + 16, r1_);
         tmem_ld16(sa + 32, r2_);
@@ -365,7 +445,7 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(PrefillArgs a) 
           sv[48 + c] = __uint_as_float(r3_[c]);
         }
       }
-      const bool need_mask = (kt + TK - 1 > pos0 + warp * 32) || (a.window > 0 && kt <= pos0 + warp * 32 + 31 - a.window);
+      const bool need_mask = (kt + TK - 1 > pos0 + gw * 32) || (a.window > 0 && kt <= pos0 + gw * 32 + 31 - a.window);
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < TK; ++c) {
@@ -386,93 +466,81 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(PrefillArgs a) 
       const float corr = (!raise || m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * sc);
       const float ms = (m_new == -INFINITY) ? 0.f : m_new * sc;
       m_run = m_new;
-      // two elements per instruction where the arithmetic allows it (fma.rn.f32x2, add.rn.f32x2)
+      // two elements per instruction where the arithmetic allows it (fma.rn.f32x2, add.rn.f32x2); the
+      // weights go straight into the tile's P buffer, which the product of two tiles ago has left
       const float2 sc2 = make_float2(sc, sc), nms2 = make_float2(-ms, -ms);
       float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      uint32_t pk[TK / 2];
+      unsigned char* prow = Ps + (g * 2 + (j & 1)) * P_BYTES;
 #pragma unroll
-      for (int c2 = 0; c2 < TK / 2; ++c2) {
-        const float2 x = __ffma2_rn(make_float2(sv[2 * c2], sv[2 * c2 + 1]), sc2, nms2);
-        const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-        ps2[c2 & 1] = __fadd2_rn(ps2[c2 & 1], p);
-        pk[c2] = pack_bf16(p.x, p.y);
+      for (int c8 = 0; c8 < TK / 8; ++c8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __ffma2_rn(make_float2(sv[c8 * 8 + 2 * e], sv[c8 * 8 + 2 * e + 1]), sc2, nms2);
+          const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          ps2[e & 1] = __fadd2_rn(ps2[e & 1], p);
+          pk[e] = pack_bf16(p.x, p.y);
+        }
+        *reinterpret_cast<uint4*>(prow + swz(r, c8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
       l_run = l_run * corr + ((ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y));
 
       if (j > 0) {
-        // O += P(j-1) V(j-1) has finished: the accumulator may be rescaled, and V(j-1)'s stage reused
-        if (!mbar_wait(&bar_o, (j - 1) & 1, abortp)) {
+        // O += P(j-1) V(j-1) has finished: the accumulator may be rescaled
+        if (!mbar_wait(&o_done[g], (j - 1) & 1, abortp)) {
           if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+          ok = false;
+          break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
           for (int c0 = 0; c0 < HD; c0 += 16) {
-            uint32_t r[16];
-            tmem_ld16(lane_base + O_COL + c0, r);
+            uint32_t rr[16];
+            tmem_ld16(lane_base + O_COL + c0, rr);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * corr);
-            tmem_st16(lane_base + O_COL + c0, r);
+            for (int c = 0; c < 16; ++c) rr[c] = __float_as_uint(__uint_as_float(rr[c]) * corr);
+            tmem_st16(lane_base + O_COL + c0, rr);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
-#pragma unroll
-      for (int c8 = 0; c8 < TK / 8; ++c8)
-        *reinterpret_cast<uint4*>(Ps + swz(tid, c8)) = make_uint4(pk[4 * c8], pk[4 * c8 + 1], pk[4 * c8 + 2], pk[4 * c8 + 3]);
-      if (j + 1 < n_tiles) load_tile(Vs + ((j + 1) % VST) * KV_BYTES, j + 1, vn, vp);
-      cp_async_commit();
-      cp_async_wait<1>();                        // V(j) and K(j+2) have arrived
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       fence_async_smem();
+      mbar_arrive(&p_ready[g][j & 1]);
     }
-    __syncthreads();
-    if (*abortp) { ok = false; break; }
-    if (issue_warp && elect_one()) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs + (j % VST) * KV_BYTES);
+    if (ok && !mbar_wait(&o_done[g], (n_tiles - 1) & 1, abortp)) {
+      if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+      ok = false;
+    }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok && !*abortp) {
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      bf16* dst = (bf16*)a.out + ((long long)(q_tok0 + g * BQ + r) * a.nh + h) * HD;
 #pragma unroll
-      for (int kk = 0; kk < TK / 16; ++kk) {
-        // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-        umma_bf16(tmem + O_COL, desc_kmajor(pa + kk * 32), desc_mnmajor(va + kk * 2048, TK * 128), IDESC_O, (j | kk) != 0);
+      for (int c0 = 0; c0 < HD; c0 += 16) {
+        uint32_t rr[16];
+        tmem_ld16(lane_base + O_COL + c0, rr);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (r < ti.nq[g]) {
+          uint4 v0, v1;
+          v0.x = pack_bf16(__uint_as_float(rr[0]) * inv, __uint_as_float(rr[1]) * inv);
+          v0.y = pack_bf16(__uint_as_float(rr[2]) * inv, __uint_as_float(rr[3]) * inv);
+          v0.z = pack_bf16(__uint_as_float(rr[4]) * inv, __uint_as_float(rr[5]) * inv);
+          v0.w = pack_bf16(__uint_as_float(rr[6]) * inv, __uint_as_float(rr[7]) * inv);
+          v1.x = pack_bf16(__uint_as_float(rr[8]) * inv, __uint_as_float(rr[9]) * inv);
+          v1.y = pack_bf16(__uint_as_float(rr[10]) * inv, __uint_as_float(rr[11]) * inv);
+          v1.z = pack_bf16(__uint_as_float(rr[12]) * inv, __uint_as_float(rr[13]) * inv);
+          v1.w = pack_bf16(__uint_as_float(rr[14]) * inv, __uint_as_float(rr[15]) * inv);
+          *reinterpret_cast<uint4*>(dst + c0) = v0;
+          *reinterpret_cast<uint4*>(dst + c0 + 8) = v1;
+        }
       }
-      umma_commit(&bar_o);
-      if (j + 2 < n_tiles) issue_scores(j + 2);
     }
   }
 
-  if (ok && worker) {
-    if (!mbar_wait(&bar_o, (n_tiles - 1) & 1, abortp)) {
-      if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
-    }
-  }
-  cp_async_wait<0>();
-  __syncthreads();
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (!*abortp && worker) {
-    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-    bf16* dst = (bf16*)a.out + ((long long)(tok0 + q_off + tid) * a.nh + h) * HD;
-#pragma unroll
-    for (int c0 = 0; c0 < HD; c0 += 16) {
-      uint32_t r[16];
-      tmem_ld16(lane_base + O_COL + c0, r);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      if (tid < nq) {
-        uint4 v0, v1;
-        v0.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
-        v0.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
-        v0.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
-        v0.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
-        v1.x = pack_bf16(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
-        v1.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
-        v1.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
-        v1.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
-        *reinterpret_cast<uint4*>(dst + c0) = v0;
-        *reinterpret_cast<uint4*>(dst + c0 + 8) = v1;
-      }
-    }
-  }
+  // every role comes here, also after a wait that ran out: copies in flight have been waited for above
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
@@ -482,16 +550,15 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(PrefillArgs a) 
 
 template <int HD>
 int launch(const PrefillArgs& a, cudaStream_t stream) {
-  constexpr int smem = (HD / 64) * BQ * 128 + 4 * (HD / 64) * TK * 128 + BQ * 128;
+  constexpr int KVB = (HD / 64) * TK * 128;
+  constexpr int smem = GROUPS * (HD / 64) * BQ * 128 + (KST + VST) * KVB + GROUPS * 2 * BQ * 128;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return llg_fail("attn_prefill_tc: shared memory %d: %s", smem, cudaGetErrorString(e));
-    // two blocks share an SM only if the SM's memory is configured for the largest shared part
-    cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     configured = true;
   }
-  cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.n_tiles, a.nh), dim3(128), (size_t)smem, stream, a);
+  cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.n_tiles, a.nh), dim3(THREADS), (size_t)smem, stream, a);
   if (le != cudaSuccess) return llg_fail("attn_prefill_tc: launch: %s", cudaGetErrorString(le));
   return llg_check_launch("attn_prefill_tc");
 }

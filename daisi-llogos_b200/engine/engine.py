@@ -24,7 +24,7 @@ from ..cache.store import PAGE, SequenceCache
 from .context import StepContext, Workspace
 from .model import DecoderModel
 
-_TILE_QS = (16, 64, 128)   # queries per block of the prompt attention kernels (CUDA cores, mma.sync, tcgen05)
+_TILE_QS = (16, 64, 256)   # queries per block of the prompt attention kernels (CUDA cores, mma.sync, tcgen05)
 
 
 class StepError(ValueError):

@@ -394,7 +394,7 @@ def _use_tc_attn(dtype: torch.dtype, head_dim: int) -> bool:
 def prefill_tile_queries(dtype: torch.dtype, head_dim: int) -> int:
     """Queries per block of the prompt attention kernel that ``attn_prefill`` will run."""
     if _use_tc_attn(dtype, head_dim):
-        return 128
+        return 256
     return 64 if _use_mma(dtype, head_dim) else 16
 
 
