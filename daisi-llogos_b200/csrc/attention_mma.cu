@@ -41,6 +41,7 @@ struct PrefillArgs {      // same layout as in attention_simt.cu
   int n_tiles, nh, nkv, hd;
   float scale;
   int window;
+  int n_tokens, n_pages;     // rows of k_new / v_new, pages of k_pages / v_pages
 };
 
 struct DecodeArgs {       // same layout as in attention_simt.cu

@@ -39,6 +39,7 @@ struct PrefillArgs {
   int n_tiles, nh, nkv, hd;
   float scale;
   int window;               // 0 = all keys
+  int n_tokens, n_pages;    // rows of k_new / v_new, pages of k_pages / v_pages
 };
 
 template <typename T>

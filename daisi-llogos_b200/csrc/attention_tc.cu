@@ -9,8 +9,9 @@
 // A block owns 256 queries of one head as two tiles of 128.  Each tile has a group of four softmax
 // warps: thread r of a group owns query row r of its tile, which is lane r of tensor memory, so the
 // softmax of a row needs no exchange between threads.  Three more warps serve both groups: one lane
-// issues every product, one warp copies the key tiles and one the value tiles (cp.async; rows come
-// from the step's packed buffer or from cache pages, as in attn_prefill_simt; three stages each).
+// issues every product, one warp copies the key tiles and one the value tiles (TMA boxes from the
+// step's packed buffer or from a cache page; the one tile per sequence that lies partly in each row by
+// row with cp.async; three stages each).
 // The roles meet only at mbarriers: tiles full / free between the copying warps and the issuing lane,
 // scores ready, weights ready and accumulator updated between the issuing lane and a group.  Each
 // group has two score buffers in tensor memory, so that the tensor core computes the next tile's
@@ -25,6 +26,12 @@
 // raises a flag that ends the other roles' waits; every role waits for its own copies in flight,
 // and the block frees its tensor memory and returns.
 #include "common.cuh"
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
 
 LLG_API const char* llg_last_error() { return g_llg_error; }
 
@@ -51,7 +58,7 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-__device__ int g_error = 0;  // 0 ok; waits that ran out: 1 scores, 2 accumulator, 4 free stage, 5 tile copied, 6 weights; 3 shared memory not aligned to 1024 bytes
+__device__ int g_error = 0;  // 0 ok; waits that ran out: 1 scores, 2 accumulator, 4 free stage, 5 tile copied, 6 weights, 7 copies at the end; 3 shared memory not aligned to 1024 bytes
 
 struct PrefillArgs {         // same layout as in attention_simt.cu
   const void* q;
@@ -70,6 +77,7 @@ struct PrefillArgs {         // same layout as in attention_simt.cu
   int n_tiles, nh, nkv, hd;
   float scale;
   int window;
+  int n_tokens, n_pages;     // rows of k_new / v_new, pages of k_pages / v_pages
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -185,6 +193,22 @@ constexpr int K_LOAD_WARP = ISSUE_WARP + 1;   // copies key tiles
 constexpr int V_LOAD_WARP = ISSUE_WARP + 2;   // copies value tiles
 constexpr int THREADS = (V_LOAD_WARP + 1) * 32;
 
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -196,7 +220,10 @@ struct TileInfo {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k_pages,
+                                                                 const __grid_constant__ CUtensorMap map_v_pages,
+                                                                 const __grid_constant__ CUtensorMap map_k_new,
+                                                                 const __grid_constant__ CUtensorMap map_v_new, PrefillArgs a) {
   constexpr int KB = HD / 64;                 // 64-wide blocks of the head dimension
   constexpr int Q_BYTES = KB * BQ * 128;      // [KB][128 rows][128 bytes]
   constexpr int KV_BYTES = KB * TK * 128;     // [KB][64 keys][128 bytes]
@@ -211,7 +238,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) 
   unsigned char* Vs = Ks + KST * KV_BYTES;           // [VST]
   unsigned char* Ps = Vs + VST * KV_BYTES;           // [GROUPS][2]
   __shared__ uint64_t k_full[KST], k_free[KST], v_full[VST], v_free[VST];
-  __shared__ uint64_t s_full[GROUPS][2], p_ready[GROUPS][2], o_done[GROUPS];
+  __shared__ uint64_t s_full[GROUPS][2], p_ready[GROUPS][2], o_done[GROUPS], q_ready;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -223,11 +250,11 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) 
   }
   if (tid == 0) {
     for (int s = 0; s < KST; ++s) {
-      mbar_init(&k_full[s], 32);
+      mbar_init(&k_full[s], 1);
       mbar_init(&k_free[s], 1);
     }
     for (int s = 0; s < VST; ++s) {
-      mbar_init(&v_full[s], 32);
+      mbar_init(&v_full[s], 1);
       mbar_init(&v_free[s], 1);
     }
     for (int g = 0; g < GROUPS; ++g) {
@@ -237,6 +264,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) 
       mbar_init(&p_ready[g][1], BQ);
       mbar_init(&o_done[g], 1);
     }
+    mbar_init(&q_ready, WORKERS);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -280,7 +308,8 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) 
   const int k_end = ti.pos0[0] + (ti.nq[1] > 0 ? BQ + ti.nq[1] : ti.nq[0]);   // keys past it are never copied
   const int q_tok0 = ti.tok0 + ti.pos0[0] - ti.lb;                              // first token of the first query tile
 
-  // queries: thread r of group g copies its part of tile g
+  // queries: thread r of group g copies its part of tile g; the issuing lane waits for all of them,
+  // the copying warps start on the keys and values meanwhile
   if (tid < WORKERS) {
     const int g = tid / BQ, r = tid % BQ;
     const int ch = r % CPR;
@@ -292,63 +321,80 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) 
     cp_async_commit();
     cp_async_wait<0>();
     fence_async_smem();
+    mbar_arrive(&q_ready);
   }
-  __syncthreads();
 
   if (warp == K_LOAD_WARP || warp == V_LOAD_WARP) {
-    // ---- copies: one warp per operand, a tile ahead of the one whose arrival it announces -----------
+    // ---- copies: one warp per operand.  A tile that lies in one cache page, or in this step's packed rows,
+    // is two TMA boxes (64 keys x 64 dimensions, 128-byte swizzle) that one lane requests; the one tile per
+    // sequence that lies partly in each is copied row by row with cp.async by the whole warp. ------------
     const bool keys = warp == K_LOAD_WARP;
     const int stages = keys ? KST : VST;
     unsigned char* base = keys ? Ks : Vs;
     uint64_t* full = keys ? k_full : v_full;
     uint64_t* freeb = keys ? k_free : v_free;
+    const CUtensorMap* map_pages = keys ? &map_k_pages : &map_v_pages;
+    const CUtensorMap* map_new = keys ? &map_k_new : &map_v_new;
     const bf16* fresh_src = (const bf16*)(keys ? a.k_new : a.v_new);
     const bf16* page_src = (const bf16*)(keys ? a.k_pages : a.v_pages);
-    const int ch = lane % CPR, r0 = lane / CPR;
-    constexpr int RSTEP = 32 / CPR;             // rows per pass: 2 (head size 128) or 4 (64)
-    constexpr int PASSES = TK / RSTEP;
-    bool ok = true;
-    for (int t = 0; t < ti.n_max && ok; ++t) {
-      if (t >= 1) {
-        // the tile copied in the last round has arrived: say so before waiting for room for the next one
-        cp_async_wait<0>();
-        fence_async_smem();
-        mbar_arrive(&full[(t - 1) % stages]);
-      }
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(map_pages) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(map_new) : "memory");
+    }
+    const int ch = lane % CPR;
+    constexpr int RSTEP = 32 / CPR;
+    int requested = 0;                          // tiles whose copies have been requested
+    for (int t = 0; t < ti.n_max; ++t) {
       const int st = t % stages;
       if (t >= stages && !mbar_wait(&freeb[st], (t / stages - 1) & 1, abortp)) {
         if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 4); }
-        ok = false;
         break;
       }
-      // A tile lies in one cache page, or in this step's packed rows, or (at most once per sequence) partly in each.
+      requested = t + 1;
       const int kt = ti.k_begin + t * TK;
-      const uint32_t dst = smem_u32(base + st * KV_BYTES) + (uint32_t)((ch >> 3) * (TK * 128));
-      if (kt >= ti.lb && kt + TK <= k_end) {
-        const bf16* src = fresh_src + ((long long)(ti.tok0 + kt - ti.lb + r0) * a.nkv + kvh) * HD + ch * 8;
-        const long long step = (long long)RSTEP * a.nkv * HD;
-#pragma unroll 8
-        for (int i = 0; i < PASSES; ++i) cp_async16(dst + swz(r0 + i * RSTEP, ch & 7), src + i * step, true);
+      const uint32_t dst = smem_u32(base + st * KV_BYTES);
+      if (kt >= ti.lb) {
+        // rows past the sequence's last token are another sequence's, or zeros past the buffer: no query sees them
+        if (lane == 0) {
+          mbar_expect_tx(&full[st], KV_BYTES);
+#pragma unroll
+          for (int blk = 0; blk < KB; ++blk)
+            tma_load_3d(dst + blk * (TK * 128), map_new, blk * 64, kvh, ti.tok0 + kt - ti.lb, &full[st]);
+        }
       } else if (kt + TK <= ti.lb) {
-        const bf16* src = page_src + (kv_row(a.page_table, a.table_width, a.ring_pages, ti.slot, kt, kvh, a.nkv) + r0) * HD + ch * 8;
-#pragma unroll 8
-        for (int i = 0; i < PASSES; ++i) cp_async16(dst + swz(r0 + i * RSTEP, ch & 7), src + i * (RSTEP * HD), true);
+        if (lane == 0) {
+          const int row0 = (int)kv_row(a.page_table, a.table_width, a.ring_pages, ti.slot, kt, kvh, a.nkv);
+          mbar_expect_tx(&full[st], KV_BYTES);
+#pragma unroll
+          for (int blk = 0; blk < KB; ++blk) tma_load_2d(dst + blk * (TK * 128), map_pages, blk * 64, row0, &full[st]);
+        }
       } else {
-        const long long old_base = kt < ti.lb ? kv_row(a.page_table, a.table_width, a.ring_pages, ti.slot, kt, kvh, a.nkv) * HD : 0;
+        const long long old_base = kv_row(a.page_table, a.table_width, a.ring_pages, ti.slot, kt, kvh, a.nkv) * HD;
         const long long new_base = ((long long)(ti.tok0 + kt - ti.lb) * a.nkv + kvh) * HD;
-        for (int row = r0; row < TK; row += RSTEP) {
+        for (int row = lane / CPR; row < TK; row += RSTEP) {
           const int pos = kt + row;
           const bool valid = pos < k_end, fresh = pos >= ti.lb;
           const long long off = (fresh ? new_base + (long long)row * a.nkv * HD : old_base + (long long)row * HD) + ch * 8;
-          cp_async16(dst + swz(row, ch & 7), (fresh ? fresh_src : page_src) + (valid ? off : 0), valid);
+          cp_async16(dst + (uint32_t)((ch >> 3) * (TK * 128)) + swz(row, ch & 7), (fresh ? fresh_src : page_src) + (valid ? off : 0),
+                     valid);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[st]);
+      }
+      __syncwarp();
+    }
+    // Copies still write into this block's shared memory until their barrier completes: before the block
+    // may end, see the last tile of every stage arrive (at once, unless a wait ran out somewhere).
+    if (lane == 0) {
+      for (int t = max(0, requested - stages); t < requested; ++t) {
+        const unsigned long long t0 = now_ns();
+        while (!mbar_try_wait(&full[t % stages], (t / stages) & 1)) {
+          if (now_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(&g_error, 0, 7); break; }
         }
       }
-      cp_async_commit();
-    }
-    cp_async_wait<0>();
-    if (ok && ti.n_max > 0) {
-      fence_async_smem();
-      mbar_arrive(&full[(ti.n_max - 1) % stages]);
     }
   } else if (warp == ISSUE_WARP) {
     // ---- products: one lane issues them all.  The tensor core takes them one after the other, and a
@@ -375,6 +421,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) 
           ok = false;
         }
       };
+      wait_or_fail(&q_ready, 0, 5);
       for (int t = 0; t < 2 && t < ti.n_max; ++t) {
         wait_or_fail(&k_full[t % KST], 0, 5);
         if (!ok) break;
@@ -548,6 +595,64 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(PrefillArgs a) 
   }
 }
 
+// ---- host side: tensor maps of the key/value sources ------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// Boxes of 64 rows x 64 head dimensions (128 bytes, swizzled) out of [rows][hd] (cache pages: rows = pages x kv
+// heads x 64 positions) or, with nkv > 0, out of [rows][nkv][hd] for one kv head (the step's packed keys or values).
+bool kv_map(const void* base, long long rows, int nkv, int hd, CUtensorMap* result) {
+  static std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_tuple(base, rows, nkv, hd);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *result = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  CUtensorMap m;
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r;
+  if (nkv > 0) {
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)nkv, (cuuint64_t)rows};
+    cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)nkv * hd * 2};
+    cuuint32_t box[3] = {64, 1, (cuuint32_t)TK};
+    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)TK};
+    r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, m);
+  *result = m;
+  return true;
+}
+
 template <int HD>
 int launch(const PrefillArgs& a, cudaStream_t stream) {
   constexpr int KVB = (HD / 64) * TK * 128;
@@ -558,7 +663,13 @@ int launch(const PrefillArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return llg_fail("attn_prefill_tc: shared memory %d: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.n_tiles, a.nh), dim3(THREADS), (size_t)smem, stream, a);
+  CUtensorMap mkp, mvp, mkn, mvn;
+  const long long page_rows = (long long)a.n_pages * a.nkv * TK;
+  if (!kv_map(a.k_pages, page_rows, 0, HD, &mkp) || !kv_map(a.v_pages, page_rows, 0, HD, &mvp) ||
+      !kv_map(a.k_new, a.n_tokens, a.nkv, HD, &mkn) || !kv_map(a.v_new, a.n_tokens, a.nkv, HD, &mvn))
+    return llg_fail("attn_prefill_tc: cuTensorMapEncodeTiled failed or is not available");
+  cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.n_tiles, a.nh), dim3(THREADS), (size_t)smem, stream, mkp, mvp, mkn,
+                              mvn, a);
   if (le != cudaSuccess) return llg_fail("attn_prefill_tc: launch: %s", cudaGetErrorString(le));
   return llg_check_launch("attn_prefill_tc");
 }
@@ -576,6 +687,10 @@ LLG_API int llg_attn_prefill_tc(const PrefillArgs* args, cudaStream_t stream) {
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages && a.nh <= 65535,
               "attn_prefill_tc: bad cache geometry");
   LLG_REQUIRE(a.scale > 0.f, "attn_prefill_tc: the softmax scale must be positive");
+  LLG_REQUIRE(a.n_tokens > 0 && a.n_pages > 0, "attn_prefill_tc: needs the sizes of the packed rows and of the pages");
+  LLG_REQUIRE(((uintptr_t)a.k_new % 16) == 0 && ((uintptr_t)a.v_new % 16) == 0 && ((uintptr_t)a.k_pages % 16) == 0 &&
+                  ((uintptr_t)a.v_pages % 16) == 0,
+              "attn_prefill_tc: keys and values must be 16-byte aligned");
   if (a.n_tiles <= 0) return 0;
   return a.hd == 64 ? launch<64>(a, stream) : launch<128>(a, stream);
 }

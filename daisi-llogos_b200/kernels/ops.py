@@ -98,7 +98,7 @@ class _PrefillArgs(Structure):
         ("tiles", c_void_p), ("cu_tokens", c_void_p), ("len_before", c_void_p), ("slots", c_void_p),
         ("out", c_void_p),
         ("n_tiles", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int),
-        ("scale", c_float), ("window", c_int),
+        ("scale", c_float), ("window", c_int), ("n_tokens", c_int), ("n_pages", c_int),
     ]
 
 
@@ -433,6 +433,7 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
     a.out = _ptr(out, q.dtype)
     a.n_tiles, a.nh, a.nkv, a.hd = tiles.shape[0], nh, nkv, hd
     a.scale, a.window = float(scale), int(window)
+    a.n_tokens, a.n_pages = k_new.shape[0], k_pages.shape[0]
     if tc:
         _check(lib, lib.llg_attn_prefill_tc(byref(a), _stream()))
     elif mma:
