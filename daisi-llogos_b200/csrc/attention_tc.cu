@@ -3,8 +3,8 @@
 //
 //   per 64-key tile (one cache page):   S = Q K^T      tcgen05.mma, accumulator S[128 x 64] in TMEM
 //                                       each thread reads its row of S (tcgen05.ld), masks, updates the
-//                                       running maximum and sum, writes P (bfloat16) to shared memory
-//                                       O += P V       tcgen05.mma, accumulator O[128 x head] in TMEM
+//                                       running maximum and sum, writes P (bfloat16) over S (tcgen05.st)
+//                                       O += P V       tcgen05.mma, P from TMEM, accumulator O[128 x head] in TMEM
 //
 // A block owns 256 queries of one head as two tiles of 128.  Each tile has a group of four softmax
 // warps: thread r of a group owns query row r of its tile, which is lane r of tensor memory, so the
@@ -15,10 +15,13 @@
 // The roles meet only at mbarriers: tiles full / free between the copying warps and the issuing lane,
 // scores ready, weights ready and accumulator updated between the issuing lane and a group.  Each
 // group has two score buffers in tensor memory, so that the tensor core computes the next tile's
-// scores and the previous tile's O += P V while the group runs the softmax of the current one.
+// scores and the previous tile's O += P V while the group runs the softmax of the current one; the
+// scores of tile j + 1 are issued when O += P(j-1) V(j-1) has finished with the buffer they go into.
 //
-// Q, K and P are K-major operands with the 128-byte swizzle; V is stored as it lies in memory
-// ([key][dim], dim contiguous), which makes it the MN-major second operand of the second product.
+// Q and K are K-major operands in shared memory with the 128-byte swizzle; V is stored as it lies in
+// memory ([key][dim], dim contiguous), which makes it the MN-major second operand of the second product;
+// P never leaves tensor memory (the products' operand fetch from shared memory is what bounds this
+// kernel, and P would be a third of it).
 // A row's accumulator is rescaled in place (tcgen05.ld / tcgen05.st) only when its maximum grows by
 // more than a factor of 2^8 in the weights, warp by warp and only when some row of the warp needs it.
 //
@@ -148,6 +151,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t
       ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// first operand from tensor memory (lane = row, one 32-bit column per two k), second from shared memory
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -227,7 +239,6 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
   constexpr int KB = HD / 64;                 // 64-wide blocks of the head dimension
   constexpr int Q_BYTES = KB * BQ * 128;      // [KB][128 rows][128 bytes]
   constexpr int KV_BYTES = KB * TK * 128;     // [KB][64 keys][128 bytes]
-  constexpr int P_BYTES = BQ * 128;           // [128 rows][64 keys]
   constexpr int TMEM_COLS = 512;              // per group 256: S 2 x 64 columns, O HD columns from column 128
   constexpr uint32_t G_COLS = 256, O_COL = 128;
   constexpr int CPR = HD / 8;                 // 16-byte chunks per row of the head
@@ -236,7 +247,6 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
   unsigned char* Qs = smem;                          // [GROUPS]
   unsigned char* Ks = Qs + GROUPS * Q_BYTES;         // [KST]
   unsigned char* Vs = Ks + KST * KV_BYTES;           // [VST]
-  unsigned char* Ps = Vs + VST * KV_BYTES;           // [GROUPS][2]
   __shared__ uint64_t k_full[KST], k_free[KST], v_full[VST], v_free[VST];
   __shared__ uint64_t s_full[GROUPS][2], p_ready[GROUPS][2], o_done[GROUPS], q_ready;
   __shared__ uint32_t tmem_base_slot;
@@ -422,36 +432,43 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
         }
       };
       wait_or_fail(&q_ready, 0, 5);
-      for (int t = 0; t < 2 && t < ti.n_max; ++t) {
-        wait_or_fail(&k_full[t % KST], 0, 5);
-        if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int g = 0; g < GROUPS; ++g)
-          if (t < ti.n_tiles[g]) issue_scores(g, t);
-        umma_commit(&k_free[t % KST]);
+      if (ok && ti.n_max > 0) {
+        wait_or_fail(&k_full[0], 0, 5);
+        if (ok) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          for (int g = 0; g < GROUPS; ++g)
+            if (0 < ti.n_tiles[g]) issue_scores(g, 0);
+          umma_commit(&k_free[0]);
+        }
       }
+      // Step j: the scores of tile j + 1 go into the buffer whose weights P(j-1) the product of step j - 1 has
+      // read by now; then, once the group has turned S(j) into P(j) (written over S(j) in tensor memory),
+      // O += P(j) V(j).
       for (int j = 0; j < ti.n_max && ok; ++j) {
         wait_or_fail(&v_full[j % VST], (j / VST) & 1, 5);
-        if (j + 2 < ti.n_max) wait_or_fail(&k_full[(j + 2) % KST], ((j + 2) / KST) & 1, 5);
+        if (j + 1 < ti.n_max) wait_or_fail(&k_full[(j + 1) % KST], ((j + 1) / KST) & 1, 5);
         for (int g = 0; g < GROUPS && ok; ++g) {
           if (j >= ti.n_tiles[g]) continue;
-          // the group has turned S(j) into P(j) and, where needed, rescaled its accumulator
+          if (j + 1 < ti.n_tiles[g]) {
+            if (j >= 1) wait_or_fail(&o_done[g], (j - 1) & 1, 6);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_scores(g, j + 1);
+          }
           wait_or_fail(&p_ready[g][j & 1], (j >> 1) & 1, 6);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t pa = smem_u32(Ps + (g * 2 + (j & 1)) * P_BYTES), va = smem_u32(Vs + (j % VST) * KV_BYTES);
+          const uint32_t pa = tmem + g * G_COLS + (uint32_t)(j & 1) * TK, va = smem_u32(Vs + (j % VST) * KV_BYTES);
 #pragma unroll
           for (int kk = 0; kk < TK / 16; ++kk) {
-            // 16 keys further: 32 bytes along P's rows, 16 rows (2048 bytes) down V
-            umma_bf16(tmem + g * G_COLS + O_COL, desc_kmajor(pa + kk * 32), desc_mnmajor(va + kk * 2048, TK * 128), IDESC_O,
-                      (j | kk) != 0);
+            // 16 keys further: 8 columns of packed weights, 16 rows (2048 bytes) down V
+            umma_bf16_ts(tmem + g * G_COLS + O_COL, pa + kk * 8, desc_mnmajor(va + kk * 2048, TK * 128), IDESC_O, (j | kk) != 0);
           }
           umma_commit(&o_done[g]);
-          if (j + 2 < ti.n_tiles[g]) issue_scores(g, j + 2);      // its score buffer j % 2 has been read
         }
         if (!ok) break;
         umma_commit(&v_free[j % VST]);
-        if (j + 2 < ti.n_max) umma_commit(&k_free[(j + 2) % KST]);
+        if (j + 1 < ti.n_max) umma_commit(&k_free[(j + 1) % KST]);
       }
     }
   } else if (tid < WORKERS && ti.nq[tid / BQ] > 0) {
@@ -517,18 +534,18 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
       // weights go straight into the tile's P buffer, which the product of two tiles ago has left
       const float2 sc2 = make_float2(sc, sc), nms2 = make_float2(-ms, -ms);
       float2 ps2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      unsigned char* prow = Ps + (g * 2 + (j & 1)) * P_BYTES;
+      // P(j) takes the place of S(j) in tensor memory: 64 weights of a row in 32 columns
 #pragma unroll
-      for (int c8 = 0; c8 < TK / 8; ++c8) {
-        uint32_t pk[4];
+      for (int c16 = 0; c16 < TK / 32; ++c16) {
+        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 x = __ffma2_rn(make_float2(sv[c8 * 8 + 2 * e], sv[c8 * 8 + 2 * e + 1]), sc2, nms2);
+        for (int e = 0; e < 16; ++e) {
+          const float2 x = __ffma2_rn(make_float2(sv[c16 * 32 + 2 * e], sv[c16 * 32 + 2 * e + 1]), sc2, nms2);
           const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
           ps2[e & 1] = __fadd2_rn(ps2[e & 1], p);
           pk[e] = pack_bf16(p.x, p.y);
         }
-        *reinterpret_cast<uint4*>(prow + swz(r, c8)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        tmem_st16(lane_base + (uint32_t)(j & 1) * TK + c16 * 16, pk);
       }
       l_run = l_run * corr + ((ps2[0].x + ps2[0].y) + (ps2[1].x + ps2[1].y));
 
@@ -550,11 +567,10 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
             for (int c = 0; c < 16; ++c) rr[c] = __float_as_uint(__uint_as_float(rr[c]) * corr);
             tmem_st16(lane_base + O_COL + c0, rr);
           }
-          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
       }
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      fence_async_smem();
       mbar_arrive(&p_ready[g][j & 1]);
     }
     if (ok && !mbar_wait(&o_done[g], (n_tiles - 1) & 1, abortp)) {
@@ -656,7 +672,7 @@ bool kv_map(const void* base, long long rows, int nkv, int hd, CUtensorMap* resu
 template <int HD>
 int launch(const PrefillArgs& a, cudaStream_t stream) {
   constexpr int KVB = (HD / 64) * TK * 128;
-  constexpr int smem = GROUPS * (HD / 64) * BQ * 128 + (KST + VST) * KVB + GROUPS * 2 * BQ * 128;
+  constexpr int smem = GROUPS * (HD / 64) * BQ * 128 + (KST + VST) * KVB;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
