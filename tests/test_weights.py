@@ -104,6 +104,39 @@ def test_tensor_stored_in_32_bit_stays_so(llogos, model_dirs, tmp_path):
     assert m.embedding.weight.dtype == torch.bfloat16
 
 
+def test_shards_and_half_precision_files(llogos, model_dirs, tmp_path):
+    """A model cut into two shards with an index file, some tensors stored as float16: the same model as
+    from one file (float16 becomes bfloat16 where the value allows it exactly here), and an index that
+    names a tensor its shard does not hold is an error."""
+    import json
+    d = str(tmp_path / "sharded")
+    os.makedirs(d)
+    shutil.copy(os.path.join(model_dirs["qwen3"], "config.json"), d)
+    w = read_weights(llogos, model_dirs["qwen3"])
+    names = sorted(w)
+    first, second = names[: len(names) // 2], names[len(names) // 2:]
+    half = {n: (w[n].to(torch.float16) if n.endswith("down_proj.weight") else w[n]) for n in names}
+    llogos.weights.write_safetensors(os.path.join(d, "model-00001-of-00002.safetensors"), {n: half[n] for n in first})
+    llogos.weights.write_safetensors(os.path.join(d, "model-00002-of-00002.safetensors"), {n: half[n] for n in second})
+    weight_map = {n: "model-00001-of-00002.safetensors" for n in first}
+    weight_map.update({n: "model-00002-of-00002.safetensors" for n in second})
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)
+    one = llogos.weights.load_model(model_dirs["qwen3"], dtype=torch.bfloat16, device="cpu", ops=cpu_ops)
+    two = llogos.weights.load_model(d, dtype=torch.bfloat16, device="cpu", ops=cpu_ops)
+    for a, b in zip(one.blocks, two.blocks):
+        assert torch.equal(a.parts["mixer"].w_qkv, b.parts["mixer"].w_qkv)
+        assert b.parts["ffn"].w_down.dtype == torch.bfloat16
+        # bfloat16 -> float16 -> bfloat16 is exact for values whose exponent float16 can hold
+        big = a.parts["ffn"].w_down.float().abs() > 1e-4
+        assert torch.equal(a.parts["ffn"].w_down[big], b.parts["ffn"].w_down[big])
+    weight_map[first[0]] = "model-00002-of-00002.safetensors"
+    with open(os.path.join(d, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)
+    with pytest.raises(Exception, match="is not in"):
+        llogos.weights.load_model(d, dtype=torch.bfloat16, device="cpu", ops=cpu_ops)
+
+
 def test_one_error_lists_everything(llogos, model_dirs, tmp_path):
     d = str(tmp_path / "m")
     shutil.copytree(model_dirs["qwen3"], d)
