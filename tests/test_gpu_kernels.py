@@ -333,6 +333,72 @@ def test_attn_prefill_scores_that_rise_along_the_keys(ops, hd, shape, tc, monkey
         assert ops.attn_tc_status() == 0
 
 
+@pytest.mark.parametrize("tc", [True, False], ids=["tcgen05", "mma"])
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+@pytest.mark.parametrize("hd,window", [(64, 70), (128, 64), (128, 129), (48, 33)])
+def test_attention_window_edge(ops, dtype, hd, window, tc, monkeypatch):
+    """One key per query decides the output: the oldest key that the window still holds (position p - W + 1)
+    for one head, and the newest that it no longer holds (p - W) for another.  The first must come out as
+    that key's value, the second must leave no trace.  Prompt kernel (fresh keys and cached keys) and
+    decode kernel."""
+    if not tc and not (dtype == torch.bfloat16 and hd in (64, 128)):
+        pytest.skip("only head sizes 64 and 128 in bfloat16 have two tensor-core kernels")
+    monkeypatch.setattr(ops, "USE_TC_PROMPT_ATTENTION", tc)
+    nh, nkv, before, count = 2, 1, 150, 260
+    total = before + count
+    g = torch.Generator().manual_seed(5 + hd + window)
+    # key j carries a code of 24 signs, the query carries the code of the key it wants: the wanted key
+    # scores 24 * 1.5 * 1.5 = 54, any other key about 0 +- 11
+    k = 0.05 * torch.randn(total, nkv, hd, generator=g)
+    # values that differ much between neighbouring positions, the same in every element of a row
+    val = ((torch.arange(total) * 37) % 101).float() / 101
+    v = val[:, None, None].expand(total, nkv, hd).clone()
+    code = (torch.randint(0, 2, (total, 24), generator=g).float() * 2 - 1) * 1.5
+    k[:, 0, 0:24] = code
+    q = torch.zeros(total, nh, hd)
+    for p_ in range(total):
+        inside, outside = max(0, p_ - window + 1), p_ - window
+        q[p_, 0, 0:24] = code[inside]                     # head 0: the oldest key the window still holds
+        if outside >= 0:
+            q[p_, 1, 0:24] = code[outside]                # head 1: the newest key it no longer holds
+    k, v, q = k.to(dtype), v.to(dtype), q.to(dtype)
+    ref = P.attention(q, k, v, 1.0, window)                       # [total, nh, hd]
+    # the construction does what it says: head 0 lands on the edge key
+    p_ = total - 1
+    assert abs(float(ref[p_, 0, 5]) - float(val[p_ - window + 1])) < 0.004
+    # and the key just outside, had it been let in, would have shown: without the window most rows differ
+    free = P.attention(q, k, v, 1.0, 0)
+    assert float(((free[before:, 1, 0] - ref[before:, 1, 0]).abs() > 0.1).float().mean()) > 0.6
+    ring = (window + 63) // 64 + 1
+    table = torch.zeros(2, ring, dtype=torch.int32)
+    table[1] = torch.randperm(ring, generator=g).to(torch.int32)
+    kp = torch.zeros(ring, nkv, 64, hd, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    for j in range(max(0, before - ring * 64), before):
+        kp[int(table[1, (j // 64) % ring]), :, j % 64] = k[j]
+        vp[int(table[1, (j // 64) % ring]), :, j % 64] = v[j]
+    tq = ops.prefill_tile_queries(dtype, hd)
+    tiles = torch.tensor([(0, q0) for q0 in range(0, count, tq)], dtype=torch.int32)
+    d = lambda t: t.to(DEV)
+    out = torch.empty(count, nh * hd, dtype=dtype, device=DEV)
+    kpd, vpd = d(kp), d(vp)
+    cu, lb, sl = torch.tensor([0, count], dtype=torch.int32), torch.tensor([before], dtype=torch.int32), torch.tensor([1], dtype=torch.int32)
+    ops.attn_prefill(d(q[before:].contiguous()), d(k[before:].contiguous()), d(v[before:].contiguous()), kpd, vpd, d(table), ring,
+                     d(tiles), d(cu), d(lb), d(sl), out, scale=1.0, window=window, tile_queries=tq)
+    check(out, ref[before:].reshape(count, -1), dtype, "prompt")
+    # decode: the last token alone against the ring as the prompt step leaves it
+    pos = torch.arange(before, total, dtype=torch.int32)
+    ops.kv_write(d(k[before:].contiguous()), d(v[before:].contiguous()), kpd, vpd, d(table), ring, d(pos),
+                 d(torch.zeros(count, dtype=torch.int32)), d(sl), d(cu), d(lb))
+    out1 = torch.empty(1, nh * hd, dtype=dtype, device=DEV)
+    for splits in (1, 2):
+        scratch = torch.empty(ops.attn_decode_scratch_floats(1, nh, hd, splits), device=DEV)
+        ops.attn_decode(d(q[-1:].contiguous()), kpd, vpd, d(table), ring, d(sl), d(torch.tensor([total - 1], dtype=torch.int32)),
+                        out1, scratch, n_splits=splits, scale=1.0, window=window,
+                        counters=torch.zeros(nkv, dtype=torch.int32, device=DEV))
+        check(out1[0], ref[-1].reshape(-1), dtype, ("decode", splits))
+
+
 def test_kernels_refuse_what_they_cannot_do(ops):
     q = torch.zeros(1, 2, 272, device=DEV)
     kp = torch.zeros(1, 1, 64, 272, device=DEV)
