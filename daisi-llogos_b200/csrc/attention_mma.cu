@@ -126,10 +126,11 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
                                               // which is first needed after they are in registers
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  // later tiles of a sequence see more keys: run the list backwards so that long blocks start first
-  const int tile_id = a.n_tiles - 1 - (int)blockIdx.x;
+  // the caller lists the tiles with the most keys first; blocks start head by head within a tile, tile
+  // by tile, so the long blocks start first
+  const int tile_id = (int)blockIdx.y;
   const int b = a.tiles[2 * tile_id], q_off = a.tiles[2 * tile_id + 1];
-  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int h = blockIdx.x, kvh = h / (a.nh / a.nkv);
   const int tok0 = a.cu_tokens[b];
   const int nq = min(64, a.cu_tokens[b + 1] - tok0 - q_off);
   const int lb = a.len_before[b];
@@ -654,11 +655,11 @@ LLG_API int llg_attn_prefill_mma(const PrefillArgs* args, cudaStream_t stream) {
   LLG_REQUIRE(llg_attn_mma_supported(a.hd), "attn_prefill_mma: head_dim %d is not a multiple of 16 up to 128", a.hd);
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_prefill_mma: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
-  LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages && a.nh <= 65535,
-              "attn_prefill_mma: bad cache geometry");
+  LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_prefill_mma: bad cache geometry");
+  LLG_REQUIRE(a.n_tiles <= 65535, "attn_prefill_mma: %d query tiles in one step are more than a grid takes (65535)", a.n_tiles);
   if (a.n_tiles <= 0) return 0;
   const size_t smem = (size_t)4 * 64 * (a.hd * 2 + 16);
-  dim3 grid(a.n_tiles, a.nh);
+  dim3 grid(a.nh, a.n_tiles);
 #define GO(HDM, EX)                                                                        \
   do {                                                                                     \
     if (set_smem(attn_prefill_mma_kernel<HDM, EX>, smem, "attn_prefill_mma")) return 1;      \

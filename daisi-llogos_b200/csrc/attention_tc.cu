@@ -291,10 +291,12 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
   volatile int* abortp = &abort_flag;
   pdl_wait();
 
-  // later tiles of a sequence see more keys: run the list backwards so that long blocks start first
+  // Blocks start in the order of blockIdx.x, then blockIdx.y: all heads of the list's first tile, then all
+  // heads of its second ...  The caller lists the tiles with the most keys first, so that the long blocks
+  // start first and the short ones fill the gaps at the end.
   TileInfo ti;
   {
-    const int tile_id = a.n_tiles - 1 - (int)blockIdx.x;
+    const int tile_id = (int)blockIdx.y;
     ti.b = a.tiles[2 * tile_id];
     const int q_off = a.tiles[2 * tile_id + 1];
     ti.tok0 = a.cu_tokens[ti.b];
@@ -314,7 +316,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
       ti.n_max = max(ti.n_max, ti.n_tiles[g]);
     }
   }
-  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int h = blockIdx.x, kvh = h / (a.nh / a.nkv);
   const int k_end = ti.pos0[0] + (ti.nq[1] > 0 ? BQ + ti.nq[1] : ti.nq[0]);   // keys past it are never copied
   const int q_tok0 = ti.tok0 + ti.pos0[0] - ti.lb;                              // first token of the first query tile
 
@@ -684,7 +686,7 @@ int launch(const PrefillArgs& a, cudaStream_t stream) {
   if (!kv_map(a.k_pages, page_rows, 0, HD, &mkp) || !kv_map(a.v_pages, page_rows, 0, HD, &mvp) ||
       !kv_map(a.k_new, a.n_tokens, a.nkv, HD, &mkn) || !kv_map(a.v_new, a.n_tokens, a.nkv, HD, &mvn))
     return llg_fail("attn_prefill_tc: cuTensorMapEncodeTiled failed or is not available");
-  cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.n_tiles, a.nh), dim3(THREADS), (size_t)smem, stream, mkp, mvp, mkn,
+  cudaError_t le = llg_launch(attn_prefill_tc_kernel<HD>, dim3(a.nh, a.n_tiles), dim3(THREADS), (size_t)smem, stream, mkp, mvp, mkn,
                               mvn, a);
   if (le != cudaSuccess) return llg_fail("attn_prefill_tc: launch: %s", cudaGetErrorString(le));
   return llg_check_launch("attn_prefill_tc");
@@ -700,8 +702,8 @@ LLG_API int llg_attn_prefill_tc(const PrefillArgs* args, cudaStream_t stream) {
   LLG_REQUIRE(llg_attn_tc_supported(a.hd), "attn_prefill_tc: head_dim %d is neither 64 nor 128", a.hd);
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_prefill_tc: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
-  LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages && a.nh <= 65535,
-              "attn_prefill_tc: bad cache geometry");
+  LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_prefill_tc: bad cache geometry");
+  LLG_REQUIRE(a.n_tiles <= 65535, "attn_prefill_tc: %d query tiles in one step are more than a grid takes (65535)", a.n_tiles);
   LLG_REQUIRE(a.scale > 0.f, "attn_prefill_tc: the softmax scale must be positive");
   LLG_REQUIRE(a.n_tokens > 0 && a.n_pages > 0, "attn_prefill_tc: needs the sizes of the packed rows and of the pages");
   LLG_REQUIRE(((uintptr_t)a.k_new % 16) == 0 && ((uintptr_t)a.v_new % 16) == 0 && ((uintptr_t)a.k_pages % 16) == 0 &&

@@ -249,7 +249,10 @@ class Engine:
         token_ids = np.concatenate(toks).astype(np.int32)
         positions = np.concatenate([np.arange(lb, lb + c, dtype=np.int32) for lb, c in zip(len_before, counts)])
         seq_of = np.repeat(np.arange(b, dtype=np.int32), counts)
-        tiles = [np.array([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)],
+        # query tiles, those that see the most keys first: attention blocks start in list order, and the long
+        # ones should not be the last to start
+        tiles = [np.array(sorted(((i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)),
+                                 key=lambda t: -(len_before[t[0]] + min(counts[t[0]], t[1] + tq))),
                           dtype=np.int32).reshape(-1) for tq in _TILE_QS]
         rows = np.array([cu[i] + int(w) for i in range(b) for w in want[i]], dtype=np.int32)
         host = [token_ids, positions, seq_of, np.asarray(slots, dtype=np.int32), cu,
