@@ -143,8 +143,10 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   constexpr int A_BYTES = MT * A_TILE;
   constexpr int B_BYTES = TN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int TMEM_COLS = MT * TN < 32 ? 32 : MT * TN;
-  static_assert(EPI == 0 || (SWAP ? TN == 256 : MT == 2), "the gated epilogue needs a gate tile and an up tile");
+  constexpr int TMEM_COLS = MT * TN <= 32 ? 32 : MT * TN <= 64 ? 64 : MT * TN <= 128 ? 128 : MT * TN <= 256 ? 256 : 512;
+  static_assert(MT * TN <= 512, "the accumulators do not fit tensor memory");
+  static_assert(TN % 16 == 0, "the second operand's tile is a multiple of 16 rows");
+  static_assert(EPI == 0 || (SWAP ? TN % 32 == 0 : MT == 2), "the gated epilogue needs a gate tile and an up tile");
   // 1024-byte alignment of the operand tiles is what the swizzle pattern of TMA and of the MMA assume
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], done_bar;
@@ -312,7 +314,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
           constexpr int COLS = EPI ? TN / 2 : TN;
 #pragma unroll
           for (int c0 = 0; c0 < COLS; c0 += 16) {
-            const int f0 = EPI ? (n0 / 256) * 128 + c0 : n0 + c0;      // first feature of this run
+            const int f0 = EPI ? n0 / 2 + c0 : n0 + c0;      // first feature of this run (a gated tile: TN / 2 features)
             if (f0 >= width) break;
             float v[16];
             uint32_t r[16];
@@ -531,24 +533,54 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   const int nkb = (k + BK - 1) / BK;
   CUtensorMap map_w, map_x;
   if (n >= 256 && tile_n <= 0) {
-    // ---- prompt steps: activations are the first operand (128 tokens per tile), 256 features per tile ----
+    // ---- prompt steps: activations are the first operand (128 tokens per tile), up to 256 features per tile ----
     // in this orientation the kernel's first-operand rows (field o) are the tokens, the second's (field n) the features
     GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features, o / 2, BM};
-    // the gated product fetches the gate half and the up half of a feature tile with a box of 128 rows each
-    LLG_REQUIRE(tensor_map(x, n, k, BM, &map_x) && tensor_map(w, o, k, gated ? 128 : 256, &map_w),
-                "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
-    const long long nt = (o + 255) / 256;
-    const long long t1 = (long long)((n + BM - 1) / BM) * nt, t2 = (long long)((n + 2 * BM - 1) / (2 * BM)) * nt;
-    // two token tiles per block halve the weight traffic per flop (worth about 15 %) but double the tile
-    const bool two = ((t2 + 147) / 148) * 2 * 0.85 < (double)((t1 + 147) / 148);
-#define GOS(OTT, EP)                                                                       \
-  return two ? launch<256, 3, OTT, 2, EP, 1>(&map_x, &map_w, ps, splits, stream)             \
-             : launch<256, 4, OTT, 1, EP, 1>(&map_x, &map_w, ps, splits, stream)
-    if (gated) {
-      if (out_dtype == LLG_F32) GOS(float, 1); else GOS(__nv_bfloat16, 1);
-    } else {
-      if (out_dtype == LLG_F32) GOS(float, 0); else GOS(__nv_bfloat16, 0);
+    // Tile shape: blocks run in rounds of 148; a round costs its tile's width, and a narrower tile can save a
+    // round (4096 features: 16 tiles of 256 in two token rows of 8 are 128 blocks, 18 of 240 are 144).  Two token
+    // tiles per block halve the weight traffic per flop (worth about 15 %) but double the tile.
+    const int widths[5] = {256, gated ? 192 : 240, 224, gated ? 256 : 208, gated ? 256 : 176};
+    int best_w = 256, best_mt = 1;
+    double best_cost = 0;
+    for (int wi = 0; wi < 5; ++wi) {
+      for (int mt = 1; mt <= 2; ++mt) {
+        if (mt == 1 && widths[wi] < 224) continue;      // a single token tile wants a wide second operand
+        const long long tiles = (long long)((n + mt * BM - 1) / (mt * BM)) * ((o + widths[wi] - 1) / widths[wi]);
+        const double cost = (double)((tiles + 147) / 148) * widths[wi] * mt * (mt == 2 ? 0.85 : 1.0);
+        if (best_cost == 0 || cost < best_cost * 0.999) {
+          best_cost = cost;
+          best_w = widths[wi];
+          best_mt = mt;
+        }
+      }
     }
+    if (gated && out_dtype == LLG_F32) best_w = 256;
+    // the gated product fetches the gate half and the up half of a feature tile with a box of half the width each
+    LLG_REQUIRE(tensor_map(x, n, k, BM, &map_x) && tensor_map(w, o, k, gated ? best_w / 2 : best_w, &map_w),
+                "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
+#define GOS(W, OTT, EP)                                                                        \
+  return best_mt == 2 ? launch<W, 3, OTT, 2, EP, 1>(&map_x, &map_w, ps, splits, stream)          \
+                      : launch<W, 4, OTT, 1, EP, 1>(&map_x, &map_w, ps, splits, stream)
+    if (gated) {
+      if (out_dtype == LLG_F32) GOS(256, float, 1);      // float32 out: the widest tile only
+      if (best_w == 256) GOS(256, __nv_bfloat16, 1);
+      if (best_w == 224) GOS(224, __nv_bfloat16, 1);
+      GOS(192, __nv_bfloat16, 1);
+    }
+#define GO2(W, OTT) return launch<W, 3, OTT, 2, 0, 1>(&map_x, &map_w, ps, splits, stream)
+    if (out_dtype == LLG_F32) {
+      if (best_w == 256) GOS(256, float, 0);
+      if (best_w == 240) GOS(240, float, 0);
+      if (best_w == 224) GOS(224, float, 0);
+      if (best_w == 208) GO2(208, float);
+      GO2(176, float);
+    }
+    if (best_w == 256) GOS(256, __nv_bfloat16, 0);
+    if (best_w == 240) GOS(240, __nv_bfloat16, 0);
+    if (best_w == 224) GOS(224, __nv_bfloat16, 0);
+    if (best_w == 208) GO2(208, __nv_bfloat16);
+    GO2(176, __nv_bfloat16);
+#undef GO2
 #undef GOS
   }
   // Features per block of a gated product: with one token tile the blocks should be as many as the SMs (or a
