@@ -545,7 +545,7 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
     for (int wi = 0; wi < 5; ++wi) {
       for (int mt = 1; mt <= 2; ++mt) {
         if (mt == 1 && widths[wi] < 224) continue;      // a single token tile wants a wide second operand
-        const long long tiles = (long long)((n + mt * BM - 1) / (mt * BM)) * ((o + widths[wi] - 1) / widths[wi]);
+        const long long tiles = (long long)((n + mt * BM - 1) / (mt * BM)) * ((o + widths[wi] - 1) / widths[wi]) * splits;
         const double cost = (double)((tiles + 147) / 148) * widths[wi] * mt * (mt == 2 ? 0.85 : 1.0);
         if (best_cost == 0 || cost < best_cost * 0.999) {
           best_cost = cost;
