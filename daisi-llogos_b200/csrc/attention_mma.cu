@@ -348,8 +348,24 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 // `counters` ([n_seqs][nkv] ints, zero before the first launch) let the block that finishes last for a
 // (sequence, key/value head) join the partials of all splits and write `out`; it leaves the counter at
 // zero again.  No second kernel is needed.
-template <int HDMAX, bool EXACT>
+//
+// Work items are (sequence, key/value head, split); a block takes items blockIdx.x, blockIdx.x +
+// gridDim.x, ...  With `balance` a sequence has as many splits as its length calls for (at most
+// a.n_splits): every block works out the same number T of key tiles per item, the least with which the
+// items of all sequences fit the GPU at once, and sequence b gets ceil(tiles_b / T) splits.  A batch of
+// one long and seven short sequences then spreads the long one over most of the GPU; sequences of one
+// length get the same count each.  Without `balance` every sequence has a.n_splits splits.
+constexpr int DECODE_SLOTS = 2 * 148;         // blocks of this kernel that the GPU holds at once
+
+// 64-key tiles that a sequence of `len` keys reads
+__device__ __forceinline__ int decode_tiles(int len, int window) {
+  const int lo = window > 0 ? max(0, len - window) : 0;
+  return (len + TK - 1) / TK - lo / TK;
+}
+
+template <int HDMAX, bool EXACT, bool BALANCE>
 __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16* __restrict__ out, int* __restrict__ counters) {
+  constexpr bool balance = BALANCE;
   extern __shared__ __align__(16) unsigned char smraw[];
   __shared__ int is_last;
   pdl_launch_dependents();
@@ -366,13 +382,56 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
   float* merge = reinterpret_cast<float*>(smraw);     // after the key loop: [4 warps][GH heads][hd + 2]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = a.nh / a.nkv;
+  // ---- the plan: key tiles per item, and how many items there are.  Lane i of every warp keeps the tile
+  // count of sequence i (a balanced launch has at most 32 sequences), so no warp waits for another. ----
+  int n_items = a.n_seqs * a.n_splits * a.nkv, tiles_per_item = 0;
+  int my_tiles = 0;
+  if (balance) {
+    my_tiles = lane < a.n_seqs ? decode_tiles(a.len_before[lane] + 1, a.window) : 0;
+    int hi = max(1, my_tiles);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
+    int lo_t = 1, n = 0;
+    for (;;) {                                       // least T with nkv * sum_b min(n_splits, ceil(tiles_b / T)) <= slots
+      const int mid = lo_t < hi ? (lo_t + hi) >> 1 : hi;
+      n = lane < a.n_seqs ? max(1, min(a.n_splits, (my_tiles + mid - 1) / mid)) : 0;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
+      if (lo_t >= hi) break;
+      if (n * a.nkv <= DECODE_SLOTS) hi = mid;
+      else lo_t = mid + 1;
+    }
+    tiles_per_item = hi;
+    n_items = n * a.nkv;
+  }
+ // (without balancing the grid is (splits, key/value heads, sequences), one block per item: the body runs once)
+ for (int item = balance ? blockIdx.x : 0; item < n_items; item += balance ? gridDim.x : n_items) {
+  // balanced: item -> (sequence, split, key/value head), the heads of one (sequence, split) are neighbours
+  int kvh, b, split, ns = a.n_splits;
+  if (balance) {
+    kvh = item % a.nkv;
+    split = item / a.nkv;
+    const int mine = lane < a.n_seqs ? max(1, min(a.n_splits, (my_tiles + tiles_per_item - 1) / tiles_per_item)) : 0;
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    b = __ffs(__ballot_sync(0xffffffffu, incl > split)) - 1;       // first sequence whose items reach past this one
+    ns = __shfl_sync(0xffffffffu, mine, b);
+    split -= __shfl_sync(0xffffffffu, incl, b) - ns;
+  } else {
+    split = blockIdx.x;
+    kvh = blockIdx.y;
+    b = blockIdx.z;
+  }
   const int len = a.len_before[b] + 1;
   const int slot = a.slots[b];
   const int lo = a.window > 0 ? max(0, len - a.window) : 0;
   const int t0 = lo / TK, t_end = (len + TK - 1) / TK;
-  const int per_split = (t_end - t0 + a.n_splits - 1) / a.n_splits;
+  const int per_split = (t_end - t0 + ns - 1) / ns;
   const int my0 = t0 + split * per_split;
   const int my1 = min(t_end, my0 + per_split);
   const int n_my = max(0, my1 - my0);
@@ -580,11 +639,11 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
   __syncthreads();
   if (tid == 0) {
     const int ticket = atomicAdd(&counters[b * a.nkv + kvh], 1);   // ... before its ticket is
-    is_last = ticket == a.n_splits - 1;
+    is_last = ticket == ns - 1;
     if (is_last) counters[b * a.nkv + kvh] = 0;
   }
   __syncthreads();
-  if (!is_last) return;
+  if (!is_last) continue;
   __threadfence();
   // one warp per head; the splits' weights exp(m_s - M) are worked out by the lanes side by side and kept
   // in shared memory (64 at a time), then every lane sums its head dimensions over the splits with
@@ -593,10 +652,10 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
   for (int head = kvh * G + warp; head < (kvh + 1) * G; head += 4) {
     const long long base = ((long long)b * a.nh + head) * a.n_splits;
     float M = -INFINITY;
-    for (int s = lane; s < a.n_splits; s += 32) M = fmaxf(M, __ldcg(&a.part_ml[(base + s) * 2]));
+    for (int s = lane; s < ns; s += 32) M = fmaxf(M, __ldcg(&a.part_ml[(base + s) * 2]));
     M = warp_max(M);
     float L = 0.f;
-    for (int s = lane; s < a.n_splits; s += 32) {
+    for (int s = lane; s < ns; s += 32) {
       const float ms = __ldcg(&a.part_ml[(base + s) * 2]);
       if (ms != -INFINITY) L += expf(ms - M) * __ldcg(&a.part_ml[(base + s) * 2 + 1]);
     }
@@ -605,10 +664,10 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
     float oacc[HDMAX / 32];
 #pragma unroll
     for (int dd = 0; dd < HDMAX / 32; ++dd) oacc[dd] = 0.f;
-    for (int s0 = 0; s0 < a.n_splits; s0 += 64) {
-      const int ns = min(64, a.n_splits - s0);
+    for (int s0 = 0; s0 < ns; s0 += 64) {
+      const int nc = min(64, ns - s0);
       __syncwarp();
-      for (int s = lane; s < ns; s += 32) {
+      for (int s = lane; s < nc; s += 32) {
         const float ms = __ldcg(&a.part_ml[(base + s0 + s) * 2]);
         wsm[s] = (ms == -INFINITY) ? 0.f : expf(ms - M);
       }
@@ -620,12 +679,12 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
           const float* po = a.part_o + (base + s0) * hd + d;
           float o = 0.f;
           int s = 0;
-          for (; s + 4 <= ns; s += 4) {
+          for (; s + 4 <= nc; s += 4) {
             const float p0 = __ldcg(po + (long long)(s + 0) * hd), p1 = __ldcg(po + (long long)(s + 1) * hd);
             const float p2 = __ldcg(po + (long long)(s + 2) * hd), p3 = __ldcg(po + (long long)(s + 3) * hd);
             o += wsm[s] * p0 + wsm[s + 1] * p1 + wsm[s + 2] * p2 + wsm[s + 3] * p3;
           }
-          for (; s < ns; ++s) o += wsm[s] * __ldcg(po + (long long)s * hd);
+          for (; s < nc; ++s) o += wsm[s] * __ldcg(po + (long long)s * hd);
           oacc[dd] += o;
         }
       }
@@ -636,6 +695,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
       if (d < hd) out[((long long)b * a.nh + head) * hd + d] = __float2bfloat16_rn(oacc[dd] * inv);
     }
   }
+ }   // items
 }
 
 template <typename K>
@@ -673,23 +733,37 @@ LLG_API int llg_attn_prefill_mma(const PrefillArgs* args, cudaStream_t stream) {
   return llg_check_launch("attn_prefill_mma");
 }
 
-LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, int* counters, cudaStream_t stream) {
+// n_splits: the most blocks that share one (sequence, key/value head), and the stride of the partials.
+// balance = 1: a sequence uses as many of them as its length calls for (see the kernel); for batches whose
+// (sequence, key/value head) pairs are at most half the blocks that the GPU holds.
+LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, int* counters, int balance, cudaStream_t stream) {
   const DecodeArgs& a = *args;
   LLG_REQUIRE(llg_attn_mma_supported(a.hd), "attn_decode_mma: head_dim %d is not a multiple of 16 up to 128", a.hd);
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_decode_mma: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
   LLG_REQUIRE(a.n_splits >= 1 && a.n_splits <= 65535 && a.nkv <= 65535 && a.n_seqs <= 65535, "attn_decode_mma: grid too large");
+  LLG_REQUIRE(!balance || (a.n_seqs * a.nkv <= DECODE_SLOTS / 2 && a.n_seqs <= 32),
+              "attn_decode_mma: balanced splits are for at most 32 sequences and %d (sequence, key/value head) pairs",
+              DECODE_SLOTS / 2);
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_decode_mma: bad cache geometry");
   LLG_REQUIRE(counters != nullptr, "attn_decode_mma: needs n_seqs * nkv zeroed counters");
   if (a.n_seqs <= 0) return 0;
   size_t smem = (size_t)2 * DSTAGES * 64 * (a.hd * 2 + 16);
   const size_t merge = (size_t)4 * GH * (a.hd + 2) * sizeof(float);
   if (merge > smem) smem = merge;
-  dim3 grid(a.n_splits, a.nkv, a.n_seqs);
-#define GO(HDM, EX)                                                                       \
-  do {                                                                                    \
-    if (set_smem(attn_decode_mma_kernel<HDM, EX>, smem, "attn_decode_mma")) return 1;       \
-    llg_launch(attn_decode_mma_kernel<HDM, EX>, grid, dim3(128), smem, stream, a, (bf16*)out, counters);  \
+  // balanced: as many blocks as the GPU holds, each taking the items that fall to it; otherwise one block per
+  // item, which lets the hardware start the next block of an SM while its neighbour is still in its last tiles
+  const long long items = (long long)a.n_splits * a.nkv * a.n_seqs;
+  const dim3 grid = balance ? dim3((unsigned)(items > DECODE_SLOTS ? DECODE_SLOTS : items)) : dim3(a.n_splits, a.nkv, a.n_seqs);
+#define GO(HDM, EX)                                                                                         \
+  do {                                                                                                      \
+    if (balance) {                                                                                          \
+      if (set_smem(attn_decode_mma_kernel<HDM, EX, true>, smem, "attn_decode_mma")) return 1;                 \
+      llg_launch(attn_decode_mma_kernel<HDM, EX, true>, grid, dim3(128), smem, stream, a, (bf16*)out, counters);  \
+    } else {                                                                                                \
+      if (set_smem(attn_decode_mma_kernel<HDM, EX, false>, smem, "attn_decode_mma")) return 1;                \
+      llg_launch(attn_decode_mma_kernel<HDM, EX, false>, grid, dim3(128), smem, stream, a, (bf16*)out, counters); \
+    }                                                                                                       \
   } while (0)
   if (a.hd == 64) GO(64, true);
   else if (a.hd == 128) GO(128, true);

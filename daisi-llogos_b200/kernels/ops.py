@@ -174,7 +174,7 @@ def _load_lib(name: str):
     elif name == "attention_mma":
         lib.llg_attn_mma_supported.argtypes = [c_int]
         lib.llg_attn_prefill_mma.argtypes = [POINTER(_PrefillArgs), c_void_p]
-        lib.llg_attn_decode_mma.argtypes = [POINTER(_DecodeArgs), c_void_p, c_void_p, c_void_p]
+        lib.llg_attn_decode_mma.argtypes = [POINTER(_DecodeArgs), c_void_p, c_void_p, c_int, c_void_p]
     elif name == "attention_tc":
         lib.llg_attn_tc_supported.argtypes = [c_int]
         lib.llg_attn_prefill_tc.argtypes = [POINTER(_PrefillArgs), c_void_p]
@@ -447,17 +447,25 @@ def attn_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_split
     return n_seqs * n_heads * n_splits * (head_dim + 2)
 
 
+def attn_decode_balance_pairs() -> int:
+    """Most (sequence, key/value head) pairs for which decode attention balances its splits by length."""
+    return 148
+
+
 def attn_decode_uses_counters(dtype: torch.dtype, head_dim: int) -> bool:
     """Whether ``attn_decode`` wants ``counters`` (the tensor-core kernel joins its splits itself)."""
     return _use_mma(dtype, head_dim)
 
 
 def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
-                n_splits: int, scale: float, window: int, counters: Optional[torch.Tensor] = None) -> None:
+                n_splits: int, scale: float, window: int, counters: Optional[torch.Tensor] = None,
+                balance: bool = False) -> None:
     """Attention of one new token per sequence over the cache; ``scratch`` holds the split partials.
 
     The tensor-core kernel also needs ``counters``: ``n_seqs * n_kv_heads`` int32, zero when first used
-    (the kernel leaves them zero), through which the last block of a sequence joins the splits."""
+    (the kernel leaves them zero), through which the last block of a sequence joins the splits.
+    ``balance`` (tensor-core kernel, at most ``attn_decode_balance_pairs()`` (sequence, kv head) pairs):
+    ``n_splits`` is the most splits a sequence may have; each gets as many as its length calls for."""
     b, nh, hd = q.shape
     nkv = k_pages.shape[1]
     if scale <= 0:
@@ -479,7 +487,8 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
     if mma:
         if counters is None or counters.numel() < b * nkv:
             raise KernelError(f"attn_decode: needs {b * nkv} zeroed int32 counters")
-        _check(lib, lib.llg_attn_decode_mma(byref(a), _ptr(out, q.dtype), _ptr(counters, torch.int32), _stream()))
+        _check(lib, lib.llg_attn_decode_mma(byref(a), _ptr(out, q.dtype), _ptr(counters, torch.int32),
+                                            int(bool(balance) and b * nkv <= attn_decode_balance_pairs() and b <= 32), _stream()))
     else:
         _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()), kernels=2)
 

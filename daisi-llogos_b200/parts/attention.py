@@ -121,6 +121,12 @@ class Attention(Mixer):
             else:
                 ops.qk_prep(qkv, **common)
             splits = decode_splits(ctx.n_seqs, self.nkv, ctx.max_len_after)
+            # Sequences of unequal lengths: the kernel gives each as many splits as its length calls for, up to what
+            # one long sequence among short ones could use (the blocks the GPU holds, less one per other pair).
+            balance = 1 < ctx.n_seqs <= 32 and ctx.n_seqs * self.nkv <= ops.attn_decode_balance_pairs()
+            if balance:
+                tiles = max(1, -(-ctx.max_len_after // 64))
+                splits = max(splits, min(64, tiles, 2 * 148 // self.nkv - (ctx.n_seqs - 1)))
             scratch = ctx.buffer("attn.scratch", (ops.attn_decode_scratch_floats(n, self.nh, self.hd, splits),),
                                  torch.float32)
             counters = None
@@ -128,7 +134,7 @@ class Attention(Mixer):
                 counters = ctx.buffer("attn.counters", (n * self.nkv,), torch.int32, zero=True)
             ops.attn_decode(q, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages, ctx.slots,
                             ctx.len_before, out, scratch, n_splits=splits, scale=self.scale, window=self.window,
-                            counters=counters)
+                            counters=counters, balance=balance)
         else:
             # A group that keeps every key can take the step's keys and values into its pages right away
             # (the step reads them from the packed buffer, never from the pages).  A ring must wait until

@@ -173,8 +173,12 @@ def attn_decode_uses_counters(dtype, head_dim):
     return False
 
 
+def attn_decode_balance_pairs():
+    return 148
+
+
 def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *, n_splits,
-                scale, window, counters=None):
+                scale, window, counters=None, balance=False):
     b_n, nh, hd = q.shape
     nkv = k_pages.shape[1]
     g = nh // nkv

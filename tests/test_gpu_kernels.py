@@ -225,13 +225,15 @@ def test_attn_decode(ops, dtype, nh, nkv, hd, window):
     kp, vp, table, slots, ks, vs = _paged(nkv, hd, dtype, lens, 40, ring, 30)
     q = rnd((len(lens), nh, hd), 31, dtype)
     scale = 1 / math.sqrt(hd)
-    for splits in (1, 3, 7):
+    counters = torch.zeros(len(lens) * nkv, dtype=torch.int32, device=DEV)
+    for splits, balance in ((1, False), (3, False), (7, False), (7, True), (2, True), (40, True)):
         out = torch.empty(len(lens), nh * hd, dtype=dtype, device=DEV)
         scratch = torch.empty(ops.attn_decode_scratch_floats(len(lens), nh, hd, splits), device=DEV)
         lb = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+        # balance: every sequence takes as many of the splits as its length calls for (1 to 5 tiles here)
         ops.attn_decode(q.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV), ring, slots.to(DEV), lb.to(DEV), out,
-                        scratch, n_splits=splits, scale=scale, window=window,
-                        counters=torch.zeros(len(lens) * nkv, dtype=torch.int32, device=DEV))
+                        scratch, n_splits=splits, scale=scale, window=window, counters=counters, balance=balance)
+        assert int(counters.abs().sum()) == 0
         for b, n in enumerate(lens):
             qq = torch.zeros(n, nh, hd, dtype=dtype)
             qq[-1] = q[b]
