@@ -177,6 +177,11 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       tma_load_2d(dst, &map_x, kb * BK, n0, bar);
     }
   };
+  // first operand: MT tiles of 128 rows
+  auto load_first = [&](unsigned char* dst, int kb, int o0, uint64_t* bar) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) tma_load_2d(dst + mt * A_TILE, &map_w, kb * BK, w_row(o0, mt), bar);
+  };
   const int nkb_total = (p.k + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, nkb_total - kb0);   // >= 1 by construction of the grid
@@ -220,16 +225,19 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       // ---- producer: TMA loads into the ring ------------------------------------------------
       if (first) {
         // The weights do not depend on the previous kernel: the first ring of weight tiles is requested
-        // before this kernel waits for its predecessor, the activation tiles right after.
+        // before this kernel waits for its predecessor, the activation tiles right after.  The weights are
+        // the first operand of a decode step's product and the second of a prompt step's.
         const int pre = min(nkb, STAGES);
         for (int i = 0; i < pre; ++i) {
           mbar_expect_tx(&full_bar[i], stage_tx);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-            tma_load_2d(smem + i * STAGE_BYTES + mt * A_TILE, &map_w, (kb0 + i) * BK, w_row(o0, mt), &full_bar[i]);
+          if (SWAP) load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
+          else load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
         }
         pdl_wait();
-        for (int i = 0; i < pre; ++i) load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
+        for (int i = 0; i < pre; ++i) {
+          if (SWAP) load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
+          else load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
+        }
         it_issue = pre;
         preloaded = pre;
       }
@@ -242,8 +250,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         }
         mbar_expect_tx(&full_bar[s], stage_tx);
         unsigned char* a = smem + s * STAGE_BYTES;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * A_TILE, &map_w, (kb0 + i) * BK, w_row(o0, mt), &full_bar[s]);
+        load_first(a, kb0 + i, o0, &full_bar[s]);
         load_second(a + A_BYTES, kb0 + i, n0, &full_bar[s]);
       }
     } else if (first) {
@@ -291,8 +298,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         const int s = it_issue % STAGES;
         mbar_expect_tx(&full_bar[s], stage_tx);
         unsigned char* a = smem + s * STAGE_BYTES;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) tma_load_2d(a + mt * A_TILE, &map_w, (kb0 + i) * BK, w_row(no0, mt), &full_bar[s]);
+        load_first(a, kb0 + i, no0, &full_bar[s]);
         load_second(a + A_BYTES, kb0 + i, nn0, &full_bar[s]);
       }
       preloaded = pre;

@@ -14,7 +14,7 @@ import math
 
 import torch
 
-from ..kernels.linear import SPLIT_ROWS_MAX, linear
+from ..kernels.linear import linear
 from .base import Branch, KvNeed, Mixer, TensorDecl, register_part
 
 
@@ -103,8 +103,9 @@ class Attention(Mixer):
         ops = ctx.ops
         n = x.shape[0]
         nkv_in = self.nkv if self.own_kv else 0
-        small = ctx.decode or n <= SPLIT_ROWS_MAX     # float32 partials: the product may split K
-        qkv = linear(ctx, x, self.w_qkv, "attn.qkv", torch.float32 if small else ctx.dtype)
+        # float32 (partials when the product splits K): bias, norm and rotation see the unrounded sums whatever
+        # the size of the step, so q and k are rounded once
+        qkv = linear(ctx, x, self.w_qkv, "attn.qkv", torch.float32)
         rot = self.encoding.rotation() if self.encoding is not None else None
         q = ctx.buffer("attn.q", (n, self.nh, self.hd))
         out = ctx.buffer("attn.out", (n, self.nh * self.hd))

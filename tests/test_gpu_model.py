@@ -134,6 +134,38 @@ def test_long_decoding_from_the_first_token(llogos, model_dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_prompts_of_hundreds_of_tokens(llogos, model_dirs, name, dtype):
+    """Steps of 256 tokens and more take the products with tokens as the tensor-core rows and the large
+    attention tiles; above 512 tokens the projections write bfloat16.  Every position is compared, alone
+    and as one batch, twice in a row: each kernel starts while its predecessor still runs, and one that
+    read its input before the wait would show here."""
+    cfg = TINY[name]
+    w = read_weights(llogos, model_dirs[name])
+    seqs = random_tokens(cfg["vocab_size"], [300, 257, 500, 70], 13)
+    refs = [P.forward(w, cfg, s) for s in seqs]
+    model = llogos.weights.load_model(model_dirs[name], dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 24)
+    for rep in range(2):
+        for s, r in zip(seqs, refs):
+            slot = eng.open()
+            lg = eng.step([(slot, s)], [list(range(len(s)))])
+            ok, err = close(lg, r, dtype, float(r.abs().max()))
+            assert ok, ("alone", rep, len(s), err)
+            eng.close(slot)
+        slots = [eng.open() for _ in seqs]
+        lg = eng.step(list(zip(slots, seqs)), [list(range(len(s))) for s in seqs])
+        row = 0
+        for s, r in zip(seqs, refs):
+            ok, err = close(lg[row:row + len(s)], r, dtype, float(r.abs().max()))
+            assert ok, ("batch", rep, len(s), err)
+            row += len(s)
+        for slot in slots:
+            eng.close(slot)
+    eng.cache.audit()
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 def test_reused_pages_do_not_leak_old_keys(llogos, model_dirs, dtype):
     """A slot and its pages are used again by a shorter request: the logits must not see the
     previous owner's keys beyond the new request's length."""
