@@ -137,7 +137,7 @@ def test_long_decoding_from_the_first_token(llogos, model_dirs, name, dtype):
 @pytest.mark.parametrize("name", list(TINY))
 def test_prompts_of_hundreds_of_tokens(llogos, model_dirs, name, dtype):
     """Steps of 256 tokens and more take the products with tokens as the tensor-core rows and the large
-    attention tiles; above 512 tokens the projections write bfloat16.  Every position is compared, alone
+    attention tiles; above 512 tokens no product splits its sums.  Every position is compared, alone
     and as one batch, twice in a row: each kernel starts while its predecessor still runs, and one that
     read its input before the wait would show here."""
     cfg = TINY[name]
