@@ -6,8 +6,10 @@
 // inverse CDF from one uniform number (:334-345).  The reference sorts candidates on the host;
 // here every filter is a threshold found by bisection over the whole vocabulary, so no sort is
 // needed and nothing is truncated.  Differences that follow from that: elements that tie with
-// a threshold are all kept, and the draw walks the kept tokens in index order (the reference
-// walks them by descending probability); the distribution drawn from is the same.
+// the threshold of min-p, typical-p or top-p are all kept (the reference's sort leaves their order
+// open; top-k keeps exactly k, the smallest tokens among ties, as the reference does), and the draw
+// walks the kept tokens in index order (the reference walks them by descending probability); the
+// distribution drawn from is the same.
 //
 // The uniform number of (seed, sequence id, step) comes from a counter-based generator, so a
 // sequence's tokens do not depend on what else is in its batch.
@@ -189,6 +191,30 @@ __device__ __forceinline__ float penalised(const SampleArgs& a, float v, int cou
   return v;
 }
 
+// Exclusive prefix sum of v over the block's threads; *total gets the sum.
+__device__ int block_exclusive_scan_int(int v, int* scratch, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  int wsum = lane < (THREADS >> 5) ? scratch[lane] : 0;
+  int wincl = wsum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, wincl, o);
+    if (lane >= o) wincl += t;
+  }
+  *total = __shfl_sync(0xffffffffu, wincl, 31);
+  const int before_warp = __shfl_sync(0xffffffffu, wincl - wsum, warp);
+  return before_warp + incl - v;
+}
+
 // Filters and draw for sequence b over w[0..n): scaled logits in, probabilities left behind.  `map` (or null)
 // gives the token of entry i; entries are in the order of their tokens.  mx = the largest scaled logit.
 __device__ void filter_and_draw(const SampleArgs& a, int b, float* w, int n, const int* map, float mx,
@@ -200,8 +226,32 @@ __device__ void filter_and_draw(const SampleArgs& a, int b, float* w, int n, con
 
   // 4. top-k and min-p as one lower bound on the scaled logit
   float bound = -INFINITY;
-  if (a.top_k > 0 && a.top_k < n)
+  if (a.top_k > 0 && a.top_k < n) {
     bound = key2f(kth_largest_key(n, a.top_k, [&](int i) { return f2key(w[i]); }, is));
+    // Exactly top_k stay: of the logits equal to the k-th largest, those with the smallest tokens, as the
+    // reference's selection keeps the first it meets (Sampler.cs:249-276).  The ordered pass over the
+    // vocabulary runs only when there are more ties than places.
+    int gt = 0, eq = 0;
+    for (int i = tid; i < n; i += THREADS) {
+      gt += w[i] > bound ? 1 : 0;
+      eq += w[i] == bound ? 1 : 0;
+    }
+    gt = block_sum_int(gt, is);
+    eq = block_sum_int(eq, is);
+    const int places = a.top_k - gt;
+    if (eq > places) {
+      int seen = 0;
+      for (int i0 = 0; i0 < n; i0 += THREADS) {
+        const int i = i0 + tid;
+        const int mine = (i < n && w[i] == bound) ? 1 : 0;
+        int total;
+        const int before = block_exclusive_scan_int(mine, is, &total);
+        if (mine && seen + before >= places) w[i] = -INFINITY;
+        seen += total;
+        __syncthreads();
+      }
+    }
+  }
   if (a.min_p > 0.f && a.min_p < 1.0f) {
     float mb = mx + logf(a.min_p);
     if (min_keep > 1) {
@@ -430,30 +480,6 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
   __shared__ int chosen;
   __shared__ float scan[THREADS];
   sample_full(a, blockIdx.x, fs, is, &chosen, scan);
-}
-
-// Exclusive prefix sum of v over the block's threads; *total gets the sum.
-__device__ int block_exclusive_scan_int(int v, int* scratch, int* total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int incl = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  __syncthreads();
-  if (lane == 31) scratch[warp] = incl;
-  __syncthreads();
-  int wsum = lane < (THREADS >> 5) ? scratch[lane] : 0;
-  int wincl = wsum;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int t = __shfl_up_sync(0xffffffffu, wincl, o);
-    if (lane >= o) wincl += t;
-  }
-  *total = __shfl_sync(0xffffffffu, wincl, 31);
-  const int before_warp = __shfl_sync(0xffffffffu, wincl - wsum, warp);
-  return before_warp + incl - v;
 }
 
 // First stage of the candidate way: block (slice, sequence) keeps SLICE_LEN scaled logits in registers and

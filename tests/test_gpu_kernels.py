@@ -504,6 +504,31 @@ def test_sampler_by_candidates_equals_the_general_way(ops, case):
         assert int(res[0][0][i]) == P.draw(res[0][1][i].double(), P.uniform_of(13, int(seq_ids[i]), 2))
 
 
+@pytest.mark.parametrize("top_k", [1, 3, 40, 200])
+def test_top_k_keeps_exactly_k_at_ties(ops, top_k):
+    """Logits on a coarse grid, so that many tie with the k-th largest: exactly k stay, the smallest tokens
+    among the ties (the reference's selection keeps the first it meets, Sampler.cs:249-276), in the general
+    way and through the candidates; top_k = 1 is the greedy choice."""
+    vocab, b = 20011, 4
+    logits = (rnd((b, vocab), 80, scale=3.0) * 2).round() / 2
+    logits[1, 8000:8400] = 20.0               # 400 equal maxima across a slice boundary
+    logits[2, 19990:] = 20.0
+    for cand in (True, False):
+        work = torch.empty(b * vocab, device=DEV)
+        out = torch.empty(b, dtype=torch.int32, device=DEV)
+        probs = torch.full((b, vocab), float("nan"), device=DEV)
+        ops.sample(logits.to(DEV), work, out, seed=5, step=9, temperature=0.9, top_k=top_k, probs_out=probs,
+                   candidates=cand)
+        for i in range(b):
+            ref = P.sampling_distribution(logits[i].tolist(), temperature=0.9, top_k=top_k)
+            got = probs[i].cpu().double()
+            assert int((got > 0).sum()) == top_k, (cand, i)
+            assert ((got > 0) == (ref > 0)).all(), (cand, i)
+            assert float((got - ref).abs().max()) < 2e-6
+            if top_k == 1:
+                assert int(out[i]) == int(logits[i].argmax())      # torch: the first maximum
+
+
 def test_sampler_draws_follow_the_distribution(ops):
     vocab = 37
     logits = rnd((1, vocab), 62, scale=1.5).repeat(512, 1)
