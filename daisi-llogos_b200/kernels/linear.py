@@ -54,15 +54,16 @@ SPLIT_ROWS_MAX = 512    # with more rows the products are bound by arithmetic an
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dtype,
-           out: torch.Tensor = None) -> torch.Tensor:
-    """``out`` (a ``[1, N, O]`` view) makes the product write there instead of into the named buffer."""
+           out: torch.Tensor = None, split_k: bool = True) -> torch.Tensor:
+    """``out`` (a ``[1, N, O]`` view) makes the product write there instead of into the named buffer.
+    ``split_k=False`` is for a caller that does not sum partials: the result is ``[1, N, O]``."""
     ops = ctx.ops
     n, k = x.shape
     o = w.shape[0]
     tc = getattr(ops, "gemm_tc_supported", None)
     if tc is not None and tc(x, w):
         splits = 1
-        if out is None and out_dtype == torch.float32:
+        if out is None and out_dtype == torch.float32 and split_k:
             splits = ops.gemm_tc_splits(k, plan_splits(n, o, k))
         if out is None:
             out = ctx.buffer(name, (splits, n, o), out_dtype)

@@ -56,7 +56,8 @@ class LinearHead(Part):
                              f"expected {(self.vocab, self.hidden)}")
 
     def forward(self, x, ctx) -> torch.Tensor:
-        return linear(ctx, x, self.weight, "head.logits", torch.float32)[0]
+        # the logits go to samplers and callers as they are: one product, no partial sums to add up
+        return linear(ctx, x, self.weight, "head.logits", torch.float32, split_k=False)[0]
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

@@ -30,7 +30,7 @@ def llogos():
     return importlib.import_module("daisi-llogos_b200")
 
 
-# Three tiny configurations that differ in every size and option.
+# Tiny configurations that differ in every size and option.
 TINY_LLAMA = {
     "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 64,
     "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 176,
@@ -60,8 +60,17 @@ TINY_WIDE = {
     "tie_word_embeddings": False, "sliding_window": 90,
     "layer_types": ["sliding_attention", "full_attention"],
 }
-TINY = {"llama": TINY_LLAMA, "qwen3": TINY_QWEN3, "qwen2": TINY_QWEN2, "wide": TINY_WIDE}
+# sums long enough (k = 576 and 1096) that the tensor-core products split them: the q/k/v kernel and the
+# norms add up partial results, and the output head must not hand out half a sum
+TINY_DEEP = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 576,
+    "num_attention_heads": 9, "num_key_value_heads": 3, "head_dim": 64, "intermediate_size": 1096,
+    "vocab_size": 1003, "rope_theta": 300000.0, "rms_norm_eps": 4e-6, "max_position_embeddings": 1024,
+    "tie_word_embeddings": True, "attention_bias": True,
+}
+TINY = {"llama": TINY_LLAMA, "qwen3": TINY_QWEN3, "qwen2": TINY_QWEN2, "wide": TINY_WIDE, "deep": TINY_DEEP}
 INIT = dict(std=0.15, norm_std=0.1, bias_std=0.1)
+INIT_OF = {"deep": dict(std=0.05, norm_std=0.1, bias_std=0.1)}     # spread follows the width
 
 
 @pytest.fixture(scope="session")
@@ -70,7 +79,7 @@ def model_dirs(tmp_path_factory, llogos):
     out = {}
     for i, (name, cfg) in enumerate(TINY.items()):
         d = str(tmp_path_factory.mktemp(f"model_{name}"))
-        llogos.weights.write_random_model(d, cfg, seed=100 + i, **INIT)
+        llogos.weights.write_random_model(d, cfg, seed=100 + i, **INIT_OF.get(name, INIT))
         out[name] = d
     return out
 
