@@ -47,7 +47,7 @@ def test_embed_rows(ops, dtype):
 
 @pytest.mark.parametrize("wdtype", DTYPES, ids=["w32", "w16"])
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("hidden", [72, 1000, 4100])
+@pytest.mark.parametrize("hidden", [72, 1000, 4096, 4100])
 def test_add_rmsnorm(ops, dtype, wdtype, hidden):
     n, eps = 7, 3e-5
     res = rnd((n, hidden), 2)
@@ -70,6 +70,20 @@ def test_add_rmsnorm(ops, dtype, wdtype, hidden):
     r3 = res.to(DEV).clone()
     ops.add_rmsnorm(r3, branch.to(DEV), w.to(DEV), eps, out2, rows.to(DEV))
     check(out2, P.rms_norm(total[rows.long()], w, eps), dtype, "gathered with branch")
+    # many rows (a prompt step): blocks that work through several rows, with one and with two partials
+    for n, parts in ((700, 1), (1501, 2)):
+        res = rnd((n, hidden), 5)
+        branch = rnd((parts, n, hidden), 6)
+        r_dev = res.to(DEV).clone()
+        out = torch.empty(n, hidden, dtype=dtype, device=DEV)
+        ops.add_rmsnorm(r_dev, branch.to(DEV), w.to(DEV), eps, out)
+        total = res.double() + branch.double().sum(0)
+        check(r_dev, total, torch.float32, ("residual", n))
+        check(out, P.rms_norm(total, w, eps), dtype, ("normed", n))
+        r_dev = res.to(DEV).clone()
+        ops.add_rmsnorm(r_dev, None, w.to(DEV), eps, out)
+        assert torch.equal(r_dev.cpu(), res)
+        check(out, P.rms_norm(res, w, eps), dtype, ("normed without branch", n))
 
 
 @pytest.mark.parametrize("xd,wd,od", [(torch.float32,) * 3, (torch.bfloat16, torch.bfloat16, torch.float32),
