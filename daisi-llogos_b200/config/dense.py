@@ -89,13 +89,14 @@ class DenseDecoderConfig:
     hidden_size: int
     intermediate_size: int
     vocab_size: int
-    max_position_embeddings: int
+    max_position_embeddings: Optional[int]      # None: the file gives no limit, the cache's size is the limit
     rms_norm_eps: float
     num_attention_heads: int
     num_key_value_heads: int
     head_dim: int
     rope_theta: float
     rope_scaling: Optional[RopeScaling] = None
+    rotary_dim: Optional[int] = None            # dimensions of a head that are rotated; None = all of them
     attention_bias: bool = False
     qk_norm: bool = False
     tie_word_embeddings: bool = False
@@ -136,13 +137,13 @@ class DenseDecoderConfig:
         vocab = _need(d, "vocab_size", int)
         n_heads = _need(d, "num_attention_heads", int)
         n_kv = _need(d, "num_key_value_heads", int, default=n_heads, required=False)
-        max_pos = _need(d, "max_position_embeddings", int)
+        max_pos = _need(d, "max_position_embeddings", int, default=None, required=False)
         eps = _need(d, "rms_norm_eps", float, default=1e-6, required=False)
         for name, v in (("num_hidden_layers", n_layers), ("hidden_size", hidden),
                         ("intermediate_size", inter), ("vocab_size", vocab),
                         ("num_attention_heads", n_heads), ("num_key_value_heads", n_kv),
                         ("max_position_embeddings", max_pos)):
-            if v <= 0:
+            if v is not None and v <= 0:
                 raise ConfigError(f"config.json: key '{name}' must be positive, got {v}")
         if "head_dim" in d and d["head_dim"] is not None:
             head_dim = _need(d, "head_dim", int)
@@ -174,6 +175,14 @@ class DenseDecoderConfig:
         if scaling_raw is None and rope_params.get("rope_type") not in (None, "default"):
             scaling_raw = rope_params
         scaling = _parse_rope_scaling(scaling_raw)
+        # the first head_dim * partial_rotary_factor dimensions of a head are rotated, the rest pass through
+        factor = _need(d, "partial_rotary_factor", float, default=None, required=False)
+        if factor is None:
+            factor = _need(rope_params, "partial_rotary_factor", float, default=1.0, required=False)
+        rotary_dim = int(head_dim * factor)
+        if not 0 < factor <= 1 or rotary_dim <= 0 or rotary_dim % 2:
+            raise ConfigError(f"config.json: partial_rotary_factor {factor} of head_dim {head_dim} must give a "
+                              f"positive even number of rotated dimensions, got {rotary_dim}")
 
         bias = _need(d, "attention_bias", bool, default=None, required=False)
         if bias is None:
@@ -203,7 +212,8 @@ class DenseDecoderConfig:
             architecture=archs[0], num_hidden_layers=n_layers, hidden_size=hidden,
             intermediate_size=inter, vocab_size=vocab, max_position_embeddings=max_pos,
             rms_norm_eps=eps, num_attention_heads=n_heads, num_key_value_heads=n_kv,
-            head_dim=head_dim, rope_theta=theta, rope_scaling=scaling, attention_bias=bias,
+            head_dim=head_dim, rope_theta=theta, rope_scaling=scaling,
+            rotary_dim=None if rotary_dim == head_dim else rotary_dim, attention_bias=bias,
             qk_norm=qkn, tie_word_embeddings=tied, layer_windows=windows,
             eos_token_ids=eos_ids, bos_token_id=bos, extra=dict(d))
 
@@ -272,6 +282,8 @@ class DenseDecoderConfig:
             "tie_word_embeddings": self.tie_word_embeddings,
             "torch_dtype": "bfloat16",
         }
+        if self.rotary_dim is not None:
+            d["partial_rotary_factor"] = self.rotary_dim / self.head_dim
         if any(self.layer_windows):
             d["sliding_window"] = max(self.layer_windows)
             d["layer_types"] = ["sliding_attention" if w else "full_attention"

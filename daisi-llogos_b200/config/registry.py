@@ -84,7 +84,7 @@ def dense_decoder_spec(cfg: DenseDecoderConfig) -> ModelSpec:
         }))
     rope = PartSpec("rotary", {
         "head_dim": cfg.head_dim,
-        "rotary_dim": cfg.head_dim,
+        "rotary_dim": cfg.rotary_dim or cfg.head_dim,
         "theta": cfg.rope_theta,
         "scaling": cfg.rope_scaling.to_dict() if cfg.rope_scaling else None,
         "pairing": "half",                  # safetensors rows are not permuted: pair (i, i + d/2)

@@ -101,7 +101,9 @@ class Engine:
         self.ops = model.env.ops
         n_pages = (max_tokens + PAGE - 1) // PAGE
         if max_seq_len is None:
-            max_seq_len = min(model.spec.max_positions, n_pages * PAGE)
+            max_seq_len = n_pages * PAGE
+            if model.spec.max_positions is not None:
+                max_seq_len = min(model.spec.max_positions, max_seq_len)
         if n_slots is None:
             n_slots = max(1, min(n_pages, 1024))
         self.cache = SequenceCache(model.cache_needs(), max_tokens=max_tokens, max_seq_len=max_seq_len,

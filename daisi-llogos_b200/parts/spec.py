@@ -48,7 +48,7 @@ class ScheduleEntry:
 class ModelSpec:
     hidden_size: int
     vocab_size: int
-    max_positions: int
+    max_positions: Optional[int]      # None: no limit besides the cache's size
     embedding: PartSpec
     encodings: Dict[str, PartSpec]          # position encodings by name; mixers refer to them by name
     layers: Tuple[LayerSpec, ...]

@@ -66,7 +66,7 @@ TINY_DEEP = {
     "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 576,
     "num_attention_heads": 9, "num_key_value_heads": 3, "head_dim": 64, "intermediate_size": 1096,
     "vocab_size": 1003, "rope_theta": 300000.0, "rms_norm_eps": 4e-6, "max_position_embeddings": 1024,
-    "tie_word_embeddings": True, "attention_bias": True,
+    "tie_word_embeddings": True, "attention_bias": True, "partial_rotary_factor": 0.5,
 }
 TINY = {"llama": TINY_LLAMA, "qwen3": TINY_QWEN3, "qwen2": TINY_QWEN2, "wide": TINY_WIDE, "deep": TINY_DEEP}
 INIT = dict(std=0.15, norm_std=0.1, bias_std=0.1)

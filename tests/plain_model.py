@@ -154,7 +154,8 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int]) 
     scaling = cfg.get("rope_scaling")
     if scaling is not None and scaling.get("rope_type", scaling.get("type")) in (None, "default"):
         scaling = None
-    inv_freq = rope_inverse_frequencies(hd, cfg.get("rope_theta", 10000.0), scaling)
+    rotary_dim = int(hd * cfg.get("partial_rotary_factor", 1.0))      # the rest of a head passes through
+    inv_freq = rope_inverse_frequencies(rotary_dim, cfg.get("rope_theta", 10000.0), scaling)
     windows = layer_windows(cfg)
     t = len(tokens)
     positions = list(range(t))

@@ -43,10 +43,28 @@ def test_defaults(llogos):
     c = llogos.config.architecture_of(cfg).read_config(cfg)
     assert c.head_dim == 16 and c.num_key_value_heads == 4
     assert c.rms_norm_eps == 1e-6 and c.rope_theta == 10000.0      # the reference's defaults
+    assert c.rotary_dim is None                                      # every dimension of a head is rotated
+
+
+def test_without_a_position_limit_the_cache_is_the_limit(llogos):
+    cfg = {k: v for k, v in TINY_LLAMA.items() if k != "max_position_embeddings"}
+    c = llogos.config.architecture_of(cfg).read_config(cfg)
+    assert c.max_position_embeddings is None
+    assert llogos.config.dense_decoder_spec(c).max_positions is None
+
+
+def test_partial_rotary_factor(llogos):
+    cfg = dict(TINY_LLAMA, partial_rotary_factor=0.5)
+    c = llogos.config.architecture_of(cfg).read_config(cfg)
+    assert c.rotary_dim == 8
+    spec = llogos.config.dense_decoder_spec(c)
+    assert spec.encodings["rope"].params["rotary_dim"] == 8 and spec.encodings["rope"].params["head_dim"] == 16
+    full = dict(TINY_LLAMA, partial_rotary_factor=1.0)
+    assert llogos.config.architecture_of(full).read_config(full).rotary_dim is None
 
 
 @pytest.mark.parametrize("key", ["num_hidden_layers", "hidden_size", "intermediate_size", "vocab_size",
-                                 "num_attention_heads", "max_position_embeddings", "architectures"])
+                                 "num_attention_heads", "architectures"])
 def test_missing_key_is_named(llogos, key):
     cfg = copy.deepcopy(TINY_LLAMA)
     del cfg[key]
@@ -65,6 +83,9 @@ def test_missing_key_is_named(llogos, key):
     ({"eos_token_id": 100000}, "eos_token_id"),
     ({"rms_norm_eps": 0.0}, "rms_norm_eps"),
     ({"mlp_bias": True}, "mlp_bias"),
+    ({"partial_rotary_factor": 0.45}, "partial_rotary_factor"),
+    ({"partial_rotary_factor": 1.5}, "partial_rotary_factor"),
+    ({"max_position_embeddings": 0}, "max_position_embeddings"),
 ])
 def test_bad_values(llogos, patch, word):
     cfg = copy.deepcopy(TINY_LLAMA)
