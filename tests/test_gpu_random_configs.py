@@ -53,7 +53,27 @@ def close(got, ref, dtype, scale):
 @pytest.mark.parametrize("seed", SEEDS)
 def test_random_configuration(llogos, tmp_path, seed):
     rng = random.Random(seed)
-    cfg = draw_config(rng)
+    check_configuration(llogos, tmp_path, draw_config(rng), rng, seed)
+
+
+# widths that are no multiple of 8 (the tensor-core product refuses them: 16-byte rows for TMA) or of 4
+# (no vector accesses in the norms), with an odd intermediate size and vocabulary
+ODD = [
+    {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 102, "num_attention_heads": 6,
+     "num_key_value_heads": 2, "head_dim": 48, "intermediate_size": 99, "vocab_size": 257, "rope_theta": 1e4,
+     "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "attention_bias": True},
+    {"architectures": ["LlamaForCausalLM"], "num_hidden_layers": 3, "hidden_size": 100, "num_attention_heads": 5,
+     "num_key_value_heads": 5, "head_dim": 128, "intermediate_size": 130, "vocab_size": 1031, "rope_theta": 5e5,
+     "rms_norm_eps": 1e-6, "max_position_embeddings": 2048, "tie_word_embeddings": False},
+]
+
+
+@pytest.mark.parametrize("which", range(len(ODD)))
+def test_widths_that_fit_no_vector_access(llogos, tmp_path, which):
+    check_configuration(llogos, tmp_path, ODD[which], random.Random(200 + which), 200 + which)
+
+
+def check_configuration(llogos, tmp_path, cfg, rng, seed):
     lens = [rng.choice([1, 5, 63, 64, 65]), rng.randrange(100, 300), rng.randrange(256, 700),
             rng.randrange(2, 90), rng.randrange(500, 640)]
     d = str(tmp_path)
