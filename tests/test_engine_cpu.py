@@ -199,3 +199,46 @@ def test_tokens_fed_from_the_device_side(llogos, setup):
     for s in slots:
         eng.close(s)
     eng.cache.audit()
+
+
+def test_products_that_split_their_sums(llogos, setup, model_dirs):
+    """With a tensor-core product that splits K the engine's consumers get partial sums: the branch consumers add
+    them up, and the output head asks for one whole product.  A stand-in that always splits in three shows it."""
+    class SplittingOps:
+        def __getattr__(self, name):
+            return getattr(cpu_ops, name)
+
+        @staticmethod
+        def gemm_tc_supported(x, w):
+            return True
+
+        @staticmethod
+        def gemm_tc_splits(k, wish):
+            return min(wish, 3)
+
+        @staticmethod
+        def gemm_tc(x, w, out, tile_n=0, gated_features=0):
+            assert gated_features == 0
+            s, k = out.shape[0], x.shape[1]
+            step = -(-k // s)
+            for i in range(s):
+                sl = slice(i * step, min(k, (i + 1) * step))
+                out[i] = (x[:, sl].float() @ w[:, sl].float().t()).to(out.dtype)
+
+    lin = __import__("importlib").import_module("daisi-llogos_b200.kernels.linear")
+    wished = []
+    real_plan = lin.plan_splits
+    lin.plan_splits = lambda n, o, k: wished.append((n, o, k)) or 3
+    try:
+        name = "llama"
+        cfg = TINY[name]
+        model = llogos.weights.load_model(model_dirs[name], dtype=torch.float32, device="cpu", ops=SplittingOps())
+        eng = llogos.engine.Engine(model, max_tokens=256, use_graphs=False)
+        toks = random_tokens(cfg["vocab_size"], [21], 5)[0]
+        ref = P.forward(setup[name][1], cfg, toks)
+        slot = eng.open()
+        got = eng.step([(slot, toks)], [list(range(len(toks)))])
+        assert float((got.double() - ref).abs().max()) < 1e-4 * float(ref.abs().max())
+        assert wished and all(o != cfg["vocab_size"] for _, o, _ in wished)      # the head never asked for splits
+    finally:
+        lin.plan_splits = real_plan
