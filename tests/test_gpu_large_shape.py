@@ -59,3 +59,29 @@ def test_bfloat16_against_the_32_bit_path_at_the_headline_layer_sizes(llogos):
         assert err <= REL_TOL * scale, (k, err, scale)
     ops = llogos.kernels.ops
     assert ops.gemm_tc_status() == 0 and ops.attn_tc_status() == 0
+
+
+def test_the_same_batch_gives_the_same_bits(llogos):
+    """Nothing in a step depends on timing (sums run in a fixed order, blocks only count arrivals): a batch of
+    prompts and its decode steps, run three times over reused slots and pages, give identical logits.  A kernel
+    that read its input before its producer had finished would differ from run to run."""
+    model = llogos.weights.random_model(CFG, seed=7, dtype=torch.bfloat16, device="cuda:0", std=0.02, norm_std=0.1)
+    eng = llogos.engine.Engine(model, max_tokens=64 * 80)
+    g = torch.Generator().manual_seed(4)
+    lens = [2048, 300, 700, 1, 65]
+    seqs = [torch.randint(0, CFG["vocab_size"], (n + 4,), generator=g).tolist() for n in lens]
+    first = None
+    for rep in range(3):
+        slots = [eng.open() for _ in seqs]
+        outs = [eng.step([(s, q[:n]) for s, q, n in zip(slots, seqs, lens)], [[0, n - 1] for n in lens]).clone()]
+        for k in range(4):
+            outs.append(eng.step([(s, [q[n + k]]) for s, q, n in zip(slots, seqs, lens)]).clone())
+        for s in slots:
+            eng.close(s)
+        got = torch.cat(outs)
+        if first is None:
+            first = got
+        else:
+            assert torch.equal(got, first), rep
+    del eng, model
+    torch.cuda.empty_cache()
