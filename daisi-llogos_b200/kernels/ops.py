@@ -383,6 +383,7 @@ def _use_mma(dtype: torch.dtype, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and 16 <= head_dim <= 128 and head_dim % 16 == 0
 
 
+ATTN_MAX_HEAD_DIM = 256          # what csrc/attention_simt.cu takes; the tensor-core kernels take less and fall back to it
 USE_TC_PROMPT_ATTENTION = True     # tests switch it off to reach the mma.sync kernel at head sizes 64 and 128
 
 

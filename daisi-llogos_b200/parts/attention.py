@@ -50,6 +50,10 @@ class Attention(Mixer):
         self.hd = int(p["head_dim"])
         if self.nh % self.nkv:
             raise ValueError(f"{self.nh} heads are not a multiple of {self.nkv} key/value heads")
+        # said when the model is built, not at its first step
+        limit = getattr(env.ops, "ATTN_MAX_HEAD_DIM", None)
+        if limit is not None and not 0 < self.hd <= limit:
+            raise ValueError(f"head_dim {self.hd}: the attention kernels take head sizes from 1 to {limit}")
         self.qkv_bias = bool(p.get("qkv_bias", False))
         self.qk_norm = bool(p.get("qk_norm", False))
         self.qk_norm_eps = float(p.get("qk_norm_eps", 1e-6))
