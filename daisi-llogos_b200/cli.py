@@ -5,7 +5,9 @@ Same option names and meanings where the reference has them: ``--model/-m``, ``-
 ``--top-k`` (40), ``--top-p`` (0.9), ``--repeat-penalty`` (1.1), ``--seed``, ``--bench``,
 ``--help/-h``.  ``--model`` is a folder with config.json and safetensors.  Text is outside this
 library: ``--prompt`` is turned into ids by a byte stand-in (``byte % vocab``) and output is token
-ids; ``--prompt-ids`` gives ids directly.  ``--backend`` is replaced by ``--dtype``.
+ids; ``--prompt-ids`` and ``--prompt-file`` give ids directly.  ``--backend`` is replaced by ``--dtype``.
+``--ignore-eos``, ``--min-p``, ``--typical-p``, ``--frequency-penalty`` and ``--presence-penalty`` set the
+fields of the same meaning in the reference's GenerationParams (Inference/GenerationParams.cs:32-53).
 """
 from __future__ import annotations
 
@@ -30,6 +32,13 @@ def _parser() -> argparse.ArgumentParser:
     ap.add_argument("--bench", action="store_true", help="run benchmark (prefill + decode timing)")
     ap.add_argument("--random-config", help="config.json of a model to initialise randomly instead of --model")
     ap.add_argument("--batch", type=int, default=1, help="with --bench: copies of the prompt decoded together")
+    ap.add_argument("--prompt-file", help="file with one prompt per line, token ids separated by commas or blanks")
+    ap.add_argument("--ignore-eos", action="store_true",
+                    help="never draw or stop at the end-of-sequence tokens (the reference's PreventEOS)")
+    ap.add_argument("--min-p", type=float, default=0.0, help="min-p sampling, 0 = disabled (default 0)")
+    ap.add_argument("--typical-p", type=float, default=1.0, help="typical-p sampling, 1 = disabled (default 1)")
+    ap.add_argument("--frequency-penalty", type=float, default=0.0, help="frequency penalty (default 0)")
+    ap.add_argument("--presence-penalty", type=float, default=0.0, help="presence penalty (default 0)")
     return ap
 
 
@@ -56,12 +65,18 @@ def main(argv=None) -> int:
     load_ms = (time.perf_counter() - t_load) * 1e3
     vocab = model.model.spec.vocab_size
 
-    if args.prompt_ids:
+    if args.prompt_file:
+        with open(args.prompt_file) as f:
+            prompts = [[int(x) for x in line.replace(",", " ").split()] for line in f if line.strip()]
+        if not prompts:
+            print(f"error: {args.prompt_file} holds no prompt", file=sys.stderr)
+            return 2
+    elif args.prompt_ids:
         prompts = [[int(x) for x in part.split(",") if x.strip()] for part in args.prompt_ids.split(";")]
     else:
         text = args.prompt if args.prompt is not None else ("The meaning of life is" if args.bench else None)
         if text is None:
-            print("error: --prompt <text> or --prompt-ids is required unless --bench", file=sys.stderr)
+            print("error: --prompt <text>, --prompt-ids or --prompt-file is required unless --bench", file=sys.stderr)
             return 2
         prompts = [_ids_from_text(text, vocab)]
 
@@ -79,7 +94,9 @@ def main(argv=None) -> int:
         return 0
 
     params = GenerationParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,
-                              top_p=args.top_p, repetition_penalty=args.repeat_penalty, seed=args.seed)
+                              top_p=args.top_p, repetition_penalty=args.repeat_penalty, seed=args.seed,
+                              min_p=args.min_p, typical_p=args.typical_p, frequency_penalty=args.frequency_penalty,
+                              presence_penalty=args.presence_penalty, prevent_eos=args.ignore_eos)
     first = [True] * len(prompts)
 
     def show(i, tok):

@@ -147,3 +147,21 @@ def test_command_line(model_dirs):
     assert "Prefill:" in p.stderr and "Decode:" in p.stderr and "Load:" in p.stderr
     p = subprocess.run([sys.executable, "-m", "llogos_b200", "--prompt", "hi"], capture_output=True, text=True, env=env, cwd=ROOT)
     assert p.returncode == 2 and "--model" in p.stderr
+
+
+def test_command_line_prompt_file_and_ignore_eos(model_dirs, tmp_path):
+    """Prompts from a file, one per line; with --ignore-eos no sequence stops before its token limit."""
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    f = tmp_path / "prompts.txt"
+    f.write_text("5, 17, 3\n9 8 7 6\n\n12\n")
+    base = [sys.executable, "-m", "llogos_b200", "--model", model_dirs["qwen3"], "--dtype", "float32",
+            "--prompt-file", str(f), "-n", "20", "-t", "0.9", "--top-k", "0", "--top-p", "1.0", "--seed", "3",
+            "--max-context", "128"]
+    p = subprocess.run(base + ["--ignore-eos", "--min-p", "0.01", "--presence-penalty", "0.1"],
+                       capture_output=True, text=True, env=env, cwd=ROOT)
+    assert p.returncode == 0, p.stderr
+    lines = [l for l in p.stdout.splitlines() if l.strip()]
+    assert len(lines) == 3 and all(len(l.split()) == 20 for l in lines)
+    stop = set(TINY["qwen3"]["eos_token_id"])
+    assert not any(int(t) in stop for l in lines for t in l.split())
+    assert "prefill: 8 tokens" in p.stderr
