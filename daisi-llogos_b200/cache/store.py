@@ -89,6 +89,26 @@ class KvGroup:
             have.append(p)
         return updates
 
+    def can_shrink(self, old_len: int, new_len: int) -> bool:
+        """True when the keys that a token at position ``new_len`` looks at are still in the pages.  A ring
+        that has gone round has overwritten the oldest ones."""
+        if self.window <= 0 or pages_for(old_len) <= self.ring_pages:
+            return True
+        oldest_needed = max(0, new_len - self.window + 1) // PAGE
+        oldest_kept = (old_len - 1) // PAGE - self.ring_pages + 1
+        return oldest_needed >= oldest_kept
+
+    def shrink(self, slot: int, old_len: int, new_len: int) -> None:
+        """Gives back the pages beyond ``new_len`` tokens.  A ring that has gone round keeps all of its pages:
+        their order in the table is no longer their age."""
+        if pages_for(old_len) > self.ring_pages:
+            return
+        have = self.pages_of.get(slot, [])
+        keep = self.pages_needed(new_len)
+        if len(have) > keep:
+            self.pool.give(have[keep:])
+            del have[keep:]
+
     def extra_pages(self, slot: int, new_len: int) -> int:
         return max(0, self.pages_needed(new_len) - len(self.pages_of.get(slot, [])))
 
@@ -122,6 +142,7 @@ class SequenceCache:
         self.kv_groups: List[KvGroup] = []
         self._group_of_unit: Dict[int, KvGroup] = {}
         self.state: Dict[int, torch.Tensor] = {}
+        self._longest: Dict[int, int] = {}       # slots that were truncated: the most tokens they ever held
         by_need: Dict[KvNeed, List[int]] = {}
         for unit, need in unit_needs.items():
             if need is None:
@@ -142,6 +163,7 @@ class SequenceCache:
     def acquire(self) -> int:
         """A fresh slot: length 0, no pages, state zeroed."""
         slot = self.slots.acquire()
+        self._longest.pop(slot, None)
         for t in self.state.values():
             t[slot].zero_()
         return slot
@@ -155,6 +177,30 @@ class SequenceCache:
     def length(self, slot: int) -> int:
         self.slots.check_live(slot)
         return self.slots.length[slot]
+
+    def truncate(self, slot: int, new_len: int) -> None:
+        """Forgets the tokens of ``slot`` from position ``new_len`` on (the reference's rollback,
+        Inference/KvCache.cs:135); pages that hold none of the rest go back to the pool.  Refused, with
+        nothing changed, where the past cannot be restored: fixed-size state, or a window whose older
+        keys the ring has overwritten."""
+        self.slots.check_live(slot)
+        old = self.slots.length[slot]
+        if not 0 <= new_len <= old:
+            raise CacheError(f"slot {slot}: cannot truncate {old} tokens to {new_len}")
+        if new_len == old:
+            return
+        if self.state:
+            raise CacheError(f"slot {slot}: fixed-size state cannot be rolled back")
+        # what a ring has overwritten follows from the longest the sequence has ever been
+        written = max(old, self._longest.get(slot, 0))
+        for g in self.kv_groups:
+            if not g.can_shrink(written, new_len):
+                raise CacheError(f"slot {slot}: the window of {g.window} keys before position {new_len} has been "
+                                 f"overwritten (the sequence has held {written} tokens)")
+        for g in self.kv_groups:
+            g.shrink(slot, written, new_len)
+        self._longest[slot] = written
+        self.slots.length[slot] = new_len
 
     def check_room(self, growth: Sequence[Tuple[int, int]]) -> None:
         """``growth`` = (slot, tokens to add) for a whole step; raises before anything changes."""

@@ -126,6 +126,13 @@ class Engine:
         """Ends a sequence: its slot and pages go back to the free lists."""
         self.cache.release(slot)
 
+    def truncate(self, slot: int, length: int) -> None:
+        """Forgets a sequence's tokens from position ``length`` on; the next step continues there."""
+        try:
+            self.cache.truncate(slot, length)
+        except CacheError as e:
+            raise StepError(str(e)) from None
+
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 

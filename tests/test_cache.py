@@ -148,3 +148,39 @@ def test_random_traffic_keeps_the_books(C, P):
         c.release(s)
     c.audit()
     assert all(g.pool.free_count == g.pool.n for g in c.kv_groups) and c.slots.free_count == 8
+
+
+def test_truncate_gives_pages_back_and_refuses_what_is_lost(C, P):
+    c = make(C, P, window=100)
+    full = [g for g in c.kv_groups if g.window == 0][0]
+    ring = [g for g in c.kv_groups if g.window == 100][0]
+    s = c.acquire()
+
+    def add(n):
+        c.check_room([(s, n)])
+        c.grow([(s, n)])
+        c.commit([(s, n)])
+
+    add(190)                                       # 3 pages everywhere; the ring (3 pages) has not gone round
+    c.truncate(s, 100)
+    assert c.length(s) == 100 and len(full.pages_of[s]) == 2 and len(ring.pages_of[s]) == 2
+    assert full.pool.free_count == 8 and ring.pool.free_count == 8
+    c.audit()
+    add(250)                                       # 350 tokens: the ring has gone round (pages 3, 4, 5 are kept)
+    assert len(full.pages_of[s]) == 6 and len(ring.pages_of[s]) == 3
+    c.truncate(s, 300)                             # position 300 looks back to 201: page 3 is still there
+    assert c.length(s) == 300 and len(full.pages_of[s]) == 5 and len(ring.pages_of[s]) == 3
+    with pytest.raises(C.CacheError, match="overwritten"):
+        c.truncate(s, 250)                         # would need keys from 151 on: page 2 is gone
+    assert c.length(s) == 300 and len(full.pages_of[s]) == 5
+    with pytest.raises(C.CacheError, match="cannot truncate"):
+        c.truncate(s, 301)
+    c.truncate(s, 300)                             # no change
+    c.audit()
+    c.release(s)
+    assert full.pool.free_count == 10 and ring.pool.free_count == 10
+    c2 = make(C, P, extra_state=True)
+    s2 = c2.acquire()
+    c2.check_room([(s2, 5)]); c2.grow([(s2, 5)]); c2.commit([(s2, 5)])
+    with pytest.raises(C.CacheError, match="state"):
+        c2.truncate(s2, 2)

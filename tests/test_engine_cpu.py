@@ -242,3 +242,28 @@ def test_products_that_split_their_sums(llogos, setup, model_dirs):
         assert wished and all(o != cfg["vocab_size"] for _, o, _ in wished)      # the head never asked for splits
     finally:
         lin.plan_splits = real_plan
+
+
+@pytest.mark.parametrize("name", ["llama", "qwen3"])
+def test_truncate_and_continue(llogos, setup, name):
+    """A sequence rolled back to 25 of its 40 tokens and continued with other tokens gives the logits of
+    the new sequence (the reference rolls its cache back the same way, Inference/KvCache.cs:135)."""
+    model, w = setup[name]
+    cfg = TINY[name]
+    eng = engine_for(llogos, model)
+    a, b = random_tokens(cfg["vocab_size"], [40, 12], 44)
+    slot = eng.open()
+    eng.step([(slot, a)])
+    eng.truncate(slot, 25)
+    assert eng.cache.length(slot) == 25
+    new = a[:25] + b
+    ref = P.forward(w, cfg, new)
+    got = eng.step([(slot, b[:5])], [list(range(5))])
+    assert float((got.double() - ref[25:30]).abs().max()) < 1e-4 * float(ref.abs().max())
+    for i in range(5, 12):
+        got = eng.step([(slot, [b[i]])])
+        assert float((got[0].double() - ref[25 + i]).abs().max()) < 1e-4 * float(ref.abs().max())
+    with pytest.raises(llogos.engine.StepError, match="cannot truncate"):
+        eng.truncate(slot, 100)
+    eng.close(slot)
+    eng.cache.audit()

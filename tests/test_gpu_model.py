@@ -267,3 +267,36 @@ def test_padded_decode_batches_change_nothing(llogos, model_dirs, dtype):
         eng.close(slots[i])
     eng.cache.audit()
     assert eng.cache.slots.free_count == 8
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["llama", "qwen3", "deep"])
+def test_truncate_and_continue(engines, llogos, model_dirs, name, dtype):
+    """Rolled back from 200 tokens (a page goes back to the pool) and continued with other tokens, one prompt
+    step and then token by token: the logits of the new sequence.  The window of 24 keys of the Qwen3
+    configuration lives in a ring of two pages that has gone round by then: position 150 is refused, its
+    keys are overwritten; position 180 still has them."""
+    cfg = TINY[name]
+    w = read_weights(llogos, model_dirs[name])
+    a, b = random_tokens(cfg["vocab_size"], [200, 40], 45)
+    eng = engines(name, dtype)
+    slot = eng.open()
+    eng.step([(slot, a)])
+    cut = 150
+    if name == "qwen3":
+        with pytest.raises(llogos.engine.StepError, match="overwritten"):
+            eng.truncate(slot, 150)
+        assert eng.cache.length(slot) == 200
+        cut = 180
+    ref = P.forward(w, cfg, a[:cut] + b)
+    scale = float(ref.abs().max())
+    eng.truncate(slot, cut)
+    lg = eng.step([(slot, b[:20])], [list(range(20))])
+    ok, err = close(lg, ref[cut:cut + 20], dtype, scale)
+    assert ok, ("prompt after truncation", err)
+    for i in range(20, 40):
+        lg = eng.step([(slot, [b[i]])])
+        ok, err = close(lg[0], ref[cut + i], dtype, scale)
+        assert ok, ("decode after truncation", i, err)
+    eng.close(slot)
+    eng.cache.audit()
