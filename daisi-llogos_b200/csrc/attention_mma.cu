@@ -349,12 +349,14 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 // (sequence, key/value head) join the partials of all splits and write `out`; it leaves the counter at
 // zero again.  No second kernel is needed.
 //
-// Work items are (sequence, key/value head, split); a block takes items blockIdx.x, blockIdx.x +
-// gridDim.x, ...  With `balance` a sequence has as many splits as its length calls for (at most
-// a.n_splits): every block works out the same number T of key tiles per item, the least with which the
+// Work items are (sequence, key/value head, split).  Without `balance` every sequence has a.n_splits
+// splits and the grid is (splits, key/value heads, sequences), one block per item.  With `balance` the
+// grid is one row of at most DECODE_SLOTS blocks, a block takes items blockIdx.x, blockIdx.x +
+// gridDim.x, ..., and a sequence has as many splits as its length calls for (at most a.n_splits):
+// every block works out the same number T of key tiles per item, the least with which the
 // items of all sequences fit the GPU at once, and sequence b gets ceil(tiles_b / T) splits.  A batch of
 // one long and seven short sequences then spreads the long one over most of the GPU; sequences of one
-// length get the same count each.  Without `balance` every sequence has a.n_splits splits.
+// length get the same count each.
 constexpr int DECODE_SLOTS = 2 * 148;         // blocks of this kernel that the GPU holds at once
 
 // 64-key tiles that a sequence of `len` keys reads
