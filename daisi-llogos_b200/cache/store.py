@@ -63,6 +63,9 @@ class KvGroup:
         full = max(1, max_seq_pages)
         self.ring_pages = min(full, pages_for(need.window) + 1) if need.window > 0 else full
         self.table_width = self.ring_pages
+        # a sequence never holds more than its ring: a windowed group needs no more pages than that
+        n_pages = min(n_pages, n_slots * self.ring_pages)
+        self.n_pages = n_pages
         self.pool = FreeList(n_pages, "page")
         self.pages_of: Dict[int, List[int]] = {}
         # One row and one page beyond what sequences can get: the padding slot (row n_slots) owns page
@@ -245,6 +248,13 @@ class SequenceCache:
         if unit in self.state:
             return StateView(self.state[unit], unit, owner)
         return None
+
+    def free_pages(self) -> int:
+        """Pages that new sequences can still get: the scarcest group decides, among those whose pool can run
+        out before the slots do (a group that owns a full ring for every slot never does)."""
+        n_slots = self.slots.n_slots
+        scarce = [g.pool.free_count for g in self.kv_groups if g.n_pages < n_slots * g.ring_pages]
+        return min(scarce, default=self.n_pages)
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self.kv_groups) + sum(t.numel() * t.element_size() for t in self.state.values())

@@ -253,7 +253,11 @@ class DenseDecoderConfig:
             return tuple([0] * n_layers)
         if window <= 0:
             raise ConfigError("config.json: use_sliding_window=true needs a positive 'sliding_window'")
-        first = _need(d, "max_window_layers", int, default=0, required=False)
+        # which layers slide must be said: checkpoints disagree on what a missing key would mean
+        if d.get("max_window_layers") is None:
+            raise ConfigError("config.json: use_sliding_window=true needs 'max_window_layers' (the first layer with "
+                              "a window) or 'layer_types'")
+        first = _need(d, "max_window_layers", int)
         return tuple(window if i >= first else 0 for i in range(n_layers))
 
     @classmethod

@@ -105,6 +105,9 @@ def dense_decoder_spec(cfg: DenseDecoderConfig) -> ModelSpec:
                        "tied_to": "model.embed_tokens.weight" if cfg.tie_word_embeddings else None},
                       "lm_head."),
         stop_token_ids=cfg.eos_token_ids,
+        # exporters write the rotation's frequency buffers beside the weights, and some write the output
+        # matrix again although it is tied to the embedding table
+        ignorable_tensors=(r".*\.rotary_emb\.inv_freq",) + ((r"lm_head\.weight",) if cfg.tie_word_embeddings else ()),
     )
     spec.validate()
     return spec

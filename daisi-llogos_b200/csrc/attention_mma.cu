@@ -351,13 +351,13 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 //
 // Work items are (sequence, key/value head, split).  Without `balance` every sequence has a.n_splits
 // splits and the grid is (splits, key/value heads, sequences), one block per item.  With `balance` the
-// grid is one row of at most DECODE_SLOTS blocks, a block takes items blockIdx.x, blockIdx.x +
+// grid is one row of at most `resident` blocks (what the GPU holds of this kernel at once), a block takes items blockIdx.x, blockIdx.x +
 // gridDim.x, ..., and a sequence has as many splits as its length calls for (at most a.n_splits):
 // every block works out the same number T of key tiles per item, the least with which the
 // items of all sequences fit the GPU at once, and sequence b gets ceil(tiles_b / T) splits.  A batch of
 // one long and seven short sequences then spreads the long one over most of the GPU; sequences of one
 // length get the same count each.
-constexpr int DECODE_SLOTS = 2 * 148;         // blocks of this kernel that the GPU holds at once
+constexpr int DECODE_BLOCKS_PER_SM = 2;       // blocks of this kernel that one SM holds at once
 
 // 64-key tiles that a sequence of `len` keys reads
 __device__ __forceinline__ int decode_tiles(int len, int window) {
@@ -366,7 +366,8 @@ __device__ __forceinline__ int decode_tiles(int len, int window) {
 }
 
 template <int HDMAX, bool EXACT, bool BALANCE>
-__global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16* __restrict__ out, int* __restrict__ counters) {
+__global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16* __restrict__ out, int* __restrict__ counters,
+                                                              int resident) {
   constexpr bool balance = BALANCE;
   extern __shared__ __align__(16) unsigned char smraw[];
   __shared__ int is_last;
@@ -401,7 +402,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
       if (lo_t >= hi) break;
-      if (n * a.nkv <= DECODE_SLOTS) hi = mid;
+      if (n * a.nkv <= resident) hi = mid;
       else lo_t = mid + 1;
     }
     tiles_per_item = hi;
@@ -744,9 +745,10 @@ LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, int* counters
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_decode_mma: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
   LLG_REQUIRE(a.n_splits >= 1 && a.n_splits <= 65535 && a.nkv <= 65535 && a.n_seqs <= 65535, "attn_decode_mma: grid too large");
-  LLG_REQUIRE(!balance || (a.n_seqs * a.nkv <= DECODE_SLOTS / 2 && a.n_seqs <= 32),
+  const int resident = DECODE_BLOCKS_PER_SM * llg_sm_count();
+  LLG_REQUIRE(!balance || (a.n_seqs * a.nkv <= resident / 2 && a.n_seqs <= 32),
               "attn_decode_mma: balanced splits are for at most 32 sequences and %d (sequence, key/value head) pairs",
-              DECODE_SLOTS / 2);
+              resident / 2);
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_decode_mma: bad cache geometry");
   LLG_REQUIRE(counters != nullptr, "attn_decode_mma: needs n_seqs * nkv zeroed counters");
   if (a.n_seqs <= 0) return 0;
@@ -756,15 +758,15 @@ LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, int* counters
   // balanced: as many blocks as the GPU holds, each taking the items that fall to it; otherwise one block per
   // item, which lets the hardware start the next block of an SM while its neighbour is still in its last tiles
   const long long items = (long long)a.n_splits * a.nkv * a.n_seqs;
-  const dim3 grid = balance ? dim3((unsigned)(items > DECODE_SLOTS ? DECODE_SLOTS : items)) : dim3(a.n_splits, a.nkv, a.n_seqs);
+  const dim3 grid = balance ? dim3((unsigned)(items > resident ? resident : items)) : dim3(a.n_splits, a.nkv, a.n_seqs);
 #define GO(HDM, EX)                                                                                         \
   do {                                                                                                      \
     if (balance) {                                                                                          \
       if (set_smem(attn_decode_mma_kernel<HDM, EX, true>, smem, "attn_decode_mma")) return 1;                 \
-      llg_launch(attn_decode_mma_kernel<HDM, EX, true>, grid, dim3(128), smem, stream, a, (bf16*)out, counters);  \
+      llg_launch(attn_decode_mma_kernel<HDM, EX, true>, grid, dim3(128), smem, stream, a, (bf16*)out, counters, resident);  \
     } else {                                                                                                \
       if (set_smem(attn_decode_mma_kernel<HDM, EX, false>, smem, "attn_decode_mma")) return 1;                \
-      llg_launch(attn_decode_mma_kernel<HDM, EX, false>, grid, dim3(128), smem, stream, a, (bf16*)out, counters); \
+      llg_launch(attn_decode_mma_kernel<HDM, EX, false>, grid, dim3(128), smem, stream, a, (bf16*)out, counters, resident); \
     }                                                                                                       \
   } while (0)
   if (a.hd == 64) GO(64, true);

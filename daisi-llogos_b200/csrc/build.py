@@ -34,6 +34,7 @@ SOURCES: Dict[str, List[str]] = {
     "attention_mma": ["attention_mma.cu", "common.cuh"],
     "attention_tc": ["attention_tc.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
+    "init": ["init.cu", "common.cuh"],
 }
 
 NVCC_FLAGS = [

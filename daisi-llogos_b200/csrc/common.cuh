@@ -41,6 +41,19 @@ static inline int llg_check_launch(const char* what) {
     if (!(cond)) return llg_fail(__VA_ARGS__); \
   } while (0)
 
+// Number of multiprocessors of the current device (asked once per device and kept).
+static inline int llg_sm_count() {
+  static int count[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+  if (count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    count[dev] = n;
+  }
+  return count[dev];
+}
+
 // ---- programmatic dependent launch -----------------------------------------------------
 //
 // Kernels of a step run back to back on one stream, each consuming what the one before wrote.

@@ -555,7 +555,7 @@ LLG_API int llg_silu_mul(const void* gu, int in_dtype, int n_partials, long long
   const int width = ((inter + 127) / 128) * 256;
   const int threads = 256;
   long long blocks = (total + threads - 1) / threads;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (long long)llg_sm_count() * 16) blocks = (long long)llg_sm_count() * 16;
 #define LAUNCH(IT, OT)                                                                                          \
   silu_mul_kernel<IT, OT><<<(unsigned)blocks, threads, 0, stream>>>((const IT*)gu, n_partials, partial_stride, \
                                                                      (OT*)out, total, inter, width)

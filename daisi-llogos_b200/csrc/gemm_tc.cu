@@ -496,7 +496,7 @@ int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, in
   const long long tiles = m_tiles * ((p.n + TN - 1) / TN);
   long long blocks = tiles;
   if (TN >= 128) {
-    const long long resident = 148LL * (smem <= 113 * 1024 ? 2 : 1);
+    const long long resident = (long long)llg_sm_count() * (smem <= 113 * 1024 ? 2 : 1);
     if (blocks > resident) blocks = resident;
   }
   if (blocks > 2147483647LL) return llg_fail("gemm_tc: too many tiles");
@@ -542,17 +542,18 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
     // ---- prompt steps: activations are the first operand (128 tokens per tile), up to 256 features per tile ----
     // in this orientation the kernel's first-operand rows (field o) are the tokens, the second's (field n) the features
     GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features, o / 2, BM};
-    // Tile shape: blocks run in rounds of 148; a round costs its tile's width, and a narrower tile can save a
+    // Tile shape: blocks run in rounds of one per SM (148 on a B200); a round costs its tile's width, and a narrower tile can save a
     // round (4096 features: 16 tiles of 256 in two token rows of 8 are 128 blocks, 18 of 240 are 144).  Two token
     // tiles per block halve the weight traffic per flop (worth about 15 %) but double the tile.
     const int widths[5] = {256, gated ? 192 : 240, 224, gated ? 256 : 208, gated ? 256 : 176};
     int best_w = 256, best_mt = 1;
     double best_cost = 0;
+    const long long sms = llg_sm_count();
     for (int wi = 0; wi < 5; ++wi) {
       for (int mt = 1; mt <= 2; ++mt) {
         if (mt == 1 && widths[wi] < 224) continue;      // a single token tile wants a wide second operand
         const long long tiles = (long long)((n + mt * BM - 1) / (mt * BM)) * ((o + widths[wi] - 1) / widths[wi]) * splits;
-        const double cost = (double)((tiles + 147) / 148) * widths[wi] * mt * (mt == 2 ? 0.85 : 1.0);
+        const double cost = (double)((tiles + sms - 1) / sms) * widths[wi] * mt * (mt == 2 ? 0.85 : 1.0);
         if (best_cost == 0 || cost < best_cost * 0.999) {
           best_cost = cost;
           best_w = widths[wi];
@@ -594,8 +595,9 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   int gate_rows = BM;
   if (tile_n <= 0) tile_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
   if (gated && n <= tile_n) {
-    const int rounds = ((gated_features + BM - 1) / BM + 147) / 148;
-    gate_rows = (gated_features + 148 * rounds - 1) / (148 * rounds);
+    const int sms = llg_sm_count();
+    const int rounds = ((gated_features + BM - 1) / BM + sms - 1) / sms;
+    gate_rows = (gated_features + sms * rounds - 1) / (sms * rounds);
     if (gate_rows < 16) gate_rows = 16;
     if (gate_rows > BM) gate_rows = BM;
   }
@@ -605,10 +607,11 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
               "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
   const CUtensorMap *mw = &map_w, *mx = &map_x;
   // Two weight tiles per block halve the activation traffic per flop (worth about 15 %) but double the
-  // tile: take them when the rounds over 148 SMs come out cheaper that way.
+  // tile: take them when the rounds over the SMs come out cheaper that way.
   const long long nt = (n + tile_n - 1) / tile_n;
   const long long t1 = (long long)((o + BM - 1) / BM) * nt, t2 = (long long)((o + 2 * BM - 1) / (2 * BM)) * nt;
-  const bool wide = !gated && tile_n >= 128 && ((t2 + 147) / 148) * 2 * 0.85 < (double)((t1 + 147) / 148);
+  const long long sm_n = llg_sm_count();
+  const bool wide = !gated && tile_n >= 128 && ((t2 + sm_n - 1) / sm_n) * 2 * 0.85 < (double)((t1 + sm_n - 1) / sm_n);
 #define GATED(TN, ST2)                                                                               \
   if (gated)                                                                                          \
     return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 1, 0>(mw, mx, p, splits, stream)            \

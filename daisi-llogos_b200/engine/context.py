@@ -10,8 +10,9 @@ is what lets unequal prompts share one step.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Callable, Dict, List, Optional, Tuple
 
+import numpy as np
 import torch
 
 
@@ -64,13 +65,38 @@ class StepContext:
     slots: torch.Tensor               # [B]
     cu_tokens: torch.Tensor           # [B + 1]
     len_before: torch.Tensor          # [B] tokens each sequence held before this step
-    prefill_tiles: Optional[Dict[int, torch.Tensor]]   # queries per tile -> [n_tiles, 2] (sequence, first query)
     dtype: torch.dtype = torch.float32
     device: torch.device = None
     ops: Any = None
     workspace: Workspace = None
     max_len_after: int = 0            # host upper bound of len_before + count over the batch
+    len_before_host: Optional[List[int]] = None   # the same lengths on the host (None in a decode step, where
+                                                  # the launches are recorded once and replayed)
+    upload: Optional[Callable[[np.ndarray, torch.Tensor], None]] = None   # host int32 array -> device buffer
     extras: Dict[str, Any] = field(default_factory=dict)
 
     def buffer(self, name: str, shape, dtype=None, zero: bool = False) -> torch.Tensor:
         return self.workspace.get(name, tuple(shape), dtype or self.dtype, zero)
+
+    def query_tiles(self, tile_queries: int) -> torch.Tensor:
+        """The step's queries cut into tiles of ``tile_queries`` per sequence: int32 ``[n_tiles, 2]`` (sequence,
+        first query among its step tokens), the tiles that see the most keys first (a mixer's blocks start in
+        list order, and the long ones should not be the last to start).  Worked out when a mixer first asks
+        for a tile size and kept for the rest of the step; a step with one token per sequence has none."""
+        key = ("query_tiles", int(tile_queries))
+        tiles = self.extras.get(key)
+        if tiles is None:
+            if self.len_before_host is None:
+                raise RuntimeError("query_tiles: this step's lengths are not known on the host")
+            tq = int(tile_queries)
+            lb, counts = self.len_before_host, self.counts
+            order = sorted(((i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)),
+                           key=lambda t: -(lb[t[0]] + min(counts[t[0]], t[1] + tq)))
+            host = np.asarray(order, dtype=np.int32).reshape(-1)
+            dev = self.buffer(f"query_tiles.{tq}", (host.size,), torch.int32)
+            if self.upload is not None:
+                self.upload(host, dev)
+            else:
+                dev.copy_(torch.from_numpy(host))
+            tiles = self.extras[key] = dev.view(-1, 2)
+        return tiles

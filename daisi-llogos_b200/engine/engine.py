@@ -24,8 +24,6 @@ from ..cache.store import PAGE, SequenceCache
 from .context import StepContext, Workspace
 from .model import DecoderModel
 
-_TILE_QS = (16, 64, 256)   # queries per block of the prompt attention kernels (CUDA cores, mma.sync, tcgen05)
-
 
 class StepError(ValueError):
     """A step was asked for that cannot run; nothing was launched and the cache is unchanged."""
@@ -59,6 +57,15 @@ class _Staging:
 
 
 _BUCKETS = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512, 768, 1024)
+
+
+def length_bucket(n: int) -> int:
+    """Upper bound on the lengths of a decode step that its recorded launches are planned for: the next power
+    of two from 1,024 on.  A batch whose sequences grow past it moves on to the next bound's graph."""
+    x = 1024
+    while x < n:
+        x *= 2
+    return x
 
 
 def decode_bucket(b: int) -> int:
@@ -104,6 +111,9 @@ class Engine:
             max_seq_len = n_pages * PAGE
             if model.spec.max_positions is not None:
                 max_seq_len = min(model.spec.max_positions, max_seq_len)
+        elif model.spec.max_positions is not None and max_seq_len > model.spec.max_positions:
+            raise ValueError(f"max_seq_len {max_seq_len} exceeds the model's position limit "
+                             f"(max_position_embeddings = {model.spec.max_positions})")
         if n_slots is None:
             n_slots = max(1, min(n_pages, 1024))
         self.cache = SequenceCache(model.cache_needs(), max_tokens=max_tokens, max_seq_len=max_seq_len,
@@ -114,7 +124,7 @@ class Engine:
         self._staging = _Staging(self.device)
         self._meta = torch.zeros(1024, dtype=torch.int32, device=self.device)
         self._workspace = Workspace(self.device)
-        self._decode: Dict[int, _DecodeState] = {}
+        self._decode: Dict[Tuple[int, int], _DecodeState] = {}     # (batch size, length bound) -> buffers and graph
         self.graph_kernels = 0      # kernels inside CUDA graphs replayed by step(), for reporting
 
     # ---- sequences -----------------------------------------------------------------------
@@ -219,6 +229,10 @@ class Engine:
             raise StepError(str(e)) from None
 
         len_before = [self.cache.length(s) for s in slots]
+        longest = max(lb + c for lb, c in zip(len_before, counts))
+        limit = self.model.position_limit()
+        if limit is not None and longest > limit:
+            raise StepError(f"a sequence would reach {longest} tokens, the position tables hold {limit}")
         updates = self.cache.grow(growth)
         b = len(slots)
         decode = all(c == 1 for c in counts)
@@ -258,14 +272,9 @@ class Engine:
         token_ids = np.concatenate(toks).astype(np.int32)
         positions = np.concatenate([np.arange(lb, lb + c, dtype=np.int32) for lb, c in zip(len_before, counts)])
         seq_of = np.repeat(np.arange(b, dtype=np.int32), counts)
-        # query tiles, those that see the most keys first: attention blocks start in list order, and the long
-        # ones should not be the last to start
-        tiles = [np.array(sorted(((i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)),
-                                 key=lambda t: -(len_before[t[0]] + min(counts[t[0]], t[1] + tq))),
-                          dtype=np.int32).reshape(-1) for tq in _TILE_QS]
         rows = np.array([cu[i] + int(w) for i in range(b) for w in want[i]], dtype=np.int32)
         host = [token_ids, positions, seq_of, np.asarray(slots, dtype=np.int32), cu,
-                np.asarray(len_before, dtype=np.int32), *tiles, rows]
+                np.asarray(len_before, dtype=np.int32), rows]
         plan = self._apply_updates(updates, host)
         block = np.concatenate(host)
         meta = self._ensure_meta(block.size)
@@ -281,10 +290,10 @@ class Engine:
         ctx = StepContext(
             n_tokens=n, n_seqs=b, decode=False, counts=counts, max_count=max(counts),
             token_ids=take(n), positions=take(n), seq_of_token=take(n), slots=take(b), cu_tokens=take(b + 1),
-            len_before=take(b), prefill_tiles={tq: take(t.size).view(-1, 2) for tq, t in zip(_TILE_QS, tiles)},
-            dtype=self.dtype, device=self.device,
+            len_before=take(b), dtype=self.dtype, device=self.device,
             ops=self.ops, workspace=self._workspace,
-            max_len_after=max(lb + c for lb, c in zip(len_before, counts)))
+            max_len_after=max(lb + c for lb, c in zip(len_before, counts)),
+            len_before_host=list(len_before), upload=self._staging.upload)
         rows_dev = take(rows.size)
         for g, off, k in plan:
             self.ops.scatter_i32(g.page_table, meta[off:off + k], meta[off + k:off + 2 * k])
@@ -293,9 +302,12 @@ class Engine:
     # ---- decode step -----------------------------------------------------------------------
     def _decode_step(self, n_real, slots, toks, len_before, updates, want, fed=None) -> torch.Tensor:
         b = decode_bucket(n_real) if self.use_graphs else n_real
-        st = self._decode.get(b)
+        # the launches are planned for lengths up to a bound that the batch's own longest sequence decides
+        # (not the cache's limit), so that short sequences in a cache sized for long ones are not over-split
+        bound = min(self.cache.max_seq_len, length_bucket(max(len_before) + 1))
+        st = self._decode.get((b, bound))
         if st is None:
-            st = self._decode[b] = _DecodeState(b, self.device)
+            st = self._decode[(b, bound)] = _DecodeState(b, self.device)
         pad = b - n_real
         token_ids = np.concatenate(toks + [np.zeros(pad, dtype=np.int64)]).astype(np.int32)
         ar = np.arange(b, dtype=np.int32)
@@ -329,9 +341,9 @@ class Engine:
             ctx = StepContext(
                 n_tokens=b, n_seqs=b, decode=True, counts=[1] * b, max_count=1,
                 token_ids=m[0:b], positions=m[b:2 * b], seq_of_token=m[2 * b:3 * b], slots=m[3 * b:4 * b],
-                cu_tokens=m[4 * b:5 * b + 1], len_before=m[5 * b + 1:6 * b + 1], prefill_tiles=None,
+                cu_tokens=m[4 * b:5 * b + 1], len_before=m[5 * b + 1:6 * b + 1],
                 dtype=self.dtype, device=self.device, ops=self.ops, workspace=st.workspace,
-                max_len_after=self.cache.max_seq_len)
+                max_len_after=bound)
             if self.use_graphs and st.eager_runs >= 1:
                 # the buffers exist since the eager run; record the same launches and replay them
                 graph = torch.cuda.CUDAGraph()

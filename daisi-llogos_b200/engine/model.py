@@ -11,7 +11,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..parts.base import ROLE_FAMILY, Branch, BuildEnv, Part, TensorDecl, part_class
+from ..parts.base import Branch, BuildEnv, Part, TensorDecl, part_class, part_families
 from ..parts.spec import ModelSpec
 
 # importing the modules registers the stock parts
@@ -35,14 +35,35 @@ class DecoderModel:
             self.encodings[name] = part_class("position", ps.kind)(ps.params, ps.prefix, self.env)
         self.embedding = part_class("embedding", spec.embedding.kind)(spec.embedding.params, spec.embedding.prefix, self.env)
         self.blocks = []
-        for ls in spec.layers:
+        for l_i, ls in enumerate(spec.layers):
+            block_cls = part_class("block", ls.block)
+            roles = dict(getattr(block_cls, "ROLES", {}))
             parts: Dict[str, Part] = {}
             for role, ps in ls.parts.items():
-                family = ROLE_FAMILY.get(role)
+                family = ps.family or roles.get(role)
                 if family is None:
-                    raise ValueError(f"block role '{role}' is not known ({', '.join(ROLE_FAMILY)})")
+                    raise ValueError(f"layers[{l_i}]: block '{ls.block}' declares no role '{role}' "
+                                     f"({', '.join(roles) or 'none'}) and the part names no family")
+                if family not in part_families():
+                    raise ValueError(f"layers[{l_i}].{role}: '{family}' is not a part family ({', '.join(part_families())})")
                 parts[role] = part_class(family, ps.kind)(ps.params, ps.prefix, self.env)
-            self.blocks.append(part_class("block", ls.block)({}, "", self.env, parts))
+            self.blocks.append(block_cls({}, "", self.env, parts))
+        # an entry that reads another entry's cache: its mixer must be able to read what the owner keeps
+        self._last_reader: Dict[int, int] = {}
+        for e_i, e in enumerate(spec.schedule):
+            if e.cache_of is None:
+                continue
+            self._last_reader[e.cache_of] = e_i
+            need = self.blocks[spec.schedule[e.cache_of].layer].cache_need()
+            if need is None:
+                raise ValueError(f"schedule[{e_i}].cache_of = {e.cache_of}: that entry keeps no cache")
+            for part in self.blocks[e.layer].parts.values():
+                check = getattr(part, "check_borrowed", None)
+                if check is not None:
+                    try:
+                        check(need)
+                    except ValueError as err:
+                        raise ValueError(f"schedule[{e_i}].cache_of = {e.cache_of}: {err}") from None
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm.params, spec.final_norm.prefix, self.env)
         self.head = part_class("head", spec.head.kind)(spec.head.params, spec.head.prefix, self.env)
         self._bound = False
@@ -79,6 +100,12 @@ class DecoderModel:
         for e in self.encodings.values():
             e.prepare(max_positions)
 
+    def position_limit(self) -> Optional[int]:
+        """The most positions every position encoding has tables for (``None``: no limit)."""
+        limits = [e.limit() for e in self.encodings.values()]
+        limits = [x for x in limits if x is not None]
+        return min(limits) if limits else None
+
     # ---- cache units ---------------------------------------------------------------------
     def cache_needs(self) -> Dict[int, object]:
         """Schedule entry -> what its mixer keeps (entries that borrow a cache keep nothing)."""
@@ -86,8 +113,7 @@ class DecoderModel:
         for e_i, e in enumerate(self.spec.schedule):
             if e.cache_of is not None:
                 continue
-            mixer = self.blocks[e.layer].parts.get("mixer")
-            need = mixer.cache_need() if mixer is not None else None
+            need = self.blocks[e.layer].cache_need()
             if need is not None:
                 needs[e_i] = need
         return needs
@@ -106,6 +132,11 @@ class DecoderModel:
             view = cache.view(unit, owner=e.cache_of is None, keep_step_kv=e_i in borrowed,
                               shared=shared.setdefault(unit, {}))
             pending = self.blocks[e.layer].forward(residual, pending, ctx, view)
+            # what an owner put off until its cache's last reader has run (a ring's writes would
+            # overwrite keys that a reader of the same step still needs)
+            for unit in [u for u, last in self._last_reader.items() if last == e_i]:
+                for finish in shared.get(unit, {}).pop("after_last_reader", []):
+                    finish()
         if rows is None or rows.numel() == 0:
             # nothing wanted: the residual need not be finished, the cache already is
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)

@@ -9,20 +9,25 @@ from __future__ import annotations
 
 import torch
 
-_SMS = 148
-
-
 _plan_cache = {}
 
+# What one block of the small-tile product streams when it runs alone on its multiprocessor: a ring of
+# five 18 KB stages (about 80 KB in flight) against a memory latency near 1.8 us, measured on a B200 as
+# 43-47 GB/s per block (one o-projection tile column timed alone).  Only ratios of costs matter below.
+_BLOCK_BYTES_PER_US = 45e3
+# Rate at which split-K partials are written and read back by the consumer kernel: L2-resident float32
+# traffic, measured near 4 TB/s for the [S, N, O] buffers of a decode step.
+_PARTIAL_BYTES_PER_US = 4e6
 
-def plan_splits(n: int, o: int, k: int) -> int:
-    s = _plan_cache.get((n, o, k))
+
+def plan_splits(n: int, o: int, k: int, n_sms: int) -> int:
+    s = _plan_cache.get((n, o, k, n_sms))
     if s is None:
-        s = _plan_cache[(n, o, k)] = _plan_splits(n, o, k)
+        s = _plan_cache[(n, o, k, n_sms)] = _plan_splits(n, o, k, n_sms)
     return s
 
 
-def _plan_splits(n: int, o: int, k: int) -> int:
+def _plan_splits(n: int, o: int, k: int, n_sms: int) -> int:
     """Split-K wish for a product with few enough rows that streaming the weights is what takes the time.
 
     ``tiles`` output tiles, each with ``nkb`` k-blocks of 64, are cut into ``s`` splits; the blocks run
@@ -34,17 +39,17 @@ def _plan_splits(n: int, o: int, k: int) -> int:
         return 1
     nkb = -(-k // 64)
     if n >= 256:                  # tokens are the MMA rows: 128 tokens x 256 features per tile, one block per SM
-        tiles, tile_bytes, resident = -(-n // 128) * -(-o // 256), (128 + 256) * 128, _SMS
+        tiles, tile_bytes, resident = -(-n // 128) * -(-o // 256), (128 + 256) * 128, n_sms
     else:                         # weights are the MMA rows: 128 features x a token tile
         tile_n = 16 if n <= 16 else 32 if n <= 32 else 64 if n <= 64 else 128 if n <= 128 else 256
         tiles, tile_bytes = -(-o // 128) * -(-n // tile_n), (128 + tile_n) * 128
-        resident = 2 * _SMS if tile_n <= 64 else _SMS
-    unit_us = tile_bytes / 45e3   # a block streams about 45 GB/s
+        resident = 2 * n_sms if tile_n <= 64 else n_sms
+    unit_us = tile_bytes / _BLOCK_BYTES_PER_US
     best, best_cost = 1, None
     for s in range(1, max(1, min(nkb // 4, 32)) + 1):
         cost = -(-tiles * s // resident) * (-(-nkb // s) + 3) * unit_us
         if s > 1:
-            cost += s * n * o * 8 / 4e6          # the partials, out and in again, at about 4 TB/s
+            cost += s * n * o * 8 / _PARTIAL_BYTES_PER_US      # the partials, out and in again
         if best_cost is None or cost < best_cost:
             best, best_cost = s, cost
     return best
@@ -64,7 +69,7 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dt
     if tc is not None and tc(x, w):
         splits = 1
         if out is None and out_dtype == torch.float32 and split_k:
-            splits = ops.gemm_tc_splits(k, plan_splits(n, o, k))
+            splits = ops.gemm_tc_splits(k, plan_splits(n, o, k, ops.sm_count()))
         if out is None:
             out = ctx.buffer(name, (splits, n, o), out_dtype)
         ops.gemm_tc(x, w, out)

@@ -179,12 +179,28 @@ def _load_lib(name: str):
         lib.llg_attn_tc_supported.argtypes = [c_int]
         lib.llg_attn_prefill_tc.argtypes = [POINTER(_PrefillArgs), c_void_p]
         lib.llg_attn_tc_status.restype = c_int
+    elif name == "init":
+        lib.llg_fill_normal.argtypes = [c_void_p, c_int, c_longlong, c_ulonglong, ctypes.c_double, ctypes.c_double, c_void_p]
+        lib.llg_fill.argtypes = [c_void_p, c_int, c_longlong, c_float, c_void_p]
+        lib.llg_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
     elif name == "sampling":
         lib.llg_argmax.argtypes = [c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.llg_sample.argtypes = [POINTER(_SampleArgs), c_void_p]
         lib.llg_sample_slices.argtypes = [c_int]
     _protos_done.add(name)
     return lib
+
+
+_sm_counts = {}
+
+
+def sm_count() -> int:
+    """Multiprocessors of the current CUDA device (asked once per device)."""
+    dev = torch.cuda.current_device()
+    n = _sm_counts.get(dev)
+    if n is None:
+        n = _sm_counts[dev] = int(torch.cuda.get_device_properties(dev).multi_processor_count)
+    return n
 
 
 def require_gpu() -> None:
@@ -449,8 +465,9 @@ def attn_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_split
 
 
 def attn_decode_balance_pairs() -> int:
-    """Most (sequence, key/value head) pairs for which decode attention balances its splits by length."""
-    return 148
+    """Most (sequence, key/value head) pairs for which decode attention balances its splits by length: half the
+    blocks of that kernel that the GPU holds at once (two per multiprocessor)."""
+    return sm_count()
 
 
 def attn_decode_uses_counters(dtype: torch.dtype, head_dim: int) -> bool:
@@ -492,6 +509,26 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
                                             int(bool(balance) and b * nkv <= attn_decode_balance_pairs() and b <= 32), _stream()))
     else:
         _check(lib, lib.llg_attn_decode_simt(byref(a), _ptr(out, q.dtype), _dt(q), _stream()), kernels=2)
+
+
+def fill_normal(out: torch.Tensor, key: int, mean: float, std: float) -> None:
+    """out.flat[i] = mean + std * z(key, i): the counter-based normal values of csrc/init.cu, which
+    weights/random_init.py restates for the host."""
+    lib = _lib("init")
+    _check(lib, lib.llg_fill_normal(_ptr(out), _dt(out), out.numel(), int(key) & 0xFFFFFFFFFFFFFFFF, float(mean),
+                                    float(std), _stream()))
+
+
+def fill(out: torch.Tensor, value: float) -> None:
+    lib = _lib("init")
+    _check(lib, lib.llg_fill(_ptr(out), _dt(out), out.numel(), float(value), _stream()))
+
+
+def cast(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst = src converted between float32 and bfloat16 (to bfloat16: round to nearest even)."""
+    lib = _lib("init")
+    assert src.numel() == dst.numel()
+    _check(lib, lib.llg_cast(_ptr(src), _dt(src), _ptr(dst), _dt(dst), src.numel(), _stream()))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:

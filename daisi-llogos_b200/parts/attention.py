@@ -18,7 +18,7 @@ from ..kernels.linear import linear
 from .base import Branch, KvNeed, Mixer, TensorDecl, register_part
 
 
-def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int, blocks_per_sm: int = 2, n_sms: int = 148) -> int:
+def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int, n_sms: int, blocks_per_sm: int = 2) -> int:
     """How many blocks share one (sequence, key/value head) in decode attention.
 
     With ``pairs = n_seqs * n_kv_heads`` and ``tiles`` 64-key tiles per sequence, ``s`` splits run in
@@ -102,6 +102,16 @@ class Attention(Mixer):
     def cache_need(self):
         return KvNeed(self.nkv, self.hd, self.window) if self.own_kv else None
 
+    def check_borrowed(self, need) -> None:
+        if self.own_kv:
+            raise ValueError("an attention part that reads another entry's cache must have own_kv = False")
+        if not isinstance(need, KvNeed):
+            raise ValueError("attention can only read a cache of keys and values")
+        mine = (self.nkv, self.hd, self.window)
+        if (need.num_kv_heads, need.head_dim, need.window) != mine:
+            raise ValueError(f"the owner keeps (key/value heads, head size, window) = "
+                             f"{(need.num_kv_heads, need.head_dim, need.window)}, this reader expects {mine}")
+
     # ---- one step ------------------------------------------------------------------------
     def forward(self, x, ctx, cache) -> Branch:
         ops = ctx.ops
@@ -125,13 +135,14 @@ class Attention(Mixer):
                             seq_of_token=ctx.seq_of_token, slots=ctx.slots)
             else:
                 ops.qk_prep(qkv, **common)
-            splits = decode_splits(ctx.n_seqs, self.nkv, ctx.max_len_after)
+            n_sms = ops.sm_count()
+            splits = decode_splits(ctx.n_seqs, self.nkv, ctx.max_len_after, n_sms)
             # Sequences of unequal lengths: the kernel gives each as many splits as its length calls for, up to what
             # one long sequence among short ones could use (the blocks the GPU holds, less one per other pair).
             balance = 1 < ctx.n_seqs <= 32 and ctx.n_seqs * self.nkv <= ops.attn_decode_balance_pairs()
             if balance:
                 tiles = max(1, -(-ctx.max_len_after // 64))
-                splits = max(splits, min(64, tiles, 2 * 148 // self.nkv - (ctx.n_seqs - 1)))
+                splits = max(splits, min(64, tiles, 2 * n_sms // self.nkv - (ctx.n_seqs - 1)))
             scratch = ctx.buffer("attn.scratch", (ops.attn_decode_scratch_floats(n, self.nh, self.hd, splits),),
                                  torch.float32)
             counters = None
@@ -161,11 +172,18 @@ class Attention(Mixer):
                 k_new, v_new = cache.shared["k_new"], cache.shared["v_new"]
             tq = ops.prefill_tile_queries(q.dtype, self.hd)
             ops.attn_prefill(q, k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
-                             ctx.prefill_tiles[tq], ctx.cu_tokens, ctx.len_before, ctx.slots, out,
+                             ctx.query_tiles(tq), ctx.cu_tokens, ctx.len_before, ctx.slots, out,
                              scale=self.scale, window=self.window, tile_queries=tq)
             if self.own_kv and not write_now:
-                ops.kv_write(k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
-                             ctx.positions, ctx.seq_of_token, ctx.slots, ctx.cu_tokens, ctx.len_before)
+                def write_ring():
+                    ops.kv_write(k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
+                                 ctx.positions, ctx.seq_of_token, ctx.slots, ctx.cu_tokens, ctx.len_before)
+                if cache.keep_step_kv:
+                    # later entries of the run order read this ring in the same step: the new keys must not
+                    # replace old ones before the last of them has run
+                    cache.shared.setdefault("after_last_reader", []).append(write_ring)
+                else:
+                    write_ring()
         return Branch(linear(ctx, out, self.w_o, "attn.proj", torch.float32))
 
 

@@ -94,6 +94,10 @@ class Mixer(Part):
     def forward(self, x, ctx, cache) -> Branch:
         raise NotImplementedError
 
+    def check_borrowed(self, need) -> None:
+        """Called when the model is built for a mixer whose schedule entry reads another entry's cache
+        (``cache_of``): ``need`` is what the owner keeps.  Raise ``ValueError`` if this mixer cannot read it."""
+
 
 class FeedForward(Part):
     def forward(self, x, ctx) -> Branch:
@@ -102,7 +106,12 @@ class FeedForward(Part):
 
 class PositionEncoding(Part):
     def prepare(self, max_positions: int) -> None:
-        """Build tables for positions ``[0, max_positions)``."""
+        """Build tables for positions ``[0, max_positions)``.  May be called again with another number (a
+        second engine on the same model): tables only grow, and one that a step may still read stays alive."""
+
+    def limit(self) -> Optional[int]:
+        """Positions the tables built so far cover (``None``: no limit)."""
+        return None
 
     def rotation(self):
         """``None`` or a ``Rotation`` that a mixer applies to its queries and keys."""
@@ -113,12 +122,30 @@ class PositionEncoding(Part):
 
 
 class Block(Part):
+    """``ROLES`` names the roles this arrangement has and the family each role's part is looked up in
+    (``{"norm1": "norm", "mixer": "mixer", ...}``).  A layer's ``PartSpec`` may also carry its family
+    itself; that wins, and lets a spec give a block a role that its class did not list."""
+
+    ROLES: Dict[str, str] = {}
+
     def __init__(self, params, prefix, env, parts: Dict[str, Part]):
         super().__init__(params, prefix, env)
         self.parts = parts
 
     def forward(self, residual, pending: Optional[Branch], ctx, cache) -> Optional[Branch]:
         raise NotImplementedError
+
+    def cache_parts(self):
+        """The parts of this block that keep something per sequence (at most one: an entry of the run order
+        has one cache unit)."""
+        keepers = [p for p in self.parts.values() if p.cache_need() is not None]
+        if len(keepers) > 1:
+            raise ValueError("a block may hold only one part that keeps a cache or a state per sequence")
+        return keepers
+
+    def cache_need(self):
+        keepers = self.cache_parts()
+        return keepers[0].cache_need() if keepers else None
 
 
 @dataclass
@@ -155,5 +182,5 @@ def part_class(family: str, kind: str):
     return reg[kind]
 
 
-# a block's role names -> the family each role's part is looked up in
-ROLE_FAMILY = {"norm1": "norm", "norm2": "norm", "mixer": "mixer", "ffn": "ffn"}
+def part_families():
+    return tuple(_REGISTRIES)

@@ -15,6 +15,8 @@ from .base import Block, Branch, register_part
 class PreNormBlock(Block):
     """roles: norm1, mixer, norm2, ffn."""
 
+    ROLES = {"norm1": "norm", "mixer": "mixer", "norm2": "norm", "ffn": "ffn"}
+
     def forward(self, residual, pending: Optional[Branch], ctx, cache) -> Optional[Branch]:
         p = self.parts
         h = p["norm1"].forward(residual, pending, ctx)

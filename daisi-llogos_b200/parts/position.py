@@ -66,8 +66,16 @@ class RotaryEncoding(PositionEncoding):
             raise ValueError(f"rotary pairing '{pairing}' is not known (half, adjacent)")
         self.pairing = 0 if pairing == "half" else 1
         self._rotation: Optional[Rotation] = None
+        self._retired = []        # smaller tables that were replaced: a recorded CUDA graph may still read them
+
+    def limit(self) -> Optional[int]:
+        return None if self._rotation is None else int(self._rotation.cos.shape[0])
 
     def prepare(self, max_positions: int) -> None:
+        if self._rotation is not None:
+            if self._rotation.cos.shape[0] >= max_positions:
+                return
+            self._retired.append(self._rotation)
         inv = rotary_inverse_frequencies(self.rotary_dim, self.params["theta"], self.params.get("scaling"))
         pos = torch.arange(max_positions, dtype=torch.float64)
         ang = pos[:, None] * inv[None, :]

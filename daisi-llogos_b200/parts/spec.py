@@ -16,11 +16,14 @@ from typing import Any, Dict, List, Optional, Tuple
 
 @dataclass(frozen=True)
 class PartSpec:
-    """One part: its registered kind, its parameters, the prefix of its tensor names."""
+    """One part: its registered kind, its parameters, the prefix of its tensor names.  ``family`` (norm,
+    mixer, ffn, position, ...) is needed only where the part fills a block role whose family the block's
+    class does not declare."""
 
     kind: str
     params: Dict[str, Any] = field(default_factory=dict)
     prefix: str = ""
+    family: Optional[str] = None
 
 
 @dataclass(frozen=True)
@@ -28,7 +31,7 @@ class LayerSpec:
     """One layer: a block arrangement and the parts it arranges."""
 
     block: str                     # registered block kind, e.g. "prenorm"
-    parts: Dict[str, PartSpec]     # role in the block -> part ("norm1", "mixer", "norm2", "ffn")
+    parts: Dict[str, PartSpec]     # role in the block -> part (the block's class names its roles)
 
 
 @dataclass(frozen=True)
@@ -56,6 +59,9 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     stop_token_ids: Tuple[int, ...] = ()
+    # Regular expressions (matched against whole names) of tensors that a checkpoint of this architecture
+    # may hold although the model has no use for them; the loader skips them with a warning.
+    ignorable_tensors: Tuple[str, ...] = ()
 
     def validate(self) -> None:
         for e_i, e in enumerate(self.schedule):

@@ -81,7 +81,7 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: Generati
     """Generates for every prompt; ``on_token(request index, token)`` is called as tokens appear.
 
     ``engine`` needs ``open()``, ``close(slot)``, ``step(entries, want=None)`` and a ``cache`` with
-    ``n_pages`` / ``max_seq_len`` / ``slots.free_count``; ``sampler.sample(logits, params, seed=, step=,
+    ``n_pages`` (or ``free_pages()``) / ``max_seq_len`` / ``slots.free_count``; ``sampler.sample(logits, params, seed=, step=,
     seq_ids=, histories=, stop_tokens=)`` returns one token per row.
     """
     params.validate()
@@ -96,8 +96,10 @@ def generate(engine, sampler, prompts: Sequence[Sequence[int]], params: Generati
         return result
     cache = engine.cache
     page = getattr(cache, "page", 64)
+    # what is free now: sequences that the caller holds open keep their pages while this call runs
+    free_pages = cache.free_pages() if hasattr(cache, "free_pages") else cache.n_pages
     batches = plan_batches([len(p) for p in prompts], params.max_tokens, max_batch=min(max_batch, cache.slots.free_count),
-                           free_pages=cache.n_pages, page=page, max_seq_len=cache.max_seq_len)
+                           free_pages=free_pages, page=page, max_seq_len=cache.max_seq_len)
     for batch in batches:
         result.batches += 1
         slots = {i: engine.open() for i in batch}

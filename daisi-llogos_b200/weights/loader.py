@@ -5,21 +5,25 @@ Storage rule: with compute type bfloat16, tensors stored as BF16 stay as they ar
 converted to bfloat16, a tensor stored in 32 bits stays float32, integer tables become int32.
 With compute type float32 every floating tensor becomes float32 (the bfloat16 values exactly).
 All problems of a checkpoint are reported in ONE error that lists missing tensors, unexpected
-tensors and wrong shapes.  The reference looks tensors up by name and fails on the first
-missing one (Model/ModelLoader.cs:95-113, :144-145; optional ones :152-162).
+tensors and wrong shapes.  Tensors that the architecture declares harmless (buffers that exporters
+write beside the weights, a second copy of a tied matrix) are not an error: they are skipped and
+named in the model's ``load_warnings``.  The reference looks tensors up by name and fails on the
+first missing one (Model/ModelLoader.cs:95-113, :144-145; optional ones :152-162) and never looks at
+the names it does not ask for.
 """
 from __future__ import annotations
 
-import hashlib
 import json
 import os
-from typing import Any, Dict, Mapping, Optional
+import re
+from typing import Any, Dict, List, Mapping, Optional, Sequence
 
 import torch
 
 from ..config.dense import read_config_json
 from ..config.registry import architecture_of
 from ..engine.model import DecoderModel
+from .random_init import fill_normal, tensor_key
 from .safetensors_io import ModelFiles, write_safetensors
 
 
@@ -44,14 +48,18 @@ def _stored_as(t: torch.Tensor, compute: torch.dtype) -> torch.dtype:
     return torch.bfloat16
 
 
-def check_tensors(decls, available: Mapping[str, Any], where: str) -> None:
-    """``available`` maps name -> shape.  Raises one WeightsError that lists everything wrong."""
+def check_tensors(decls, available: Mapping[str, Any], where: str, ignorable: Sequence[str] = ()) -> List[str]:
+    """``available`` maps name -> shape.  Raises one WeightsError that lists everything wrong; returns the
+    names of tensors that were found, are not part of the model, and match one of the ``ignorable``
+    patterns (regular expressions on the whole name)."""
     missing = sorted(n for n, d in decls.items() if not d.optional and n not in available)
-    unexpected = sorted(n for n in available if n not in decls)
+    extra = sorted(n for n in available if n not in decls)
+    skipped = [n for n in extra if any(re.fullmatch(p, n) for p in ignorable)]
+    unexpected = [n for n in extra if n not in skipped]
     wrong = sorted((n, tuple(available[n]), tuple(decls[n].shape)) for n in available
                    if n in decls and tuple(available[n]) != tuple(decls[n].shape))
     if not (missing or unexpected or wrong):
-        return
+        return skipped
     lines = [f"{where}: the tensors do not fit the model that config.json describes"]
     if missing:
         lines.append(f"  missing ({len(missing)}):")
@@ -88,43 +96,54 @@ def load_model(model_dir: str, *, dtype: torch.dtype = torch.bfloat16, device="c
     decls = model.tensor_decls()
     files = ModelFiles(model_dir)
     try:
-        check_tensors(decls, {n: files.info(n)[1] for n in files.names()}, model_dir)
+        skipped = check_tensors(decls, {n: files.info(n)[1] for n in files.names()}, model_dir,
+                                model.spec.ignorable_tensors)
+        model.load_warnings = [f"{model_dir}: tensor '{n}' is not part of the model and was skipped" for n in skipped]
         tensors: Dict[str, torch.Tensor] = {}
         for name in decls:
             if name not in files.names():
                 continue
-            t = files.tensor(name)
-            tensors[name] = t.to(device=device, dtype=_stored_as(t, dtype)).contiguous()
+            tensors[name] = _to_device(files.tensor(name), device, dtype, ops)
         model.bind(tensors)
     finally:
         files.close()
     return model
 
 
+def _to_device(t: torch.Tensor, device: torch.device, compute: torch.dtype, ops) -> torch.Tensor:
+    """The tensor on ``device`` in the type the storage rule gives it.  On the GPU float32 <-> bfloat16 is
+    converted by the library's own kernel after the copy; what the kernel does not take (float16, float64,
+    integers) is converted on the host first."""
+    want = _stored_as(t, compute)
+    if device.type != "cuda" or want == torch.int32:
+        return t.to(device=device, dtype=want).contiguous()
+    if t.dtype not in (torch.float32, torch.bfloat16):
+        t = t.to(torch.float32)
+    src = t.contiguous().to(device)
+    if src.dtype == want:
+        return src
+    dst = torch.empty(src.shape, dtype=want, device=device)
+    ops.cast(src, dst)
+    return dst
+
+
 # ---- random weights -----------------------------------------------------------------------
 
-def _tensor_seed(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
-
-
 def random_tensors(decls, seed: int, *, std: float = 0.02, norm_std: float = 0.0, bias_std: float = 0.02,
-                   dtype: torch.dtype = torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:
+                   dtype: torch.dtype = torch.bfloat16, device="cpu", ops=None) -> Dict[str, torch.Tensor]:
     """One tensor per declaration: matrices and tables N(0, std), norm weights 1 + N(0, norm_std),
-    biases N(0, bias_std); each tensor's generator is seeded by (seed, its name)."""
+    biases N(0, bias_std).  Every element is a function of (seed, tensor name, element index) alone
+    (weights/random_init.py), so the values do not depend on the device that makes them: on the GPU the
+    library's fill kernel writes them, on the CPU numpy does."""
     device = torch.device(device)
+    if device.type == "cuda" and ops is None:
+        ops = _ops_for(device)
     out = {}
     for name, d in decls.items():
-        g = torch.Generator(device=device)
-        g.manual_seed(_tensor_seed(seed, name))
-        x = torch.randn(d.shape, generator=g, device=device, dtype=torch.float32)
-        if d.role == "norm":
-            x = 1.0 + norm_std * x
-        elif d.role == "bias":
-            x = bias_std * x
-        else:
-            x = std * x
-        out[name] = x.to(dtype)
+        mean, spread = (1.0, norm_std) if d.role == "norm" else (0.0, bias_std) if d.role == "bias" else (0.0, std)
+        t = torch.empty(d.shape, dtype=dtype, device=device)
+        fill_normal(t, tensor_key(seed, name), mean, spread, ops)
+        out[name] = t
     return out
 
 
@@ -151,8 +170,15 @@ def random_model(config_dict: Mapping[str, Any], seed: int, *, dtype: torch.dtyp
     model = build_model(config_dict, dtype=dtype, device=device, ops=ops)
     store = torch.bfloat16
     tensors = random_tensors(model.tensor_decls(), seed, std=std, norm_std=norm_std, bias_std=bias_std,
-                             dtype=store, device=device)
+                             dtype=store, device=device, ops=ops)
     if dtype == torch.float32:
-        tensors = {n: t.to(torch.float32) for n, t in tensors.items()}
+        wide = {}
+        for n, t in tensors.items():                  # the bfloat16 values exactly, stored in 32 bits
+            wide[n] = torch.empty(t.shape, dtype=torch.float32, device=device)
+            if device.type == "cuda":
+                ops.cast(t, wide[n])
+            else:
+                wide[n].copy_(t)
+        tensors = wide
     model.bind(tensors)
     return model

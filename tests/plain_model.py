@@ -94,12 +94,15 @@ def rope_rotate(x: torch.Tensor, positions: Sequence[int], inv_freq: torch.Tenso
     return x
 
 
-def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0) -> torch.Tensor:
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0,
+              round_weights=None) -> torch.Tensor:
     """Causal softmax attention of one whole sequence.  q [T, nH, hd], k/v [T, nKV, hd];
     query head h uses key/value head h // (nH / nKV); score = (q . k) * scale, applied after the
     dot product; query t sees keys j <= t, and with a window W only j > t - W.
     Daisi.Llogos.Cpu/CpuBackend.cs:476-590 (scores :527-537, softmax :540-553, values :556-571);
-    window: Inference/AttentionStrategy.cs:64-71."""
+    window: Inference/AttentionStrategy.cs:64-71.
+    ``round_weights``: a rounding applied to the unnormalised softmax weights as they enter the
+    product with the values (the sum that normalises them stays unrounded)."""
     t, nh, hd = q.shape
     nkv = k.shape[1]
     g = nh // nkv
@@ -114,17 +117,22 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, w
         s = s.masked_fill(~visible, float("-inf"))
         s = s - s.max(dim=-1, keepdim=True).values
         p = torch.exp(s)
-        p = p / p.sum(dim=-1, keepdim=True)
-        out[:, h, :] = p @ v[:, kh, :].to(F64)
+        if round_weights is None:
+            p = p / p.sum(dim=-1, keepdim=True)
+            out[:, h, :] = p @ v[:, kh, :].to(F64)
+        else:
+            out[:, h, :] = (round_weights(p) @ v[:, kh, :].to(F64)) / p.sum(dim=-1, keepdim=True)
     return out
 
 
-def swiglu(x: torch.Tensor, w_gate, w_up, w_down) -> torch.Tensor:
+def swiglu(x: torch.Tensor, w_gate, w_up, w_down, rnd=None) -> torch.Tensor:
     """down( silu(gate(x)) * up(x) ), silu(g) = g / (1 + exp(-g)).
-    Inference/ForwardPass.cs:242-246; Daisi.Llogos.Cpu/Silu.cs:9-16."""
+    Inference/ForwardPass.cs:242-246; Daisi.Llogos.Cpu/Silu.cs:9-16.
+    ``rnd``: a rounding applied to the gated values before the last product."""
     g = linear(x, w_gate)
     u = linear(x, w_up)
-    return linear(g / (1.0 + torch.exp(-g)) * u, w_down)
+    m = g / (1.0 + torch.exp(-g)) * u
+    return linear(m if rnd is None else rnd(m), w_down)
 
 
 # ---- the model --------------------------------------------------------------------------------
@@ -140,10 +148,23 @@ def layer_windows(cfg: dict) -> List[int]:
     return [0] * n
 
 
-def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int]) -> torch.Tensor:
+def round_bfloat16(t: torch.Tensor) -> torch.Tensor:
+    """The nearest bfloat16 value (ties to even), as float64."""
+    return t.to(torch.float32).to(torch.bfloat16).to(F64)
+
+
+def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], rounded: bool = False) -> torch.Tensor:
     """Logits [T, vocab] of one whole sequence.  Order as Inference/ForwardPass.cs:199-267 (layers)
     and :174-184 (final norm, head): norm, q/k/v, per-head norm, bias, rotation, attention, output
-    projection, residual, norm, SwiGLU, residual (ForwardPass.cs:368-404 for the attention part)."""
+    projection, residual, norm, SwiGLU, residual (ForwardPass.cs:368-404 for the attention part).
+
+    ``rounded``: values that a bfloat16 engine keeps in bfloat16 between its kernels are rounded to
+    bfloat16 here as well: the output of every norm, q, k and v after the rotation, the softmax weights
+    as they enter the product with the values, the attention output and the gated feed-forward values.
+    Sums, statistics, the residual stream and the logits stay unrounded.  The reference keeps every
+    activation in 32 bits (Inference/ForwardPass.cs:1046-1047), so this form has no counterpart there;
+    it tells a bfloat16 engine's rounding from a fault."""
+    r = round_bfloat16 if rounded else (lambda t: t)
     arch = cfg["architectures"][0]
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)
@@ -162,7 +183,7 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int]) 
     h = embedding(weights["model.embed_tokens.weight"], tokens)
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        x = rms_norm(h, weights[p + "input_layernorm.weight"], eps)
+        x = r(rms_norm(h, weights[p + "input_layernorm.weight"], eps))
         a = p + "self_attn."
         q = linear(x, weights[a + "q_proj.weight"]).view(t, nh, hd)
         k = linear(x, weights[a + "k_proj.weight"]).view(t, nkv, hd)
@@ -174,14 +195,16 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int]) 
             q = q + weights[a + "q_proj.bias"].to(F64).view(nh, hd)
             k = k + weights[a + "k_proj.bias"].to(F64).view(nkv, hd)
             v = v + weights[a + "v_proj.bias"].to(F64).view(nkv, hd)
-        q = rope_rotate(q, positions, inv_freq, "half")
-        k = rope_rotate(k, positions, inv_freq, "half")
-        o = attention(q, k, v, 1.0 / math.sqrt(hd), windows[i]).reshape(t, nh * hd)
+        q = r(rope_rotate(q, positions, inv_freq, "half"))
+        k = r(rope_rotate(k, positions, inv_freq, "half"))
+        v = r(v)
+        o = r(attention(q, k, v, 1.0 / math.sqrt(hd), windows[i], r if rounded else None).reshape(t, nh * hd))
         h = h + linear(o, weights[a + "o_proj.weight"])
-        x = rms_norm(h, weights[p + "post_attention_layernorm.weight"], eps)
+        x = r(rms_norm(h, weights[p + "post_attention_layernorm.weight"], eps))
         m = p + "mlp."
-        h = h + swiglu(x, weights[m + "gate_proj.weight"], weights[m + "up_proj.weight"], weights[m + "down_proj.weight"])
-    x = rms_norm(h, weights["model.norm.weight"], eps)
+        h = h + swiglu(x, weights[m + "gate_proj.weight"], weights[m + "up_proj.weight"], weights[m + "down_proj.weight"],
+                       r if rounded else None)
+    x = r(rms_norm(h, weights["model.norm.weight"], eps))
     head = weights["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else weights["lm_head.weight"]
     return linear(x, head)
 

@@ -79,6 +79,7 @@ def test_missing_key_is_named(llogos, key):
     ({"hidden_act": "gelu"}, "hidden_act"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "yarn"),
     ({"use_sliding_window": True}, "sliding_window"),
+    ({"use_sliding_window": True, "sliding_window": 32}, "max_window_layers"),
     ({"layer_types": ["full_attention"]}, "layer_types"),
     ({"eos_token_id": 100000}, "eos_token_id"),
     ({"rms_norm_eps": 0.0}, "rms_norm_eps"),

@@ -100,6 +100,37 @@ def test_errors_come_before_any_launch(llogos, setup):
     eng.cache.audit()
 
 
+def test_context_beyond_the_models_positions_is_refused(llogos, setup, model_dirs):
+    """A cache for longer sequences than ``max_position_embeddings`` allows is an error that names both numbers,
+    through the engine and through the Python entry point; without an explicit length the model's limit caps it."""
+    model, _ = setup["llama"]                       # max_position_embeddings 512
+    with pytest.raises(ValueError, match="600.*512"):
+        llogos.engine.Engine(model, max_tokens=64 * 20, max_seq_len=600, use_graphs=False)
+    assert llogos.engine.Engine(model, max_tokens=64 * 20, use_graphs=False).cache.max_seq_len == 512
+    api = __import__("importlib").import_module("daisi-llogos_b200.api")
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        api.LlogosModel(model, max_context=4096, max_batch=1, use_graphs=False)
+
+
+def test_a_second_engine_leaves_the_first_ones_tables_alone(llogos, setup):
+    """Two engines on one model with different longest sequences: the rotation tables only grow, so the
+    first engine's steps see the same tables before and after the second engine exists."""
+    model, w = setup["qwen2"]
+    cfg = TINY["qwen2"]
+    toks = random_tokens(cfg["vocab_size"], [200], 3)[0]
+    ref = P.forward(w, cfg, toks)
+    big = engine_for(llogos, model, max_tokens=64 * 8, max_seq_len=400)
+    rot = next(iter(model.encodings.values())).rotation()
+    small = engine_for(llogos, model, max_tokens=64 * 2, max_seq_len=100)
+    assert next(iter(model.encodings.values())).rotation() is rot and model.position_limit() >= 400
+    slot = big.open()
+    lg = big.step([(slot, toks)])
+    assert float((lg[0].double() - ref[-1]).abs().max()) < 2e-4
+    with pytest.raises(llogos.engine.StepError, match="longest sequence"):
+        s2 = small.open()
+        small.step([(s2, toks)])
+
+
 def test_padding_free_layout(llogos, setup):
     """Exactly the given tokens run: the packed layout has no padding rows."""
     model, _ = setup["llama"]
@@ -213,6 +244,10 @@ def test_products_that_split_their_sums(llogos, setup, model_dirs):
             return True
 
         @staticmethod
+        def sm_count():
+            return 4
+
+        @staticmethod
         def gemm_tc_splits(k, wish):
             return min(wish, 3)
 
@@ -228,7 +263,7 @@ def test_products_that_split_their_sums(llogos, setup, model_dirs):
     lin = __import__("importlib").import_module("daisi-llogos_b200.kernels.linear")
     wished = []
     real_plan = lin.plan_splits
-    lin.plan_splits = lambda n, o, k: wished.append((n, o, k)) or 3
+    lin.plan_splits = lambda n, o, k, n_sms: wished.append((n, o, k)) or 3
     try:
         name = "llama"
         cfg = TINY[name]

@@ -14,8 +14,10 @@ from conftest import ROOT, TINY, read_weights, random_tokens
 pytestmark = pytest.mark.gpu
 
 
-def plain_generate(w, cfg, prompt, n, stop=(), params=None, seed=0, seq_id=0):
-    """Greedy (params None) or sampled continuation with the plain model and the plain sampler."""
+def plain_generate(w, cfg, prompt, n, stop=(), params=None, seed=0, seq_id=0, margins=None):
+    """Greedy (params None) or sampled continuation with the plain model and the plain sampler.  ``margins``
+    (a list) receives, per drawn token, how far the draw's uniform number lay from the nearest boundary
+    between two tokens of the cumulative distribution."""
     toks, out = list(prompt), []
     for step in range(n):
         logits = P.forward(w, cfg, toks)[-1]
@@ -23,12 +25,26 @@ def plain_generate(w, cfg, prompt, n, stop=(), params=None, seed=0, seq_id=0):
             t = int(max(range(len(logits)), key=lambda i: (float(logits[i]), -i)))
         else:
             probs = P.sampling_distribution(logits.float().tolist(), previous=toks[-64:], **params)
-            t = P.draw(probs, P.uniform_of(seed, seq_id, step))
+            u = P.uniform_of(seed, seq_id, step)
+            t = P.draw(probs, u)
+            if margins is not None:
+                cdf = torch.cumsum(probs, 0) / probs.sum()
+                margins.append(float((cdf - u).abs().min()))
         if t in stop:
             break
         toks.append(t)
         out.append(t)
     return out
+
+
+def same_draws(got, want, margins, excuse=1e-5):
+    """True when the engine drew what the plain sampler drew; a first difference is excused only where the
+    plain draw fell within ``excuse`` of a boundary of the cumulative distribution (float32 logits move a
+    boundary by about 1e-6), and nothing after it is compared, since the sequences differ from there."""
+    for j, (a, b) in enumerate(zip(got, want)):
+        if a != b:
+            return margins[j] < excuse
+    return len(got) == len(want)
 
 
 def margin_ok(w, cfg, prompt, out, min_gap=1e-3):
@@ -78,20 +94,21 @@ def test_seeded_sampling_matches_plain_and_ignores_batch_mates(llogos, model_dir
     again = model.generate(prompts, params)
     assert r.tokens == again.tokens
     plain_params = dict(temperature=0.8)
-    agree = 0
     for i, p in enumerate(prompts):
-        want = plain_generate(w, cfg, p, 12, params=plain_params, seed=1234, seq_id=i)
-        agree += int(r.tokens[i] == want)
-    assert agree >= 3            # a draw that falls within 1e-6 of a boundary may differ in float32
+        margins = []
+        want = plain_generate(w, cfg, p, 12, params=plain_params, seed=1234, seq_id=i, margins=margins)
+        assert same_draws(r.tokens[i], want, margins), (i, r.tokens[i], want, margins)
     other = model.generate(prompts, L.GenerationParams(max_tokens=12, temperature=0.8, top_k=0, top_p=1.0,
                                                        repetition_penalty=1.0, seed=99, stop_tokens=()))
     assert other.tokens != r.tokens
     # with the reference's default filters and penalties on
     full = L.GenerationParams(max_tokens=10, seed=5, stop_tokens=())
     rf = model.generate(prompts[:2], full)
-    wantf = [plain_generate(w, cfg, p, 10, params=dict(temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1),
-                            seed=5, seq_id=i) for i, p in enumerate(prompts[:2])]
-    assert sum(int(a == b) for a, b in zip(rf.tokens, wantf)) >= 1
+    for i, p in enumerate(prompts[:2]):
+        margins = []
+        want = plain_generate(w, cfg, p, 10, params=dict(temperature=0.8, top_k=40, top_p=0.95, repetition_penalty=1.1),
+                              seed=5, seq_id=i, margins=margins)
+        assert same_draws(rf.tokens[i], want, margins), (i, rf.tokens[i], want, margins)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

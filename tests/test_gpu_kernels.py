@@ -562,3 +562,37 @@ def test_sampler_draws_follow_the_distribution(ops):
     assert torch.equal(a, out)
     ops.sample(logits.to(DEV), work, a, temperature=1.0, seed=124, step=7)
     assert not torch.equal(a, out)
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_fill_normal_is_the_hosts_generator(ops, llogos, dtype):
+    """The fill kernel and the numpy restatement of the same counter-based generator give the same bits, for
+    sizes that are no multiple of anything, a mean and a spread, and keys of different tensors; so a model
+    initialised on the GPU holds the weights that a model written to a file from the same seed holds."""
+    ri = importlib.import_module("daisi-llogos_b200.weights.random_init")
+    for n, name, mean, std in ((1, "a", 0.0, 1.0), (1000003, "model.layers.3.mlp.up_proj.weight", 0.0, 0.02),
+                               (4097, "model.norm.weight", 1.0, 0.1), (65536, "b", -2.0, 3.0)):
+        key = ri.tensor_key(11, name)
+        got = torch.empty(n, dtype=dtype, device=DEV)
+        ops.fill_normal(got, key, mean, std)
+        want = torch.from_numpy(ri.normal_values(key, n, mean, std)).to(dtype)
+        assert torch.equal(got.cpu(), want), (n, name)
+    decls = {"x.weight": llogos.parts.TensorDecl((33, 70)), "x.norm": llogos.parts.TensorDecl((70,), "norm"),
+             "x.bias": llogos.parts.TensorDecl((33,), "bias")}
+    kw = dict(std=0.3, norm_std=0.1, bias_std=0.05, dtype=dtype)
+    on_gpu = llogos.weights.random_tensors(decls, 5, device=DEV, **kw)
+    on_cpu = llogos.weights.random_tensors(decls, 5, device="cpu", **kw)
+    for k in decls:
+        assert torch.equal(on_gpu[k].cpu(), on_cpu[k]), k
+
+
+def test_cast_and_fill(ops):
+    x = rnd((5, 1001), 71)
+    half = torch.empty(5, 1001, dtype=torch.bfloat16, device=DEV)
+    ops.cast(x.to(DEV), half)
+    assert torch.equal(half.cpu(), x.to(torch.bfloat16))            # round to nearest even
+    back = torch.empty(5, 1001, device=DEV)
+    ops.cast(half, back)
+    assert torch.equal(back.cpu(), x.to(torch.bfloat16).float())
+    ops.fill(back, 88.0)
+    assert float(back.min()) == 88.0 == float(back.max())

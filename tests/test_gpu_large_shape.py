@@ -1,9 +1,21 @@
-"""Two layers of Llama-3.1-8B's sizes: the bfloat16 engine (tensor-core products whose blocks work
-through several tiles, prompt attention over 2,048 tokens, decode attention with splits) against the
-engine's own 32-bit path (CUDA-core kernels throughout) on the same weights.  The plain implementation
-is too slow at these sizes; the 32-bit path is compared with it on the small configurations."""
+"""Layers of Llama-3.1-8B's sizes.
+
+First against the plain implementation: one layer of the headline sizes (width 4096, 32 heads in 8 groups,
+head size 128, 14336 gated features, llama3 rotation scaling) with a vocabulary short enough for the plain
+model, in float32 and bfloat16: a prompt of 300 tokens whole, a second request in portions (80 tokens on a
+length of 64) and decode steps of both.  The weights come from the counter-based generator, so the plain
+model on the host holds exactly what the engine holds on the GPU.
+
+Then two layers with the full vocabulary and a prompt of 2,048 tokens, which the plain model is too slow for:
+the bfloat16 engine (tensor-core products whose blocks work through several tiles, prompt attention over
+2,048 tokens, decode attention with splits) against the engine's own 32-bit path (CUDA-core kernels
+throughout) on the same weights."""
+import importlib
+
 import pytest
 import torch
+
+from compare import Reference
 
 pytestmark = pytest.mark.gpu
 
@@ -16,6 +28,49 @@ CFG = {
                      "original_max_position_embeddings": 8192},
 }
 REL_TOL = 4e-2
+ONE_LAYER = dict(CFG, num_hidden_layers=1, vocab_size=8003)
+
+
+@pytest.fixture(scope="module")
+def one_layer(llogos):
+    """The weights by name on the host (for the plain model) and the requests with their references."""
+    model = llogos.weights.build_model(ONE_LAYER, dtype=torch.bfloat16, device="cuda:0",
+                                       ops=importlib.import_module("daisi-llogos_b200.kernels.ops"))
+    on_gpu = llogos.weights.random_tensors(model.tensor_decls(), 7, std=0.02, norm_std=0.1, device="cuda:0")
+    weights = {n: t.cpu() for n, t in on_gpu.items()}
+    del on_gpu, model
+    torch.cuda.empty_cache()
+    g = torch.Generator().manual_seed(5)
+    a, b = (torch.randint(0, ONE_LAYER["vocab_size"], (n,), generator=g).tolist() for n in (306, 150))
+    return weights, (a, Reference(weights, ONE_LAYER, a)), (b, Reference(weights, ONE_LAYER, b))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_one_layer_of_the_headline_sizes_against_the_plain_model(llogos, one_layer, dtype):
+    weights, (a, ra), (b, rb) = one_layer
+    # the same seed on the device: the generator's values depend on (seed, name, index) alone
+    model = llogos.weights.random_model(ONE_LAYER, seed=7, dtype=dtype, device="cuda:0", std=0.02, norm_std=0.1)
+    got = model.blocks[0].parts["ffn"].w_down
+    assert torch.equal(got.cpu().float(), weights["model.layers.0.mlp.down_proj.weight"].float())
+    eng = llogos.engine.Engine(model, max_tokens=64 * 10)
+    sa, sb = eng.open(), eng.open()
+    lg = eng.step([(sa, a[:300])], [list(range(300))])
+    ra.check(lg, range(300), dtype, ("300 tokens whole",))
+    lg = eng.step([(sb, b[:64])], [list(range(64))])
+    rb.check(lg, range(64), dtype, ("64 tokens",))
+    lg = eng.step([(sb, b[64:144])], [list(range(80))])
+    rb.check(lg, range(64, 144), dtype, ("80 tokens on 64",))
+    for j in range(6):
+        lg = eng.step([(sa, [a[300 + j]]), (sb, [b[144 + j]])])
+        ra.check(lg[0], [300 + j], dtype, ("decode a", j))
+        rb.check(lg[1], [144 + j], dtype, ("decode b", j))
+    eng.close(sa)
+    eng.close(sb)
+    eng.cache.audit()
+    ops = llogos.kernels.ops
+    assert ops.gemm_tc_status() == 0 and ops.attn_tc_status() == 0
+    del eng, model
+    torch.cuda.empty_cache()
 
 
 def run(llogos, dtype, seqs, want_first, decode_steps):

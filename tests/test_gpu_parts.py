@@ -49,13 +49,13 @@ def prompt_ctx(llogos, ops, dtype, counts, before, slots):
         cu.append(cu[-1] + c)
     pos = [p for b, c in zip(before, counts) for p in range(b, b + c)]
     seq = [i for i, c in enumerate(counts) for _ in range(c)]
-    tiles = {tq: i32([(i, q0) for i, c in enumerate(counts) for q0 in range(0, c, tq)]).view(-1, 2) for tq in (16, 64, 128)}
     decode = all(c == 1 for c in counts)
     return ctx_mod.StepContext(
         n_tokens=cu[-1], n_seqs=len(counts), decode=decode, counts=list(counts), max_count=max(counts),
         token_ids=i32([0] * cu[-1]), positions=i32(pos), seq_of_token=i32(seq), slots=i32(slots), cu_tokens=i32(cu),
-        len_before=i32(before), prefill_tiles=None if decode else tiles, dtype=dtype, device=DEV, ops=ops,
-        workspace=ctx_mod.Workspace(DEV), max_len_after=max(b + c for b, c in zip(before, counts)))
+        len_before=i32(before), dtype=dtype, device=DEV, ops=ops,
+        workspace=ctx_mod.Workspace(DEV), max_len_after=max(b + c for b, c in zip(before, counts)),
+        len_before_host=None if decode else list(before))
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
@@ -499,3 +499,182 @@ def test_toy_routed_feedforward_and_learned_positions(llogos, tmp_path):
         Pt.unregister_part("ffn", "toy_top1")
         Pt.unregister_part("position", "toy_learned")
         reg._ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
+
+
+def test_borrowed_cache_with_a_window(llogos, tmp_path):
+    """An entry that reads the ring of an earlier entry: a window of 100 keys lives in a ring of three pages, and
+    a second portion of 100 tokens on a length of 150 lets the positions 192..249 land on the rows of the
+    positions 0..57.  The owner's writes have to wait until the reader has run, for the reader's query at
+    position 150 still looks at the keys 51..57.  Then single tokens."""
+    from conftest import read_weights, random_tokens
+    import dataclasses
+    reg = importlib.import_module("daisi-llogos_b200.config.registry")
+    S = llogos.parts
+    W = 100
+
+    def build(cfg):
+        spec = llogos.config.dense_decoder_spec(cfg)
+        layers = list(spec.layers)
+        for i in (0, 1):
+            parts = dict(layers[i].parts)
+            params = dict(parts["mixer"].params, window=W, own_kv=(i == 0))
+            parts["mixer"] = S.PartSpec("attention", params, parts["mixer"].prefix)
+            layers[i] = S.LayerSpec("prenorm", parts)
+        sched = (S.ScheduleEntry(0), S.ScheduleEntry(1, cache_of=0))
+        return dataclasses.replace(spec, layers=tuple(layers), schedule=sched)
+
+    def build_mismatch(cfg):
+        spec = build(cfg)
+        layers = list(spec.layers)
+        parts = dict(layers[1].parts)
+        parts["mixer"] = S.PartSpec("attention", dict(parts["mixer"].params, window=W + 1), parts["mixer"].prefix)
+        layers[1] = S.LayerSpec("prenorm", parts)
+        return dataclasses.replace(spec, layers=tuple(layers))
+
+    llogos.config.register_architecture("ToyRingForCausalLM", reg._dense_reader(qk_norm=False, force_bias=False), build)
+    llogos.config.register_architecture("ToyRingMismatchForCausalLM", reg._dense_reader(qk_norm=False, force_bias=False),
+                                        build_mismatch)
+    try:
+        cfg = {"architectures": ["ToyRingForCausalLM"], "num_hidden_layers": 2, "hidden_size": 48,
+               "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16, "intermediate_size": 80,
+               "vocab_size": 99, "rope_theta": 777.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 512}
+        d = str(tmp_path / "ring")
+        llogos.weights.write_random_model(d, cfg, seed=12, std=0.25, norm_std=0.1)
+        w = read_weights(llogos, d)
+        assert "model.layers.1.self_attn.k_proj.weight" not in w
+
+        def plain(tokens):
+            t, nh, nkv, hd, eps = len(tokens), 3, 1, 16, 1e-5
+            inv = P.rope_inverse_frequencies(hd, 777.0, None)
+            h = P.embedding(w["model.embed_tokens.weight"], tokens)
+            kept = None
+            for layer in (0, 1):
+                p = f"model.layers.{layer}."
+                a = p + "self_attn."
+                x = P.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+                q = P.rope_rotate(P.linear(x, w[a + "q_proj.weight"]).view(t, nh, hd), range(t), inv, "half")
+                if layer == 0:
+                    k = P.rope_rotate(P.linear(x, w[a + "k_proj.weight"]).view(t, nkv, hd), range(t), inv, "half")
+                    kept = (k, P.linear(x, w[a + "v_proj.weight"]).view(t, nkv, hd))
+                o = P.attention(q, kept[0], kept[1], 0.25, W).reshape(t, nh * hd)
+                h = h + P.linear(o, w[a + "o_proj.weight"])
+                x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+                m = p + "mlp."
+                h = h + P.swiglu(x, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+        for dtype, tol_ in ((torch.float32, 1e-4), (torch.bfloat16, 4e-2)):
+            model = llogos.weights.load_model(d, dtype=dtype, device="cuda:0")
+            eng = llogos.engine.Engine(model, max_tokens=64 * 10)
+            assert eng.cache.kv_groups[0].ring_pages == 3
+            seqs = random_tokens(99, [256, 180], 19)
+            refs = [plain(s) for s in seqs]
+            scale = [float(r.abs().max()) for r in refs]
+            slots = [eng.open(), eng.open()]
+            lg = eng.step([(slots[0], seqs[0][:150]), (slots[1], seqs[1][:70])], [list(range(150)), list(range(70))])
+            assert float((lg[:150].cpu().double() - refs[0][:150]).abs().max()) < tol_ * scale[0]
+            assert float((lg[150:].cpu().double() - refs[1][:70]).abs().max()) < tol_ * scale[1]
+            lg = eng.step([(slots[0], seqs[0][150:250]), (slots[1], seqs[1][70:174])], [list(range(100)), list(range(104))])
+            err = (lg[:100].cpu().double() - refs[0][150:250]).abs().max(dim=1).values
+            assert float(err.max()) < tol_ * scale[0], ("second portion, worst position", 150 + int(err.argmax()), float(err.max()))
+            assert float((lg[100:].cpu().double() - refs[1][70:174]).abs().max()) < tol_ * scale[1]
+            for j in range(6):
+                lg = eng.step([(slots[0], [seqs[0][250 + j]]), (slots[1], [seqs[1][174 + j]])])
+                assert float((lg[0].cpu().double() - refs[0][250 + j]).abs().max()) < tol_ * scale[0], j
+                assert float((lg[1].cpu().double() - refs[1][174 + j]).abs().max()) < tol_ * scale[1], j
+        # a reader whose window is not the owner's is refused when the model is built
+        with pytest.raises(ValueError, match="window"):
+            llogos.weights.build_model(dict(cfg, architectures=["ToyRingMismatchForCausalLM"]), dtype=torch.float32,
+                                       device="cuda:0", ops=importlib.import_module("daisi-llogos_b200.kernels.ops"))
+    finally:
+        reg._ARCHITECTURES.pop("ToyRingForCausalLM", None)
+        reg._ARCHITECTURES.pop("ToyRingMismatchForCausalLM", None)
+
+
+def test_a_block_with_roles_of_its_own(llogos, tmp_path):
+    """A block defined here whose branches run side by side (one norm feeds the mixer and the feed-forward, both
+    outputs are added): it names two of its roles in ``ROLES``, and the spec gives the third role's family
+    itself.  Layer 0 keeps the stock arrangement, layer 1 takes the new one; nothing in the library changes."""
+    from conftest import read_weights, random_tokens
+    import dataclasses
+    reg = importlib.import_module("daisi-llogos_b200.config.registry")
+    Pt = llogos.parts
+
+    class SideBySide(Pt.Block):
+        ROLES = {"mixer": "mixer", "ffn": "ffn"}          # "ln" is not listed: its PartSpec says family="norm"
+
+        def forward(self, residual, pending, ctx, cache):
+            h = self.parts["ln"].forward(residual, pending, ctx)
+            a = self.parts["mixer"].forward(h, ctx, cache)
+            f = self.parts["ffn"].forward(h, ctx)
+            return Pt.Branch(torch.cat([a.data, f.data], dim=0))       # partial sums, added by whoever comes next
+
+    def build(cfg):
+        spec = llogos.config.dense_decoder_spec(cfg)
+        layers = list(spec.layers)
+        old = layers[1].parts
+        ln = dataclasses.replace(old["norm1"], family="norm")
+        layers[1] = Pt.LayerSpec("toy_side_by_side", {"ln": ln, "mixer": old["mixer"], "ffn": old["ffn"]})
+        return dataclasses.replace(spec, layers=tuple(layers))
+
+    def build_without_family(cfg):
+        spec = build(cfg)
+        layers = list(spec.layers)
+        parts = dict(layers[1].parts)
+        parts["ln"] = dataclasses.replace(parts["ln"], family=None)
+        layers[1] = Pt.LayerSpec("toy_side_by_side", parts)
+        return dataclasses.replace(spec, layers=tuple(layers))
+
+    Pt.register_part("block", "toy_side_by_side", SideBySide)
+    llogos.config.register_architecture("ToySideForCausalLM", reg._dense_reader(qk_norm=False, force_bias=False), build)
+    llogos.config.register_architecture("ToySideBadForCausalLM", reg._dense_reader(qk_norm=False, force_bias=False),
+                                        build_without_family)
+    try:
+        cfg = {"architectures": ["ToySideForCausalLM"], "num_hidden_layers": 2, "hidden_size": 48,
+               "num_attention_heads": 3, "num_key_value_heads": 3, "head_dim": 16, "intermediate_size": 80,
+               "vocab_size": 99, "rope_theta": 777.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 256}
+        d = str(tmp_path / "side")
+        llogos.weights.write_random_model(d, cfg, seed=13, std=0.2, norm_std=0.1)
+        w = read_weights(llogos, d)
+        assert "model.layers.1.post_attention_layernorm.weight" not in w
+        assert "model.layers.0.post_attention_layernorm.weight" in w
+
+        def plain(tokens):
+            t, nh, hd, eps = len(tokens), 3, 16, 1e-5
+            inv = P.rope_inverse_frequencies(hd, 777.0, None)
+            h = P.embedding(w["model.embed_tokens.weight"], tokens)
+            for i in range(2):
+                p = f"model.layers.{i}."
+                a, m = p + "self_attn.", p + "mlp."
+                x = P.rms_norm(h, w[p + "input_layernorm.weight"], eps)
+                q = P.rope_rotate(P.linear(x, w[a + "q_proj.weight"]).view(t, nh, hd), range(t), inv, "half")
+                k = P.rope_rotate(P.linear(x, w[a + "k_proj.weight"]).view(t, nh, hd), range(t), inv, "half")
+                v = P.linear(x, w[a + "v_proj.weight"]).view(t, nh, hd)
+                att = P.linear(P.attention(q, k, v, 0.25).reshape(t, nh * hd), w[a + "o_proj.weight"])
+                if i == 0:
+                    h = h + att
+                    x = P.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps)
+                    h = h + P.swiglu(x, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+                else:
+                    h = h + att + P.swiglu(x, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+            return P.linear(P.rms_norm(h, w["model.norm.weight"], eps), w["lm_head.weight"])
+
+        model = llogos.weights.load_model(d, dtype=torch.float32, device="cuda:0")
+        eng = llogos.engine.Engine(model, max_tokens=64 * 4)
+        seqs = random_tokens(99, [60, 25], 20)
+        refs = [plain(s) for s in seqs]
+        slots = [eng.open(), eng.open()]
+        lg = eng.step([(slots[0], seqs[0][:50]), (slots[1], seqs[1][:20])], [list(range(50)), list(range(20))])
+        assert float((lg[:50].cpu().double() - refs[0][:50]).abs().max()) < 1e-4
+        assert float((lg[50:].cpu().double() - refs[1][:20]).abs().max()) < 1e-4
+        for j in range(5):                                  # the second of these replays a recorded graph
+            lg = eng.step([(slots[0], [seqs[0][50 + j]]), (slots[1], [seqs[1][20 + j]])])
+            assert float((lg[0].cpu().double() - refs[0][50 + j]).abs().max()) < 1e-4
+            assert float((lg[1].cpu().double() - refs[1][20 + j]).abs().max()) < 1e-4
+        with pytest.raises(ValueError, match="no role 'ln'"):
+            llogos.weights.build_model(dict(cfg, architectures=["ToySideBadForCausalLM"]), dtype=torch.float32,
+                                       device="cuda:0", ops=importlib.import_module("daisi-llogos_b200.kernels.ops"))
+    finally:
+        Pt.unregister_part("block", "toy_side_by_side")
+        reg._ARCHITECTURES.pop("ToySideForCausalLM", None)
+        reg._ARCHITECTURES.pop("ToySideBadForCausalLM", None)

@@ -9,11 +9,11 @@ import numpy as np
 import pytest
 import torch
 
-import plain_model as P
+from compare import reference
 from conftest import ROOT, TINY, read_weights, random_tokens
 
 pytestmark = pytest.mark.gpu
-REL_TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 class Replay:
@@ -43,12 +43,8 @@ class Replay:
         assert self.p.wait(timeout=60) == 0
 
 
-def close(got, ref, dtype, scale):
-    """``scale``: the largest |logit| of the request's whole reference; bfloat16 noise is absolute
-    across a request's positions, so every position is judged against the same scale."""
-    ref = ref.double().numpy()
-    err = float(np.abs(got.astype(np.float64) - ref).max())
-    return err <= REL_TOL[dtype] * scale, err
+def check(ref, got, positions, dtype, what):
+    ref.check(torch.from_numpy(got.astype(np.float32)), positions, TORCH[dtype], what)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -58,39 +54,61 @@ def test_replay_schedules(llogos, model_dirs, tmp_path, name, dtype):
     vocab = cfg["vocab_size"]
     w = read_weights(llogos, model_dirs[name])
     seqs = random_tokens(vocab, [70, 33, 129, 40], 21)
-    refs = [P.forward(w, cfg, s) for s in seqs]
-    scales = [float(x.abs().max()) for x in refs]
+    refs = [reference(model_dirs[name], w, cfg, s) for s in seqs]
     r = Replay(model_dirs[name], dtype, str(tmp_path / "out"), max_tokens=64 * 6)
     # each request alone and whole, all places wanted
     for i, s in enumerate(seqs):
         got = r.step([(f"w{i}", s, list(range(len(s))))], end=[f"w{i}"]).reshape(len(s), vocab)
-        ok, err = close(got, refs[i], dtype, scales[i])
-        assert ok, ("whole", i, err)
+        check(refs[i], got, range(len(s)), dtype, ("whole", i))
     # the last 32 tokens one by one
     for i, s in enumerate(seqs):
         cut = len(s) - 32
         assert r.step([(f"d{i}", s[:cut], [])]) is None
         for p in range(cut, len(s)):
             got = r.step([(f"d{i}", [s[p]], [0])], end=[f"d{i}"] if p == len(s) - 1 else [])
-            ok, err = close(got, refs[i][p], dtype, scales[i])
-            assert ok, ("decode", i, p, err)
+            check(refs[i], got, [p], dtype, ("decode", i, p))
     # batches of unequal lengths, one after another; 6 pages hold seqs 0, 1 and 3, then seq 2 with 1
     for batch in ([0, 1, 3], [2, 1]):
         cut = {i: len(seqs[i]) - 4 - 3 * k for k, i in enumerate(batch)}
         got = r.step([(f"b{i}", seqs[i][:cut[i]], [cut[i] - 1]) for i in batch]).reshape(len(batch), vocab)
         for k, i in enumerate(batch):
-            ok, err = close(got[k], refs[i][cut[i] - 1], dtype, scales[i])
-            assert ok, ("batch prompt", i, err)
+            check(refs[i], got[k], [cut[i] - 1], dtype, ("batch prompt", i))
         pos, live = dict(cut), list(batch)
         while live:
             ending = [i for i in live if pos[i] == len(seqs[i]) - 1]
             got = r.step([(f"b{i}", [seqs[i][pos[i]]], [0]) for i in live], end=[f"b{i}" for i in ending])
             got = got.reshape(len(live), vocab)
             for k, i in enumerate(live):
-                ok, err = close(got[k], refs[i][pos[i]], dtype, scales[i])
-                assert ok, ("batch decode", i, pos[i], err)
+                check(refs[i], got[k], [pos[i]], dtype, ("batch decode", i, pos[i]))
                 pos[i] += 1
             live = [i for i in live if i not in ending]
+    r.finish()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["qwen3", "wide"])
+def test_replay_of_portions_and_mixed_steps(llogos, model_dirs, tmp_path, name, dtype):
+    """The replay program takes any cut of a request into steps: a prompt in portions (300 tokens on a length
+    of 70, one token alone, 257 on 371), then a second request that joins with its whole prompt while the first
+    goes on by one token, both windows of the configurations shorter than the portions."""
+    cfg = TINY[name]
+    vocab = cfg["vocab_size"]
+    w = read_weights(llogos, model_dirs[name])
+    a, b = random_tokens(vocab, [640, 200], 23)
+    ra, rb = reference(model_dirs[name], w, cfg, a), reference(model_dirs[name], w, cfg, b)
+    r = Replay(model_dirs[name], dtype, str(tmp_path / "out"), max_tokens=64 * 15)
+    done = 0
+    for n in (70, 300, 1, 257):
+        got = r.step([("a", a[done:done + n], list(range(n)))]).reshape(n, vocab)
+        check(ra, got, range(done, done + n), dtype, ("portion", n, "on", done))
+        done += n
+    got = r.step([("a", a[done:done + 1], [0]), ("b", b[:190], [0, 100, 189])]).reshape(4, vocab)
+    check(ra, got[0], [done], dtype, ("one token beside a prompt",))
+    check(rb, got[1:], [0, 100, 189], dtype, ("a prompt beside one token",))
+    done += 1
+    got = r.step([("b", b[190:], list(range(10))), ("a", a[done:done + 11], [10])], end=["a", "b"]).reshape(11, vocab)
+    check(rb, got[:10], range(190, 200), dtype, ("second portion of b",))
+    check(ra, got[10], [done + 10], dtype, ("a goes on",))
     r.finish()
 
 

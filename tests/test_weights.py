@@ -143,17 +143,63 @@ def test_one_error_lists_everything(llogos, model_dirs, tmp_path):
     w = read_weights(llogos, d)
     del w["model.layers.1.mlp.down_proj.weight"]
     del w["model.layers.2.self_attn.q_norm.weight"]
-    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
-    w["lm_head.weight"] = torch.zeros(384, 96, dtype=torch.bfloat16)        # tied model: not expected
+    w["model.layers.0.self_attn.o_proj.bias"] = torch.zeros(96)             # the architecture has no such bias
+    w["model.layers.7.mlp.up_proj.weight"] = torch.zeros(256, 96, dtype=torch.bfloat16)   # there is no layer 7
     w["model.layers.0.self_attn.k_proj.weight"] = torch.zeros(96, 95, dtype=torch.bfloat16)
     llogos.weights.write_safetensors(os.path.join(d, "model.safetensors"), w)
     with pytest.raises(llogos.weights.WeightsError) as e:
         llogos.weights.load_model(d, dtype=torch.float32, device="cpu", ops=cpu_ops)
     msg = str(e.value)
     for needle in ("missing (2)", "model.layers.1.mlp.down_proj.weight", "model.layers.2.self_attn.q_norm.weight",
-                   "unexpected (2)", "rotary_emb.inv_freq", "lm_head.weight", "wrong shape (1)",
+                   "unexpected (2)", "self_attn.o_proj.bias", "model.layers.7.mlp.up_proj.weight", "wrong shape (1)",
                    "model.layers.0.self_attn.k_proj.weight", "(96, 95)", "(96, 96)"):
         assert needle in msg, (needle, msg)
+
+
+def test_harmless_extras_are_skipped_with_a_warning(llogos, model_dirs, tmp_path):
+    """Checkpoints of this architecture often carry the rotation's frequency buffers, and a tied model may
+    carry the output matrix a second time: both are skipped and named in ``load_warnings``.  Any other
+    tensor that the model has no place for stays an error, even when nothing is missing."""
+    d = str(tmp_path / "m")
+    shutil.copytree(model_dirs["qwen3"], d)
+    w = read_weights(llogos, d)
+    w["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
+    w["lm_head.weight"] = torch.zeros(384, 96, dtype=torch.bfloat16)        # tied model: a second copy
+    llogos.weights.write_safetensors(os.path.join(d, "model.safetensors"), w)
+    m = llogos.weights.load_model(d, dtype=torch.float32, device="cpu", ops=cpu_ops)
+    assert len(m.load_warnings) == 2
+    assert any("rotary_emb.inv_freq" in x for x in m.load_warnings) and any("lm_head.weight" in x for x in m.load_warnings)
+    assert m.head.weight is m.embedding.weight
+    clean = llogos.weights.load_model(model_dirs["qwen3"], dtype=torch.float32, device="cpu", ops=cpu_ops)
+    assert clean.load_warnings == []
+    # an untied model has a use for lm_head.weight, so there it is no extra; a stray tensor is an error alone
+    w["model.layers.0.self_attn.o_proj.bias"] = torch.zeros(96)
+    llogos.weights.write_safetensors(os.path.join(d, "model.safetensors"), w)
+    with pytest.raises(llogos.weights.WeightsError, match=r"unexpected \(1\)"):
+        llogos.weights.load_model(d, dtype=torch.float32, device="cpu", ops=cpu_ops)
+
+
+def test_random_values_are_a_function_of_seed_name_and_index(llogos):
+    """The counter-based generator: fixed values for a fixed key (so that the device kernel, which restates
+    the same arithmetic, can be checked against them), moments of a normal distribution, and independence
+    of how a tensor is cut into pieces."""
+    ri = __import__("importlib").import_module("daisi-llogos_b200.weights.random_init")
+    assert ri.splitmix64(0) == 0xE220A8397B1DCDAF
+    assert ri.fnv1a64("") == 0xCBF29CE484222325 and ri.fnv1a64("a") == 0xAF63DC4C8601EC8C
+    key = ri.tensor_key(7, "model.embed_tokens.weight")
+    assert key != ri.tensor_key(8, "model.embed_tokens.weight") != ri.tensor_key(7, "model.norm.weight")
+    v = ri.normal_values(key, 200000, 0.0, 1.0)
+    assert v.dtype.name == "float32" and abs(float(v.mean())) < 0.01 and abs(float(v.std()) - 1.0) < 0.01
+    assert abs(float((v ** 3).mean())) < 0.03 and abs(float((v ** 4).mean()) - 3.0) < 0.1
+    part = ri.normal_values(key, 1000, 0.0, 1.0, start=150000)
+    assert (part == v[150000:151000]).all()
+    shifted = ri.normal_values(key, 1000, 1.0, 0.1)
+    assert abs(float(shifted.mean()) - 1.0) < 0.02
+    decls = {"a.weight": llogos.parts.TensorDecl((5, 8)), "a.norm": llogos.parts.TensorDecl((8,), "norm")}
+    t1 = llogos.weights.random_tensors(decls, 3, std=0.5, norm_std=0.1)
+    t2 = llogos.weights.random_tensors(dict(reversed(list(decls.items()))), 3, std=0.5, norm_std=0.1)
+    assert torch.equal(t1["a.weight"], t2["a.weight"]) and torch.equal(t1["a.norm"], t2["a.norm"])
+    assert t1["a.weight"].dtype == torch.bfloat16 and abs(float(t1["a.norm"].float().mean()) - 1.0) < 0.2
 
 
 def test_missing_bias_when_config_wants_it(llogos, model_dirs, tmp_path):

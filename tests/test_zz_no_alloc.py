@@ -14,6 +14,8 @@ import math
 import pytest
 import torch
 
+import plain_model as P
+
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 MAX_FLOATS = 1 << 20
@@ -45,6 +47,29 @@ def _case(seed, dtype, lens, nh, nkv, hd, n_pages=48, ring=8):
     return [t.to(DEV) for t in (q, kp, vp, table, slots, lb)]
 
 
+def plain_decode(q, kp, vp, table, slots, lb, scale, window):
+    """What the entry point has to give, from the plain attention of whole sequences: the keys and values of
+    sequence b are gathered from its pages in position order (position p lies in page ``table[slot][(p // 64)
+    % ring]`` at row ``p % 64``), the new token's query is the last row, and the last row of the plain causal
+    attention (with the window, if any) is the answer."""
+    q, kp, vp = q.cpu().double(), kp.cpu().double(), vp.cpu().double()
+    table, slots, lb = table.cpu(), slots.cpu().tolist(), lb.cpu().tolist()
+    nh, hd = q.shape[1], q.shape[2]
+    ring = table.shape[1]
+    out = torch.zeros(q.shape[0], nh * hd, dtype=torch.float64)
+    for b, (slot, before) in enumerate(zip(slots, lb)):
+        n = before + 1
+        first = max(0, n - window) if window > 0 else 0          # earlier keys are outside the window anyway
+        pos = list(range(first, n))
+        pages = [int(table[slot, (p // 64) % ring]) for p in pos]
+        k = torch.stack([kp[pg, :, p % 64] for pg, p in zip(pages, pos)])
+        v = torch.stack([vp[pg, :, p % 64] for pg, p in zip(pages, pos)])
+        qs = torch.zeros(len(pos), nh, hd, dtype=torch.float64)
+        qs[-1] = q[b]
+        out[b] = P.attention(qs, k, v, scale, window)[-1].reshape(-1)
+    return out
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_matches_the_ordinary_entry_point_twice_in_a_row(dtype):
     ops = importlib.import_module("daisi-llogos_b200.kernels.ops")
@@ -67,6 +92,34 @@ def test_matches_the_ordinary_entry_point_twice_in_a_row(dtype):
         torch.cuda.synchronize()
         err = float((got.double() - want.double()).abs().max())
         assert err <= tol * max(1.0, float(want.double().abs().max())), (seed, err)
+        # and against the plain formula, which shares nothing with either entry point
+        plain = plain_decode(q, kp, vp, table, slots, lb, scale, window)
+        err = float((got.double().cpu() - plain).abs().max())
+        assert err <= tol * max(1.0, float(plain.abs().max())), (seed, "plain", err)
+
+
+def test_a_request_that_fills_the_array_exactly_runs():
+    """8 sequences x 32 heads x 64 splits x (62 + 2) floats are the array's 1,048,576 floats to the last one;
+    most sequences have fewer key tiles than splits, so many splits stay empty."""
+    lib, fn = _library()
+    lens, nh, nkv, hd, splits = [1500, 70, 1, 129, 640, 64, 65, 900], 32, 8, 62, 64
+    assert len(lens) * nh * splits * (hd + 2) == MAX_FLOATS
+    q, kp, vp, table, slots, lb = _case(4, torch.float32, lens, nh, nkv, hd, n_pages=64, ring=24)
+    scale = 1 / math.sqrt(hd)
+    got = torch.full((len(lens), nh * hd), float("nan"), device=DEV)
+    rc = fn(q.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), table.shape[1], table.shape[1],
+            slots.data_ptr(), lb.data_ptr(), got.data_ptr(), 0, len(lens), nh, nkv, hd, splits, scale, 0,
+            torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.llg_last_error()
+    torch.cuda.synchronize()
+    plain = plain_decode(q, kp, vp, table, slots, lb, scale, 0)
+    err = float((got.double().cpu() - plain).abs().max())
+    assert err <= 2e-5 * max(1.0, float(plain.abs().max())), err
+    # one split more is one float too many
+    rc = fn(q.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), table.shape[1], table.shape[1],
+            slots.data_ptr(), lb.data_ptr(), got.data_ptr(), 0, len(lens), nh, nkv, hd, splits + 1, scale, 0,
+            torch.cuda.current_stream().cuda_stream)
+    assert rc != 0 and "1048576" in lib.llg_last_error().decode()
 
 
 def test_refuses_more_than_its_array_holds():
