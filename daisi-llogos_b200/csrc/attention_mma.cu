@@ -108,6 +108,16 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 2^d for a whole number d <= 0 (or -inf), exactly.
+__device__ __forceinline__ float pow2_whole(float d) {
+  return d < -126.f ? 0.f : __int_as_float((127 + (int)d) << 23);
+}
+
+// The running maximum of a softmax row is kept in the exponent's own unit (score * scale * log2 e) and rounded
+// up to a whole number M.  The weights are then 2^(x - M), rescaling between two maxima multiplies by an exact
+// power of two, and rounding a weight to bfloat16 gives the same bits whatever M was when the weight was made:
+// how the keys are cut into tiles, warps, blocks or steps does not show in the rounded weights.
+
 // ---- prompt steps --------------------------------------------------------------------------------
 
 // EXACT: the head size is HDMAX itself, known at compile time (all offsets become constants)
@@ -264,12 +274,12 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
     for (int r = 0; r < 2; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float m_new = fmaxf(m[r], mx[r]);
-      corr[r] = (m_new == -INFINITY) ? 1.f : fast_exp2((m[r] - m_new) * sc);
+      const float m_new = fmaxf(m[r], ceilf(mx[r] * sc));
+      corr[r] = (m_new == -INFINITY) ? 1.f : pow2_whole(m[r] - m_new);
       m[r] = m_new;
       l[r] *= corr[r];
     }
-    const float ms0 = (m[0] == -INFINITY) ? 0.f : m[0] * sc, ms1 = (m[1] == -INFINITY) ? 0.f : m[1] * sc;
+    const float ms0 = (m[0] == -INFINITY) ? 0.f : m[0], ms1 = (m[1] == -INFINITY) ? 0.f : m[1];
 #pragma unroll
     for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -549,15 +559,15 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 4));
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
         mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
-        const float m_new = fmaxf(m[c], mx[c]);
-        corr[c] = (m_new == -INFINITY) ? 1.f : fast_exp2((m[c] - m_new) * sc);
+        const float m_new = fmaxf(m[c], ceilf(mx[c] * sc));
+        corr[c] = (m_new == -INFINITY) ? 1.f : pow2_whole(m[c] - m_new);
         m[c] = m_new;
       }
       float pv[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int c = e & 1;
-        pv[e] = (m[c] == -INFINITY) ? 0.f : fast_exp2((sv[e] - m[c]) * sc);
+        pv[e] = (m[c] == -INFINITY) ? 0.f : fast_exp2(fmaf(sv[e], sc, -m[c]));
       }
       l[0] = l[0] * corr[0] + pv[0] + pv[2];
       l[1] = l[1] * corr[1] + pv[1] + pv[3];
@@ -618,7 +628,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
       float L = 0.f, scw[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        scw[w] = (mw[w] == -INFINITY) ? 0.f : fast_exp2((mw[w] - M) * sc);
+        scw[w] = (mw[w] == -INFINITY) ? 0.f : pow2_whole(mw[w] - M);
         L += scw[w] * merge[(w * GH + row) * (hd + 2) + hd + 1];
       }
       const int head = kvh * G + g0 + row;
@@ -630,9 +640,8 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
         a.part_o[pidx * hd + d] = acc;
       }
       if (lane == 0) {
-        // the running maximum is kept in units of the raw score; the reduce kernel works with
-        // natural exponentials of (m * scale), so hand it the scaled value
-        a.part_ml[pidx * 2] = (M == -INFINITY) ? -INFINITY : M * a.scale;
+        // the running maximum is a whole number of binary orders; the join works with natural exponentials
+        a.part_ml[pidx * 2] = (M == -INFINITY) ? -INFINITY : M * 0.6931471805599453f;
         a.part_ml[pidx * 2 + 1] = L;
       }
     }

@@ -54,6 +54,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 2^d for a whole number d <= 0 (or -inf), exactly.
+__device__ __forceinline__ float pow2_whole(float d) {
+  return d < -126.f ? 0.f : __int_as_float((127 + (int)d) << 23);
+}
+
 // the largest of three (one instruction on sm_100)
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -479,10 +484,12 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
     const uint32_t lane_base = tmem + g * G_COLS + ((uint32_t)(gw * 32) << 16);
     const int n_tiles = ti.n_tiles[g], pos0 = ti.pos0[g];
     const float sc = a.scale * LOG2E;
-    // A row's exponentials use its maximum so far, which is raised only when a tile exceeds it by more than
-    // 2^8 in the weights: the weights stay below 2^8 and the accumulator is rescaled rarely.  The common
-    // factor cancels in the final division.
-    const float raise_by = 8.0f / sc;
+    // A row's weights are 2^(x - M) with x = score * scale * log2 e and M a whole number that is raised (to the
+    // tile's maximum, rounded up) only when a tile exceeds it by more than 8: the weights stay below 2^8 and the
+    // accumulator is rescaled rarely, by an exact power of two.  The common factor cancels in the final division,
+    // and rounding a weight to bfloat16 gives the same bits whatever M was: how the keys are cut into tiles or
+    // steps does not show in the rounded weights.
+    const float raise_by = 8.0f;
     const int qpos = pos0 + r;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -527,10 +534,11 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
         for (int k = 0; k < 4; ++k) mx4[k] = max3(mx4[k], sv[c + 2 * k], sv[c + 2 * k + 1]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const bool raise = mx > m_run + raise_by || m_run == -INFINITY;
-      const float m_new = raise ? fmaxf(m_run, mx) : m_run;
-      const float corr = (!raise || m_new == -INFINITY) ? 1.f : fast_exp2((m_run - m_new) * sc);
-      const float ms = (m_new == -INFINITY) ? 0.f : m_new * sc;
+      const float mxs = mx * sc;
+      const bool raise = mxs > m_run + raise_by || m_run == -INFINITY;
+      const float m_new = raise ? fmaxf(m_run, ceilf(mxs)) : m_run;
+      const float corr = (!raise || m_new == -INFINITY) ? 1.f : pow2_whole(m_run - m_new);
+      const float ms = (m_new == -INFINITY) ? 0.f : m_new;
       m_run = m_new;
       // two elements per instruction where the arithmetic allows it (fma.rn.f32x2, add.rn.f32x2); the
       // weights go straight into the tile's P buffer, which the product of two tiles ago has left

@@ -1,10 +1,21 @@
 """How the GPU tests judge logits against the plain implementation.
 
 float32: every logit within 2e-5 of the request's largest |logit| of the plain model.
-bfloat16: two lines.  Against the plain model that rounds to bfloat16 where the engine does
-(``plain_model.forward(..., rounded=True)``) the bound is 1e-2 of the largest |logit|: what remains
-between the two is the order of the sums and a softmax weight rounded on the other side of a tie.
-Against the exact plain model the looser 4e-2 holds as well, which bounds the rounding noise itself.
+
+bfloat16: against the exact plain model every logit within 4e-2 of the largest |logit| (this bounds the
+rounding noise itself: measured 0.007 to 0.026 on the tiny configurations), and against the plain model
+that rounds to bfloat16 where the engine does (``plain_model.forward(..., rounded=True)``):
+
+* every logit within 1.5e-2 of the largest |logit| (measured: at most 0.0082), and
+* where a check covers 16 positions or more, the root-mean-square error within 8e-3 of the reference's
+  root mean square (measured: at most 0.0054), so that an error of one percent in every logit shows.
+
+What remains between the engine and the rounding plain model is not a rounding that the plain model leaves
+out (one layer of the smallest configuration agrees bit for bit in every intermediate tensor): it is the
+order of the float32 sums.  The tensor cores add with truncation (a product over 4,096 terms is 4e-6 low,
+relative, against 6e-7 for a chain of fused multiply-adds), a value that lies within that distance of a
+bfloat16 tie rounds the other way, and one such value makes a few percent of the values downstream of it
+round the other way too.  Per layer that adds about 1e-3 (root mean square, relative) to the logits.
 The reference compares its backends' logits with 0.001 absolute in float32
 (tests/Daisi.Llogos.Tests/Chat/LayerByLayerCompareTest.cs:110) and below 1.0 for a 16-bit cache
 (tests/Daisi.Llogos.Tests/Inference/LongContextTests.cs:40).
@@ -14,8 +25,10 @@ import torch
 import plain_model as P
 
 TOL_F32 = 2e-5
-TOL_BF16_ROUNDED = 1e-2
+TOL_BF16_ROUNDED = 1.5e-2
+TOL_BF16_ROUNDED_RMS = 8e-3
 TOL_BF16_EXACT = 4e-2
+RMS_ROWS = 16
 
 
 _kept = {}
@@ -55,10 +68,14 @@ class Reference:
         exact = float((got - self.exact[idx]).abs().max()) / self.scale
         if dtype == torch.float32:
             return exact, TOL_F32
-        rounded = float((got - self.rounded[idx]).abs().max()) / self.scale
         if exact > TOL_BF16_EXACT:
             return exact, TOL_BF16_EXACT
-        return rounded, TOL_BF16_ROUNDED
+        ref = self.rounded[idx]
+        if idx.numel() >= RMS_ROWS:
+            rms = float((got - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt())
+            if rms > TOL_BF16_ROUNDED_RMS:
+                return rms, TOL_BF16_ROUNDED_RMS
+        return float((got - ref).abs().max()) / self.scale, TOL_BF16_ROUNDED
 
     def check(self, got, positions, dtype, what=()):
         err, tol = self.errors(got, positions, dtype)

@@ -102,7 +102,10 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, w
     Daisi.Llogos.Cpu/CpuBackend.cs:476-590 (scores :527-537, softmax :540-553, values :556-571);
     window: Inference/AttentionStrategy.cs:64-71.
     ``round_weights``: a rounding applied to the unnormalised softmax weights as they enter the
-    product with the values (the sum that normalises them stays unrounded)."""
+    product with the values (the sum that normalises them stays unrounded).  The weights are then taken
+    as 2^(x - M) with x = score * log2(e) and M the row's largest x rounded up to a whole number: a
+    floating-point rounding gives the same digits for any whole M, so this pins the rounded weights
+    without saying in which order or in how many pieces an engine visits the keys."""
     t, nh, hd = q.shape
     nkv = k.shape[1]
     g = nh // nkv
@@ -115,12 +118,13 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, w
         kh = h // g
         s = (q[:, h, :].to(F64) @ k[:, kh, :].to(F64).t()) * scale
         s = s.masked_fill(~visible, float("-inf"))
-        s = s - s.max(dim=-1, keepdim=True).values
-        p = torch.exp(s)
         if round_weights is None:
+            p = torch.exp(s - s.max(dim=-1, keepdim=True).values)
             p = p / p.sum(dim=-1, keepdim=True)
             out[:, h, :] = p @ v[:, kh, :].to(F64)
         else:
+            x = s * math.log2(math.e)
+            p = torch.exp2(x - torch.ceil(x.max(dim=-1, keepdim=True).values))
             out[:, h, :] = (round_weights(p) @ v[:, kh, :].to(F64)) / p.sum(dim=-1, keepdim=True)
     return out
 

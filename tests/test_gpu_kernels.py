@@ -415,6 +415,70 @@ def test_attention_window_edge(ops, dtype, hd, window, tc, monkeypatch):
         check(out1[0], ref[-1].reshape(-1), dtype, ("decode", splits))
 
 
+@pytest.mark.parametrize("tc", [True, False], ids=["tcgen05", "mma"])
+@pytest.mark.parametrize("hd", [64, 128, 48])
+def test_attention_with_whole_number_scores_rounds_like_the_plain_model(ops, hd, tc, monkeypatch):
+    """Queries and keys of -1, 0 and 1 with a softmax scale of ln 2 give scores that are whole numbers of binary
+    orders, so every softmax weight is a power of two and bfloat16 holds it exactly: the only rounding left is
+    that of the output.  The kernels must then give the plain model's bits, but for the few values that lie
+    within float32 error of a tie (each one unit in the last place off).  A kernel that loses a hundredth of a
+    row's weight, drops a tile or counts a key twice moves nearly every value of the row instead.  Prompt step
+    on cached tokens, then the last token alone with its keys split over blocks in several ways."""
+    if not tc and hd not in (64, 128):
+        pytest.skip("only head sizes 64 and 128 have two tensor-core kernels")
+    monkeypatch.setattr(ops, "USE_TC_PROMPT_ATTENTION", tc)
+    dtype, nh, nkv, before, count = torch.bfloat16, 4, 2, 130, 330
+    total = before + count
+    g = torch.Generator().manual_seed(900 + hd)
+    k = torch.randint(-1, 2, (total, nkv, hd), generator=g).to(dtype)
+    q = torch.randint(-1, 2, (total, nh, hd), generator=g).to(dtype)
+    v = torch.randn(total, nkv, hd, generator=g).to(dtype)
+    scale = math.log(2.0)
+    ref = P.round_bfloat16(P.attention(q, k, v, scale, 0, round_weights=P.round_bfloat16))      # [total, nh, hd]
+
+    def same_bits(got, want, what):
+        got, want = got.detach().cpu().double().reshape(-1), want.reshape(-1)
+        off = (got != want)
+        assert float(off.float().mean()) <= 0.005, (what, "values that differ", int(off.sum()), "of", off.numel())
+        # what differs is one unit in the last place of a bfloat16 value (2^-7 of it, at most); a value that is
+        # small because its terms cancel carries the float32 error of those terms (values are of order one)
+        assert bool(((got - want).abs()[off] <= want.abs()[off] * 2.0 ** -7 + 2e-6).all()), what
+
+    ring = 8
+    table = torch.zeros(2, ring, dtype=torch.int32)
+    table[1] = torch.randperm(ring, generator=g).to(torch.int32)
+    kp = torch.zeros(ring, nkv, 64, hd, dtype=dtype)
+    vp = torch.zeros_like(kp)
+    for j in range(before):
+        kp[int(table[1, j // 64]), :, j % 64] = k[j]
+        vp[int(table[1, j // 64]), :, j % 64] = v[j]
+    tq = ops.prefill_tile_queries(dtype, hd)
+    tiles = torch.tensor([(0, q0) for q0 in range(0, count, tq)], dtype=torch.int32)
+    d = lambda t: t.to(DEV)
+    out = torch.empty(count, nh * hd, dtype=dtype, device=DEV)
+    kpd, vpd = d(kp), d(vp)
+    cu, lb, sl = torch.tensor([0, count], dtype=torch.int32), torch.tensor([before], dtype=torch.int32), torch.tensor([1], dtype=torch.int32)
+    ops.attn_prefill(d(q[before:].contiguous()), d(k[before:].contiguous()), d(v[before:].contiguous()), kpd, vpd, d(table), ring,
+                     d(tiles), d(cu), d(lb), d(sl), out, scale=scale, window=0, tile_queries=tq)
+    same_bits(out, ref[before:], "prompt")
+    ops.kv_write(d(k[before:].contiguous()), d(v[before:].contiguous()), kpd, vpd, d(table), ring,
+                 d(torch.arange(before, total, dtype=torch.int32)), d(torch.zeros(count, dtype=torch.int32)), d(sl), d(cu), d(lb))
+    # the last 24 tokens as a batch of 24 sequences that share the pages (each sees its own length)
+    n_dec = 24
+    qd = q[total - n_dec:].contiguous()
+    slots = torch.ones(n_dec, dtype=torch.int32)
+    lens = torch.arange(total - n_dec, total, dtype=torch.int32)             # keys before the token
+    counters = torch.zeros(n_dec * nkv, dtype=torch.int32, device=DEV)
+    for splits, balance in ((1, False), (3, False), (8, True)):
+        out1 = torch.empty(n_dec, nh * hd, dtype=dtype, device=DEV)
+        scratch = torch.empty(ops.attn_decode_scratch_floats(n_dec, nh, hd, splits), device=DEV)
+        ops.attn_decode(d(qd), kpd, vpd, d(table), ring, d(slots), d(lens), out1, scratch, n_splits=splits, scale=scale,
+                        window=0, counters=counters, balance=balance)
+        same_bits(out1, ref[total - n_dec:], ("decode", splits, balance))
+    if tc:
+        assert ops.attn_tc_status() == 0
+
+
 def test_kernels_refuse_what_they_cannot_do(ops):
     q = torch.zeros(1, 2, 272, device=DEV)
     kp = torch.zeros(1, 1, 64, 272, device=DEV)

@@ -539,7 +539,7 @@ def test_borrowed_cache_with_a_window(llogos, tmp_path):
                "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16, "intermediate_size": 80,
                "vocab_size": 99, "rope_theta": 777.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 512}
         d = str(tmp_path / "ring")
-        llogos.weights.write_random_model(d, cfg, seed=12, std=0.25, norm_std=0.1)
+        llogos.weights.write_random_model(d, cfg, seed=12, std=0.15, norm_std=0.1)
         w = read_weights(llogos, d)
         assert "model.layers.1.self_attn.k_proj.weight" not in w
 

@@ -184,4 +184,4 @@ def test_random_cuts_and_batches(llogos, model_dirs, name, dtype):
             if live[i][1] == len(seqs[i]):
                 eng.close(live.pop(i)[0])
         eng.cache.audit()
-    assert eng.cache.slots.free_count == 4 and n_steps > 20
+    assert eng.cache.slots.free_count == 4 and n_steps >= 10
