@@ -33,6 +33,7 @@ SOURCES: Dict[str, List[str]] = {
     "attention_simt": ["attention_simt.cu", "common.cuh", "attention_noalloc.h"],
     "attention_mma": ["attention_mma.cu", "common.cuh"],
     "attention_tc": ["attention_tc.cu", "common.cuh"],
+    "attention_decode_tma": ["attention_decode_tma.cu", "common.cuh"],
     "sampling": ["sampling.cu", "common.cuh"],
     "init": ["init.cu", "common.cuh"],
 }

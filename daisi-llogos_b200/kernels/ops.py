@@ -112,6 +112,14 @@ class _DecodeArgs(Structure):
     ]
 
 
+class _DecodeTmaArgs(Structure):
+    _fields_ = [
+        ("q", c_void_p), ("page_table", c_void_p), ("table_width", c_int), ("ring_pages", c_int),
+        ("slots", c_void_p), ("len_before", c_void_p), ("part", c_void_p), ("counters", c_void_p), ("out", c_void_p),
+        ("n_seqs", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("scale", c_float), ("window", c_int),
+    ]
+
+
 class _SampleArgs(Structure):
     _fields_ = [
         ("logits", c_void_p), ("work", c_void_p), ("out", c_void_p), ("probs_out", c_void_p),
@@ -179,6 +187,12 @@ def _load_lib(name: str):
         lib.llg_attn_tc_supported.argtypes = [c_int]
         lib.llg_attn_prefill_tc.argtypes = [POINTER(_PrefillArgs), c_void_p]
         lib.llg_attn_tc_status.restype = c_int
+    elif name == "attention_decode_tma":
+        lib.llg_attn_decode_tma_supported.argtypes = [c_int, c_int, c_int, c_int]
+        lib.llg_attn_decode_tma_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        lib.llg_attn_decode_tma_scratch_floats.restype = c_longlong
+        lib.llg_attn_decode_tma.argtypes = [POINTER(_DecodeTmaArgs), c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.llg_attn_decode_tma_status.restype = c_int
     elif name == "init":
         lib.llg_fill_normal.argtypes = [c_void_p, c_int, c_longlong, c_ulonglong, ctypes.c_double, ctypes.c_double, c_void_p]
         lib.llg_fill.argtypes = [c_void_p, c_int, c_longlong, c_float, c_void_p]
@@ -459,40 +473,129 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
         _check(lib, lib.llg_attn_prefill_simt(byref(a), _dt(q), _stream()))
 
 
+USE_TMA_DECODE_ATTENTION = True     # tests switch it off to reach the cp.async kernel at head sizes 64 and 128
+
+
+def _use_tma_decode(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int, n_seqs: int) -> bool:
+    """bfloat16 decode attention with a geometry the TMA kernel takes (csrc/attention_decode_tma.cu)."""
+    return (USE_TMA_DECODE_ATTENTION and dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv_heads > 0
+            and n_heads % n_kv_heads == 0 and n_heads // n_kv_heads <= 8 and n_seqs <= 1024)
+
+
+class DecodePlan:
+    """How ``attn_decode`` will run for one batch shape: which kernel, how the keys are split over blocks, and what
+    scratch it wants.  Made by ``attn_decode_plan``; callers only read ``scratch_floats`` and ``n_counters``."""
+
+    def __init__(self, kind: str, n_splits: int, balance: bool, max_len: int, scratch_floats: int, n_counters: int):
+        self.kind, self.n_splits, self.balance, self.max_len = kind, n_splits, balance, max_len
+        self.scratch_floats, self.n_counters = scratch_floats, n_counters
+
+
+def _splits_for(n_seqs: int, n_kv_heads: int, max_len: int, n_sms: int, blocks_per_sm: int = 2) -> int:
+    """How many blocks share one (sequence, key/value head) in the kernels that take one split count for all.
+
+    With ``pairs = n_seqs * n_kv_heads`` and ``tiles`` 64-key tiles per sequence, ``s`` splits run in
+    ``ceil(pairs * s / resident blocks)`` rounds of ``ceil(tiles / s)`` tiles each; the ``s`` with
+    the least rounds x tiles wins (the smallest on ties), so that no nearly empty last round of
+    blocks doubles the time."""
+    pairs = max(1, n_seqs * n_kv_heads)
+    tiles = max(1, -(-max_len // PAGE))
+    resident = blocks_per_sm * n_sms
+    best, best_cost = 1, None
+    for s in range(1, min(64, tiles) + 1):
+        cost = -(-pairs * s // resident) * (-(-tiles // s) + 3)     # + 3: prologue and join of a block
+        if best_cost is None or cost < best_cost:
+            best, best_cost = s, cost
+    return best
+
+
+def attn_decode_plan(dtype: torch.dtype, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, max_len: int) -> DecodePlan:
+    """The plan for a batch of ``n_seqs`` sequences of at most ``max_len`` keys (the new token's included).
+
+    bfloat16 at head sizes 64 / 128: the TMA kernel, which balances the work itself from the lengths it finds on
+    the device.  Other multiples of 16 up to 128: the mma.sync kernel with a split count from ``max_len`` (per
+    sequence by its length for small batches).  Everything else: the CUDA-core kernel."""
+    if _use_tma_decode(dtype, head_dim, n_heads, n_kv_heads, n_seqs):
+        lib = _lib("attention_decode_tma")
+        floats = lib.llg_attn_decode_tma_scratch_floats(n_seqs, n_heads, n_kv_heads, head_dim, max_len)
+        return DecodePlan("tma", 0, False, max_len, int(floats), n_seqs * n_heads)
+    n_sms = sm_count()
+    splits = _splits_for(n_seqs, n_kv_heads, max_len, n_sms)
+    mma = _use_mma(dtype, head_dim)
+    # Sequences of unequal lengths: the kernel gives each as many splits as its length calls for, up to what
+    # one long sequence among short ones could use (the blocks the GPU holds, less one per other pair).
+    balance = mma and 1 < n_seqs <= 32 and n_seqs * n_kv_heads <= attn_decode_balance_pairs()
+    if balance:
+        tiles = max(1, -(-max_len // PAGE))
+        splits = max(splits, min(64, tiles, 2 * n_sms // n_kv_heads - (n_seqs - 1)))
+    return DecodePlan("mma" if mma else "simt", splits, balance, max_len,
+                      attn_decode_scratch_floats(n_seqs, n_heads, head_dim, splits), n_seqs * n_kv_heads if mma else 0)
+
+
 def attn_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
-    """Floats of scratch ``attn_decode`` needs for the partial results of its key splits."""
+    """Floats of scratch the split kernels need for the partial results of ``n_splits`` key splits."""
     return n_seqs * n_heads * n_splits * (head_dim + 2)
 
 
 def attn_decode_balance_pairs() -> int:
-    """Most (sequence, key/value head) pairs for which decode attention balances its splits by length: half the
-    blocks of that kernel that the GPU holds at once (two per multiprocessor)."""
+    """Most (sequence, key/value head) pairs for which the mma.sync decode kernel balances its splits by length: half
+    the blocks of that kernel that the GPU holds at once (two per multiprocessor)."""
     return sm_count()
 
 
 def attn_decode_uses_counters(dtype: torch.dtype, head_dim: int) -> bool:
-    """Whether ``attn_decode`` wants ``counters`` (the tensor-core kernel joins its splits itself)."""
+    """Whether the split kernels want ``counters`` (the tensor-core kernel joins its splits itself)."""
     return _use_mma(dtype, head_dim)
 
 
-def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
-                n_splits: int, scale: float, window: int, counters: Optional[torch.Tensor] = None,
-                balance: bool = False) -> None:
-    """Attention of one new token per sequence over the cache; ``scratch`` holds the split partials.
+def attn_decode_tma_status() -> int:
+    """Error code the TMA decode attention recorded when a wait ran out (0 = none); synchronises."""
+    return _lib("attention_decode_tma").llg_attn_decode_tma_status()
 
-    The tensor-core kernel also needs ``counters``: ``n_seqs * n_kv_heads`` int32, zero when first used
-    (the kernel leaves them zero), through which the last block of a sequence joins the splits.
-    ``balance`` (tensor-core kernel, at most ``attn_decode_balance_pairs()`` (sequence, kv head) pairs):
+
+def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
+                scale: float, window: int, plan: Optional[DecodePlan] = None, n_splits: int = 0,
+                counters: Optional[torch.Tensor] = None, balance: bool = False) -> None:
+    """Attention of one new token per sequence over the cache; ``scratch`` holds the partial results.
+
+    With ``plan`` (from ``attn_decode_plan`` for this batch shape) the kernel is the plan's.  Without it the
+    caller names ``n_splits`` (and ``balance``) and gets the mma.sync kernel (bfloat16, head sizes in steps of 16
+    up to 128) or the CUDA-core kernel.
+
+    The tensor-core kernels need ``counters`` (``plan.n_counters``, or ``n_seqs * n_kv_heads`` without a plan):
+    int32, zero when first used (the kernels leave them zero), through which the last block of a sequence joins
+    the partial results.
+    ``balance`` (mma.sync kernel, at most ``attn_decode_balance_pairs()`` (sequence, kv head) pairs):
     ``n_splits`` is the most splits a sequence may have; each gets as many as its length calls for."""
     b, nh, hd = q.shape
     nkv = k_pages.shape[1]
     if scale <= 0:
         raise KernelError("attn_decode: the softmax scale must be positive")
+    if scratch.dtype != torch.float32:
+        raise KernelError("attn_decode: the scratch must be float32")
+    if plan is not None and plan.kind == "tma":
+        lib = _lib("attention_decode_tma")
+        if scratch.numel() < plan.scratch_floats:
+            raise KernelError(f"attn_decode: scratch of {scratch.numel()} floats, {plan.scratch_floats} needed")
+        if counters is None or counters.numel() < b * nh:
+            raise KernelError(f"attn_decode: needs {b * nh} zeroed int32 counters")
+        a = _DecodeTmaArgs()
+        a.q = _ptr(q, torch.bfloat16)
+        a.page_table, a.table_width, a.ring_pages = _ptr(page_table, torch.int32), page_table.shape[1], ring_pages
+        a.slots, a.len_before = _ptr(slots, torch.int32), _ptr(len_before, torch.int32)
+        a.part, a.counters, a.out = _ptr(scratch), _ptr(counters, torch.int32), _ptr(out, torch.bfloat16)
+        a.n_seqs, a.nh, a.nkv, a.hd = b, nh, nkv, hd
+        a.scale, a.window = float(scale), int(window)
+        _check(lib, lib.llg_attn_decode_tma(byref(a), _ptr(k_pages, torch.bfloat16), _ptr(v_pages, torch.bfloat16),
+                                            k_pages.shape[0], int(plan.max_len), _stream()))
+        return
+    if plan is not None:
+        n_splits, balance = plan.n_splits, plan.balance
     mma = _use_mma(q.dtype, hd)
     lib = _lib("attention_mma" if mma else "attention_simt")
     need = b * nh * n_splits * (hd + 2)
-    if scratch.numel() < need or scratch.dtype != torch.float32:
-        raise KernelError(f"attn_decode: scratch of {scratch.numel()} floats, {need} needed")
+    if n_splits < 1 or scratch.numel() < need:
+        raise KernelError(f"attn_decode: {n_splits} splits, scratch of {scratch.numel()} floats, {need} needed")
     a = _DecodeArgs()
     a.q, a.k_pages, a.v_pages = _ptr(q), _ptr(k_pages, q.dtype), _ptr(v_pages, q.dtype)
     a.page_table, a.table_width, a.ring_pages = _ptr(page_table, torch.int32), page_table.shape[1], ring_pages

@@ -18,24 +18,6 @@ from ..kernels.linear import linear
 from .base import Branch, KvNeed, Mixer, TensorDecl, register_part
 
 
-def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int, n_sms: int, blocks_per_sm: int = 2) -> int:
-    """How many blocks share one (sequence, key/value head) in decode attention.
-
-    With ``pairs = n_seqs * n_kv_heads`` and ``tiles`` 64-key tiles per sequence, ``s`` splits run in
-    ``ceil(pairs * s / resident blocks)`` rounds of ``ceil(tiles / s)`` tiles each; the ``s`` with
-    the least rounds x tiles wins (the smallest on ties), so that no nearly empty last round of
-    blocks doubles the time."""
-    pairs = max(1, n_seqs * n_kv_heads)
-    tiles = max(1, -(-max_len // 64))
-    resident = blocks_per_sm * n_sms
-    best, best_cost = 1, None
-    for s in range(1, min(64, tiles) + 1):
-        cost = -(-pairs * s // resident) * (-(-tiles // s) + 3)     # + 3: prologue and join of a block
-        if best_cost is None or cost < best_cost:
-            best, best_cost = s, cost
-    return best
-
-
 class Attention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, qkv_bias, qk_norm, qk_norm_eps,
     window (0 = all keys), position (name of a position encoding or None), softmax_scale
@@ -135,22 +117,15 @@ class Attention(Mixer):
                             seq_of_token=ctx.seq_of_token, slots=ctx.slots)
             else:
                 ops.qk_prep(qkv, **common)
-            n_sms = ops.sm_count()
-            splits = decode_splits(ctx.n_seqs, self.nkv, ctx.max_len_after, n_sms)
-            # Sequences of unequal lengths: the kernel gives each as many splits as its length calls for, up to what
-            # one long sequence among short ones could use (the blocks the GPU holds, less one per other pair).
-            balance = 1 < ctx.n_seqs <= 32 and ctx.n_seqs * self.nkv <= ops.attn_decode_balance_pairs()
-            if balance:
-                tiles = max(1, -(-ctx.max_len_after // 64))
-                splits = max(splits, min(64, tiles, 2 * n_sms // self.nkv - (ctx.n_seqs - 1)))
-            scratch = ctx.buffer("attn.scratch", (ops.attn_decode_scratch_floats(n, self.nh, self.hd, splits),),
-                                 torch.float32)
+            # which kernel runs and how it splits the keys is the kernels' business: the plan says what scratch it wants
+            plan = ops.attn_decode_plan(q.dtype, ctx.n_seqs, self.nh, self.nkv, self.hd, ctx.max_len_after)
+            scratch = ctx.buffer("attn.scratch", (max(1, plan.scratch_floats),), torch.float32)
             counters = None
-            if ops.attn_decode_uses_counters(q.dtype, self.hd):
-                counters = ctx.buffer("attn.counters", (n * self.nkv,), torch.int32, zero=True)
+            if plan.n_counters:
+                counters = ctx.buffer("attn.counters", (plan.n_counters,), torch.int32, zero=True)
             ops.attn_decode(q, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages, ctx.slots,
-                            ctx.len_before, out, scratch, n_splits=splits, scale=self.scale, window=self.window,
-                            counters=counters, balance=balance)
+                            ctx.len_before, out, scratch, scale=self.scale, window=self.window, plan=plan,
+                            counters=counters)
         else:
             # A group that keeps every key can take the step's keys and values into its pages right away
             # (the step reads them from the packed buffer, never from the pages).  A ring must wait until

@@ -169,20 +169,16 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
                 o[t, h] = _attend(q[t, h], torch.stack(ks), torch.stack(vs), scale).to(out.dtype)
 
 
-def attn_decode_scratch_floats(n_seqs, n_heads, head_dim, n_splits):
-    return n_seqs * n_heads * n_splits * (head_dim + 2)
+class _Plan:
+    scratch_floats, n_counters = 1, 0
 
 
-def attn_decode_uses_counters(dtype, head_dim):
-    return False
+def attn_decode_plan(dtype, n_seqs, n_heads, n_kv_heads, head_dim, max_len):
+    return _Plan()
 
 
-def attn_decode_balance_pairs():
-    return 148
-
-
-def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *, n_splits,
-                scale, window, counters=None, balance=False):
+def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
+                scale, window, plan=None, n_splits=0, counters=None, balance=False):
     b_n, nh, hd = q.shape
     nkv = k_pages.shape[1]
     g = nh // nkv

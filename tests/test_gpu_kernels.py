@@ -253,6 +253,84 @@ def test_attn_decode(ops, dtype, nh, nkv, hd, window):
             qq[-1] = q[b]
             ref = P.attention(qq, ks[b], vs[b], scale, window)[-1].reshape(-1)
             check(out[b], ref, dtype, (b, n, splits))
+    # and as the engine calls it: the kernels' own plan for this batch (the TMA kernel where it applies)
+    plan = ops.attn_decode_plan(dtype, len(lens), nh, nkv, hd, max(lens))
+    out = torch.full((len(lens), nh * hd), float("nan"), dtype=dtype, device=DEV)
+    scratch = torch.empty(max(1, plan.scratch_floats), device=DEV)
+    counters = torch.zeros(max(1, plan.n_counters), dtype=torch.int32, device=DEV)
+    ops.attn_decode(q.to(DEV), kp.to(DEV), vp.to(DEV), table.to(DEV), ring, slots.to(DEV), lb.to(DEV), out,
+                    scratch, scale=scale, window=window, plan=plan, counters=counters)
+    assert int(counters.abs().sum()) == 0
+    for b, n in enumerate(lens):
+        qq = torch.zeros(n, nh, hd, dtype=dtype)
+        qq[-1] = q[b]
+        ref = P.attention(qq, ks[b], vs[b], scale, window)[-1].reshape(-1)
+        check(out[b], ref, dtype, (b, n, plan.kind))
+    if plan.kind == "tma":
+        assert ops.attn_decode_tma_status() == 0
+
+
+def _one_query(q, k, v, scale):
+    """softmax(k q * scale) v for one query of one head, in float64 (the plain formula of
+    Daisi.Llogos.Cpu/CpuBackend.cs:527-571 for a single row)."""
+    s = (k.double() @ q.double()) * scale
+    p = torch.exp(s - s.max())
+    return (p / p.sum()) @ v.double()
+
+
+@pytest.mark.parametrize("seed,n_seqs,nh,nkv,hd,window,longest", [
+    (1, 1, 8, 8, 128, 0, 5000), (2, 3, 32, 8, 128, 0, 3000), (3, 40, 8, 2, 64, 0, 900), (4, 200, 4, 1, 128, 0, 300),
+    (5, 7, 16, 2, 64, 200, 2500), (6, 64, 6, 6, 128, 100, 400), (7, 2, 5, 5, 64, 0, 70), (8, 300, 2, 2, 64, 0, 130)])
+def test_attn_decode_tma_cuts_any_batch_evenly(ops, seed, n_seqs, nh, nkv, hd, window, longest):
+    """The TMA kernel cuts the list of (sequence, key/value head, tile) units into equal runs per block, wherever
+    the cuts fall: batches of one to hundreds of sequences with lengths from 1 to thousands of keys (so that some
+    pairs are spread over dozens of blocks and some blocks hold dozens of pairs), pages in scrambled order, a
+    window, twice in a row over the same counters and scratch."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(seed)
+    lens = [int(x) for x in torch.randint(1, longest + 1, (n_seqs,), generator=g)]
+    lens[0] = longest
+    if n_seqs > 2:
+        lens[1], lens[2] = 1, 64
+    ring = (longest + 63) // 64 if window == 0 else (window + 63) // 64 + 1
+    pages_of = [min((n + 63) // 64, ring) for n in lens]
+    n_pages = sum(pages_of) + 3
+    order = torch.randperm(n_pages, generator=g).tolist()
+    kp = torch.randn(n_pages, nkv, 64, hd, generator=g).to(dtype)
+    vp = torch.randn(n_pages, nkv, 64, hd, generator=g).to(dtype)
+    table = torch.zeros(n_seqs + 2, ring, dtype=torch.int32)
+    slots = torch.randperm(n_seqs + 2, generator=g)[:n_seqs].to(torch.int32)
+    for b in range(n_seqs):
+        for j in range(pages_of[b]):
+            table[slots[b], j] = order.pop()
+    q = torch.randn(n_seqs, nh, hd, generator=g).to(dtype)
+    lb = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    scale = 1 / math.sqrt(hd)
+    plan = ops.attn_decode_plan(dtype, n_seqs, nh, nkv, hd, longest)
+    assert plan.kind == "tma"
+    counters = torch.zeros(plan.n_counters, dtype=torch.int32, device=DEV)
+    scratch = torch.full((plan.scratch_floats,), float("nan"), device=DEV)
+    d = lambda t: t.to(DEV)
+    kpd, vpd, qd, td, sd, lbd = d(kp), d(vp), d(q), d(table), d(slots), d(lb)
+    outs = []
+    for rep in range(2):
+        out = torch.full((n_seqs, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        ops.attn_decode(qd, kpd, vpd, td, ring, sd, lbd, out, scratch, scale=scale, window=window, plan=plan, counters=counters)
+        outs.append(out.cpu())
+        assert int(counters.abs().sum()) == 0
+    assert ops.attn_decode_tma_status() == 0
+    assert torch.equal(outs[0], outs[1])                                   # sums run in a fixed order
+    grp = nh // nkv
+    for b in [0, 1, 2, n_seqs // 2, n_seqs - 1] if n_seqs > 4 else range(n_seqs):
+        n = lens[b]
+        first = max(0, n - window) if window > 0 else 0
+        pos = torch.arange(first, n)
+        pg = table[slots[b]][(pos // 64) % ring].long()
+        for h in range(nh):
+            k, v = kp[pg, h // grp, pos % 64], vp[pg, h // grp, pos % 64]
+            check(outs[0][b].view(nh, hd)[h], _one_query(q[b, h], k, v, scale), dtype, (seed, b, n, h))
+    # every row is a number: no pair was left out
+    assert bool(torch.isfinite(outs[0].float()).all())
 
 
 @pytest.mark.parametrize("tc", [True, False], ids=["tcgen05", "mma"])
@@ -413,6 +491,11 @@ def test_attention_window_edge(ops, dtype, hd, window, tc, monkeypatch):
                         out1, scratch, n_splits=splits, scale=1.0, window=window,
                         counters=torch.zeros(nkv, dtype=torch.int32, device=DEV))
         check(out1[0], ref[-1].reshape(-1), dtype, ("decode", splits))
+    plan = ops.attn_decode_plan(dtype, 1, nh, nkv, hd, total)
+    ops.attn_decode(d(q[-1:].contiguous()), kpd, vpd, d(table), ring, d(sl), d(torch.tensor([total - 1], dtype=torch.int32)),
+                    out1, torch.empty(max(1, plan.scratch_floats), device=DEV), scale=1.0, window=window, plan=plan,
+                    counters=torch.zeros(max(1, plan.n_counters), dtype=torch.int32, device=DEV))
+    check(out1[0], ref[-1].reshape(-1), dtype, ("decode", plan.kind))
 
 
 @pytest.mark.parametrize("tc", [True, False], ids=["tcgen05", "mma"])
@@ -475,6 +558,12 @@ def test_attention_with_whole_number_scores_rounds_like_the_plain_model(ops, hd,
         ops.attn_decode(d(qd), kpd, vpd, d(table), ring, d(slots), d(lens), out1, scratch, n_splits=splits, scale=scale,
                         window=0, counters=counters, balance=balance)
         same_bits(out1, ref[total - n_dec:], ("decode", splits, balance))
+    plan = ops.attn_decode_plan(dtype, n_dec, nh, nkv, hd, total)
+    out1 = torch.empty(n_dec, nh * hd, dtype=dtype, device=DEV)
+    ops.attn_decode(d(qd), kpd, vpd, d(table), ring, d(slots), d(lens), out1,
+                    torch.empty(max(1, plan.scratch_floats), device=DEV), scale=scale, window=0, plan=plan,
+                    counters=torch.zeros(max(1, plan.n_counters), dtype=torch.int32, device=DEV))
+    same_bits(out1, ref[total - n_dec:], ("decode", plan.kind))
     if tc:
         assert ops.attn_tc_status() == 0
 
