@@ -11,6 +11,13 @@ from the arrival of the tokens; ``whole_call_tokens_per_s`` is the rate over all
 ``prefill`` is one prompt of 2,048 tokens; ``roofline`` relates the decode step to the bytes it has
 to read; ``points`` holds decode at batch 1 and 64.  Every step reads far more than the 126 MB of
 L2 (16 GB of weights plus the cache), so no L2 flush is needed between steps.
+
+``points`` also holds the three workloads the metric is quoted on, as they are written, each through the Python
+entry point (prompts really run, every step sampled): ``llama8b_b8_ragged_to_8192`` (8 prompts of 128 to 2,048
+tokens decoded until each holds 8,192), ``qwen3_8b_b16_256steps_greedy`` / ``..._t0.7`` (16 prompts of 64 to 4,096
+tokens, 256 steps) and ``qwen25_14b_b32_128steps`` (32 prompts of 256 to 8,192 tokens, 128 greedy steps); each gives
+decoded tokens per second over the whole run and the mean fraction of the copy bandwidth that the bytes of its decode
+steps stand for.  ``--no-workloads`` leaves them out.
 """
 import argparse
 import json
@@ -51,7 +58,7 @@ PREFILL_TOKENS = 2048
 
 
 def peaks():
-    """Measured peaks if the driver wrote them, else the pool's earlier measurement."""
+    """Measured peaks from MEASURED_PEAKS.json beside this file when it exists, else an earlier measurement of a B200."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     out = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
     if os.path.isfile(path):
@@ -127,6 +134,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--no-workloads", action="store_true", help="leave out the workloads of the other shapes and the ragged run")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -203,6 +211,8 @@ def main():
     prefill = {"value": round(t / (pre_ms / 1e3), 1), "tokens": t, "ms": round(pre_ms, 3),
                "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                "ms_after_idle": round(idle_ms, 3)}
+    if pk.get("bf16_tflops_sustained"):       # back-to-back steps run under the power cap: the sustained figure is their peak
+        prefill["frac_sustained"] = round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops_sustained"] * 1e12), 4)
     print(f"[bench] prefill {prefill}", file=sys.stderr, flush=True)
 
     # ---- decode steps at the context length --------------------------------------------------
@@ -255,9 +265,10 @@ def main():
 
     # ---- the same batch through the Python entry point ----------------------------------------
     e2e = None
+    del engine
+    torch.cuda.empty_cache()
+    api = None
     if not args.no_e2e:
-        del engine
-        torch.cuda.empty_cache()
         api = L.LlogosModel(model, max_context=context, max_batch=args.batch)
         # A request's own prompt (8 x 8k tokens, most of a second at the power cap) leaves the SM clock
         # throttled for the first twenty or so decode steps; they are run untimed, as warm-up steps are,
@@ -282,6 +293,74 @@ def main():
                "whole_call_tokens_per_s": round(r.decode_tokens_per_second, 1),
                "prefill_tokens_per_s": round(r.prefill_tokens_per_second, 1), "decode_steps": r.decode_steps}
         print(f"[bench] e2e {e2e}", file=sys.stderr, flush=True)
+
+    # ---- the workloads as they are written ------------------------------------------------------
+    if not args.no_workloads and not args.no_points and args.shape == "llama-3.1-8b" and args.layers == shape["num_hidden_layers"]:
+        measure = importlib.import_module("daisi-llogos_b200.measure")
+        import random
+
+        def workload(api, tag, lo, hi, batch, *, steps=None, to_context=None, temperature=0.0):
+            rng = random.Random(7)
+            vocab = api.model.spec.vocab_size
+            prompts = [[rng.randrange(vocab) for _ in range(rng.randint(lo, hi))] for _ in range(batch)]
+            n_new = steps if steps is not None else to_context
+            if temperature == 0.0:
+                params = L.GenerationParams.greedy_params(n_new, stop_tokens=())
+            else:
+                params = L.GenerationParams(max_tokens=n_new, temperature=temperature, top_k=0, top_p=1.0,
+                                            repetition_penalty=1.0, seed=1, stop_tokens=())
+            api.generate([p[:64] for p in prompts], L.GenerationParams.greedy_params(4, stop_tokens=()))       # graphs
+            r = api.generate(prompts, params)
+            costs = measure.model_costs(api.model)
+            lens, made = [len(p) for p in prompts], [len(t) for t in r.tokens]
+            nbytes, n_steps = measure.decode_bytes_of_run(costs, lens, made)
+            frac = nbytes / r.decode_seconds / 1e9 / pk["hbm_gbs"] if r.decode_seconds > 0 else None
+            points[tag] = round(r.decode_tokens_per_second, 1)
+            points[tag + "_hbm_frac"] = round(frac, 4) if frac else None
+            points[tag + "_prefill_tok_s"] = round(r.prefill_tokens_per_second, 1)
+            print(f"[bench] {tag}: {points[tag]} tok/s over {r.decode_steps} decode steps, {points[tag + '_hbm_frac']} of the copy "
+                  f"bandwidth; prompts {r.prompt_tokens} tokens at {points[tag + '_prefill_tok_s']} tok/s; longest sequence at the "
+                  f"end {max(a + b for a, b in zip(lens, made))}", file=sys.stderr, flush=True)
+
+        try:
+            if api is None:
+                api = L.LlogosModel(model, max_context=context, max_batch=args.batch)
+            workload(api, "llama8b_b8_ragged_to_8192", 128, 2048, args.batch, to_context=context)
+        except Exception as e:                                   # a point that cannot run is reported, not fatal
+            points["llama8b_b8_ragged_to_8192"] = None
+            print(f"[bench] llama8b_b8_ragged_to_8192 failed: {e}", file=sys.stderr, flush=True)
+        del api, model
+        torch.cuda.empty_cache()
+        for tag, cfg2, batch, lo, hi, steps, temps in (
+                ("qwen3_8b_b16_256steps", QWEN3_8B, 16, 64, 4096, 256, (0.0, 0.7)),
+                ("qwen25_14b_b32_128steps", QWEN25_14B, 32, 256, 8192, 128, (0.0,))):
+            try:
+                api2 = L.LlogosModel.random(cfg2, seed=0, dtype="bfloat16", max_context=hi + steps, max_batch=batch, std=0.02)
+                for t in temps:
+                    name = tag if len(temps) == 1 else f"{tag}_{'greedy' if t == 0.0 else 't' + str(t)}"
+                    workload(api2, name, lo, hi, batch, steps=steps, temperature=t)
+                del api2
+            except Exception as e:
+                points[tag] = None
+                print(f"[bench] {tag} failed: {e}", file=sys.stderr, flush=True)
+            torch.cuda.empty_cache()
+        # the 32-bit path against the bfloat16 path on one short sequence, two layers of the 14B shape's 48
+        try:
+            small = dict(QWEN25_14B, num_hidden_layers=2)
+            toks2 = torch.randint(0, small["vocab_size"], (96,), generator=gen).tolist()
+            got = {}
+            for dt in (torch.float32, torch.bfloat16):
+                m2 = L.weights.random_model(small, seed=0, dtype=dt, device=dev, std=0.02)
+                e2 = L.engine.Engine(m2, max_tokens=128)
+                got[dt] = e2.step([(e2.open(), toks2)], [list(range(96))]).double().cpu()
+                del e2, m2
+                torch.cuda.empty_cache()
+            rel = float((got[torch.float32] - got[torch.bfloat16]).abs().max() / got[torch.float32].abs().max())
+            points["qwen25_14b_2of48_layers_fp32_vs_bf16_max_rel_diff"] = round(rel, 5)
+            print(f"[bench] 32-bit path against bfloat16, 96 tokens, 2 of 48 layers of the 14B shape: {rel:.5f} of the largest logit",
+                  file=sys.stderr, flush=True)
+        except Exception as e:
+            print(f"[bench] 32-bit cross-check failed: {e}", file=sys.stderr, flush=True)
 
     line = {
         "metric": f"decode tokens/s at batch {args.batch}, context {context} ({shape_name}, bf16, random weights)",

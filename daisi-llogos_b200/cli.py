@@ -8,6 +8,12 @@ library: ``--prompt`` is turned into ids by a byte stand-in (``byte % vocab``) a
 ids; ``--prompt-ids`` and ``--prompt-file`` give ids directly.  ``--backend`` is replaced by ``--dtype``.
 ``--ignore-eos``, ``--min-p``, ``--typical-p``, ``--frequency-penalty`` and ``--presence-penalty`` set the
 fields of the same meaning in the reference's GenerationParams (Inference/GenerationParams.cs:32-53).
+
+``--bench`` prints the reference's four lines (``Prefill:``, ``Decode:``, ``Total:``, ``Load:``,
+Program.cs:283-297, which its dashboard parses) and, below them, what the reference does not measure: batch
+and context, the bytes a decode step had to read, the operations of the prompt step, and both as fractions of
+the measured peaks.  ``--batch``, ``--prompt-len`` (a number, or ``LOW:HIGH`` for lengths drawn uniformly per
+sequence) and ``--context`` (decode until every sequence holds that many tokens) select the workload.
 """
 from __future__ import annotations
 
@@ -31,7 +37,12 @@ def _parser() -> argparse.ArgumentParser:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="compute type")
     ap.add_argument("--bench", action="store_true", help="run benchmark (prefill + decode timing)")
     ap.add_argument("--random-config", help="config.json of a model to initialise randomly instead of --model")
-    ap.add_argument("--batch", type=int, default=1, help="with --bench: copies of the prompt decoded together")
+    ap.add_argument("--batch", type=int, default=1, help="with --bench: sequences decoded together")
+    ap.add_argument("--prompt-len", help="with --bench: random prompts of this many tokens, or LOW:HIGH for lengths "
+                                         "drawn uniformly per sequence (instead of --prompt)")
+    ap.add_argument("--context", type=int, default=0,
+                    help="with --bench: decode until every sequence holds this many tokens (sets --max-context)")
+    ap.add_argument("--peaks", help="JSON file with hbm_gbs and bf16_tflops to compute the roofline fractions against")
     ap.add_argument("--prompt-file", help="file with one prompt per line, token ids separated by commas or blanks")
     ap.add_argument("--ignore-eos", action="store_true",
                     help="never draw or stop at the end-of-sequence tokens (the reference's PreventEOS)")
@@ -54,18 +65,41 @@ def main(argv=None) -> int:
     from .api import LlogosModel
     from .sampling.params import GenerationParams
 
+    import json
     t_load = time.perf_counter()
-    kw = dict(dtype=args.dtype, max_context=args.max_context, max_batch=max(1, args.batch))
+    max_context = args.max_context
+    if args.bench and args.context > 0:
+        max_context = args.context
+    if args.model:
+        with open(f"{args.model}/config.json") as f:
+            limit = json.load(f).get("max_position_embeddings")
+    else:
+        with open(args.random_config) as f:
+            limit = json.load(f).get("max_position_embeddings")
+    if isinstance(limit, int) and max_context > limit:
+        if args.bench and args.context > 0 or "--max-context" in (argv if argv is not None else sys.argv):
+            print(f"error: a context of {max_context} tokens exceeds the model's max_position_embeddings ({limit})", file=sys.stderr)
+            return 2
+        max_context = limit              # the default of 2048 gives way to a model with fewer positions
+    kw = dict(dtype=args.dtype, max_context=max_context, max_batch=max(1, args.batch))
     if args.model:
         model = LlogosModel.load(args.model, **kw)
     else:
-        import json
         with open(args.random_config) as f:
             model = LlogosModel.random(json.load(f), seed=args.seed or 0, **kw)
     load_ms = (time.perf_counter() - t_load) * 1e3
     vocab = model.model.spec.vocab_size
 
-    if args.prompt_file:
+    if args.bench and args.prompt_len:
+        import random
+        lo, _, hi = args.prompt_len.partition(":")
+        lo, hi = int(lo), int(hi or lo)
+        if not 0 < lo <= hi < max_context:
+            print(f"error: --prompt-len {args.prompt_len} must lie between 1 and the context ({max_context})", file=sys.stderr)
+            return 2
+        rng = random.Random(args.seed or 0)
+        prompts = [[rng.randrange(vocab) for _ in range(rng.randint(lo, hi))] for _ in range(max(1, args.batch))]
+    elif args.prompt_file:
         with open(args.prompt_file) as f:
             prompts = [[int(x) for x in line.replace(",", " ").split()] for line in f if line.strip()]
         if not prompts:
@@ -81,9 +115,12 @@ def main(argv=None) -> int:
         prompts = [_ids_from_text(text, vocab)]
 
     if args.bench:
-        prompts = [prompts[0]] * max(1, args.batch)
-        greedy = GenerationParams.greedy_params(args.max_tokens, stop_tokens=())
-        model.generate(prompts, GenerationParams.greedy_params(min(4, args.max_tokens), stop_tokens=()))   # warm-up
+        from .measure import decode_bytes_of_run, model_costs, peaks
+        if not args.prompt_len:
+            prompts = [prompts[0]] * max(1, args.batch)
+        n_new = max_context if args.context > 0 else args.max_tokens          # with --context the cache's limit ends a sequence
+        greedy = GenerationParams.greedy_params(n_new, stop_tokens=())
+        model.generate([p[:64] for p in prompts], GenerationParams.greedy_params(min(4, n_new), stop_tokens=()))   # warm-up
         r = model.generate(prompts, greedy)
         total_ms = (r.prefill_seconds + r.decode_seconds) * 1e3
         print("=== Benchmark Results ===", file=sys.stderr)
@@ -91,6 +128,25 @@ def main(argv=None) -> int:
         print(f"  Decode:   {r.generated_tokens:6d} tokens in {r.decode_seconds * 1e3:8.1f} ms  ({r.decode_tokens_per_second:8.1f} tok/s)", file=sys.stderr)
         print(f"  Total:    {r.prompt_tokens + r.generated_tokens:6d} tokens in {total_ms:8.1f} ms", file=sys.stderr)
         print(f"  Load:     {load_ms:8.1f} ms", file=sys.stderr)
+        # beyond the reference's lines: what the steps had to move and compute, against the measured peaks
+        pk = peaks(args.peaks)
+        costs = model_costs(model.model)
+        lens = [len(p) for p in prompts]
+        made = [len(t) for t in r.tokens]
+        decode_bytes, n_steps = decode_bytes_of_run(costs, lens, made)
+        steps = max(1, n_steps)
+        flops = costs.prompt_step_flops(lens, wanted_rows=len(lens))
+        print(f"  Batch:    {len(prompts)} sequences, prompts of {min(lens)} to {max(lens)} tokens, "
+              f"longest sequence at the end {max(n + m for n, m in zip(lens, made))} tokens", file=sys.stderr)
+        if r.decode_seconds > 0 and n_steps:
+            gbs = decode_bytes / r.decode_seconds / 1e9
+            print(f"  Decode step: {r.decode_seconds / steps * 1e3:8.3f} ms mean over {steps} steps, {decode_bytes / steps / 1e9:7.3f} GB to read "
+                  f"per step, {gbs:7.1f} GB/s = {100 * gbs / pk['hbm_gbs']:5.1f} % of {pk['hbm_gbs']:.0f} GB/s ({pk['source']} copy bandwidth)",
+                  file=sys.stderr)
+        if r.prefill_seconds > 0:
+            tf = flops / r.prefill_seconds / 1e12
+            print(f"  Prompt step: {flops / 1e12:8.3f} TFLOP, {tf:7.1f} TFLOP/s = {100 * tf / pk['bf16_tflops']:5.1f} % of "
+                  f"{pk['bf16_tflops']:.0f} TFLOP/s ({pk['source']} bfloat16 matrix throughput)", file=sys.stderr)
         return 0
 
     params = GenerationParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,

@@ -162,6 +162,19 @@ def test_command_line(model_dirs):
     p = subprocess.run(base + ["--bench", "-n", "5", "--max-context", "128"], capture_output=True, text=True, env=env, cwd=ROOT)
     assert p.returncode == 0, p.stderr
     assert "Prefill:" in p.stderr and "Decode:" in p.stderr and "Load:" in p.stderr
+    # a workload by numbers: three sequences with prompts of 20 to 60 tokens, decoded until each holds 100
+    p = subprocess.run(base + ["--bench", "--batch", "3", "--prompt-len", "20:60", "--context", "100", "--seed", "4"],
+                       capture_output=True, text=True, env=env, cwd=ROOT)
+    assert p.returncode == 0, p.stderr
+    import re
+    m = re.search(r"Decode:\s+(\d+) tokens", p.stderr)
+    pre = re.search(r"Prefill:\s+(\d+) tokens", p.stderr)
+    assert m and pre and int(m.group(1)) + int(pre.group(1)) == 300          # every sequence reached the context
+    assert "longest sequence at the end 100 tokens" in p.stderr
+    assert re.search(r"Decode step: .* GB to read per step, .* GB/s = .* % of", p.stderr), p.stderr
+    assert re.search(r"Prompt step: .* TFLOP/s = .* % of", p.stderr), p.stderr
+    p = subprocess.run(base + ["--bench", "--context", "4096"], capture_output=True, text=True, env=env, cwd=ROOT)
+    assert p.returncode == 2 and "max_position_embeddings" in p.stderr
     p = subprocess.run([sys.executable, "-m", "llogos_b200", "--prompt", "hi"], capture_output=True, text=True, env=env, cwd=ROOT)
     assert p.returncode == 2 and "--model" in p.stderr
 
