@@ -48,6 +48,7 @@ constexpr int THREADS = (WORK_WARPS + 1) * 32;
 constexpr int MAX_SEQS = 1024;               // sequences whose tile counts fit the plan in shared memory
 constexpr int GH = 8;                        // query heads per key/value head, at most (one MMA n-tile)
 constexpr int MERGE_HEADS = 4;               // heads whose four warp results are added up in shared memory at a time
+constexpr int PART_PAD = 4;                  // a partial result is [head size] sums, the maximum, the sum of weights, and 2 unused: rows stay 16-byte aligned
 constexpr int BLOCKS_PER_SM = 2;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 constexpr float LOG2E = 1.4426950408889634f;
@@ -61,7 +62,7 @@ struct DecodeTmaArgs {
   int ring_pages;
   const int* slots;
   const int* len_before;
-  float* part;                // [part_slots][G][hd + 2]
+  float* part;                // [part_slots][G][hd + PART_PAD]
   int* counters;              // [n_seqs][nh], zero
   void* out;                  // [n_seqs][nh * hd]
   int n_seqs, nh, nkv, hd;
@@ -305,7 +306,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   int pend_ticket = 0, pend_parts = 0;
   const float* pend_base = nullptr;
   long long pend_row = 0;
-  const long long part_stride = (long long)(a.nh / a.nkv) * (HD + 2);     // from one block's partial of a head to the next block's
+  const long long part_stride = (long long)(a.nh / a.nkv) * (HD + PART_PAD);     // from one block's partial of a head to the next block's
   // If the pending ticket was the last of its head, this warp adds up the head's partials (their weights 2^(m - M)
   // are exact powers of two) and writes the head's output; it leaves the counter at zero.
   auto join_if_last = [&]() {
@@ -318,40 +319,41 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int s2 = lane; s2 < pend_parts; s2 += 32) M = fmaxf(M, __ldcg(pend_base + s2 * part_stride + HD));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    // A lane sums four neighbouring head dimensions (one 16-byte load per partial; lanes beyond the head's size idle),
+    // eight partials' loads in flight at a time.
+    constexpr int LANES = HD / 4;
     float L = 0.f;
-    float acc[HD / 32];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const bool live = lane < LANES;
+    for (int s0 = 0; s0 < pend_parts; s0 += 8) {
+      float ms[8], ls[8];
+      float4 v[8];
 #pragma unroll
-    for (int dd = 0; dd < HD / 32; ++dd) acc[dd] = 0.f;
-    int s2 = 0;
-    for (; s2 + 4 <= pend_parts; s2 += 4) {               // four partials' loads in flight at a time
-      float ms[4], ls[4], v[4][HD / 32];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float* row = pend_base + (s2 + k) * part_stride;
-        ms[k] = __ldcg(row + HD);
-        ls[k] = __ldcg(row + HD + 1);
-#pragma unroll
-        for (int dd = 0; dd < HD / 32; ++dd) v[k][dd] = __ldcg(row + lane + 32 * dd);
+      for (int k = 0; k < 8; ++k) {
+        const bool there = s0 + k < pend_parts;
+        const float* row = pend_base + (long long)(there ? s0 + k : 0) * part_stride;
+        const float2 ml = there ? __ldcg(reinterpret_cast<const float2*>(row + HD)) : make_float2(-INFINITY, 0.f);
+        ms[k] = ml.x;
+        ls[k] = ml.y;
+        v[k] = (there && live) ? __ldcg(reinterpret_cast<const float4*>(row) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
+      for (int k = 0; k < 8; ++k) {
         const float w = (ms[k] == -INFINITY) ? 0.f : pow2_whole(ms[k] - M);
         L += w * ls[k];
-#pragma unroll
-        for (int dd = 0; dd < HD / 32; ++dd) acc[dd] += w * v[k][dd];
+        acc.x += w * v[k].x;
+        acc.y += w * v[k].y;
+        acc.z += w * v[k].z;
+        acc.w += w * v[k].w;
       }
     }
-    for (; s2 < pend_parts; ++s2) {
-      const float* row = pend_base + s2 * part_stride;
-      const float ms = __ldcg(row + HD);
-      const float w = (ms == -INFINITY) ? 0.f : pow2_whole(ms - M);
-      L += w * __ldcg(row + HD + 1);
-#pragma unroll
-      for (int dd = 0; dd < HD / 32; ++dd) acc[dd] += w * __ldcg(row + lane + 32 * dd);
-    }
     const float inv = L > 0.f ? 1.0f / L : 0.f;
-#pragma unroll
-    for (int dd = 0; dd < HD / 32; ++dd) out[pend_row * HD + lane + 32 * dd] = __float2bfloat16_rn(acc[dd] * inv);
+    if (live) {
+      uint2 packed;
+      packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+      packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(out + pend_row * HD + 4 * lane) = packed;
+    }
   };
   int i = 0;                                            // tiles consumed so far
   bool ok = true;
@@ -515,7 +517,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           for (int dd = 0; dd < HD / 32; ++dd) out[head_row * HD + lane + 32 * dd] = __float2bfloat16_rn(acc[dd] * inv);
         } else {
           if (pending) join_if_last();                  // a ticket of an earlier pair (or of this pair's head h0 - 4)
-          float* mine = a.part + ((long long)(blockIdx.x + pair) * G + head) * (HD + 2);
+          float* mine = a.part + ((long long)(blockIdx.x + pair) * G + head) * (HD + PART_PAD);
 #pragma unroll
           for (int dd = 0; dd < HD / 32; ++dd) mine[lane + 32 * dd] = acc[dd];
           if (lane == 0) {
@@ -526,7 +528,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           __syncwarp();
           if (lane == 0) pend_ticket = atomicAdd(&a.counters[head_row], 1);     // ... before its ticket is
           pending = true;
-          pend_base = a.part + ((long long)(blk_first + pair) * G + head) * (HD + 2);
+          pend_base = a.part + ((long long)(blk_first + pair) * G + head) * (HD + PART_PAD);
           pend_parts = blk_last - blk_first + 1;
           pend_row = head_row;
         }
@@ -625,7 +627,7 @@ LLG_API int llg_attn_decode_tma_supported(int hd, int nh, int nkv, int n_seqs) {
 // Floats of scratch for the partial results of a launch over sequences of up to `max_len` keys.
 LLG_API long long llg_attn_decode_tma_scratch_floats(int n_seqs, int nh, int nkv, int hd, int max_len) {
   const long long slots = (long long)grid_blocks(n_seqs, nkv, max_len) + (long long)n_seqs * nkv;
-  return slots * (nh / nkv) * (hd + 2);
+  return slots * (nh / nkv) * (hd + PART_PAD);
 }
 
 // `max_len`: an upper bound of len_before + 1 over the batch (it sizes the grid and was given to

@@ -9,6 +9,8 @@
 // kv_cache_write :198-224.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 LLG_API const char* llg_last_error() { return g_llg_error; }
 LLG_API int llg_page_size() { return LLG_PAGE; }
 
@@ -161,6 +163,89 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const floa
   }
 }
 
+// For steps of few rows (one token per sequence): a row is shared by a cluster of NC blocks, each taking a slice of
+// the columns, so that the partial sums of a row are fetched by NC multiprocessors at once instead of one.  The blocks
+// exchange their sums of squares through distributed shared memory and add them in rank order, so every block of a
+// row computes the same scale.  One float4 per thread.
+constexpr int NORM_CLUSTER = 8;
+
+template <typename OT, typename WT>
+__global__ void __launch_bounds__(256) add_rmsnorm_cluster_kernel(float* __restrict__ residual, const float* __restrict__ branch,
+                                                                  int n_partials, long long partial_stride,
+                                                                  const WT* __restrict__ weight, float eps, OT* __restrict__ out,
+                                                                  const int* __restrict__ rows, int hidden) {
+  namespace cg = cooperative_groups;
+  __shared__ float red[32];
+  __shared__ float slice_sum;
+  pdl_launch_dependents();
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank();
+  const int nv = hidden >> 2, per = nv / NORM_CLUSTER;          // float4 per row and per block (the host checks divisibility)
+  const int i = rank * per + threadIdx.x;
+  const bool mine = threadIdx.x < per;
+  // the norm's weight is no result of an earlier kernel: fetch it while the predecessor still runs
+  float wv[4] = {0.f, 0.f, 0.f, 0.f};
+  if (mine) vec_load4(weight + 4 * i, wv);
+  pdl_wait();
+  const int j = blockIdx.y;
+  const int r = rows ? rows[j] : j;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (mine) {
+    float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
+    v = res[i];
+    if (branch) {
+      const float4* b = reinterpret_cast<const float4*>(branch + (long long)r * hidden) + i;
+      const long long ps = partial_stride >> 2;
+      int s = 0;
+      for (; s + 4 <= n_partials; s += 4) {
+        const float4 b0 = b[(s + 0) * ps], b1 = b[(s + 1) * ps], b2 = b[(s + 2) * ps], b3 = b[(s + 3) * ps];
+        v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+        v.x += b1.x; v.y += b1.y; v.z += b1.z; v.w += b1.w;
+        v.x += b2.x; v.y += b2.y; v.z += b2.z; v.w += b2.w;
+        v.x += b3.x; v.y += b3.y; v.z += b3.z; v.w += b3.w;
+      }
+      for (; s < n_partials; ++s) {
+        const float4 b0 = b[s * ps];
+        v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+      }
+      res[i] = v;
+    }
+  }
+  float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+  if (threadIdx.x == 0) slice_sum = ss;
+  cluster.sync();                                    // every block's slice sum is in its shared memory
+  float total = 0.f;
+#pragma unroll
+  for (int k = 0; k < NORM_CLUSTER; ++k) total += *cluster.map_shared_rank(&slice_sum, k);
+  cluster.sync();                                    // nobody leaves while its shared memory may still be read
+  if (mine) {
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    const float y[4] = {v.x * inv * wv[0], v.y * inv * wv[1], v.z * inv * wv[2], v.w * inv * wv[3]};
+    vec_store4(out + (long long)j * hidden + 4 * i, y);
+  }
+}
+
+template <typename OT, typename WT>
+static cudaError_t launch_norm_cluster(int n_out, int threads, cudaStream_t stream, float* residual, const float* branch,
+                                       int n_partials, long long partial_stride, const WT* weight, float eps, OT* out,
+                                       const int* rows, int hidden) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(NORM_CLUSTER, n_out);
+  cfg.blockDim = dim3(threads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = NORM_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = llg_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, add_rmsnorm_cluster_kernel<OT, WT>, residual, branch, n_partials, partial_stride, weight, eps, out,
+                            rows, hidden);
+}
+
 LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials, long long partial_stride,
                             const void* weight, int weight_dtype, float eps, void* out, int out_dtype,
                             const int* rows, int n_out, int hidden, cudaStream_t stream) {
@@ -187,9 +272,16 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
     }
   }
   const bool vec_ok = vec && vpt <= 8;
+  // few rows: a cluster of blocks per row (slices of at most 256 float4)
+  const bool clustered = vec && n_out <= 64 && hidden % (4 * NORM_CLUSTER) == 0 && hidden / (4 * NORM_CLUSTER) <= 256 &&
+                         hidden >= 1024;
+  const int cluster_threads = ((hidden / (4 * NORM_CLUSTER)) + 31) / 32 * 32;
 #define LAUNCH(OT, WT)                                                                                         \
   do {                                                                                                         \
-    if (vec_ok && vpt <= 1)                                                                                    \
+    if (clustered)                                                                                             \
+      launch_norm_cluster<OT, WT>(n_out, cluster_threads, stream, residual, branch, n_partials, partial_stride, \
+                                  (const WT*)weight, eps, (OT*)out, rows, hidden);                             \
+    else if (vec_ok && vpt <= 1)                                                                                    \
       llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 1>, n_out, threads, 0, stream, residual, branch, n_partials,    \
                  partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
     else if (vec_ok && vpt <= 2)                                                                               \
@@ -337,6 +429,7 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   const int kind = h < a.nh ? 0 : (h < a.nh + a.nkv ? 1 : 2);
   const IT* src = (const IT*)a.qkv + (long long)n * heads * HD + (long long)h * HD + 4 * l;
   float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f};   // elements 4l.. of the first and second half
+#pragma unroll 4
   for (int s = 0; s < a.n_partials; ++s) {
     float t0[4], t1[4];
     vec_load4(src + s * a.partial_stride, t0);
@@ -431,8 +524,10 @@ LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stre
                        aligned(a.qkv) && aligned(a.q_norm_w) && aligned(a.k_norm_w) && aligned(a.bias) &&
                        aligned(a.cos_table) && aligned(a.sin_table) && aligned(a.q_out) && aligned(a.k_new) &&
                        aligned(a.v_new) && aligned(a.k_pages) && aligned(a.v_pages);
-  const int warps = lane_ok ? 8 : 4;
   const long long items = (long long)a.n_tokens * (a.nh + 2 * a.nkv);
+  // a step of few tokens spreads its heads over many small blocks: nothing but memory latency bounds it
+  const bool few = lane_ok && items * (a.hd / 8) <= (long long)2 * 64 * llg_sm_count();
+  const int warps = lane_ok ? (few ? 2 : 8) : 4;
   // the vector kernel gives a head to head_dim / 8 lanes, the general one to a warp
   const long long per_block = lane_ok ? (long long)warps * 32 / (a.hd / 8) : warps;
   const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
