@@ -30,6 +30,7 @@
 // The reference's kernel for the same step runs one block per query head and re-reads the keys for every head of
 // a group (Daisi.Llogos.Cuda/kernels/composite_ops.cu:275-387).
 #include "common.cuh"
+#include "kernel_args.h"
 
 #include <cuda.h>
 
@@ -54,21 +55,6 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ int g_error = 0;   // 0 ok; waits that ran out: 1 tile landed, 2 stage free, 3 copies at the end; 4 shared memory not aligned
-
-struct DecodeTmaArgs {
-  const void* q;              // [n_seqs][nh][hd]
-  const int* page_table;
-  int table_width;
-  int ring_pages;
-  const int* slots;
-  const int* len_before;
-  float* part;                // [part_slots][G][hd + PART_PAD]
-  int* counters;              // [n_seqs][nh], zero
-  void* out;                  // [n_seqs][nh * hd]
-  int n_seqs, nh, nkv, hd;
-  float scale;
-  int window;
-};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

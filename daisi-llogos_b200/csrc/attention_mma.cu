@@ -17,48 +17,13 @@
 // (Daisi.Llogos.Cuda/kernels/composite_ops.cu:275-387 one block per query head, :396-512 one
 // block per query token and head) and re-read keys for every head of a group.
 #include "common.cuh"
+#include "kernel_args.h"
 
 LLG_API const char* llg_last_error() { return g_llg_error; }
 
 namespace {
 
 constexpr int TK = 64;   // keys per tile = one cache page
-
-struct PrefillArgs {      // same layout as in attention_simt.cu
-  const void* q;
-  const void* k_new;
-  const void* v_new;
-  const void* k_pages;
-  const void* v_pages;
-  const int* page_table;
-  int table_width;
-  int ring_pages;
-  const int* tiles;       // [n_tiles][2]: (sequence, first query), 64 queries per tile
-  const int* cu_tokens;
-  const int* len_before;
-  const int* slots;
-  void* out;
-  int n_tiles, nh, nkv, hd;
-  float scale;
-  int window;
-  int n_tokens, n_pages;     // rows of k_new / v_new, pages of k_pages / v_pages
-};
-
-struct DecodeArgs {       // same layout as in attention_simt.cu
-  const void* q;
-  const void* k_pages;
-  const void* v_pages;
-  const int* page_table;
-  int table_width;
-  int ring_pages;
-  const int* slots;
-  const int* len_before;
-  float* part_o;
-  float* part_ml;
-  int n_seqs, nh, nkv, hd, n_splits;
-  float scale;
-  int window;
-};
 
 typedef __nv_bfloat16 bf16;
 

@@ -13,6 +13,7 @@
 // for one token, :396-512 for several): score = (q . k) * scale with scale applied after the
 // dot product, running maximum, exponentials, sum, weighted values, division by the sum.
 #include "common.cuh"
+#include "kernel_args.h"
 
 LLG_API const char* llg_last_error() { return g_llg_error; }
 
@@ -21,26 +22,6 @@ namespace {
 constexpr int KT = 32;      // keys per tile (one per lane)
 constexpr int MAXD = 8;     // head_dim / 32 rounded up, at most
 constexpr int BQ = 16;      // queries per block in attn_prefill (4 per warp)
-
-struct PrefillArgs {
-  const void* q;            // [n_tokens][nh][hd]
-  const void* k_new;        // [n_tokens][nkv][hd]
-  const void* v_new;
-  const void* k_pages;      // [pages][nkv][LLG_PAGE][hd]
-  const void* v_pages;
-  const int* page_table;
-  int table_width;
-  int ring_pages;
-  const int* tiles;         // [n_tiles][2]: (sequence index in the batch, first query among its step tokens)
-  const int* cu_tokens;     // [B + 1]
-  const int* len_before;    // [B]
-  const int* slots;         // [B]
-  void* out;                // [n_tokens][nh * hd]
-  int n_tiles, nh, nkv, hd;
-  float scale;
-  int window;               // 0 = all keys
-  int n_tokens, n_pages;    // rows of k_new / v_new, pages of k_pages / v_pages
-};
 
 template <typename T>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
@@ -167,22 +148,6 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
 // ---- one new token per sequence -----------------------------------------------------
 
 constexpr int GC = 8;  // query heads of one key/value head handled per pass
-
-struct DecodeArgs {
-  const void* q;            // [B][nh][hd]
-  const void* k_pages;
-  const void* v_pages;
-  const int* page_table;
-  int table_width;
-  int ring_pages;
-  const int* slots;         // [B]
-  const int* len_before;    // [B]; the new token's key is already in the cache at this position
-  float* part_o;            // [B][nh][n_splits][hd]  un-normalised
-  float* part_ml;           // [B][nh][n_splits][2]   running maximum, sum
-  int n_seqs, nh, nkv, hd, n_splits;
-  float scale;
-  int window;
-};
 
 template <typename T>
 __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {

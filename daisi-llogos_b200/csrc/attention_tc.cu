@@ -29,6 +29,7 @@
 // raises a flag that ends the other roles' waits; every role waits for its own copies in flight,
 // and the block frees its tensor memory and returns.
 #include "common.cuh"
+#include "kernel_args.h"
 
 #include <cuda.h>
 
@@ -67,26 +68,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 }
 
 __device__ int g_error = 0;  // 0 ok; waits that ran out: 1 scores, 2 accumulator, 4 free stage, 5 tile copied, 6 weights, 7 copies at the end; 3 shared memory not aligned to 1024 bytes
-
-struct PrefillArgs {         // same layout as in attention_simt.cu
-  const void* q;
-  const void* k_new;
-  const void* v_new;
-  const void* k_pages;
-  const void* v_pages;
-  const int* page_table;
-  int table_width;
-  int ring_pages;
-  const int* tiles;          // [n_tiles][2]: (sequence, first query), 256 queries per tile
-  const int* cu_tokens;
-  const int* len_before;
-  const int* slots;
-  void* out;
-  int n_tiles, nh, nkv, hd;
-  float scale;
-  int window;
-  int n_tokens, n_pages;     // rows of k_new / v_new, pages of k_pages / v_pages
-};
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

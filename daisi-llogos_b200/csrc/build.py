@@ -27,15 +27,16 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 # library name -> sources (first is the .cu that is compiled; the rest are hashed with it)
 SOURCES: Dict[str, List[str]] = {
-    "elementwise": ["elementwise.cu", "common.cuh"],
+    "elementwise": ["elementwise.cu", "common.cuh", "kernel_args.h"],
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
     "gemm_tc": ["gemm_tc.cu", "common.cuh"],
-    "attention_simt": ["attention_simt.cu", "common.cuh", "attention_noalloc.h"],
-    "attention_mma": ["attention_mma.cu", "common.cuh"],
-    "attention_tc": ["attention_tc.cu", "common.cuh"],
-    "attention_decode_tma": ["attention_decode_tma.cu", "common.cuh"],
+    "attention_simt": ["attention_simt.cu", "common.cuh", "kernel_args.h", "attention_noalloc.h"],
+    "attention_mma": ["attention_mma.cu", "common.cuh", "kernel_args.h"],
+    "attention_tc": ["attention_tc.cu", "common.cuh", "kernel_args.h"],
+    "attention_decode_tma": ["attention_decode_tma.cu", "common.cuh", "kernel_args.h"],
     "sampling": ["sampling.cu", "common.cuh"],
     "init": ["init.cu", "common.cuh"],
+    "block_runner": ["block_runner.cu", "kernel_args.h"],
 }
 
 NVCC_FLAGS = [

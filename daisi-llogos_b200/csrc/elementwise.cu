@@ -8,6 +8,7 @@
 // embedding_lookup :402-457; kernels/composite_ops.cu per_head_rms_norm :106-136,
 // kv_cache_write :198-224.
 #include "common.cuh"
+#include "kernel_args.h"
 
 #include <cooperative_groups.h>
 
@@ -307,36 +308,6 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
 }
 
 // ---- query/key preparation ----------------------------------------------------------
-
-struct QkPrepArgs {
-  const void* qkv;            // [n_partials][n_tokens][(nh + 2 nkv) * hd], float32 or bfloat16
-  int qkv_dtype;
-  int n_partials;
-  long long partial_stride;   // elements between partials
-  const void* q_norm_w;       // [hd] or null
-  const void* k_norm_w;       // [hd] or null
-  int norm_w_dtype;
-  float norm_eps;
-  const void* bias;           // [(nh + 2 nkv) * hd] or null
-  int bias_dtype;
-  const float* cos_table;     // [positions][rotary_dim / 2] or null
-  const float* sin_table;
-  int rotary_dim;
-  int pairing;                // 0: (i, i + rotary_dim/2), 1: (2i, 2i+1)
-  int table_positions;
-  const int* positions;       // [n_tokens]
-  void* q_out;                // [n_tokens][nh][hd]
-  void* k_new;                // [n_tokens][nkv][hd] or null
-  void* v_new;
-  void* k_pages;              // paged store or null
-  void* v_pages;
-  const int* page_table;
-  int table_width;
-  int ring_pages;
-  const int* seq_of_token;    // [n_tokens] -> index into slots
-  const int* slots;
-  int n_tokens, nh, nkv, hd;
-};
 
 template <typename IT, typename OT, typename WT>
 __global__ void qk_prep_kernel(QkPrepArgs a) {

@@ -119,6 +119,11 @@ class Engine:
         self.cache = SequenceCache(model.cache_needs(), max_tokens=max_tokens, max_seq_len=max_seq_len,
                                    n_slots=n_slots, dtype=self.dtype, device=self.device)
         model.prepare(self.cache.max_seq_len)
+        # the stock blocks' launch chain in native code, where the model is made of nothing else
+        self._runner = None
+        if self.device.type == "cuda":
+            from .runner import BlockRunner
+            self._runner = BlockRunner.build(model, self.cache)
         self.vocab = model.spec.vocab_size
         self.use_graphs = use_graphs and self.device.type == "cuda"
         self._staging = _Staging(self.device)
@@ -297,7 +302,7 @@ class Engine:
         rows_dev = take(rows.size)
         for g, off, k in plan:
             self.ops.scatter_i32(g.page_table, meta[off:off + k], meta[off + k:off + 2 * k])
-        return self.model.forward(ctx, self.cache, rows_dev)
+        return self.model.forward(ctx, self.cache, rows_dev, self._runner)
 
     # ---- decode step -----------------------------------------------------------------------
     def _decode_step(self, n_real, slots, toks, len_before, updates, want, fed=None) -> torch.Tensor:
@@ -350,14 +355,14 @@ class Engine:
                 st.workspace.frozen = True
                 before = getattr(self.ops, "launches", lambda: 0)()
                 with torch.cuda.graph(graph):
-                    st.logits = self.model.forward(ctx, self.cache, st.rows)
+                    st.logits = self.model.forward(ctx, self.cache, st.rows, self._runner)
                 st.kernels = getattr(self.ops, "launches", lambda: 0)() - before
                 st.graph = graph
                 graph.replay()
                 self.graph_kernels += st.kernels
                 logits = st.logits
             else:
-                logits = self.model.forward(ctx, self.cache, st.rows)
+                logits = self.model.forward(ctx, self.cache, st.rows, self._runner)
                 st.eager_runs += 1
         flat_want = [(i, int(w)) for i in range(n_real) for w in want[i]]
         if len(flat_want) == n_real and all(i == j for j, (i, _) in enumerate(flat_want)):

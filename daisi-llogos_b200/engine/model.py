@@ -119,15 +119,18 @@ class DecoderModel:
         return needs
 
     # ---- forward -------------------------------------------------------------------------
-    def forward(self, ctx, cache, rows: Optional[torch.Tensor]) -> torch.Tensor:
-        """Runs the step's tokens; returns float32 logits of ``rows`` (token indices), [len(rows), vocab]."""
+    def forward(self, ctx, cache, rows: Optional[torch.Tensor], runner=None) -> torch.Tensor:
+        """Runs the step's tokens; returns float32 logits of ``rows`` (token indices), [len(rows), vocab].
+        ``runner``: an ``engine.runner.BlockRunner`` built for this model and cache; it then runs the layers."""
         residual = self.embedding.forward(ctx)
         for enc in self.encodings.values():
             enc.on_embeddings(residual, ctx)
         pending: Optional[Branch] = None
+        if runner is not None:
+            pending = runner.run(ctx, residual)
         borrowed = {e.cache_of for e in self.spec.schedule if e.cache_of is not None}
         shared: Dict[int, Dict] = {}
-        for e_i, e in enumerate(self.spec.schedule):
+        for e_i, e in enumerate(self.spec.schedule if runner is None else ()):
             unit = e.cache_of if e.cache_of is not None else e_i
             view = cache.view(unit, owner=e.cache_of is None, keep_step_kv=e_i in borrowed,
                               shared=shared.setdefault(unit, {}))
