@@ -46,8 +46,8 @@ def main(argv=None) -> int:
     print(f"[trace_run] loading {args.model} as {args.dtype}", file=sys.stderr, flush=True)
     model = load_model(args.model, dtype=_DTYPES[args.dtype], device=args.device)
     pages = (args.max_tokens + 63) // 64
-    engine = Engine(model, max_tokens=pages * 64, max_seq_len=min(pages * 64, 1 << 20),
-                    use_graphs=not args.no_graphs)
+    # the longest single request: what the cache holds, or the model's position limit where that is less
+    engine = Engine(model, max_tokens=pages * 64, use_graphs=not args.no_graphs)
     print(f"[trace_run] ready: cache of {pages} pages of 64 tokens ({engine.cache.bytes() / 2**20:.1f} MiB)",
           file=sys.stderr, flush=True)
 

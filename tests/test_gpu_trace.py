@@ -112,6 +112,22 @@ def test_replay_of_portions_and_mixed_steps(llogos, model_dirs, tmp_path, name, 
     r.finish()
 
 
+def test_replay_with_a_cache_larger_than_the_models_positions(llogos, tmp_path):
+    """--max-tokens sizes the cache for all live requests together; it may exceed what one request can reach
+    (max_position_embeddings), and two requests then share it."""
+    cfg = dict(TINY["llama"], max_position_embeddings=128)
+    d = str(tmp_path / "m")
+    llogos.weights.write_random_model(d, cfg, seed=5, std=0.15)
+    w = read_weights(llogos, d)
+    a, b = random_tokens(cfg["vocab_size"], [120, 100], 24)
+    ra, rb = reference(d, w, cfg, a), reference(d, w, cfg, b)
+    r = Replay(d, "float32", str(tmp_path / "out"), max_tokens=256)
+    got = r.step([("a", a, [0, 119]), ("b", b, [99])], end=["a", "b"]).reshape(3, cfg["vocab_size"])
+    check(ra, got[:2], [0, 119], "float32", ("a",))
+    check(rb, got[2], [99], "float32", ("b",))
+    r.finish()
+
+
 def test_replay_rejects_nonsense(model_dirs, tmp_path):
     p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dirs["llama"],
                         "--dtype", "float16", "--out", str(tmp_path), "--max-tokens", "64"],
