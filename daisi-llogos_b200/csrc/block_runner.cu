@@ -27,7 +27,8 @@ enum { F32 = 0, BF16 = 1 };
 
 }  // namespace
 
-// Entry points of the kernel libraries (filled in by the caller with the addresses of the loaded functions).
+// Entry points of the kernel libraries (filled in by the caller with the addresses of the loaded functions; an entry
+// may stay empty as long as no step needs it, so that a caller loads only the libraries its model uses).
 struct RunnerApi {
   int (*add_rmsnorm)(float*, const float*, int, long long, const void*, int, float, void*, int, const int*, int, int, cudaStream_t);
   int (*gemm_tc)(const void*, const void*, void*, int, int, int, int, int, int, int, cudaStream_t);
@@ -124,12 +125,24 @@ int fail(const char* what, const char* (*err)()) {
   return 1;
 }
 
+int unbound(const char* what) {
+  snprintf(g_error, sizeof(g_error), "runner: the entry point of %s has not been bound", what);
+  return 1;
+}
+
+#define NEED(fn) \
+  do {           \
+    if (!g_api.fn) return unbound(#fn); \
+  } while (0)
+
 // y[n][o] = x[n][k] w[o][k] as `splits` float32 partials (tensor cores) or one result (CUDA cores)
 int product(const RunnerStep& s, const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int tc, int splits,
             int* launches) {
   if (tc) {
+    NEED(gemm_tc);
     if (g_api.gemm_tc(x, w, out, out_dtype, n, o, k, splits, 0, 0, s.stream)) return fail("gemm_tc", g_api.err_gemm_tc);
   } else {
+    NEED(gemm_simt);
     if (g_api.gemm_simt(x, s.dtype, w, s.dtype, out, out_dtype, n, o, k, s.stream)) return fail("gemm_simt", g_api.err_gemm_simt);
   }
   ++*launches;
@@ -140,6 +153,8 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
   const int n = s.n_tokens;
   const long long nh_stride = (long long)n * s.hidden;
   const int qkv_dim = (s.nh + 2 * s.nkv) * s.hd;
+  NEED(add_rmsnorm);
+  NEED(qk_prep);
   // residual += pending; x = norm1(residual)
   if (g_api.add_rmsnorm(s.residual, pending, pending ? pending_parts : 0, nh_stride, L.norm1_w, L.norm_w_dtype, L.norm1_eps,
                         s.norm_out, s.dtype, nullptr, n, s.hidden, s.stream))
@@ -208,6 +223,7 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
       a.hd = s.hd;
       a.scale = L.scale;
       a.window = L.window;
+      NEED(attn_decode_tma);
       if (g_api.attn_decode_tma(&a, L.k_pages, L.v_pages, L.n_pages, s.max_len_after, s.stream))
         return fail("attn_decode_tma", g_api.err_attn_decode_tma);
       ++*launches;
@@ -232,10 +248,12 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
       a.scale = L.scale;
       a.window = L.window;
       if (s.decode_kind == 1) {
+        NEED(attn_decode_mma);
         if (g_api.attn_decode_mma(&a, s.attn_out, s.attn_counters, s.decode_balance, s.stream))
           return fail("attn_decode_mma", g_api.err_attn_mma);
         ++*launches;
       } else {
+        NEED(attn_decode_simt);
         if (g_api.attn_decode_simt(&a, s.attn_out, s.dtype, s.stream)) return fail("attn_decode_simt", g_api.err_attn_simt);
         *launches += 2;
       }
@@ -267,18 +285,22 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
     int rc;
     const char* (*err)();
     if (s.prefill_kind == 2) {
+      NEED(attn_prefill_tc);
       rc = g_api.attn_prefill_tc(&a, s.stream);
       err = g_api.err_attn_tc;
     } else if (s.prefill_kind == 1) {
+      NEED(attn_prefill_mma);
       rc = g_api.attn_prefill_mma(&a, s.stream);
       err = g_api.err_attn_mma;
     } else {
+      NEED(attn_prefill_simt);
       rc = g_api.attn_prefill_simt(&a, s.dtype, s.stream);
       err = g_api.err_attn_simt;
     }
     if (rc) return fail("attn_prefill", err);
     ++*launches;
     if (!write_now) {
+      NEED(kv_write);
       if (g_api.kv_write(s.k_new, s.v_new, L.k_pages, L.v_pages, L.page_table, L.table_width, L.ring_pages, s.positions,
                          s.seq_of_token, s.slots, s.cu_tokens, s.len_before, n, s.nkv, s.hd, s.dtype, s.stream))
         return fail("kv_write", g_api.err_elementwise);
@@ -295,10 +317,13 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
   // act = silu(gate) * up
   const int gated_rows = ((s.inter + 127) / 128) * 256;
   if (s.tc_gate_up && s.dtype == BF16) {
+    NEED(gemm_tc);
     if (g_api.gemm_tc(s.norm_out, L.w_gate_up, s.act, BF16, n, gated_rows, s.hidden, 1, 0, s.inter, s.stream))
       return fail("gemm_tc", g_api.err_gemm_tc);
     ++*launches;
   } else {
+    NEED(gemm_simt);
+    NEED(silu_mul);
     const size_t el = s.dtype == BF16 ? 2 : 4;
     for (int r0 = 0; r0 < n; r0 += s.gate_up_rows) {
       const int rows = n - r0 < s.gate_up_rows ? n - r0 : s.gate_up_rows;
@@ -324,13 +349,6 @@ LLG_API int llg_runner_bind(const RunnerApi* api) {
   if (!api) {
     snprintf(g_error, sizeof(g_error), "runner: no function table");
     return 1;
-  }
-  const void* const* p = reinterpret_cast<const void* const*>(api);
-  for (size_t i = 0; i < sizeof(RunnerApi) / sizeof(void*); ++i) {
-    if (!p[i]) {
-      snprintf(g_error, sizeof(g_error), "runner: entry %zu of the function table is empty", i);
-      return 1;
-    }
   }
   g_api = *api;
   g_bound = true;

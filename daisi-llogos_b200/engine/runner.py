@@ -67,12 +67,28 @@ class _RunnerStep(Structure):
     ]
 
 
-_lib = None
 _GATED_CHUNK = 16384          # rows per pass of the two-kernel gating path (as in kernels/linear.py)
+
+# entry of the function table -> (library, function); the error text of a library goes with its first entry
+_ENTRIES = {
+    "add_rmsnorm": ("elementwise", "llg_add_rmsnorm"), "qk_prep": ("elementwise", "llg_qk_prep"),
+    "kv_write": ("elementwise", "llg_kv_write"), "silu_mul": ("elementwise", "llg_silu_mul"),
+    "gemm_tc": ("gemm_tc", "llg_gemm_tc"), "gemm_simt": ("gemm_simt", "llg_gemm_simt"),
+    "attn_prefill_tc": ("attention_tc", "llg_attn_prefill_tc"), "attn_prefill_mma": ("attention_mma", "llg_attn_prefill_mma"),
+    "attn_prefill_simt": ("attention_simt", "llg_attn_prefill_simt"),
+    "attn_decode_tma": ("attention_decode_tma", "llg_attn_decode_tma"), "attn_decode_mma": ("attention_mma", "llg_attn_decode_mma"),
+    "attn_decode_simt": ("attention_simt", "llg_attn_decode_simt"),
+}
+_ERR_FIELD = {"elementwise": "err_elementwise", "gemm_tc": "err_gemm_tc", "gemm_simt": "err_gemm_simt",
+              "attention_tc": "err_attn_tc", "attention_mma": "err_attn_mma", "attention_simt": "err_attn_simt",
+              "attention_decode_tma": "err_attn_decode_tma"}
+_lib = None
+_api = _RunnerApi()
+_bound = set()
 
 
 def _library():
-    """The runner's library with the kernels' entry points bound into it (once per process)."""
+    """The runner's own library (once per process)."""
     global _lib
     if _lib is not None:
         return _lib
@@ -83,35 +99,27 @@ def _library():
     want = (ctypes.sizeof(_RunnerApi), ctypes.sizeof(_DenseLayer), ctypes.sizeof(_RunnerStep))
     if got != want:
         raise ops.KernelError(f"block runner: structure sizes {got} in the library, {want} here")
-    libs = {n: ops._lib(n) for n in ("elementwise", "gemm_tc", "gemm_simt", "attention_tc", "attention_mma",
-                                     "attention_simt", "attention_decode_tma")}
-
-    def addr(lib_name, fn):
-        return ctypes.cast(getattr(libs[lib_name], fn), c_void_p).value
-
-    api = _RunnerApi()
-    api.add_rmsnorm = addr("elementwise", "llg_add_rmsnorm")
-    api.gemm_tc = addr("gemm_tc", "llg_gemm_tc")
-    api.gemm_simt = addr("gemm_simt", "llg_gemm_simt")
-    api.qk_prep = addr("elementwise", "llg_qk_prep")
-    api.kv_write = addr("elementwise", "llg_kv_write")
-    api.silu_mul = addr("elementwise", "llg_silu_mul")
-    api.attn_prefill_tc = addr("attention_tc", "llg_attn_prefill_tc")
-    api.attn_prefill_mma = addr("attention_mma", "llg_attn_prefill_mma")
-    api.attn_prefill_simt = addr("attention_simt", "llg_attn_prefill_simt")
-    api.attn_decode_tma = addr("attention_decode_tma", "llg_attn_decode_tma")
-    api.attn_decode_mma = addr("attention_mma", "llg_attn_decode_mma")
-    api.attn_decode_simt = addr("attention_simt", "llg_attn_decode_simt")
-    for field, name in (("err_elementwise", "elementwise"), ("err_gemm_tc", "gemm_tc"), ("err_gemm_simt", "gemm_simt"),
-                        ("err_attn_tc", "attention_tc"), ("err_attn_mma", "attention_mma"),
-                        ("err_attn_simt", "attention_simt"), ("err_attn_decode_tma", "attention_decode_tma")):
-        setattr(api, field, addr(name, "llg_last_error"))
     lib.llg_runner_bind.argtypes = [POINTER(_RunnerApi)]
     lib.llg_runner_run.argtypes = [c_void_p, c_int, POINTER(_RunnerStep), c_void_p, c_int, POINTER(c_int), POINTER(c_int)]
-    if lib.llg_runner_bind(byref(api)) != 0:
-        raise ops.KernelError(lib.llg_last_error().decode("utf-8", "replace"))
     _lib = lib
     return lib
+
+
+def _ensure(entries) -> None:
+    """Binds the kernels' entry points that a step needs into the runner, loading (and, in a fresh checkout,
+    compiling) only the libraries they live in."""
+    missing = [e for e in entries if e not in _bound]
+    if not missing:
+        return
+    lib = _library()
+    for e in missing:
+        lib_name, fn = _ENTRIES[e]
+        kernels = ops._lib(lib_name)
+        setattr(_api, e, ctypes.cast(getattr(kernels, fn), c_void_p).value)
+        setattr(_api, _ERR_FIELD[lib_name], ctypes.cast(kernels.llg_last_error, c_void_p).value)
+        _bound.add(e)
+    if lib.llg_runner_bind(byref(_api)) != 0:
+        raise ops.KernelError(lib.llg_last_error().decode("utf-8", "replace"))
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -131,6 +139,7 @@ class BlockRunner:
         self.g = geom
         self.step = _RunnerStep()
         self._out_parts, self._launches = c_int(), c_int()
+        self._ensured = set()
 
     # ---- eligibility -----------------------------------------------------------------------
     @classmethod
@@ -242,6 +251,21 @@ class BlockRunner:
             tiles = ctx.query_tiles(tq)
             s.tiles, s.n_tiles = tiles.data_ptr(), tiles.shape[0]
             s.prefill_kind = 2 if ops._use_tc_attn(dtype, hd) else 1 if ops._use_mma(dtype, hd) else 0
+        need = ["add_rmsnorm", "qk_prep"]
+        need.append("gemm_tc" if (s.tc_qkv or s.tc_o or s.tc_down or (s.tc_gate_up and bf16)) else "gemm_simt")
+        if not (s.tc_qkv and s.tc_o and s.tc_down):
+            need.append("gemm_simt")
+        if not (s.tc_gate_up and bf16):
+            need += ["gemm_simt", "silu_mul"]
+        if ctx.decode:
+            need.append(("attn_decode_simt", "attn_decode_mma", "attn_decode_tma")[s.decode_kind])
+        else:
+            need.append(("attn_prefill_simt", "attn_prefill_mma", "attn_prefill_tc")[s.prefill_kind])
+            need.append("kv_write")
+        key = tuple(need)
+        if key not in self._ensured:
+            _ensure(need)
+            self._ensured.add(key)
         s.stream = ops._stream()
         rc = self.lib.llg_runner_run(self.table, self.n_layers, byref(s), None, 0, byref(self._out_parts), byref(self._launches))
         ops._launches += self._launches.value
