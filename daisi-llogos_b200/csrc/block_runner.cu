@@ -43,6 +43,7 @@ struct RunnerApi {
   int (*attn_decode_tma)(const DecodeTmaArgs*, const void*, const void*, int, int, cudaStream_t);
   int (*attn_decode_mma)(const DecodeArgs*, void*, int*, int, cudaStream_t);
   int (*attn_decode_simt)(const DecodeArgs*, void*, int, cudaStream_t);
+  int (*gemm_tc_qkv)(const void*, const void*, int, int, const QkPrepArgs*, cudaStream_t);
   // the libraries' own error texts: elementwise, gemm_tc, gemm_simt, attention (tc, mma, simt, decode tma)
   const char* (*err_elementwise)();
   const char* (*err_gemm_tc)();
@@ -98,6 +99,7 @@ struct RunnerStep {
   int decode_splits, decode_balance;
   int tc_qkv, tc_o, tc_gate_up, tc_down;    // 1: the tensor-core product takes this matrix
   int splits_qkv, splits_o, splits_down;    // split-K partials of the three products that feed a sum
+  int fused_qkv;                            // prompt steps: the q/k/v product prepares queries and keys in its epilogue
   float* residual;                          // [n][hidden]
   void* norm_out;                           // [n][hidden]
   float* qkv;                               // [splits_qkv][n][(nh + 2 nkv) * hd]
@@ -160,9 +162,10 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
                         s.norm_out, s.dtype, nullptr, n, s.hidden, s.stream))
     return fail("add_rmsnorm", g_api.err_elementwise);
   ++*launches;
-  // q/k/v in float32 (partials when the product splits its sums)
+  // q/k/v in float32 (partials when the product splits its sums), unless the product prepares them itself
+  const bool fused = s.fused_qkv && !s.decode;
   const int s_qkv = s.tc_qkv ? s.splits_qkv : 1;
-  if (product(s, s.norm_out, L.w_qkv, s.qkv, F32, n, qkv_dim, s.hidden, s.tc_qkv, s_qkv, launches)) return 1;
+  if (!fused && product(s, s.norm_out, L.w_qkv, s.qkv, F32, n, qkv_dim, s.hidden, s.tc_qkv, s_qkv, launches)) return 1;
   QkPrepArgs p;
   memset(&p, 0, sizeof(p));
   p.qkv = s.qkv;
@@ -202,7 +205,13 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
     p.seq_of_token = s.seq_of_token;
     p.slots = s.slots;
   }
-  if (g_api.qk_prep(&p, s.dtype, s.stream)) return fail("qk_prep", g_api.err_elementwise);
+  if (fused) {
+    NEED(gemm_tc_qkv);
+    p.qkv = nullptr;
+    if (g_api.gemm_tc_qkv(s.norm_out, L.w_qkv, n, s.hidden, &p, s.stream)) return fail("gemm_tc_qkv", g_api.err_gemm_tc);
+  } else {
+    if (g_api.qk_prep(&p, s.dtype, s.stream)) return fail("qk_prep", g_api.err_elementwise);
+  }
   ++*launches;
   if (s.decode) {
     if (s.decode_kind == 2) {

@@ -29,7 +29,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 SOURCES: Dict[str, List[str]] = {
     "elementwise": ["elementwise.cu", "common.cuh", "kernel_args.h"],
     "gemm_simt": ["gemm_simt.cu", "common.cuh"],
-    "gemm_tc": ["gemm_tc.cu", "common.cuh"],
+    "gemm_tc": ["gemm_tc.cu", "common.cuh", "kernel_args.h"],
     "attention_simt": ["attention_simt.cu", "common.cuh", "kernel_args.h", "attention_noalloc.h"],
     "attention_mma": ["attention_mma.cu", "common.cuh", "kernel_args.h"],
     "attention_tc": ["attention_tc.cu", "common.cuh", "kernel_args.h"],

@@ -23,6 +23,7 @@
 // Daisi.Llogos.Cuda/CudaBackend.cs:246-260; its decode path is a scalar GEMV,
 // kernels/dequant_matmul.cu:593-619).
 #include "common.cuh"
+#include "kernel_args.h"
 
 #include <cuda.h>
 
@@ -124,7 +125,13 @@ struct GemmParams {
   int gated_features;
   int up_offset;    // gated: row of w that holds the up row of feature 0 (gate rows come first)
   int gate_rows;    // gated, weights as first operand: features per block (at most 128)
+  QkPrepArgs prep;  // EPI 2 / 3: what the q/k/v preparation needs (its `qkv` field is not used)
 };
+
+// an element of a weight vector stored as float32 or bfloat16
+__device__ __forceinline__ float vec_elem(const void* p, int dtype, int i) {
+  return dtype == LLG_BF16 ? __bfloat162float(((const __nv_bfloat16*)p)[i]) : ((const float*)p)[i];
+}
 
 // MT: weight tiles of 128 rows per block (1 or 2; two tiles share every activation tile, which halves
 // the shared-memory traffic per flop of a large product).  EPI 1 (MT = 2): the first tile holds gate
@@ -135,6 +142,12 @@ struct GemmParams {
 // out[n][o] with o along the lanes (decode steps: the token tile can be as small as 16).
 // SWAP 1: the first operand is the activations (128 tokens per tile), the second the weights (TN features):
 // a thread owns a token and writes runs of consecutive features with 16-byte stores (prompt steps).
+// EPI 2 (head size 128) and EPI 3 (head size 64), SWAP 1 only: the product is the q/k/v projection and its epilogue
+// is the preparation of queries and keys: a thread holds whole heads of its token (the tile is a whole number of
+// heads wide), so the per-head norm, the bias and the rotation need no exchange between threads; queries go out as
+// bfloat16 [token][head][head size], keys and values into the step's packed buffers and the cache pages.  The sums
+// are never rounded before that, and the float32 q/k/v array of the two-kernel way is neither written nor read.
+// Order as in the reference: norm, bias, rotation (Inference/ForwardPass.cs:372-385).
 template <int TN, int STAGES, typename OT, int MT, int EPI, int SWAP>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, GemmParams p) {
@@ -146,7 +159,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   constexpr int TMEM_COLS = MT * TN <= 32 ? 32 : MT * TN <= 64 ? 64 : MT * TN <= 128 ? 128 : MT * TN <= 256 ? 256 : 512;
   static_assert(MT * TN <= 512, "the accumulators do not fit tensor memory");
   static_assert(TN % 16 == 0, "the second operand's tile is a multiple of 16 rows");
-  static_assert(EPI == 0 || (SWAP ? TN % 32 == 0 : MT == 2), "the gated epilogue needs a gate tile and an up tile");
+  static_assert(EPI != 1 || (SWAP ? TN % 32 == 0 : MT == 2), "the gated epilogue needs a gate tile and an up tile");
+  static_assert(EPI < 2 || (SWAP == 1 && TN % 128 == 0), "the q/k/v epilogue works on token rows and whole heads");
   // 1024-byte alignment of the operand tiles is what the swizzle pattern of TMA and of the MMA assume
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], done_bar;
@@ -306,10 +320,93 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     {
       const uint32_t lane_base = tmem_d + ((uint32_t)(warp * 32) << 16);
-      if (SWAP) {
+      if (SWAP && EPI >= 2) {
+        // lanes are tokens, columns are the features of whole heads: norm, bias, rotation, and the writes of q, k, v
+        constexpr int HD = EPI == 2 ? 128 : 64, HALF = HD / 2;
+        const QkPrepArgs& a = p.prep;
+        const int heads = a.nh + 2 * a.nkv;
+        typedef __nv_bfloat16 bf;
+#pragma unroll 1
+        for (int mt = 0; mt < MT; ++mt) {
+          if (o0 + mt * BM >= p.o) break;
+          const int tok = o0 + mt * BM + warp * 32 + lane;
+          const bool live = tok < p.o;
+          const int pos = live ? a.positions[tok] : 0;
+          const int slot = (live && a.k_pages) ? a.slots[a.seq_of_token[tok]] : 0;
+#pragma unroll 1
+          for (int hb = 0; hb < TN / HD; ++hb) {
+            const int head = n0 / HD + hb;
+            if (head >= heads) break;                   // uniform: the tile's tail lies past the last head
+            float h[HD];
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 16) {
+              uint32_t r[16];
+              tmem_ld16(lane_base + (uint32_t)(mt * TN + hb * HD + c0), r);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int c = 0; c < 16; ++c) h[c0 + c] = __uint_as_float(r[c]);
+            }
+            const int kind = head < a.nh ? 0 : (head < a.nh + a.nkv ? 1 : 2);      // query, key, value
+            const void* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
+            if (nw) {
+              float ss = 0.f;
+#pragma unroll
+              for (int d = 0; d < HD; ++d) ss += h[d] * h[d];
+              const float inv = 1.0f / sqrtf(ss / (float)HD + a.norm_eps);
+#pragma unroll
+              for (int d = 0; d < HD; ++d) h[d] = h[d] * inv * vec_elem(nw, a.norm_w_dtype, d);
+            }
+            if (a.bias) {
+#pragma unroll
+              for (int d = 0; d < HD; ++d) h[d] += vec_elem(a.bias, a.bias_dtype, head * HD + d);
+            }
+            if (kind != 2 && a.cos_table) {
+              const int pp = pos < a.table_positions ? pos : a.table_positions - 1;     // bounded; the host checks capacity
+              const float4* cs = reinterpret_cast<const float4*>(a.cos_table + (long long)pp * HALF);
+              const float4* sn = reinterpret_cast<const float4*>(a.sin_table + (long long)pp * HALF);
+#pragma unroll
+              for (int i4 = 0; i4 < HALF / 4; ++i4) {
+                const float4 c = cs[i4], sgn = sn[i4];
+                const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sgn.x, sgn.y, sgn.z, sgn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int i = 4 * i4 + e;
+                  const float u = h[i], v = h[i + HALF];
+                  h[i] = u * cc[e] - v * sv[e];
+                  h[i + HALF] = u * sv[e] + v * cc[e];
+                }
+              }
+            }
+            if (live) {
+              auto store_head = [&](bf* dst) {
+#pragma unroll
+                for (int q8 = 0; q8 < HD / 8; ++q8) {
+                  __nv_bfloat162 h0 = __floats2bfloat162_rn(h[8 * q8], h[8 * q8 + 1]), h1 = __floats2bfloat162_rn(h[8 * q8 + 2], h[8 * q8 + 3]);
+                  __nv_bfloat162 h2 = __floats2bfloat162_rn(h[8 * q8 + 4], h[8 * q8 + 5]), h3 = __floats2bfloat162_rn(h[8 * q8 + 6], h[8 * q8 + 7]);
+                  uint4 u;
+                  u.x = *reinterpret_cast<uint32_t*>(&h0);
+                  u.y = *reinterpret_cast<uint32_t*>(&h1);
+                  u.z = *reinterpret_cast<uint32_t*>(&h2);
+                  u.w = *reinterpret_cast<uint32_t*>(&h3);
+                  *reinterpret_cast<uint4*>(dst + 8 * q8) = u;
+                }
+              };
+              if (kind == 0) {
+                store_head((bf*)a.q_out + ((long long)tok * a.nh + head) * HD);
+              } else {
+                const int kvh = kind == 1 ? head - a.nh : head - a.nh - a.nkv;
+                bf* packed = (bf*)(kind == 1 ? a.k_new : a.v_new);
+                if (packed) store_head(packed + ((long long)tok * a.nkv + kvh) * HD);
+                bf* pages = (bf*)(kind == 1 ? a.k_pages : a.v_pages);
+                if (pages) store_head(pages + kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv) * HD);
+              }
+            }
+          }
+        }
+      } else if (SWAP) {
         // lanes are tokens (p.o of them), columns are features (p.n, or gate|up blocks of 128 + 128)
         constexpr int VEC = 16 / (int)sizeof(OT);      // outputs per 16-byte store
-        const int width = EPI ? p.gated_features : p.n;
+        const int width = EPI == 1 ? p.gated_features : p.n;
         const bool vec_ok = width % VEC == 0;
         OT* out = (OT*)p.out + (long long)split * p.n * p.o;
 #pragma unroll
@@ -317,15 +414,15 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
           if (o0 + mt * BM >= p.o) break;
           const int tok = o0 + mt * BM + warp * 32 + lane;
           OT* row = out + (long long)tok * width;
-          constexpr int COLS = EPI ? TN / 2 : TN;
+          constexpr int COLS = EPI == 1 ? TN / 2 : TN;
 #pragma unroll
           for (int c0 = 0; c0 < COLS; c0 += 16) {
-            const int f0 = EPI ? n0 / 2 + c0 : n0 + c0;      // first feature of this run (a gated tile: TN / 2 features)
+            const int f0 = EPI == 1 ? n0 / 2 + c0 : n0 + c0;      // first feature of this run (a gated tile: TN / 2 features)
             if (f0 >= width) break;
             float v[16];
             uint32_t r[16];
             tmem_ld16(lane_base + (uint32_t)(mt * TN + c0), r);
-            if (EPI) {
+            if (EPI == 1) {
               uint32_t ru[16];
               tmem_ld16(lane_base + (uint32_t)(mt * TN + TN / 2 + c0), ru);
               asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -634,6 +731,47 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
 #undef GATED
 #undef PLAIN
 #undef WIDE
+}
+
+// 1 when llg_gemm_tc_qkv takes this q/k/v projection: 256 tokens or more (tokens are the tensor cores' rows), head
+// size 64 or 128, rotation over the whole head by halves (or none), operands as llg_gemm_tc_supported wants them.
+LLG_API int llg_gemm_tc_qkv_supported(int n, int k, int hd, int has_rotation, int rotary_dim, int pairing) {
+  return n >= 256 && k > 0 && k % 8 == 0 && (hd == 64 || hd == 128) && (!has_rotation || (pairing == 0 && rotary_dim == hd));
+}
+
+// The q/k/v projection of a prompt step with the preparation of queries and keys as its epilogue: what llg_gemm_tc into a
+// float32 array followed by llg_qk_prep gives, in one kernel.  x [n][k] and w [(nh + 2 nkv) * hd][k] are bfloat16, all
+// outputs named in `prep` are bfloat16; prep->qkv is ignored.
+LLG_API int llg_gemm_tc_qkv(const void* x, const void* w, int n, int k, const QkPrepArgs* prep, cudaStream_t stream) {
+  const QkPrepArgs& a = *prep;
+  const int o = (a.nh + 2 * a.nkv) * a.hd;
+  LLG_REQUIRE(a.nh > 0 && a.nkv >= 0 && llg_gemm_tc_supported(x, w, n, o, k), "gemm_tc_qkv: needs k %% 8 == 0 and 16-byte aligned operands");
+  LLG_REQUIRE(llg_gemm_tc_qkv_supported(n, k, a.hd, a.cos_table != nullptr, a.rotary_dim, a.pairing),
+              "gemm_tc_qkv: needs 256 tokens or more, head size 64 or 128 and rotation over the whole head by halves "
+              "(n=%d hd=%d rotary_dim=%d pairing=%d)", n, a.hd, a.rotary_dim, a.pairing);
+  LLG_REQUIRE(a.n_tokens == n && a.positions && a.q_out, "gemm_tc_qkv: the preparation's sizes do not fit the product");
+  LLG_REQUIRE(!a.k_pages || (a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
+              "gemm_tc_qkv: a cache write needs page_table, slots and seq_of_token");
+  if ((a.q_norm_w || a.k_norm_w) && a.bias)
+    LLG_REQUIRE(a.norm_w_dtype == a.bias_dtype, "gemm_tc_qkv: norm weights and bias must share a dtype");
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
+  LLG_REQUIRE(aligned(a.cos_table) && aligned(a.sin_table) && aligned(a.q_out) && aligned(a.k_new) && aligned(a.v_new) &&
+                  aligned(a.k_pages) && aligned(a.v_pages),
+              "gemm_tc_qkv: tables and outputs must be 16-byte aligned");
+  const int nkb = (k + BK - 1) / BK;
+  GemmParams ps{nullptr, /*n=*/o, /*o=*/n, k, nkb, 0, 0, BM, a};
+  CUtensorMap map_w, map_x;
+  LLG_REQUIRE(tensor_map(x, n, k, BM, &map_x) && tensor_map(w, o, k, 256, &map_w),
+              "gemm_tc_qkv: cuTensorMapEncodeTiled failed or is not available");
+  // one or two token tiles per block, by the rounds of blocks over the SMs (as in llg_gemm_tc)
+  const long long sms = llg_sm_count();
+  const long long t1 = (long long)((n + BM - 1) / BM) * ((o + 255) / 256), t2 = (long long)((n + 2 * BM - 1) / (2 * BM)) * ((o + 255) / 256);
+  const bool two = (double)((t2 + sms - 1) / sms) * 2 * 0.85 < (double)((t1 + sms - 1) / sms);
+  if (a.hd == 128)
+    return two ? launch<256, 3, __nv_bfloat16, 2, 2, 1>(&map_x, &map_w, ps, 1, stream)
+               : launch<256, 4, __nv_bfloat16, 1, 2, 1>(&map_x, &map_w, ps, 1, stream);
+  return two ? launch<256, 3, __nv_bfloat16, 2, 3, 1>(&map_x, &map_w, ps, 1, stream)
+             : launch<256, 4, __nv_bfloat16, 1, 3, 1>(&map_x, &map_w, ps, 1, stream);
 }
 
 // Error code that a block recorded when one of its waits ran out (0 = none); clears it.  Synchronises the device.

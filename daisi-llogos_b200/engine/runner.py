@@ -31,7 +31,7 @@ from ..parts.norm import RmsNorm
 
 _API_FIELDS = ["add_rmsnorm", "gemm_tc", "gemm_simt", "qk_prep", "kv_write", "silu_mul", "attn_prefill_tc",
                "attn_prefill_mma", "attn_prefill_simt", "attn_decode_tma", "attn_decode_mma", "attn_decode_simt",
-               "err_elementwise", "err_gemm_tc", "err_gemm_simt", "err_attn_tc", "err_attn_mma", "err_attn_simt",
+               "gemm_tc_qkv", "err_elementwise", "err_gemm_tc", "err_gemm_simt", "err_attn_tc", "err_attn_mma", "err_attn_simt",
                "err_attn_decode_tma"]
 
 
@@ -59,7 +59,7 @@ class _RunnerStep(Structure):
         ("len_before", c_void_p), ("tiles", c_void_p), ("n_tiles", c_int), ("max_len_after", c_int),
         ("prefill_kind", c_int), ("decode_kind", c_int), ("decode_splits", c_int), ("decode_balance", c_int),
         ("tc_qkv", c_int), ("tc_o", c_int), ("tc_gate_up", c_int), ("tc_down", c_int),
-        ("splits_qkv", c_int), ("splits_o", c_int), ("splits_down", c_int),
+        ("splits_qkv", c_int), ("splits_o", c_int), ("splits_down", c_int), ("fused_qkv", c_int),
         ("residual", c_void_p), ("norm_out", c_void_p), ("qkv", c_void_p), ("q", c_void_p), ("k_new", c_void_p),
         ("v_new", c_void_p), ("attn_out", c_void_p), ("proj", c_void_p), ("act", c_void_p), ("ffn_out", c_void_p),
         ("gate_up", c_void_p), ("gate_up_rows", c_int), ("attn_scratch", c_void_p), ("attn_counters", c_void_p),
@@ -74,6 +74,7 @@ _ENTRIES = {
     "add_rmsnorm": ("elementwise", "llg_add_rmsnorm"), "qk_prep": ("elementwise", "llg_qk_prep"),
     "kv_write": ("elementwise", "llg_kv_write"), "silu_mul": ("elementwise", "llg_silu_mul"),
     "gemm_tc": ("gemm_tc", "llg_gemm_tc"), "gemm_simt": ("gemm_simt", "llg_gemm_simt"),
+    "gemm_tc_qkv": ("gemm_tc", "llg_gemm_tc_qkv"),
     "attn_prefill_tc": ("attention_tc", "llg_attn_prefill_tc"), "attn_prefill_mma": ("attention_mma", "llg_attn_prefill_mma"),
     "attn_prefill_simt": ("attention_simt", "llg_attn_prefill_simt"),
     "attn_decode_tma": ("attention_decode_tma", "llg_attn_decode_tma"), "attn_decode_mma": ("attention_mma", "llg_attn_decode_mma"),
@@ -151,7 +152,7 @@ class BlockRunner:
         spec = model.spec
         if not spec.schedule or any(e.cache_of is not None for e in spec.schedule):
             return None
-        layers, keep, geom = [], [], None
+        layers, keep, geom, fusable = [], [], None, 1
         for e_i, e in enumerate(spec.schedule):
             block = model.blocks[e.layer]
             if type(block) is not PreNormBlock or set(block.parts) != {"norm1", "mixer", "norm2", "ffn"}:
@@ -195,11 +196,13 @@ class BlockRunner:
                 keep += [rot.cos, rot.sin]
             L.w_o, L.w_gate_up, L.w_down = mx.w_o.data_ptr(), ff.w_gate_up.data_ptr(), ff.w_down.data_ptr()
             L.window, L.scale = mx.window, mx.scale
+            if rot is not None and not (rot.pairing == 0 and rot.rotary_dim == mx.hd):
+                fusable = 0                                 # the q/k/v product's own epilogue rotates whole heads by halves only
             L.k_pages, L.v_pages, L.page_table = view.k_pages.data_ptr(), view.v_pages.data_ptr(), view.page_table.data_ptr()
             L.table_width, L.ring_pages, L.n_pages = view.page_table.shape[1], view.ring_pages, view.k_pages.shape[0]
             keep += [view.k_pages, view.v_pages, view.page_table]
             layers.append(L)
-        return cls(model, cache, layers, keep, geom)
+        return cls(model, cache, layers, keep, dict(geom, fusable_rotation=fusable))
 
     # ---- one step ----------------------------------------------------------------------------
     def run(self, ctx, residual: torch.Tensor) -> Branch:
@@ -222,6 +225,9 @@ class BlockRunner:
         s.cu_tokens, s.len_before = ctx.cu_tokens.data_ptr(), ctx.len_before.data_ptr()
         s.max_len_after = ctx.max_len_after
         s.tc_qkv, s.tc_o, s.tc_gate_up, s.tc_down = tc(hidden), tc(q_dim), tc(hidden), tc(inter)
+        # the rule of kernels/ops.py gemm_tc_qkv_supported, on sizes
+        s.fused_qkv = int(ops.USE_FUSED_QKV and not ctx.decode and bool(s.tc_qkv) and n > 512 and hd in (64, 128)
+                          and g.get("fusable_rotation", 1) == 1)
         s.splits_qkv, s.splits_o, s.splits_down = splits(qkv_dim, hidden), splits(hidden, q_dim), splits(hidden, inter)
         s.residual = residual.data_ptr()
         s.norm_out = ctx.buffer("norm.out", (n, hidden)).data_ptr()
@@ -251,7 +257,7 @@ class BlockRunner:
             tiles = ctx.query_tiles(tq)
             s.tiles, s.n_tiles = tiles.data_ptr(), tiles.shape[0]
             s.prefill_kind = 2 if ops._use_tc_attn(dtype, hd) else 1 if ops._use_mma(dtype, hd) else 0
-        need = ["add_rmsnorm", "qk_prep"]
+        need = ["add_rmsnorm", "qk_prep"] + (["gemm_tc_qkv"] if s.fused_qkv else [])
         need.append("gemm_tc" if (s.tc_qkv or s.tc_o or s.tc_down or (s.tc_gate_up and bf16)) else "gemm_simt")
         if not (s.tc_qkv and s.tc_o and s.tc_down):
             need.append("gemm_simt")

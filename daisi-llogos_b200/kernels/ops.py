@@ -174,6 +174,7 @@ def _load_lib(name: str):
         lib.llg_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
         lib.llg_gemm_tc_splits.argtypes = [c_int, c_int]
         lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_gemm_tc_qkv.argtypes = [c_void_p, c_void_p, c_int, c_int, POINTER(_QkPrepArgs), c_void_p]
     elif name == "attention_simt":
         lib.llg_attn_prefill_simt.argtypes = [POINTER(_PrefillArgs), c_int, c_void_p]
         lib.llg_attn_decode_simt.argtypes = [POINTER(_DecodeArgs), c_void_p, c_int, c_void_p]
@@ -336,8 +337,16 @@ def qk_prep(qkv: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
     lib = _lib("elementwise")
     s, n, width = qkv.shape
     assert width == (n_heads + 2 * n_kv_heads) * head_dim
-    a = _QkPrepArgs()
+    a = _prep_args(n, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim, pairing,
+                   positions, q_out, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
     a.qkv, a.qkv_dtype, a.n_partials, a.partial_stride = _ptr(qkv), _dt(qkv), s, n * width
+    _check(lib, lib.llg_qk_prep(byref(a), _dt(q_out), _stream()))
+
+
+def _prep_args(n, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim, pairing,
+               positions, q_out, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots) -> "_QkPrepArgs":
+    """The argument block of the q/k/v preparation, without the q/k/v input itself."""
+    a = _QkPrepArgs()
     a.q_norm_w, a.k_norm_w = _ptr(q_norm_w), _ptr(k_norm_w)
     a.norm_w_dtype = _dt(q_norm_w) if q_norm_w is not None else F32
     a.norm_eps = float(norm_eps)
@@ -359,7 +368,36 @@ def qk_prep(qkv: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
     for t in (k_new, v_new, k_pages, v_pages):
         if t is not None and t.dtype != q_out.dtype:
             raise KernelError("qk_prep: all outputs must share one dtype")
-    _check(lib, lib.llg_qk_prep(byref(a), _dt(q_out), _stream()))
+    return a
+
+
+USE_FUSED_QKV = True        # tests switch it off to compare with the product followed by the preparation kernel
+
+
+def gemm_tc_qkv_supported(x: torch.Tensor, w: torch.Tensor, head_dim: int, rotary_dim: int, pairing: int) -> bool:
+    """Whether ``gemm_tc_qkv`` takes this q/k/v projection: tensor-core operands, 513 rows or more (with fewer the
+    product splits its sums over blocks, which leaves partial sums and no place for an epilogue), head size 64 or
+    128, rotation over the whole head by halves or none (``rotary_dim`` 0)."""
+    return (USE_FUSED_QKV and gemm_tc_supported(x, w) and x.shape[0] > 512 and head_dim in (64, 128)
+            and (rotary_dim == 0 or (pairing == 0 and rotary_dim == head_dim)))
+
+
+def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
+                q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], norm_eps: float,
+                bias: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                rotary_dim: int, pairing: int, positions: torch.Tensor, q_out: torch.Tensor,
+                k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
+                k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
+                seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
+    """The q/k/v projection ``x w^T`` on the tensor cores with ``qk_prep`` as its epilogue (one kernel; the float32
+    q/k/v array is never written).  Same arguments and results as ``gemm_tc`` followed by ``qk_prep``."""
+    lib = _lib("gemm_tc")
+    n, k = x.shape
+    assert w.shape == ((n_heads + 2 * n_kv_heads) * head_dim, k) and q_out.dtype == torch.bfloat16
+    a = _prep_args(n, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim, pairing,
+                   positions, q_out, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
+    _check(lib, lib.llg_gemm_tc_qkv(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), n, k, byref(a), _stream()))
 
 
 def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, seq_of_token, slots,

@@ -99,10 +99,20 @@ class Attention(Mixer):
         ops = ctx.ops
         n = x.shape[0]
         nkv_in = self.nkv if self.own_kv else 0
-        # float32 (partials when the product splits K): bias, norm and rotation see the unrounded sums whatever
-        # the size of the step, so q and k are rounded once
-        qkv = linear(ctx, x, self.w_qkv, "attn.qkv", torch.float32)
         rot = self.encoding.rotation() if self.encoding is not None else None
+        # A large prompt step on the tensor cores prepares q and k in the projection's own epilogue.  Otherwise the
+        # projection writes float32 (partials when the product splits K) and a second kernel prepares them; either
+        # way bias, norm and rotation see the unrounded sums, so q and k are rounded once.
+        fused_qkv = getattr(ops, "gemm_tc_qkv_supported", None)
+        fused = (not ctx.decode and fused_qkv is not None
+                 and fused_qkv(x, self.w_qkv, self.hd, rot.rotary_dim if rot else 0, rot.pairing if rot else 0))
+        if fused:
+            def prep(qkv_, **kw):
+                ops.gemm_tc_qkv(x, self.w_qkv, **kw)
+            qkv = None
+        else:
+            prep = ops.qk_prep
+            qkv = linear(ctx, x, self.w_qkv, "attn.qkv", torch.float32)
         q = ctx.buffer("attn.q", (n, self.nh, self.hd))
         out = ctx.buffer("attn.out", (n, self.nh * self.hd))
         common = dict(n_heads=self.nh, n_kv_heads=nkv_in, head_dim=self.hd,
@@ -136,14 +146,14 @@ class Attention(Mixer):
                 k_new = ctx.buffer("attn.k_new" + suffix, (n, self.nkv, self.hd))
                 v_new = ctx.buffer("attn.v_new" + suffix, (n, self.nkv, self.hd))
                 if write_now:
-                    ops.qk_prep(qkv, **common, k_new=k_new, v_new=v_new, k_pages=cache.k_pages, v_pages=cache.v_pages,
-                                page_table=cache.page_table, ring_pages=cache.ring_pages,
-                                seq_of_token=ctx.seq_of_token, slots=ctx.slots)
+                    prep(qkv, **common, k_new=k_new, v_new=v_new, k_pages=cache.k_pages, v_pages=cache.v_pages,
+                         page_table=cache.page_table, ring_pages=cache.ring_pages,
+                         seq_of_token=ctx.seq_of_token, slots=ctx.slots)
                 else:
-                    ops.qk_prep(qkv, **common, k_new=k_new, v_new=v_new)
+                    prep(qkv, **common, k_new=k_new, v_new=v_new)
                 cache.shared["k_new"], cache.shared["v_new"] = k_new, v_new
             else:
-                ops.qk_prep(qkv, **common)
+                prep(qkv, **common)
                 k_new, v_new = cache.shared["k_new"], cache.shared["v_new"]
             tq = ops.prefill_tile_queries(q.dtype, self.hd)
             ops.attn_prefill(q, k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,

@@ -568,6 +568,78 @@ def test_attention_with_whole_number_scores_rounds_like_the_plain_model(ops, hd,
         assert ops.attn_tc_status() == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,k,norm,bias,rotate,pages", [(3, 1, 128, 264, True, True, True, True), (5, 2, 64, 96, False, False, True, False),
+                                                            (2, 2, 128, 512, True, False, False, True), (4, 1, 64, 200, False, True, True, True)])
+def test_qkv_product_with_the_preparation_as_its_epilogue(ops, nh, nkv, hd, k, norm, bias, rotate, pages):
+    """The q/k/v projection whose epilogue normalises, adds the bias, rotates and writes q, k and v (one kernel)
+    against the plain formulas, and against the product followed by the preparation kernel (the same float32
+    sums, so at most a value here and there rounds the other way).  Two sequences in one step of 700 tokens, the
+    second continuing at position 70; widths that are no multiple of the tile."""
+    dtype = torch.bfloat16
+    counts, before = [430, 270], [0, 70]
+    n = sum(counts)
+    o = (nh + 2 * nkv) * hd
+    x = rnd((n, k), 81, dtype)
+    w = rnd((o, k), 82, dtype, 1.0 / math.sqrt(k))
+    qw = (rnd((hd,), 83, dtype, 0.1) + 1) if norm else None
+    kw_ = (rnd((hd,), 84, dtype, 0.1) + 1) if norm else None
+    b = rnd((o,), 85, dtype, 0.3) if bias else None
+    pos = torch.cat([torch.arange(bf, bf + c) for bf, c in zip(before, counts)]).to(torch.int32)
+    seq_of = torch.repeat_interleave(torch.arange(2), torch.tensor(counts)).to(torch.int32)
+    inv = P.rope_inverse_frequencies(hd, 3e4, None)
+    ang = torch.arange(600, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    # plain: sums, per-head norm, bias, rotation
+    y = P.linear(x, w).view(n, nh + 2 * nkv, hd)
+    q, kk, v = y[:, :nh], y[:, nh:nh + nkv], y[:, nh + nkv:]
+    if norm:
+        q, kk = P.per_head_rms_norm(q, qw, 1e-5), P.per_head_rms_norm(kk, kw_, 1e-5)
+    if bias:
+        bb = b.double().view(nh + 2 * nkv, hd)
+        q, kk, v = q + bb[:nh], kk + bb[nh:nh + nkv], v + bb[nh + nkv:]
+    if rotate:
+        q, kk = P.rope_rotate(q, pos.tolist(), inv, "half"), P.rope_rotate(kk, pos.tolist(), inv, "half")
+    d = lambda t: None if t is None else t.to(DEV)
+    ring, n_pages = 8, 16
+    table = torch.zeros(3, ring, dtype=torch.int32)
+    table[1] = torch.tensor([9, 3, 7, 0, 11, 1, 5, 10])
+    table[2] = torch.tensor([2, 8, 4, 6, 12, 13, 14, 15])
+    slots = torch.tensor([2, 1], dtype=torch.int32)
+    common = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, q_norm_w=d(qw), k_norm_w=d(kw_), norm_eps=1e-5, bias=d(b),
+                  cos=d(cos) if rotate else None, sin=d(sin) if rotate else None, rotary_dim=hd if rotate else 0, pairing=0,
+                  positions=d(pos))
+    outs = {}
+    for way in ("fused", "two kernels"):
+        q_out = torch.full((n, nh, hd), float("nan"), dtype=dtype, device=DEV)
+        k_new, v_new = torch.full((n, nkv, hd), float("nan"), dtype=dtype, device=DEV), torch.full((n, nkv, hd), float("nan"), dtype=dtype, device=DEV)
+        kp, vp = torch.zeros(n_pages, nkv, 64, hd, dtype=dtype, device=DEV), torch.zeros(n_pages, nkv, 64, hd, dtype=dtype, device=DEV)
+        extra = dict(k_pages=kp, v_pages=vp, page_table=d(table), ring_pages=ring, seq_of_token=d(seq_of), slots=d(slots)) if pages else {}
+        if way == "fused":
+            assert ops.gemm_tc_qkv_supported(d(x), d(w), hd, hd if rotate else 0, 0)
+            ops.gemm_tc_qkv(d(x), d(w), **common, q_out=q_out, k_new=k_new, v_new=v_new, **extra)
+        else:
+            sums = torch.empty(1, n, o, device=DEV)
+            ops.gemm_tc(d(x), d(w), sums)
+            ops.qk_prep(sums, **common, q_out=q_out, k_new=k_new, v_new=v_new, **extra)
+        outs[way] = (q_out.cpu(), k_new.cpu(), v_new.cpu(), kp.cpu(), vp.cpu())
+    assert ops.gemm_tc_status() == 0
+    fq, fk, fv, fkp, fvp = outs["fused"]
+    check(fq, q, dtype, "q")
+    check(fk, kk, dtype, "k")
+    check(fv, v, dtype, "v")
+    for name_, a_, b_ in zip("qkv", outs["fused"][:3], outs["two kernels"][:3]):
+        off = a_.float() != b_.float()
+        assert float(off.float().mean()) < 0.005, (name_, int(off.sum()))
+        assert bool(((a_.float() - b_.float()).abs()[off] <= b_.float().abs()[off] * 2.0 ** -7 + 1e-6).all()), name_
+    if pages:
+        for t in range(n):                              # every key and value lies where its position says
+            s_, p_ = int(slots[seq_of[t]]), int(pos[t])
+            pg = int(table[s_, (p_ // 64) % ring])
+            assert torch.equal(fkp[pg, :, p_ % 64], fk[t]) and torch.equal(fvp[pg, :, p_ % 64], fv[t]), t
+    else:
+        assert float(fkp.abs().sum()) == 0
+
+
 def test_kernels_refuse_what_they_cannot_do(ops):
     q = torch.zeros(1, 2, 272, device=DEV)
     kp = torch.zeros(1, 1, 64, 272, device=DEV)

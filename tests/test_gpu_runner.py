@@ -26,8 +26,8 @@ def engines(llogos, model_dir, dtype, monkeypatch, **kw):
 @pytest.mark.parametrize("name", list(TINY))
 def test_native_chain_gives_the_parts_bits(llogos, model_dirs, monkeypatch, name, dtype, graphs):
     cfg = TINY[name]
-    a, b, c = random_tokens(cfg["vocab_size"], [300, 90, 41], 61)
-    native, by_parts = engines(llogos, model_dirs[name], dtype, monkeypatch, max_tokens=64 * 10, use_graphs=graphs)
+    a, b, c, d, e = random_tokens(cfg["vocab_size"], [300, 90, 41, 300, 290], 61)
+    native, by_parts = engines(llogos, model_dirs[name], dtype, monkeypatch, max_tokens=64 * 18, use_graphs=graphs)
     outs = []
     for eng in (native, by_parts):
         got = []
@@ -38,6 +38,11 @@ def test_native_chain_gives_the_parts_bits(llogos, model_dirs, monkeypatch, name
             got.append(eng.step([(sa, [a[290 + j]]), (sc, [c[30 + j]])]))
         for s in (sa, sb, sc):
             eng.close(s)
+        # 590 tokens in one step: above 512 rows the q/k/v product prepares queries and keys itself where it can
+        sd, se = eng.open(), eng.open()
+        got.append(eng.step([(sd, d), (se, e)], [[0, 299], [289]]))
+        eng.close(sd)
+        eng.close(se)
         eng.cache.audit()
         outs.append([g.clone() for g in got])
     for k, (x, y) in enumerate(zip(*outs)):
