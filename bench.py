@@ -121,6 +121,122 @@ def model_numbers(cfg, n_layers):
             "kv_bytes_per_token": 2 * kv * 2 * n_layers}
 
 
+def probe_decode_attention(torch, ops, shape, pk):
+    """Decode attention alone with CUDA events: the cache contents are rotated through several layers' worth of pages
+    so that L2 holds none of them.  One line per batch shape: bytes, time, rate, fraction of the copy bandwidth."""
+    dev = "cuda:0"
+    nh, nkv, hd = shape["num_attention_heads"], shape["num_key_value_heads"], shape["head_dim"]
+    g = torch.Generator().manual_seed(0)
+    cases = [("1 x 8192", [8192]), ("8 x 8192", [8192] * 8), ("64 x 8192", [8192] * 64), ("8 x 2048", [2048] * 8),
+             ("8 x 32768", [32768] * 8), ("one of 8000, seven of 100", [8000] + [100] * 7),
+             ("8, lengths 128..8192", [int(x) for x in torch.randint(128, 8192, (8,), generator=g)]),
+             ("64, lengths 128..8192", [int(x) for x in torch.randint(128, 8192, (64,), generator=g)]),
+             ("256 x 500", [500] * 256)]
+    for label, lens in cases:
+        b = len(lens)
+        pages_per = [(n + 63) // 64 for n in lens]
+        n_pages = sum(pages_per) + 1
+        layer_bytes = n_pages * nkv * 64 * hd * 2 * 2
+        layers = max(2, min(16, int(600e6 // layer_bytes) + 1))
+        kps = [torch.randn(n_pages, nkv, 64, hd, device=dev).bfloat16() for _ in range(layers)]
+        vps = [torch.randn(n_pages, nkv, 64, hd, device=dev).bfloat16() for _ in range(layers)]
+        ring = max(pages_per)
+        table = torch.zeros(b + 1, ring, dtype=torch.int32)
+        p = 0
+        for i in range(b):
+            for j in range(pages_per[i]):
+                table[i, j] = p
+                p += 1
+        table = table.to(dev)
+        slots = torch.arange(b, dtype=torch.int32, device=dev)
+        lb = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=dev)
+        q = torch.randn(b, nh, hd, device=dev).bfloat16()
+        out = torch.empty(b, nh * hd, device=dev, dtype=torch.bfloat16)
+        nbytes = sum(lens) * nkv * hd * 2 * 2
+        plan = ops.attn_decode_plan(torch.bfloat16, b, nh, nkv, hd, max(lens))
+        scratch = torch.empty(max(1, plan.scratch_floats), device=dev)
+        counters = torch.zeros(max(1, plan.n_counters), dtype=torch.int32, device=dev)
+
+        def run(i):
+            ops.attn_decode(q, kps[i % layers], vps[i % layers], table, ring, slots, lb, out, scratch,
+                            scale=hd ** -0.5, window=0, plan=plan, counters=counters)
+        for i in range(layers + 3):
+            run(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(40):
+            run(i)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) / 40 * 1e3
+        gbs = nbytes / us / 1e3
+        print(f"decode attention ({plan.kind}) {label:28s} {nbytes / 1e6:8.1f} MB {us:8.1f} us {gbs:7.0f} GB/s "
+              f"{gbs / pk['hbm_gbs']:.2f} of {pk['hbm_gbs']:.0f}", flush=True)
+        del kps, vps
+        torch.cuda.empty_cache()
+    return 0
+
+
+def probe_leave_one_out(torch, L, ops, cfg, batch, context):
+    """The decode step of the whole model, recorded as a CUDA graph with one kernel left out at a time (the results are
+    then meaningless; only the time is read): what each kernel costs where it stands, overlap and boundaries included."""
+    os.environ["LLOGOS_RUNNER"] = "0"           # the parts call the kernels one by one, so each can be left out
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
+    gen = torch.Generator().manual_seed(1)
+    names = ("add_rmsnorm", "qk_prep", "attn_decode", "gemm_tc")
+    real = {n: getattr(ops, n) for n in names}
+    q_rows = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    h, inter, vocab, n_layers = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+
+    def measure(patch):
+        for n, f in real.items():
+            setattr(ops, n, f)
+        patch()
+        eng = L.engine.Engine(model, max_tokens=batch * context, max_seq_len=context, n_slots=batch)
+        steps, warmup = 16, 4
+        slots = [eng.open() for _ in range(batch)]
+        for s in slots:
+            eng.assume(s, context - (steps + warmup))
+        tok = torch.randint(0, vocab, (steps + warmup, batch), generator=gen).tolist()
+        for i in range(warmup):
+            eng.step([(s, [tok[i][j]]) for j, s in enumerate(slots)])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warmup, warmup + steps):
+            eng.step([(s, [tok[i][j]]) for j, s in enumerate(slots)])
+        e1.record()
+        torch.cuda.synchronize()
+        del eng
+        torch.cuda.empty_cache()
+        return e0.elapsed_time(e1) / steps
+
+    def without_product(pred):
+        def f(x, w, out, **kw):
+            if not pred(w, kw):
+                real["gemm_tc"](x, w, out, **kw)
+        return lambda: setattr(ops, "gemm_tc", f)
+
+    base = measure(lambda: None)
+    print(f"batch {batch} context {context}: whole step {base:.3f} ms, {base / n_layers * 1e3:.1f} us per layer (head included)")
+    cases = [("add_rmsnorm (two per layer)", lambda: setattr(ops, "add_rmsnorm", lambda *a, **k: None), n_layers),
+             ("qk_prep", lambda: setattr(ops, "qk_prep", lambda *a, **k: None), n_layers),
+             ("attn_decode", lambda: setattr(ops, "attn_decode", lambda *a, **k: None), n_layers),
+             ("q/k/v product", without_product(lambda w, kw: w.shape[0] == q_rows and not kw.get("gated_features")), n_layers),
+             ("output product", without_product(lambda w, kw: tuple(w.shape) == (h, cfg["num_attention_heads"] * cfg["head_dim"])
+                                                and w.shape[0] != q_rows), n_layers),
+             ("gate/up product", without_product(lambda w, kw: kw.get("gated_features", 0) > 0), n_layers),
+             ("down product", without_product(lambda w, kw: tuple(w.shape) == (h, inter)), n_layers),
+             ("head product", without_product(lambda w, kw: w.shape[0] == vocab), 1)]
+    for label, patch, per in cases:
+        ms = measure(patch)
+        print(f"  without {label:30s} {ms:.3f} ms: {(base - ms) * 1e3 / per:7.1f} us each", flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -135,6 +251,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-workloads", action="store_true", help="leave out the workloads of the other shapes and the ragged run")
+    ap.add_argument("--probe", choices=["decode-attention", "leave-one-out"],
+                    help="instead of the bench line, print a table: decode attention alone over batch shapes, or what "
+                         "the decode step loses when each kernel in turn is left out of the recorded graph")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -153,6 +272,10 @@ def main():
     L = importlib.import_module("llogos_b200")
     ops = importlib.import_module("daisi-llogos_b200.kernels.ops")
     pk = peaks()
+    if args.probe == "decode-attention":
+        return probe_decode_attention(torch, ops, SHAPES[args.shape][1], pk)
+    if args.probe == "leave-one-out":
+        return probe_leave_one_out(torch, L, ops, dict(SHAPES[args.shape][1]), args.batch, args.context)
     shape_name, shape = SHAPES[args.shape]
     if args.layers <= 0:
         args.layers = shape["num_hidden_layers"]
