@@ -5,6 +5,7 @@ back: a tensor that is not on the GPU, or a library that cannot be built, is an 
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, byref, c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -511,7 +512,9 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
         _check(lib, lib.llg_attn_prefill_simt(byref(a), _dt(q), _stream()))
 
 
-USE_TMA_DECODE_ATTENTION = True     # tests switch it off to reach the cp.async kernel at head sizes 64 and 128
+# tests switch it off to reach the cp.async kernel at head sizes 64 and 128; LLOGOS_DECODE_ATTENTION=mma does the same
+# for a whole process (for comparing the two kernels with the same measurement program)
+USE_TMA_DECODE_ATTENTION = os.environ.get("LLOGOS_DECODE_ATTENTION", "tma") != "mma"
 
 
 def _use_tma_decode(dtype: torch.dtype, head_dim: int, n_heads: int, n_kv_heads: int, n_seqs: int) -> bool:
