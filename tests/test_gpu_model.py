@@ -7,7 +7,7 @@ import torch
 
 import plain_model as P
 from compare import Reference, reference
-from conftest import TINY, read_weights, random_tokens
+from conftest import INIT, INIT_OF, TINY, read_weights, random_tokens
 
 pytestmark = pytest.mark.gpu
 
@@ -117,6 +117,37 @@ def test_long_decoding_from_the_first_token(llogos, model_dirs, name, dtype):
                 rb.check(lg[1], [p], dtype, ("b", p))
         if p == 199:
             eng.close(sb)
+
+
+@pytest.mark.parametrize("graphs", [True, False], ids=["graph", "eager"])
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+@pytest.mark.parametrize("name", ["wide", "qwen2", "deep"])
+def test_decoding_across_the_length_bound_of_the_recorded_steps(llogos, tmp_path, name, dtype, graphs):
+    """Decode steps are planned and recorded for lengths up to a bound (1,024, then 2,048): a sequence that grows
+    from 1,000 to 1,060 tokens moves at position 1,024 to the next bound's workspace, counters and recorded launches
+    (a first step run directly, the following ones replayed), beside a short sequence that stays far below.  Every
+    decoded position of both against the plain model.  (The kernels take the lengths themselves from the device;
+    the bound only sizes their scratch and their split of the keys, so a bound that is too small must not change a
+    result either: the same test passes with the bound held at 1,024.)"""
+    cfg = dict(TINY[name], max_position_embeddings=2304)
+    d = str(tmp_path / "model")
+    llogos.weights.write_random_model(d, cfg, seed=77, **INIT_OF.get(name, INIT))
+    w = read_weights(llogos, d)
+    a, b = random_tokens(cfg["vocab_size"], [1060, 300], 41)
+    ra, rb = Reference(w, cfg, a), Reference(w, cfg, b)
+    model = llogos.weights.load_model(d, dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 24, use_graphs=graphs)
+    sa, sb = eng.open(), eng.open()
+    lg = eng.step([(sa, a[:1000]), (sb, b[:240])])
+    ra.check(lg[0], [999], dtype, "a, prompt end")
+    rb.check(lg[1], [239], dtype, "b, prompt end")
+    for i in range(60):
+        lg = eng.step([(sa, [a[1000 + i]]), (sb, [b[240 + i]])])
+        ra.check(lg[0], [1000 + i], dtype, ("a", 1000 + i))
+        rb.check(lg[1], [240 + i], dtype, ("b", 240 + i))
+    eng.close(sa)
+    eng.close(sb)
+    eng.cache.audit()
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
