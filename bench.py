@@ -51,8 +51,28 @@ QWEN25_14B = {
     "vocab_size": 152064, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "max_position_embeddings": 131072,
     "tie_word_embeddings": False,
 }
+# Further sizes of the same architecture, for looking at the kernels away from the headline shape (`--shape`): a
+# small model with heads of 64 and tied embeddings, and the layer sizes of a 70B model (run with --layers 8 or so:
+# all 80 layers do not fit beside a cache).
+LLAMA_1B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 16, "hidden_size": 2048,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192,
+    "vocab_size": 128256, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 131072,
+    "attention_bias": False, "tie_word_embeddings": True,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+}
+LLAMA_70B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 80, "hidden_size": 8192,
+    "num_attention_heads": 64, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 28672,
+    "vocab_size": 128256, "rope_theta": 500000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 131072,
+    "attention_bias": False, "tie_word_embeddings": False,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+}
 SHAPES = {"llama-3.1-8b": ("Llama-3.1-8B shape", LLAMA_8B), "qwen3-8b": ("Qwen3-8B shape", QWEN3_8B),
-          "qwen2.5-14b": ("Qwen2.5-14B shape", QWEN25_14B)}
+          "qwen2.5-14b": ("Qwen2.5-14B shape", QWEN25_14B), "llama-3.2-1b": ("Llama-3.2-1B shape", LLAMA_1B),
+          "llama-3.1-70b": ("Llama-3.1-70B shape", LLAMA_70B)}
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
 

@@ -301,14 +301,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     if (ticket != pend_parts - 1) return;
     if (lane == 0) a.counters[pend_row] = 0;
     __threadfence();
-    float M = -INFINITY;
-    for (int s2 = lane; s2 < pend_parts; s2 += 32) M = fmaxf(M, __ldcg(pend_base + s2 * part_stride + HD));
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
     // A lane sums four neighbouring head dimensions (one 16-byte load per partial; lanes beyond the head's size idle),
-    // eight partials' loads in flight at a time.
+    // eight partials' loads in flight at a time.  The largest maximum is found on the way: when a batch raises it, what
+    // has been summed is scaled down by the difference, an exact power of two, so the sums are those of one pass
+    // against the final maximum, bit for bit, without a pass of their own to find it.
     constexpr int LANES = HD / 4;
-    float L = 0.f;
+    float M = -INFINITY, L = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const bool live = lane < LANES;
     for (int s0 = 0; s0 < pend_parts; s0 += 8) {
@@ -322,6 +320,18 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         ms[k] = ml.x;
         ls[k] = ml.y;
         v[k] = (there && live) ? __ldcg(reinterpret_cast<const float4*>(row) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      float mb = ms[0];
+#pragma unroll
+      for (int k = 1; k < 8; ++k) mb = fmaxf(mb, ms[k]);
+      if (mb > M) {
+        const float r = (M == -INFINITY) ? 0.f : pow2_whole(M - mb);
+        L *= r;
+        acc.x *= r;
+        acc.y *= r;
+        acc.z *= r;
+        acc.w *= r;
+        M = mb;
       }
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
