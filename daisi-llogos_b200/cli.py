@@ -115,38 +115,30 @@ def main(argv=None) -> int:
         prompts = [_ids_from_text(text, vocab)]
 
     if args.bench:
-        from .measure import decode_bytes_of_run, model_costs, peaks
         if not args.prompt_len:
             prompts = [prompts[0]] * max(1, args.batch)
         n_new = max_context if args.context > 0 else args.max_tokens          # with --context the cache's limit ends a sequence
-        greedy = GenerationParams.greedy_params(n_new, stop_tokens=())
-        model.generate([p[:64] for p in prompts], GenerationParams.greedy_params(min(4, n_new), stop_tokens=()))   # warm-up
-        r = model.generate(prompts, greedy)
-        total_ms = (r.prefill_seconds + r.decode_seconds) * 1e3
+        b = model.benchmark(prompts, n_new, peaks_file=args.peaks)
+        total_ms = (b.prefill_seconds + b.decode_seconds) * 1e3
+        # the reference's four lines (Daisi.Llogos.Cli/Program.cs:283-297)
         print("=== Benchmark Results ===", file=sys.stderr)
-        print(f"  Prefill:  {r.prompt_tokens:6d} tokens in {r.prefill_seconds * 1e3:8.1f} ms  ({r.prefill_tokens_per_second:8.1f} tok/s)", file=sys.stderr)
-        print(f"  Decode:   {r.generated_tokens:6d} tokens in {r.decode_seconds * 1e3:8.1f} ms  ({r.decode_tokens_per_second:8.1f} tok/s)", file=sys.stderr)
-        print(f"  Total:    {r.prompt_tokens + r.generated_tokens:6d} tokens in {total_ms:8.1f} ms", file=sys.stderr)
+        print(f"  Prefill:  {b.prompt_tokens:6d} tokens in {b.prefill_seconds * 1e3:8.1f} ms  ({b.prefill_tokens_per_second:8.1f} tok/s)", file=sys.stderr)
+        print(f"  Decode:   {b.generated_tokens:6d} tokens in {b.decode_seconds * 1e3:8.1f} ms  ({b.decode_tokens_per_second:8.1f} tok/s)", file=sys.stderr)
+        print(f"  Total:    {b.prompt_tokens + b.generated_tokens:6d} tokens in {total_ms:8.1f} ms", file=sys.stderr)
         print(f"  Load:     {load_ms:8.1f} ms", file=sys.stderr)
-        # beyond the reference's lines: what the steps had to move and compute, against the measured peaks
-        pk = peaks(args.peaks)
-        costs = model_costs(model.model)
-        lens = [len(p) for p in prompts]
-        made = [len(t) for t in r.tokens]
-        decode_bytes, n_steps = decode_bytes_of_run(costs, lens, made)
-        steps = max(1, n_steps)
-        flops = costs.prompt_step_flops(lens, wanted_rows=len(lens))
-        print(f"  Batch:    {len(prompts)} sequences, prompts of {min(lens)} to {max(lens)} tokens, "
-              f"longest sequence at the end {max(n + m for n, m in zip(lens, made))} tokens", file=sys.stderr)
-        if r.decode_seconds > 0 and n_steps:
-            gbs = decode_bytes / r.decode_seconds / 1e9
-            print(f"  Decode step: {r.decode_seconds / steps * 1e3:8.3f} ms mean over {steps} steps, {decode_bytes / steps / 1e9:7.3f} GB to read "
-                  f"per step, {gbs:7.1f} GB/s = {100 * gbs / pk['hbm_gbs']:5.1f} % of {pk['hbm_gbs']:.0f} GB/s ({pk['source']} copy bandwidth)",
+        # beyond them: what the steps had to move and compute, against the measured peaks
+        pk = b.peaks
+        print(f"  Batch:    {b.batch} sequences, prompts of {min(b.prompt_lengths)} to {max(b.prompt_lengths)} tokens, "
+              f"longest sequence at the end {max(b.final_lengths)} tokens", file=sys.stderr)
+        if b.decode_seconds > 0 and b.decode_steps:
+            print(f"  Decode step: {b.decode_seconds / b.decode_steps * 1e3:8.3f} ms mean over {b.decode_steps} steps, "
+                  f"{b.decode_bytes_per_step / 1e9:7.3f} GB to read per step, {b.decode_gb_per_second:7.1f} GB/s = "
+                  f"{100 * b.decode_fraction_of_copy_bandwidth:5.1f} % of {pk['hbm_gbs']:.0f} GB/s ({pk['source']} copy bandwidth)",
                   file=sys.stderr)
-        if r.prefill_seconds > 0:
-            tf = flops / r.prefill_seconds / 1e12
-            print(f"  Prompt step: {flops / 1e12:8.3f} TFLOP, {tf:7.1f} TFLOP/s = {100 * tf / pk['bf16_tflops']:5.1f} % of "
-                  f"{pk['bf16_tflops']:.0f} TFLOP/s ({pk['source']} bfloat16 matrix throughput)", file=sys.stderr)
+        if b.prefill_seconds > 0:
+            print(f"  Prompt step: {b.prompt_step_flops / 1e12:8.3f} TFLOP, {b.prompt_tflops:7.1f} TFLOP/s = "
+                  f"{100 * b.prompt_fraction_of_matrix_peak:5.1f} % of {pk['bf16_tflops']:.0f} TFLOP/s ({pk['source']} bfloat16 matrix "
+                  f"throughput)", file=sys.stderr)
         return 0
 
     params = GenerationParams(max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k,

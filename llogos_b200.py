@@ -11,6 +11,7 @@ _params = _importlib.import_module("daisi-llogos_b200.sampling.params")
 _gen = _importlib.import_module("daisi-llogos_b200.sampling.generate")
 
 LlogosModel = _api.LlogosModel
+BenchmarkResult = _api.BenchmarkResult
 GenerationParams = _params.GenerationParams
 GenerationResult = _gen.GenerationResult
 config, weights, parts, cache, engine = _pkg.config, _pkg.weights, _pkg.parts, _pkg.cache, _pkg.engine

@@ -151,6 +151,36 @@ def test_bfloat16_generation_runs_and_is_deterministic(model_dirs):
     assert a.decode_tokens_per_second > 0 and a.prefill_tokens_per_second > 0
 
 
+def test_benchmark_through_the_entry_point(model_dirs):
+    """``LlogosModel.benchmark``: the reference's counts and rates, and the bytes and flops the steps had by the
+    model's own sizes (worked out here from the configuration)."""
+    cfg = TINY["llama"]
+    model = L.LlogosModel.load(model_dirs["llama"], dtype="bfloat16", max_context=128, max_batch=3)
+    prompts = random_tokens(cfg["vocab_size"], [20, 33, 7], 9)
+    b = model.benchmark(prompts, 10)
+    assert isinstance(b, L.BenchmarkResult)
+    assert b.prompt_tokens == 60 and b.generated_tokens == 30 and b.batch == 3 and b.final_lengths == [30, 43, 17]
+    assert b.decode_steps == 9 and b.decode_tokens_per_second > 0 and b.prefill_tokens_per_second > 0
+    h, i, v, layers = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    matrix = layers * (h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * h * i)
+    kv_per_token = layers * 2 * nkv * hd * 2
+    # step k (1..9) reads every matrix and the head once, and prompt + k keys and values per sequence
+    want = (matrix + v * h) * 2 + kv_per_token * sum(n + k for n in (20, 33, 7) for k in range(1, 10)) / 9
+    assert abs(b.decode_bytes_per_step - want) < 1e-6 * want
+    pairs = sum(n * (n + 1) / 2 for n in (20, 33, 7))
+    assert abs(b.prompt_step_flops - (2.0 * 60 * matrix + 2.0 * 3 * v * h + layers * 4 * nh * hd * pairs)) < 1e-6 * b.prompt_step_flops
+    assert 0 < b.decode_fraction_of_copy_bandwidth < 1 and 0 < b.prompt_fraction_of_matrix_peak < 1
+    assert not model.engine.cache.slots.live()
+    # a sequence rolled back through the entry point continues as if the dropped tokens had never come
+    s = model.open()
+    full = model.step([(s, prompts[1])])[0]
+    model.truncate(s, 20)
+    again = model.step([(s, prompts[1][20:])])[0]
+    assert float((full - again).abs().max()) <= 1.5e-2 * float(full.abs().max())      # another cut of the tokens: rounding only
+    model.close(s)
+
+
 def test_command_line(model_dirs):
     env = dict(os.environ, PYTHONPATH=ROOT)
     base = [sys.executable, "-m", "llogos_b200", "--model", model_dirs["llama"], "--dtype", "float32"]
