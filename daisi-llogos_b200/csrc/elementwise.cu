@@ -195,17 +195,18 @@ __global__ void __launch_bounds__(256) add_rmsnorm_cluster_kernel(float* __restr
     float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
     v = res[i];
     if (branch) {
+      // A step of few rows has nothing to hide a load behind: the row and its first twelve partials are all asked
+      // for before the first is added (one trip to L2 instead of one per group); they are added in their order.
       const float4* b = reinterpret_cast<const float4*>(branch + (long long)r * hidden) + i;
       const long long ps = partial_stride >> 2;
-      int s = 0;
-      for (; s + 4 <= n_partials; s += 4) {
-        const float4 b0 = b[(s + 0) * ps], b1 = b[(s + 1) * ps], b2 = b[(s + 2) * ps], b3 = b[(s + 3) * ps];
-        v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
-        v.x += b1.x; v.y += b1.y; v.z += b1.z; v.w += b1.w;
-        v.x += b2.x; v.y += b2.y; v.z += b2.z; v.w += b2.w;
-        v.x += b3.x; v.y += b3.y; v.z += b3.z; v.w += b3.w;
-      }
-      for (; s < n_partials; ++s) {
+      constexpr int AT_ONCE = 12;
+      float4 pv[AT_ONCE];
+#pragma unroll
+      for (int s = 0; s < AT_ONCE; ++s) pv[s] = s < n_partials ? b[s * ps] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int s = 0; s < AT_ONCE; ++s)
+        if (s < n_partials) { v.x += pv[s].x; v.y += pv[s].y; v.z += pv[s].z; v.w += pv[s].w; }
+      for (int s = AT_ONCE; s < n_partials; ++s) {
         const float4 b0 = b[s * ps];
         v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
       }
@@ -388,7 +389,6 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
 template <typename IT, typename OT, typename WT, int HD>
 __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   pdl_launch_dependents();
-  pdl_wait();
   constexpr int LPH = HD / 8, HALF = HD / 2;      // lanes per head
   const int heads = a.nh + 2 * a.nkv;
   const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / LPH;
@@ -398,20 +398,65 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   const int n = live ? (int)(item / heads) : 0;
   const int h = live ? (int)(item % heads) : 0;
   const int kind = h < a.nh ? 0 : (h < a.nh + a.nkv ? 1 : 2);
+  const int kvh = kind == 1 ? h - a.nh : h - a.nh - a.nkv;
+  // Everything but the sums themselves was written before this step's first kernel started (positions, the batch's
+  // slots, the page table) or never changes (weights, biases, rotation tables): it is fetched while the product ahead
+  // still runs, so that after the wait only the sums are a trip to memory away.
+  const WT* nw = kind == 0 ? (const WT*)a.q_norm_w : (kind == 1 ? (const WT*)a.k_norm_w : nullptr);
+  float w0[4] = {1.f, 1.f, 1.f, 1.f}, w1[4] = {1.f, 1.f, 1.f, 1.f}, b0[4] = {0.f, 0.f, 0.f, 0.f}, b1[4] = {0.f, 0.f, 0.f, 0.f};
+  float cs[4] = {1.f, 1.f, 1.f, 1.f}, si[4] = {0.f, 0.f, 0.f, 0.f};
+  if (nw) {
+    vec_load4(nw + 4 * l, w0);
+    vec_load4(nw + 4 * l + HALF, w1);
+  }
+  if (a.bias && live) {
+    const WT* bsrc = (const WT*)a.bias + (long long)h * HD + 4 * l;
+    vec_load4(bsrc, b0);
+    vec_load4(bsrc + HALF, b1);
+  }
+  const int pos = a.positions[n];
+  const bool rotate = kind != 2 && a.cos_table;
+  if (rotate) {
+    const int p = pos < a.table_positions ? pos : a.table_positions - 1;
+    vec_load4(a.cos_table + (long long)p * HALF + 4 * l, cs);
+    vec_load4(a.sin_table + (long long)p * HALF + 4 * l, si);
+  }
+  void* pages = kind == 0 ? nullptr : (kind == 1 ? a.k_pages : a.v_pages);
+  long long page_row = 0;
+  if (pages && live) page_row = kv_row(a.page_table, a.table_width, a.ring_pages, a.slots[a.seq_of_token[n]], pos, kvh, a.nkv);
+  pdl_wait();
   const IT* src = (const IT*)a.qkv + (long long)n * heads * HD + (long long)h * HD + 4 * l;
   float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f};   // elements 4l.. of the first and second half
-#pragma unroll 4
-  for (int s = 0; s < a.n_partials; ++s) {
-    float t0[4], t1[4];
-    vec_load4(src + s * a.partial_stride, t0);
-    vec_load4(src + s * a.partial_stride + HALF, t1);
+  // the first eight partials are all asked for before the first is added; they are added in their order
+  constexpr int AT_ONCE = 8;
+  float t0[AT_ONCE][4], t1[AT_ONCE][4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      x0[k] += t0[k];
-      x1[k] += t1[k];
+  for (int s = 0; s < AT_ONCE; ++s) {
+    if (s < a.n_partials) {
+      vec_load4(src + s * a.partial_stride, t0[s]);
+      vec_load4(src + s * a.partial_stride + HALF, t1[s]);
     }
   }
-  const WT* nw = kind == 0 ? (const WT*)a.q_norm_w : (kind == 1 ? (const WT*)a.k_norm_w : nullptr);
+#pragma unroll
+  for (int s = 0; s < AT_ONCE; ++s) {
+    if (s < a.n_partials) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        x0[k] += t0[s][k];
+        x1[k] += t1[s][k];
+      }
+    }
+  }
+  for (int s = AT_ONCE; s < a.n_partials; ++s) {
+    float u0[4], u1[4];
+    vec_load4(src + s * a.partial_stride, u0);
+    vec_load4(src + s * a.partial_stride + HALF, u1);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x0[k] += u0[k];
+      x1[k] += u1[k];
+    }
+  }
   if (a.q_norm_w || a.k_norm_w) {                  // uniform over the block: the shuffles need every lane
     float ss = 0.f;
 #pragma unroll
@@ -420,9 +465,6 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
     for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
     if (nw) {
       const float inv = 1.0f / sqrtf(ss / (float)HD + a.norm_eps);
-      float w0[4], w1[4];
-      vec_load4(nw + 4 * l, w0);
-      vec_load4(nw + 4 * l + HALF, w1);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         x0[k] = x0[k] * inv * w0[k];
@@ -432,22 +474,13 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   }
   if (!live) return;
   if (a.bias) {
-    const WT* bsrc = (const WT*)a.bias + (long long)h * HD + 4 * l;
-    float b0[4], b1[4];
-    vec_load4(bsrc, b0);
-    vec_load4(bsrc + HALF, b1);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       x0[k] += b0[k];
       x1[k] += b1[k];
     }
   }
-  const int pos = a.positions[n];
-  if (kind != 2 && a.cos_table) {
-    const int p = pos < a.table_positions ? pos : a.table_positions - 1;
-    float cs[4], si[4];
-    vec_load4(a.cos_table + (long long)p * HALF + 4 * l, cs);
-    vec_load4(a.sin_table + (long long)p * HALF + 4 * l, si);
+  if (rotate) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const float u = x0[k], v = x1[k];
@@ -461,18 +494,14 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
     vec_store4(o + HALF, x1);
     return;
   }
-  const int kvh = kind == 1 ? h - a.nh : h - a.nh - a.nkv;
   void* packed = kind == 1 ? a.k_new : a.v_new;
   if (packed) {
     OT* o = (OT*)packed + ((long long)n * a.nkv + kvh) * HD + 4 * l;
     vec_store4(o, x0);
     vec_store4(o + HALF, x1);
   }
-  void* pages = kind == 1 ? a.k_pages : a.v_pages;
   if (pages) {
-    const int slot = a.slots[a.seq_of_token[n]];
-    const long long row = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv);
-    OT* o = (OT*)pages + row * HD + 4 * l;
+    OT* o = (OT*)pages + page_row * HD + 4 * l;
     vec_store4(o, x0);
     vec_store4(o + HALF, x1);
   }
