@@ -592,9 +592,17 @@ bool page_map(const void* base, long long rows, int hd, CUtensorMap* result) {
   return true;
 }
 
+// Blocks of a launch.  As many as the GPU holds at once (two per multiprocessor) while that leaves a block fewer than
+// about a hundred tiles.  With more work per block, more and shorter blocks: the multiprocessors do not stream at the
+// same rate (the time from the first block's end to the last's was a sixth of the kernel with one run per place), and
+// blocks that start as places come free even that out; a block's start costs a few microseconds, so it has to be worth
+// some fifty tiles.
 int grid_blocks(int n_seqs, int nkv, int max_len) {
-  const long long most = (long long)BLOCKS_PER_SM * llg_sm_count();
+  const long long resident = (long long)BLOCKS_PER_SM * llg_sm_count();
   const long long units = (long long)n_seqs * nkv * ((max_len + TK - 1) / TK);
+  long long rounds = units / (resident * 48);
+  rounds = rounds < 1 ? 1 : (rounds > 4 ? 4 : rounds);
+  const long long most = resident * rounds;
   return (int)(units < most ? (units < 1 ? 1 : units) : most);
 }
 
