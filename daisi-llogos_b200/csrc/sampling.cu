@@ -22,6 +22,14 @@
 // top-k keeps is among these candidates; a second kernel runs the same filters and the same draw
 // on the candidates alone (a few thousand at most, in shared memory).  A slice with more than 64
 // candidates (ties) sends its row through the general way.
+//
+// Without top-k the same two kernels serve as long as the 64 largest logits of every slice can decide the
+// outcome.  The first kernel then also leaves each slice's maximum and its sum of exp(v - maximum), from which
+// the second has the softmax's normaliser over the whole row, and the scaled logits in the work row.  Pure
+// temperature sampling draws over the whole row: the slice that holds the drawn point is found from the slices'
+// masses, the point within it by one pass over that slice.  With top-p or min-p the filters run on the candidates
+// with the whole row's normaliser, after a check that no token outside the candidates can belong to the kept set
+// (every such token is no larger than its slice's 64th largest); if the check fails, the general way runs.
 #include "common.cuh"
 
 LLG_API const char* llg_last_error() { return g_llg_error; }
@@ -145,6 +153,7 @@ struct SampleArgs {
   int n_slices;
   const int* history_rows; // [B] or null
   int history_append;      // 1: the drawn token is written into the sequence's ring and its count goes up
+  float* slice_stats;      // [B][n_slices][3] or null: a slice's maximum, its sum of exp(v - maximum), its least candidate
 };
 
 __device__ __forceinline__ int history_row(const SampleArgs& a, int b) { return a.history_rows ? a.history_rows[b] : b; }
@@ -217,8 +226,12 @@ __device__ int block_exclusive_scan_int(int v, int* scratch, int* total) {
 
 // Filters and draw for sequence b over w[0..n): scaled logits in, probabilities left behind.  `map` (or null)
 // gives the token of entry i; entries are in the order of their tokens.  mx = the largest scaled logit.
+// `z_row` > 0: the entries are a part of a larger row whose sum of exp(v - mx) is z_row (that is the softmax's
+// normaliser then), and sums of probabilities are whole only over entries of probability `whole_above` and more; when
+// the entries cannot decide the outcome, *undecided is set and nothing is drawn.
 __device__ void filter_and_draw(const SampleArgs& a, int b, float* w, int n, const int* map, float mx,
-                                float* fs, int* is, int* chosen_slot, float* scan) {
+                                float* fs, int* is, int* chosen_slot, float* scan, float z_row = 0.f,
+                                float whole_above = 0.f, int* undecided = nullptr) {
   const int tid = threadIdx.x;
   int& chosen = *chosen_slot;
 
@@ -270,7 +283,7 @@ __device__ void filter_and_draw(const SampleArgs& a, int b, float* w, int n, con
     z += e;
   }
   z = block_sum(z, fs);
-  const float inv_z = 1.0f / z;
+  const float inv_z = 1.0f / (z_row > 0.f ? z_row : z);
   for (int i = tid; i < n; i += THREADS) w[i] *= inv_z;
   __syncthreads();
 
@@ -320,8 +333,29 @@ __device__ void filter_and_draw(const SampleArgs& a, int b, float* w, int n, con
   if (a.top_p > 0.f && a.top_p < 1.0f) {
     // largest t (a float's bits, probabilities are >= 0) with mass(p >= t) > top_p
     unsigned cur = 0u;
+    // Entries of a larger row: below `whole_above` the sums miss tokens that are not among the entries.  If the mass
+    // from there up does not exceed top_p, the kept set reaches further down than the entries can tell; if it does,
+    // every threshold at or below it is known to pass without a sum.
+    const unsigned whole_key = whole_above > 0.f ? __float_as_uint(whole_above) : 0u;
+    if (whole_key) {
+      float mass = 0.f;
+      for (int i = tid; i < n; i += THREADS) {
+        const float p = w[i];
+        if (p > 0.f && __float_as_uint(p) >= whole_key) mass += p;
+      }
+      mass = block_sum(mass, fs);
+      if (!(mass > a.top_p)) {
+        if (tid == 0) *undecided = 1;
+        __syncthreads();
+        return;
+      }
+    }
     for (int bit = 30; bit >= 0; --bit) {
       const unsigned t = cur | (1u << bit);
+      if (t <= whole_key) {
+        cur = t;
+        continue;
+      }
       float mass = 0.f;
       for (int i = tid; i < n; i += THREADS) {
         const float p = w[i];
@@ -486,6 +520,10 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
 // passes on those that reach its own top_k-th largest, in index order.
 __global__ void __launch_bounds__(THREADS) sample_candidates_kernel(SampleArgs a) {
   __shared__ int is[32];
+  __shared__ float fs[32];
+  // without a top-k of its own the slice passes on its 64 largest, and what the second kernel needs of the rest
+  const bool wide = !(a.top_k > 0 && a.top_k <= CAND_CAP);
+  const int k_eff = wide ? CAND_CAP : a.top_k;
   __shared__ int pen_tok[HIST_MAX];
   __shared__ float pen_val[HIST_MAX];
   const int s = blockIdx.x, b = blockIdx.y, n = a.vocab, tid = threadIdx.x;
@@ -541,9 +579,29 @@ __global__ void __launch_bounds__(THREADS) sample_candidates_kernel(SampleArgs a
 #pragma unroll
     for (int e = 0; e < SLICE_PER; ++e) c += f2key(v[e]) >= t ? 1 : 0;
     c = block_sum_int(c, is);
-    if (c >= a.top_k) lo = t;
+    if (c >= k_eff) lo = t;
   }
   const float thr = key2f(lo);
+  if (wide) {
+    float* w = a.work + (long long)b * n;
+    float m = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < SLICE_PER; ++e) {
+      if (i0 + e < n) w[i0 + e] = v[e];
+      m = fmaxf(m, v[e]);
+    }
+    m = block_max(m, fs);
+    float sum = 0.f;
+#pragma unroll
+    for (int e = 0; e < SLICE_PER; ++e) sum += v[e] > -INFINITY ? expf(v[e] - m) : 0.f;
+    sum = block_sum(sum, fs);
+    if (tid == 0) {
+      float* st = a.slice_stats + ((long long)b * a.n_slices + s) * 3;
+      st[0] = m;
+      st[1] = m > -INFINITY ? sum : 0.f;
+      st[2] = thr;
+    }
+  }
   int cnt = 0;
 #pragma unroll
   for (int e = 0; e < SLICE_PER; ++e) cnt += (v[e] >= thr && v[e] > -INFINITY) ? 1 : 0;
@@ -602,9 +660,108 @@ __global__ void __launch_bounds__(THREADS) sample_from_candidates_kernel(SampleA
   float mx = -INFINITY;
   for (int i = tid; i < n_c; i += THREADS) mx = fmaxf(mx, cw[i]);
   mx = block_max(mx, fs);
-  filter_and_draw(a, b, cw, n_c, cidx, mx, fs, is, &chosen, scan);
-}
+  const bool wide = !(a.top_k > 0 && a.top_k <= CAND_CAP);
+  if (!wide) {
+    filter_and_draw(a, b, cw, n_c, cidx, mx, fs, is, &chosen, scan);
+    return;
+  }
 
+  // ---- no top-k: the candidates are the 64 largest of every slice, the slices' sums give the whole row's ----
+  __shared__ float smass[MAX_SLICES];       // a slice's sum of exp(v - mx)
+  __shared__ float z_row_s, whole_s, target_s;
+  __shared__ int slice_s, undecided;
+  const float* st = a.slice_stats + (long long)b * ns * 3;
+  if (tid < ns) smass[tid] = st[3 * tid] > -INFINITY ? st[3 * tid + 1] * expf(st[3 * tid] - mx) : 0.f;
+  __syncthreads();
+  const bool top_p_on = a.top_p > 0.f && a.top_p < 1.0f, min_p_on = a.min_p > 0.f && a.min_p < 1.0f;
+  if (tid == 0) {
+    float z = 0.f, least = -INFINITY;
+    for (int s = 0; s < ns; ++s) {            // in slice order, by one thread: the same sum whatever else runs
+      z += smass[s];
+      least = fmaxf(least, st[3 * s + 2]);    // the largest of the slices' least candidates
+    }
+    z_row_s = z;
+    whole_s = expf(least - mx) / z;           // every token outside the candidates is at most this probable
+    // min-p keeps v >= mx + log(min_p): decidable when that bound lies above every slice's least candidate
+    undecided = (min_p_on && !(mx + logf(a.min_p) > least)) ? 1 : 0;
+  }
+  __syncthreads();
+  if (top_p_on || min_p_on) {
+    if (!undecided)        // with min-p the kept tokens are all candidates, and the softmax is over them alone
+      filter_and_draw(a, b, cw, n_c, cidx, mx, fs, is, &chosen, scan, min_p_on ? 0.f : z_row_s, min_p_on ? 0.f : whole_s, &undecided);
+    __syncthreads();
+    if (undecided) sample_full(a, b, fs, is, &chosen, scan);      // uniform over the block
+    return;
+  }
+
+  // ---- temperature alone: a draw over the whole row ----
+  const int n = a.vocab;
+  const float* w = a.work + (long long)b * n;
+  const int seq = a.seq_ids ? a.seq_ids[b] : b;
+  const float u = uniform_of(a.seed, seq, a.step);
+  if (tid == 0) {
+    const float target = u * z_row_s;
+    float before = 0.f;
+    int pick = ns - 1;
+    for (int s = 0; s < ns; ++s) {
+      if (target < before + smass[s]) {
+        pick = s;
+        break;
+      }
+      if (s < ns - 1) before += smass[s];
+    }
+    slice_s = pick;
+    target_s = target - before;               // where the drawn point lies within the slice's own mass
+    chosen = 0x7fffffff;
+  }
+  __syncthreads();
+  if (a.probs_out) {
+    const float inv = 1.0f / z_row_s;
+    for (int i = tid; i < n; i += THREADS) a.probs_out[(long long)b * n + i] = w[i] > -INFINITY ? expf(w[i] - mx) * inv : 0.f;
+  }
+  {
+    const int i0 = slice_s * SLICE_LEN + tid * SLICE_PER;
+    float p[SLICE_PER], mine = 0.f;
+#pragma unroll
+    for (int e = 0; e < SLICE_PER; ++e) {
+      p[e] = (i0 + e < n && w[i0 + e] > -INFINITY) ? expf(w[i0 + e] - mx) : 0.f;
+      mine += p[e];
+    }
+    scan[tid] = mine;
+    __syncthreads();
+    for (int o = 1; o < THREADS; o <<= 1) {
+      const float add = tid >= o ? scan[tid - o] : 0.f;
+      __syncthreads();
+      scan[tid] += add;
+      __syncthreads();
+    }
+    const float target = target_s, before = scan[tid] - mine;
+    if (target >= before && target < scan[tid]) {
+      float c = before;
+      int pick = -1;
+#pragma unroll
+      for (int e = 0; e < SLICE_PER; ++e) {
+        c += p[e];
+        if (pick < 0 && p[e] > 0.f && target < c) pick = i0 + e;
+      }
+      if (pick < 0)          // rounding left the point past this thread's last token: its last token that can be drawn
+        for (int e = SLICE_PER - 1; e >= 0; --e)
+          if (pick < 0 && p[e] > 0.f) pick = i0 + e;
+      if (pick >= 0) atomicMin(&chosen, pick);
+    }
+    __syncthreads();
+    if (chosen == 0x7fffffff) {
+      // rounding left the point past the slice's last token: the most probable token of the row
+      const int r = block_argmax(cw, n_c, fs, is);
+      if (tid == 0) chosen = cidx[r];
+      __syncthreads();
+    }
+    if (tid == 0) {
+      a.out[b] = chosen;
+      history_push(a, b, chosen);
+    }
+  }
+}
 
 }  // namespace
 
@@ -630,10 +787,17 @@ LLG_API int llg_sample(const SampleArgs* args, cudaStream_t stream) {
   LLG_REQUIRE(a.repetition_penalty > 0.f, "sample: repetition penalty must be positive");
   if (a.n_seqs == 0) return 0;
   const int slices = (a.vocab + SLICE_LEN - 1) / SLICE_LEN;
-  const bool by_candidates = a.cand_val && a.cand_idx && a.cand_count && a.n_slices == slices && slices <= MAX_SLICES &&
-                             a.temperature > 0.f && a.top_k > 0 && a.top_k <= CAND_CAP && a.top_k < a.vocab &&
-                             a.min_keep <= a.top_k && (!a.history || a.history_stride <= HIST_MAX) &&
-                             a.n_banned <= BANNED_MAX && a.n_seqs <= 65535;
+  const bool scratch = a.cand_val && a.cand_idx && a.cand_count && a.n_slices == slices && slices <= MAX_SLICES &&
+                       a.temperature > 0.f && (!a.history || a.history_stride <= HIST_MAX) && a.n_banned <= BANNED_MAX &&
+                       a.n_seqs <= 65535;
+  const bool narrow = a.top_k > 0 && a.top_k <= CAND_CAP && a.top_k < a.vocab && a.min_keep <= a.top_k;
+  // no top-k at all, no typical-p (its entropy is over the whole row), at least one token kept is all min_keep asks
+  const bool wide = (a.top_k <= 0 || a.top_k >= a.vocab) && !(a.typical_p > 0.f && a.typical_p < 1.0f) && a.min_keep <= 1 &&
+                    a.slice_stats != nullptr && a.vocab >= CAND_CAP &&
+                    // one block per (slice, row): worth it while they all run at once; a large batch fills the GPU with
+                    // one block per row anyway (measured: 64 rows 136 us this way, 88 us the general way)
+                    8LL * a.n_seqs * slices <= 18LL * llg_sm_count();        // two resident blocks per multiprocessor, and a few more
+  const bool by_candidates = scratch && (narrow || wide);
   if (by_candidates) {
     sample_candidates_kernel<<<dim3(slices, a.n_seqs), THREADS, 0, stream>>>(a);
     if (llg_check_launch("sample (candidates)")) return 1;

@@ -133,6 +133,7 @@ class _SampleArgs(Structure):
         ("banned", c_void_p), ("n_banned", c_int),
         ("cand_val", c_void_p), ("cand_idx", c_void_p), ("cand_count", c_void_p), ("n_slices", c_int),
         ("history_rows", c_void_p), ("history_append", c_int),
+        ("slice_stats", c_void_p),
     ]
 
 
@@ -727,8 +728,10 @@ def sample(logits: torch.Tensor, work: torch.Tensor, out: torch.Tensor, *, tempe
         if ws is None:
             ws = _sample_scratch[key] = (torch.empty(b * slices * cap, dtype=torch.float32, device=logits.device),
                                          torch.empty(b * slices * cap, dtype=torch.int32, device=logits.device),
-                                         torch.empty(b * slices, dtype=torch.int32, device=logits.device))
+                                         torch.empty(b * slices, dtype=torch.int32, device=logits.device),
+                                         torch.empty(b * slices * 3, dtype=torch.float32, device=logits.device))
         a.cand_val, a.cand_idx, a.cand_count, a.n_slices = _ptr(ws[0]), _ptr(ws[1]), _ptr(ws[2]), slices
+        a.slice_stats = _ptr(ws[3])
     _check(lib, lib.llg_sample(byref(a), _stream()))
 
 

@@ -743,6 +743,55 @@ def test_sampler_by_candidates_equals_the_general_way(ops, case):
         assert int(res[0][0][i]) == P.draw(res[0][1][i].double(), P.uniform_of(13, int(seq_ids[i]), 2))
 
 
+@pytest.mark.parametrize("case", [dict(temperature=0.7), dict(temperature=1.3, repetition_penalty=1.2, banned=[5, 9000, 20010]),
+                                  dict(temperature=0.8, top_p=0.9), dict(temperature=1.0, top_p=0.5, frequency_penalty=0.4),
+                                  dict(temperature=0.9, min_p=0.05), dict(temperature=1.1, min_p=0.01, top_p=0.8),
+                                  dict(temperature=6.0, top_p=0.97), dict(temperature=5.0, min_p=0.001)])
+def test_sampler_without_top_k_through_the_slices(ops, case):
+    """Without top-k the slices' 64 largest logits and their sums stand for the row as long as they can decide the
+    outcome: temperature alone draws over the whole row (the slice by the slices' masses, the token by one pass
+    over that slice); top-p and min-p run on the candidates with the whole row's normaliser.  Distribution and draw
+    are those of the general way; where the kept set reaches below the candidates (high temperatures here) or a
+    slice has more ties than candidates fit, the row takes the general way by itself."""
+    c = dict(case)
+    banned = c.pop("banned", None)
+    vocab, b = 20011, 6
+    logits = rnd((b, vocab), 72, scale=3.0)
+    logits[1, 100:400] = 9.5                  # more ties at the top of a slice than candidates fit
+    logits[2, 8190:8194] = 12.0               # the best tokens straddle a slice boundary
+    logits[3, 19000:] = -50.0                 # a short last slice with nothing worth keeping
+    logits[4] = rnd((vocab,), 73, scale=0.2)  # nearly flat: the kept set is most of the row
+    g = torch.Generator().manual_seed(74)
+    hist = torch.randint(0, vocab, (b, 64), generator=g, dtype=torch.int32)
+    hist[2, 0], hist[2, 1], hist[2, 2] = 8191, 8192, 8193
+    hl = torch.tensor([64, 20, 64, 0, 33, 5], dtype=torch.int32)
+    seq_ids = torch.tensor([3, 1, 4, 1, 5, 9], dtype=torch.int32)
+    for step in (2, 3, 4):                    # three uniform numbers per row
+        res = []
+        for cand in (True, False):
+            work = torch.empty(b * vocab, device=DEV)
+            out = torch.empty(b, dtype=torch.int32, device=DEV)
+            probs = torch.full((b, vocab), float("nan"), device=DEV)
+            ops.sample(logits.to(DEV), work, out, seed=13, step=step, history=hist.to(DEV), history_len=hl.to(DEV),
+                       probs_out=probs, seq_ids=seq_ids.to(DEV), candidates=cand,
+                       banned=None if banned is None else torch.tensor(banned, dtype=torch.int32, device=DEV), **c)
+            res.append((out.cpu(), probs.cpu()))
+        assert ((res[0][1] > 0) == (res[1][1] > 0)).all()
+        assert float((res[0][1] - res[1][1]).abs().max()) < 1e-6
+        for i in range(b):
+            pd = res[0][1][i].double()
+            u = P.uniform_of(13, int(seq_ids[i]), step)
+            cdf = torch.cumsum(pd, 0) / pd.sum()
+            near = float((cdf - u).abs().min()) < 1e-5          # the drawn point within rounding of a boundary
+            assert int(res[0][0][i]) == int(res[1][0][i]) or near, (i, step)
+            assert int(res[0][0][i]) == P.draw(pd, u) or near, (i, step)
+            assert float(pd[int(res[0][0][i])]) > 0
+    for i in (0, 2, 4):
+        ref = P.sampling_distribution(logits[i].tolist(), previous=hist[i, :hl[i]].tolist(), banned=banned or (),
+                                      top_k=0, **c)
+        assert float((res[0][1][i].double() - ref).abs().max()) < 2e-6
+
+
 @pytest.mark.parametrize("top_k", [1, 3, 40, 200])
 def test_top_k_keeps_exactly_k_at_ties(ops, top_k):
     """Logits on a coarse grid, so that many tie with the k-th largest: exactly k stay, the smallest tokens
