@@ -2,7 +2,8 @@
 // step's packed-token layout, it issues
 //     residual add + norm -> q/k/v product -> per-head norm, bias, rotation, cache write -> attention ->
 //     output product -> residual add + norm -> gate/up product with gating -> down product
-// for every block, with one call from Python per step instead of nine per block.  It computes nothing itself and
+// for every block, with one call from Python per step instead of nine per block.  A bfloat16 step's norms leave their
+// division to the products that consume them (RowScale), as the parts do.  It computes nothing itself and
 // launches no kernel of its own: it calls the kernels' entry points of the other libraries through a table of
 // function pointers (llg_runner_bind), in the order and with the arguments that the parts of parts/attention.py,
 // parts/feedforward.py, parts/norm.py and parts/block.py use.  Blocks with other parts, or entries that read another
@@ -30,9 +31,9 @@ enum { F32 = 0, BF16 = 1 };
 // Entry points of the kernel libraries (filled in by the caller with the addresses of the loaded functions; an entry
 // may stay empty as long as no step needs it, so that a caller loads only the libraries its model uses).
 struct RunnerApi {
-  int (*add_rmsnorm)(float*, const float*, int, long long, const void*, int, float, void*, int, const int*, int, int, cudaStream_t);
-  int (*gemm_tc)(const void*, const void*, void*, int, int, int, int, int, int, int, cudaStream_t);
-  int (*gemm_simt)(const void*, int, const void*, int, void*, int, int, int, int, cudaStream_t);
+  int (*add_rmsnorm)(float*, const float*, int, long long, const void*, int, float, void*, int, const int*, int, int, float*, cudaStream_t);
+  int (*gemm_tc)(const void*, const void*, void*, int, int, int, int, int, int, int, const RowScale*, cudaStream_t);
+  int (*gemm_simt)(const void*, int, const void*, int, void*, int, int, int, int, const RowScale*, cudaStream_t);
   int (*qk_prep)(const QkPrepArgs*, int, cudaStream_t);
   int (*kv_write)(const void*, const void*, void*, void*, const int*, int, int, const int*, const int*, const int*, const int*,
                   const int*, int, int, int, int, cudaStream_t);
@@ -100,6 +101,8 @@ struct RunnerStep {
   int tc_qkv, tc_o, tc_gate_up, tc_down;    // 1: the tensor-core product takes this matrix
   int splits_qkv, splits_o, splits_down;    // split-K partials of the three products that feed a sum
   int fused_qkv;                            // prompt steps: the q/k/v product prepares queries and keys in its epilogue
+  float* ss;                                // bfloat16: the norms' sums of squares, [n][ss_parts]
+  int ss_parts;                             // sums per row that the norm kernel writes for this step's sizes
   float* residual;                          // [n][hidden]
   void* norm_out;                           // [n][hidden]
   float* qkv;                               // [splits_qkv][n][(nh + 2 nkv) * hd]
@@ -142,32 +145,43 @@ int product(const RunnerStep& s, const void* x, const void* w, void* out, int ou
             int* launches) {
   if (tc) {
     NEED(gemm_tc);
-    if (g_api.gemm_tc(x, w, out, out_dtype, n, o, k, splits, 0, 0, s.stream)) return fail("gemm_tc", g_api.err_gemm_tc);
+    if (g_api.gemm_tc(x, w, out, out_dtype, n, o, k, splits, 0, 0, nullptr, s.stream)) return fail("gemm_tc", g_api.err_gemm_tc);
   } else {
     NEED(gemm_simt);
-    if (g_api.gemm_simt(x, s.dtype, w, s.dtype, out, out_dtype, n, o, k, s.stream)) return fail("gemm_simt", g_api.err_gemm_simt);
+    if (g_api.gemm_simt(x, s.dtype, w, s.dtype, out, out_dtype, n, o, k, nullptr, s.stream)) return fail("gemm_simt", g_api.err_gemm_simt);
   }
   ++*launches;
   return 0;
 }
 
-int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, int pending_parts, int* launches) {
+// residual += the pending partial sums (or nothing); norm_out = the norm of it.  A bfloat16 step leaves the division
+// to the consumer (*scale).
+int norm_after(const RunnerStep& s, const float* pending, int pending_parts, const void* norm_w, int norm_w_dtype, float eps,
+               RowScale* scale, int* launches) {
   const int n = s.n_tokens;
-  const long long nh_stride = (long long)n * s.hidden;
-  const int qkv_dim = (s.nh + 2 * s.nkv) * s.hd;
+  const bool defer = s.dtype == BF16 && s.ss != nullptr;
   NEED(add_rmsnorm);
-  NEED(qk_prep);
-  // residual += pending; x = norm1(residual)
-  if (g_api.add_rmsnorm(s.residual, pending, pending ? pending_parts : 0, nh_stride, L.norm1_w, L.norm_w_dtype, L.norm1_eps,
-                        s.norm_out, s.dtype, nullptr, n, s.hidden, s.stream))
+  if (g_api.add_rmsnorm(s.residual, pending, pending ? pending_parts : 0, (long long)n * s.hidden, norm_w, norm_w_dtype, eps, s.norm_out,
+                        s.dtype, nullptr, n, s.hidden, defer ? s.ss : nullptr, s.stream))
     return fail("add_rmsnorm", g_api.err_elementwise);
   ++*launches;
+  *scale = defer ? RowScale{s.ss, s.ss_parts, 1.0f / (float)s.hidden, eps} : RowScale{nullptr, 0, 0.f, 0.f};
+  return 0;
+}
+
+int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, int pending_parts, int* launches) {
+  const int n = s.n_tokens;
+  const int qkv_dim = (s.nh + 2 * s.nkv) * s.hd;
+  // residual += what is pending; x = norm1(residual)
+  RowScale scale;
+  if (norm_after(s, pending, pending_parts, L.norm1_w, L.norm_w_dtype, L.norm1_eps, &scale, launches)) return 1;
   // q/k/v in float32 (partials when the product splits its sums), unless the product prepares them itself
   const bool fused = s.fused_qkv && !s.decode;
   const int s_qkv = s.tc_qkv ? s.splits_qkv : 1;
   if (!fused && product(s, s.norm_out, L.w_qkv, s.qkv, F32, n, qkv_dim, s.hidden, s.tc_qkv, s_qkv, launches)) return 1;
   QkPrepArgs p;
   memset(&p, 0, sizeof(p));
+  p.row_scale = scale;
   p.qkv = s.qkv;
   p.qkv_dtype = F32;
   p.n_partials = s_qkv;
@@ -210,6 +224,7 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
     p.qkv = nullptr;
     if (g_api.gemm_tc_qkv(s.norm_out, L.w_qkv, n, s.hidden, &p, s.stream)) return fail("gemm_tc_qkv", g_api.err_gemm_tc);
   } else {
+    NEED(qk_prep);
     if (g_api.qk_prep(&p, s.dtype, s.stream)) return fail("qk_prep", g_api.err_elementwise);
   }
   ++*launches;
@@ -319,15 +334,13 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
   // output projection, then residual += it; x = norm2(residual)
   const int s_o = s.tc_o ? s.splits_o : 1;
   if (product(s, s.attn_out, L.w_o, s.proj, F32, n, s.hidden, s.nh * s.hd, s.tc_o, s_o, launches)) return 1;
-  if (g_api.add_rmsnorm(s.residual, s.proj, s_o, nh_stride, L.norm2_w, L.norm_w_dtype, L.norm2_eps, s.norm_out, s.dtype, nullptr, n,
-                        s.hidden, s.stream))
-    return fail("add_rmsnorm", g_api.err_elementwise);
-  ++*launches;
+  if (norm_after(s, s.proj, s_o, L.norm2_w, L.norm_w_dtype, L.norm2_eps, &scale, launches)) return 1;
+  const RowScale* sc = scale.ss ? &scale : nullptr;
   // act = silu(gate) * up
   const int gated_rows = ((s.inter + 127) / 128) * 256;
   if (s.tc_gate_up && s.dtype == BF16) {
     NEED(gemm_tc);
-    if (g_api.gemm_tc(s.norm_out, L.w_gate_up, s.act, BF16, n, gated_rows, s.hidden, 1, 0, s.inter, s.stream))
+    if (g_api.gemm_tc(s.norm_out, L.w_gate_up, s.act, BF16, n, gated_rows, s.hidden, 1, 0, s.inter, sc, s.stream))
       return fail("gemm_tc", g_api.err_gemm_tc);
     ++*launches;
   } else {
@@ -337,7 +350,9 @@ int run_block(const DenseLayer& L, const RunnerStep& s, const float* pending, in
     for (int r0 = 0; r0 < n; r0 += s.gate_up_rows) {
       const int rows = n - r0 < s.gate_up_rows ? n - r0 : s.gate_up_rows;
       const char* x = (const char*)s.norm_out + (size_t)r0 * s.hidden * el;
-      if (g_api.gemm_simt(x, s.dtype, L.w_gate_up, s.dtype, s.gate_up, s.dtype, rows, gated_rows, s.hidden, s.stream))
+      RowScale part = scale;
+      if (part.ss) part.ss += (long long)r0 * part.parts;
+      if (g_api.gemm_simt(x, s.dtype, L.w_gate_up, s.dtype, s.gate_up, s.dtype, rows, gated_rows, s.hidden, sc ? &part : nullptr, s.stream))
         return fail("gemm_simt", g_api.err_gemm_simt);
       if (g_api.silu_mul(s.gate_up, s.dtype, 1, (long long)rows * gated_rows, (char*)s.act + (size_t)r0 * s.inter * el, s.dtype, rows,
                          s.inter, s.stream))

@@ -70,10 +70,13 @@ __device__ __forceinline__ void vec_store4(__nv_bfloat16* p, const float (&v)[4]
 // For output row j (token r = rows ? rows[j] : j):
 //   v = residual[r] + sum_s branch[s][r]   (written back to residual when there is a branch)
 //   out[j] = v * rsqrt(mean(v^2) + eps) * weight         (eps inside the root, weight after)
+// With ss_out the division is left to the consumer of out (RowScale in kernel_args.h): out[j] = v * weight and
+// ss_out[j] = sum(v^2), whole or in parts.
 template <typename OT, typename WT>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ branch,
                                    int n_partials, long long partial_stride, const WT* __restrict__ weight,
-                                   float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+                                   float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden,
+                                   float* __restrict__ ss_out) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[32];
@@ -91,7 +94,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
     ss += v * v;
   }
   ss = block_sum(ss, red);
-  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  const float inv = ss_out ? 1.0f : 1.0f / sqrtf(ss / (float)hidden + eps);
+  if (ss_out && threadIdx.x == 0) ss_out[j] = ss;
   OT* o = out + (long long)j * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x)
     o[i] = from_f32<OT>(res[i] * inv * to_f32(weight[i]));
@@ -105,7 +109,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const float* __
 template <typename OT, typename WT, int VPT>
 __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const float* __restrict__ branch,
                                         int n_partials, long long partial_stride, const WT* __restrict__ weight,
-                                        float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden) {
+                                        float eps, OT* __restrict__ out, const int* __restrict__ rows, int hidden,
+                                        float* __restrict__ ss_out) {
   __shared__ float red[32];
   pdl_launch_dependents();
   const int nv = hidden >> 2;
@@ -162,7 +167,8 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const floa
     ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
   }
   ss = block_sum(ss, red);
-  const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+  const float inv = ss_out ? 1.0f : 1.0f / sqrtf(ss / (float)hidden + eps);
+  if (ss_out && threadIdx.x == 0) ss_out[j] = ss;
   OT* o = out + (long long)j * hidden;
 #pragma unroll
   for (int k = 0; k < VPT; ++k) {
@@ -175,9 +181,60 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const floa
   }
 }
 
+// The norm of a step of few rows when the division is left to the consumer: nothing then needs a whole row, so a
+// row is cut into slices of PARTS_THREADS float4 and every (slice, row) is a block of its own that adds up its
+// columns' partial sums, writes the residual stream, the weighted row and its slice's sum of squares (the consumer
+// adds the slices' sums in their order).  One multiprocessor fetches a row's partial sums at some 40 GB/s (4 us
+// for the 147 KB of a 4096-wide row with nine partials); spread over sixteen blocks they are there in one trip.
+constexpr int PARTS_THREADS = 64;
+
+template <typename OT, typename WT>
+__global__ void __launch_bounds__(PARTS_THREADS) add_rmsnorm_parts_kernel(float* __restrict__ residual, const float* __restrict__ branch,
+                                                                           int n_partials, long long partial_stride,
+                                                                           const WT* __restrict__ weight, OT* __restrict__ out,
+                                                                           const int* __restrict__ rows, int hidden,
+                                                                           float* __restrict__ ss_out) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  const int i = blockIdx.x * PARTS_THREADS + threadIdx.x;          // float4 of the row (the host checks divisibility)
+  float wv[4];
+  vec_load4(weight + 4 * i, wv);                                   // no result of an earlier kernel
+  const int j = blockIdx.y;
+  pdl_wait();
+  const int r = rows ? rows[j] : j;
+  float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
+  float4 v = res[i];
+  if (branch) {
+    const float4* b = reinterpret_cast<const float4*>(branch + (long long)r * hidden) + i;
+    const long long ps = partial_stride >> 2;
+    constexpr int AT_ONCE = 12;                                    // all asked for before the first is added, added in order
+    float4 pv[AT_ONCE];
+#pragma unroll
+    for (int q = 0; q < AT_ONCE; ++q) pv[q] = q < n_partials ? b[q * ps] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int q = 0; q < AT_ONCE; ++q)
+      if (q < n_partials) { v.x += pv[q].x; v.y += pv[q].y; v.z += pv[q].z; v.w += pv[q].w; }
+    for (int q = AT_ONCE; q < n_partials; ++q) {
+      const float4 b0 = b[q * ps];
+      v.x += b0.x; v.y += b0.y; v.z += b0.z; v.w += b0.w;
+    }
+    res[i] = v;
+  }
+  const float y[4] = {v.x * wv[0], v.y * wv[1], v.z * wv[2], v.w * wv[3]};
+  vec_store4(out + (long long)j * hidden + 4 * i, y);
+  const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
+  if (threadIdx.x == 0) ss_out[(long long)j * gridDim.x + blockIdx.x] = ss;
+}
+
+// Parts that llg_add_rmsnorm writes per row into ss_out for these sizes (the consumer's RowScale.parts).
+LLG_API int llg_add_rmsnorm_parts(int n_out, int hidden) {
+  const bool spread = n_out <= 64 && hidden >= 1024 && hidden % (4 * PARTS_THREADS) == 0 && hidden / (4 * PARTS_THREADS) <= 64;
+  return spread ? hidden / (4 * PARTS_THREADS) : 1;
+}
+
 LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials, long long partial_stride,
                             const void* weight, int weight_dtype, float eps, void* out, int out_dtype,
-                            const int* rows, int n_out, int hidden, cudaStream_t stream) {
+                            const int* rows, int n_out, int hidden, float* ss_out, cudaStream_t stream) {
   LLG_REQUIRE(n_out >= 0 && hidden > 0, "add_rmsnorm: bad sizes n_out=%d hidden=%d", n_out, hidden);
   LLG_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
   LLG_REQUIRE(!branch || n_partials >= 1, "add_rmsnorm: a branch needs n_partials >= 1");
@@ -201,23 +258,29 @@ LLG_API int llg_add_rmsnorm(float* residual, const float* branch, int n_partials
     }
   }
   const bool vec_ok = vec && vpt <= 8;
+  // the division left to the consumer and few rows: every slice of a row is a block of its own
+  const int parts = ss_out ? llg_add_rmsnorm_parts(n_out, hidden) : 1;
+  LLG_REQUIRE(parts == 1 || vec, "add_rmsnorm: operands of a norm in parts must be 16-byte aligned");
 #define LAUNCH(OT, WT)                                                                                         \
   do {                                                                                                         \
-    if (vec_ok && vpt <= 1)                                                                                    \
+    if (parts > 1)                                                                                             \
+      llg_launch(add_rmsnorm_parts_kernel<OT, WT>, dim3(parts, n_out), PARTS_THREADS, 0, stream, residual, branch, \
+                 n_partials, partial_stride, (const WT*)weight, (OT*)out, rows, hidden, ss_out);               \
+    else if (vec_ok && vpt <= 1)                                                                                    \
       llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 1>, n_out, threads, 0, stream, residual, branch, n_partials,    \
-                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden, ss_out);                      \
     else if (vec_ok && vpt <= 2)                                                                               \
       llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 2>, n_out, threads, 0, stream, residual, branch, n_partials,    \
-                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden, ss_out);                      \
     else if (vec_ok && vpt <= 4)                                                                               \
       llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 4>, n_out, threads, 0, stream, residual, branch, n_partials,    \
-                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden, ss_out);                      \
     else if (vec_ok)                                                                                           \
       llg_launch(add_rmsnorm_vec4_kernel<OT, WT, 8>, n_out, threads, 0, stream, residual, branch, n_partials,    \
-                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden, ss_out);                      \
     else                                                                                                       \
       llg_launch(add_rmsnorm_kernel<OT, WT>, n_out, threads, 0, stream, residual, branch, n_partials,            \
-                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden);                              \
+                 partial_stride, (const WT*)weight, eps, (OT*)out, rows, hidden, ss_out);                      \
   } while (0)
   if (out_dtype == LLG_F32 && weight_dtype == LLG_F32) LAUNCH(float, float);
   else if (out_dtype == LLG_F32 && weight_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
@@ -248,10 +311,12 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
   const long long off = (long long)n * heads * hd + (long long)h * hd;
   const IT* src = (const IT*)a.qkv + off;
 
+  const float rs = row_scale_of(a.row_scale, n);
   float ss = 0.f;
   for (int d = lane; d < hd; d += 32) {
     float v = 0.f;
     for (int s = 0; s < a.n_partials; ++s) v += to_f32(src[s * a.partial_stride + d]);
+    v *= rs;
     x[d] = v;
     ss += v * v;
   }
@@ -345,6 +410,7 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   long long page_row = 0;
   if (pages && live) page_row = kv_row(a.page_table, a.table_width, a.ring_pages, a.slots[a.seq_of_token[n]], pos, kvh, a.nkv);
   pdl_wait();
+  const float rs = row_scale_of(a.row_scale, n);      // the norm's sums: a kernel of this step wrote them, so after the wait
   const IT* src = (const IT*)a.qkv + (long long)n * heads * HD + (long long)h * HD + 4 * l;
   float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f};   // elements 4l.. of the first and second half
   // the first eight partials are all asked for before the first is added; they are added in their order
@@ -375,6 +441,13 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
     for (int k = 0; k < 4; ++k) {
       x0[k] += u0[k];
       x1[k] += u1[k];
+    }
+  }
+  if (a.row_scale.ss) {                             // what the norm ahead left to its consumer
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x0[k] *= rs;
+      x1[k] *= rs;
     }
   }
   if (a.q_norm_w || a.k_norm_w) {                  // uniform over the block: the shuffles need every lane

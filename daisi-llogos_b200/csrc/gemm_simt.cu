@@ -5,6 +5,7 @@
 // (Daisi.Llogos.Cuda/CudaBackend.cs:506-519) and has a one-row-per-block GEMV for 16-bit
 // weights (kernels/dequant_matmul.cu:593-619).
 #include "common.cuh"
+#include "kernel_args.h"
 
 LLG_API const char* llg_last_error() { return g_llg_error; }
 
@@ -16,7 +17,7 @@ constexpr int BK = 16;
 
 template <typename AT, typename WT, typename CT>
 __global__ void __launch_bounds__(256) gemm_tn_kernel(const AT* __restrict__ x, const WT* __restrict__ w,
-                                                      CT* __restrict__ out, int n, int o, int k) {
+                                                      CT* __restrict__ out, int n, int o, int k, RowScale scale) {
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -62,24 +63,27 @@ __global__ void __launch_bounds__(256) gemm_tn_kernel(const AT* __restrict__ x, 
   for (int i = 0; i < 4; ++i) {
     const int r = n0 + ty * 4 + i;
     if (r >= n) continue;
+    const float rs = row_scale_of(scale, r);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = o0 + tx * 4 + j;
-      if (c < o) out[(long long)r * o + c] = from_f32<CT>(acc[i][j]);
+      if (c < o) out[(long long)r * o + c] = from_f32<CT>(scale.ss ? acc[i][j] * rs : acc[i][j]);
     }
   }
 }
 
 }  // namespace
 
+// With `scale` (may be null) row r of the result is multiplied by the scale that a norm left for row r of x.
 LLG_API int llg_gemm_simt(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype,
-                          int n, int o, int k, cudaStream_t stream) {
+                          int n, int o, int k, const RowScale* scale, cudaStream_t stream) {
   LLG_REQUIRE(n >= 0 && o > 0 && k > 0, "gemm_simt: bad sizes n=%d o=%d k=%d", n, o, k);
   if (n == 0) return 0;
   dim3 grid((o + BN - 1) / BN, (n + BM - 1) / BM);
   LLG_REQUIRE(grid.y <= 65535, "gemm_simt: %d rows need more than 65535 row blocks", n);
+  const RowScale rs = scale ? *scale : RowScale{nullptr, 0, 0.f, 0.f};
 #define LAUNCH(AT, WT, CT) \
-  gemm_tn_kernel<AT, WT, CT><<<grid, 256, 0, stream>>>((const AT*)x, (const WT*)w, (CT*)out, n, o, k)
+  gemm_tn_kernel<AT, WT, CT><<<grid, 256, 0, stream>>>((const AT*)x, (const WT*)w, (CT*)out, n, o, k, rs)
   const int key = x_dtype * 4 + w_dtype * 2 + out_dtype;
   switch (key) {
     case 0: LAUNCH(float, float, float); break;

@@ -126,6 +126,7 @@ struct GemmParams {
   int up_offset;    // gated: row of w that holds the up row of feature 0 (gate rows come first)
   int gate_rows;    // gated, weights as first operand: features per block (at most 128)
   QkPrepArgs prep;  // EPI 2 / 3: what the q/k/v preparation needs (its `qkv` field is not used)
+  RowScale scale;   // of the token rows of x: the result's rows are multiplied by it (EPI 2 / 3 take prep.row_scale)
 };
 
 // an element of a weight vector stored as float32 or bfloat16
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], done_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float col_scale[SWAP ? 1 : TN];      // tokens along the columns: their scales, worked out during the products
 
   pdl_launch_dependents();      // the next kernel may set itself up while this one runs
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -271,6 +273,11 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       pdl_wait();               // every other thread: before anything of the previous kernel is read or overwritten
     }
     first = false;
+    if (!SWAP && p.scale.ss && tid >= 64) {
+      // two warps have nothing to do until the epilogue: they work out the scales of this tile's tokens meanwhile
+      // (the block-wide barrier before the epilogue makes them visible)
+      for (int c = tid - 64; c < TN; c += 64) col_scale[c] = n0 + c < p.n ? row_scale_of(p.scale, n0 + c) : 0.f;
+    }
     if (tid == 32) {
       // ---- consumer: one thread issues every MMA ----------------------------------------------
       constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -333,6 +340,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
           const bool live = tok < p.o;
           const int pos = live ? a.positions[tok] : 0;
           const int slot = (live && a.k_pages) ? a.slots[a.seq_of_token[tok]] : 0;
+          const float rs = live ? row_scale_of(a.row_scale, tok) : 1.0f;
 #pragma unroll 1
           for (int hb = 0; hb < TN / HD; ++hb) {
             const int head = n0 / HD + hb;
@@ -344,7 +352,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
               tmem_ld16(lane_base + (uint32_t)(mt * TN + hb * HD + c0), r);
               asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-              for (int c = 0; c < 16; ++c) h[c0 + c] = __uint_as_float(r[c]);
+              for (int c = 0; c < 16; ++c) h[c0 + c] = __uint_as_float(r[c]) * rs;
             }
             const int kind = head < a.nh ? 0 : (head < a.nh + a.nkv ? 1 : 2);      // query, key, value
             const void* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
@@ -413,6 +421,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         for (int mt = 0; mt < MT; ++mt) {
           if (o0 + mt * BM >= p.o) break;
           const int tok = o0 + mt * BM + warp * 32 + lane;
+          const float rs = tok < p.o ? row_scale_of(p.scale, tok) : 1.0f;
           OT* row = out + (long long)tok * width;
           constexpr int COLS = EPI == 1 ? TN / 2 : TN;
 #pragma unroll
@@ -428,13 +437,13 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
               asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
               for (int c = 0; c < 16; ++c) {
-                const float g = __uint_as_float(r[c]);
-                v[c] = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(ru[c]);
+                const float g = __uint_as_float(r[c]) * rs;
+                v[c] = __fdividef(g, 1.0f + __expf(-g)) * (__uint_as_float(ru[c]) * rs);
               }
             } else {
               asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-              for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+              for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]) * rs;
             }
             if (tok < p.o) {
               if (vec_ok && f0 + 16 <= width) {
@@ -479,7 +488,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
               for (int c = 0; c < 16; ++c) {
                 const int n = n0 + c0 + c;
-                if (n < p.n) out[(long long)n * p.o + o] = from_f32<OT>(__uint_as_float(r[c]));
+                const float v = p.scale.ss ? __uint_as_float(r[c]) * col_scale[c0 + c] : __uint_as_float(r[c]);
+                if (n < p.n) out[(long long)n * p.o + o] = from_f32<OT>(v);
               }
             }
           }
@@ -501,7 +511,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int c = 0; c < 16; ++c) {
               const int n = n0 + c0 + c;
-              const float g = __uint_as_float(rg[c]), u = __uint_as_float(ru[c]);
+              const float rs = p.scale.ss ? col_scale[c0 + c] : 1.0f;
+              const float g = __uint_as_float(rg[c]) * rs, u = __uint_as_float(ru[c]) * rs;
               if (n < p.n) out[(long long)n * inter + f] = from_f32<OT>(__fdividef(g, 1.0f + __expf(-g)) * u);
             }
           }
@@ -528,6 +539,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TMEM_COLS) : "memory");
   }
 }
+
 
 // ---- host side: tensor maps ------------------------------------------------------------------
 
@@ -623,8 +635,11 @@ LLG_API int llg_gemm_tc_splits(int k, int splits) {
 // out[s][n][o] for s < llg_gemm_tc_splits(k, splits); out_dtype float32, or bfloat16 when there is one split.
 // gated_features > 0 (one split only): w has 2 * P rows with P = F rounded up to a multiple of 128: the gate rows of
 // all features, zero rows up to P, then the up rows in the same way; out is [n][F] = silu(gate) * up.
+// `scale` (may be null): what a norm left for the rows of x; the rows of the result are multiplied by it (with several
+// splits every partial is).
 LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int splits,
-                        int tile_n, int gated_features, cudaStream_t stream) {
+                        int tile_n, int gated_features, const RowScale* scale, cudaStream_t stream) {
+  const RowScale rs = scale ? *scale : RowScale{nullptr, 0, 0.f, 0.f};
   LLG_REQUIRE(llg_gemm_tc_supported(x, w, n, o, k), "gemm_tc: needs k %% 8 == 0 and 16-byte aligned operands (n=%d o=%d k=%d)",
               n, o, k);
   splits = llg_gemm_tc_splits(k, splits);
@@ -638,7 +653,7 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   if (n >= 256 && tile_n <= 0) {
     // ---- prompt steps: activations are the first operand (128 tokens per tile), up to 256 features per tile ----
     // in this orientation the kernel's first-operand rows (field o) are the tokens, the second's (field n) the features
-    GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features, o / 2, BM};
+    GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features, o / 2, BM, QkPrepArgs{}, rs};
     // Tile shape: blocks run in rounds of one per SM (148 on a B200); a round costs its tile's width, and a narrower tile can save a
     // round (4096 features: 16 tiles of 256 in two token rows of 8 are 128 blocks, 18 of 240 are 144).  Two token
     // tiles per block halve the weight traffic per flop (worth about 15 %) but double the tile.
@@ -698,7 +713,7 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
     if (gate_rows < 16) gate_rows = 16;
     if (gate_rows > BM) gate_rows = BM;
   }
-  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features, o / 2, gate_rows};
+  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features, o / 2, gate_rows, QkPrepArgs{}, rs};
   LLG_REQUIRE(splits <= 65535, "gemm_tc: grid too large");
   LLG_REQUIRE(tensor_map(w, o, k, gated ? gate_rows : BM, &map_w) && tensor_map(x, n, k, tile_n, &map_x),
               "gemm_tc: cuTensorMapEncodeTiled failed or is not available");
@@ -759,7 +774,7 @@ LLG_API int llg_gemm_tc_qkv(const void* x, const void* w, int n, int k, const Qk
                   aligned(a.k_pages) && aligned(a.v_pages),
               "gemm_tc_qkv: tables and outputs must be 16-byte aligned");
   const int nkb = (k + BK - 1) / BK;
-  GemmParams ps{nullptr, /*n=*/o, /*o=*/n, k, nkb, 0, 0, BM, a};
+  GemmParams ps{nullptr, /*n=*/o, /*o=*/n, k, nkb, 0, 0, BM, a, RowScale{nullptr, 0, 0.f, 0.f}};
   CUtensorMap map_w, map_x;
   LLG_REQUIRE(tensor_map(x, n, k, BM, &map_x) && tensor_map(w, o, k, 256, &map_w),
               "gemm_tc_qkv: cuTensorMapEncodeTiled failed or is not available");
@@ -773,6 +788,7 @@ LLG_API int llg_gemm_tc_qkv(const void* x, const void* w, int n, int k, const Qk
   return two ? launch<256, 3, __nv_bfloat16, 2, 3, 1>(&map_x, &map_w, ps, 1, stream)
              : launch<256, 4, __nv_bfloat16, 1, 3, 1>(&map_x, &map_w, ps, 1, stream);
 }
+
 
 // Error code that a block recorded when one of its waits ran out (0 = none); clears it.  Synchronises the device.
 LLG_API int llg_gemm_tc_status() {

@@ -3,6 +3,34 @@
 // int or a float; the layouts are part of the libraries' interface.
 #pragma once
 
+// What a norm leaves to the consumer of its output when it does not divide by the root mean square itself: the norm
+// wrote x * weight and, per row, the sum of the row's squares, whole (parts = 1) or as `parts` partial sums (one per
+// block of columns of whoever produced the row).  The consumer multiplies the rows of its product by
+// 1 / sqrt(sum / width + eps): a product is linear in its rows, so the result is that of the normalised input, and
+// nobody had to wait for a whole row before the product's operand could be written.
+struct RowScale {
+  const float* ss;            // [rows][parts], or null: rows are used as they are
+  int parts;
+  float inv_width;            // 1 / (elements of a row)
+  float eps;
+};
+
+#ifdef __CUDACC__
+__device__ __forceinline__ float row_scale_of(const RowScale& s, long long row) {
+  if (!s.ss) return 1.0f;
+  const float* p = s.ss + row * s.parts;
+  float t = 0.f;
+  for (int j0 = 0; j0 < s.parts; j0 += 8) {           // eight loads under way at a time; added in their order, so
+    float v[8];                                       // the scale is the same whoever computes it
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = j0 + j < s.parts ? p[j0 + j] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t += v[j];
+  }
+  return 1.0f / sqrtf(t * s.inv_width + s.eps);
+}
+#endif
+
 struct QkPrepArgs {
   const void* qkv;            // [n_partials][n_tokens][(nh + 2 nkv) * hd], float32 or bfloat16
   int qkv_dtype;
@@ -31,6 +59,7 @@ struct QkPrepArgs {
   const int* seq_of_token;    // [n_tokens] -> index into slots
   const int* slots;
   int n_tokens, nh, nkv, hd;
+  RowScale row_scale;         // of the token rows of qkv (applied to the summed partials, before anything else)
 };
 
 // Attention for a step with several tokens per sequence (attention_simt.cu, attention_mma.cu, attention_tc.cu).

@@ -16,7 +16,7 @@ from ..parts.spec import ModelSpec
 
 # importing the modules registers the stock parts
 from ..parts import attention as _attention  # noqa: F401
-from ..parts import block as _block  # noqa: F401
+from ..parts.block import normed_for
 from ..parts import embedding as _embedding  # noqa: F401
 from ..parts import feedforward as _feedforward  # noqa: F401
 from ..parts import norm as _norm  # noqa: F401
@@ -143,5 +143,5 @@ class DecoderModel:
         if rows is None or rows.numel() == 0:
             # nothing wanted: the residual need not be finished, the cache already is
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        x = self.final_norm.forward(residual, pending, ctx, rows=rows)
-        return self.head.forward(x, ctx)
+        x, kw = normed_for(self.final_norm, self.head, residual, pending, ctx, rows)
+        return self.head.forward(x, ctx, **kw)

@@ -60,6 +60,7 @@ class _RunnerStep(Structure):
         ("prefill_kind", c_int), ("decode_kind", c_int), ("decode_splits", c_int), ("decode_balance", c_int),
         ("tc_qkv", c_int), ("tc_o", c_int), ("tc_gate_up", c_int), ("tc_down", c_int),
         ("splits_qkv", c_int), ("splits_o", c_int), ("splits_down", c_int), ("fused_qkv", c_int),
+        ("ss", c_void_p), ("ss_parts", c_int),
         ("residual", c_void_p), ("norm_out", c_void_p), ("qkv", c_void_p), ("q", c_void_p), ("k_new", c_void_p),
         ("v_new", c_void_p), ("attn_out", c_void_p), ("proj", c_void_p), ("act", c_void_p), ("ffn_out", c_void_p),
         ("gate_up", c_void_p), ("gate_up_rows", c_int), ("attn_scratch", c_void_p), ("attn_counters", c_void_p),
@@ -229,6 +230,9 @@ class BlockRunner:
         s.fused_qkv = int(ops.USE_FUSED_QKV and not ctx.decode and bool(s.tc_qkv) and n > 512 and hd in (64, 128)
                           and g.get("fusable_rotation", 1) == 1)
         s.splits_qkv, s.splits_o, s.splits_down = splits(qkv_dim, hidden), splits(hidden, q_dim), splits(hidden, inter)
+        # a bfloat16 step's norms leave their division to the products that consume them (parts/norm.py)
+        s.ss_parts = ops.norm_ss_parts(n, hidden) if bf16 else 0
+        s.ss = ctx.buffer("norm.ss", (n, s.ss_parts), torch.float32).data_ptr() if bf16 else None
         s.residual = residual.data_ptr()
         s.norm_out = ctx.buffer("norm.out", (n, hidden)).data_ptr()
         s.qkv = ctx.buffer("attn.qkv", (s.splits_qkv, n, qkv_dim), torch.float32).data_ptr()
@@ -257,7 +261,7 @@ class BlockRunner:
             tiles = ctx.query_tiles(tq)
             s.tiles, s.n_tiles = tiles.data_ptr(), tiles.shape[0]
             s.prefill_kind = 2 if ops._use_tc_attn(dtype, hd) else 1 if ops._use_mma(dtype, hd) else 0
-        need = ["add_rmsnorm", "qk_prep"] + (["gemm_tc_qkv"] if s.fused_qkv else [])
+        need = ["add_rmsnorm"] + (["gemm_tc_qkv"] if s.fused_qkv else ["qk_prep"])
         need.append("gemm_tc" if (s.tc_qkv or s.tc_o or s.tc_down or (s.tc_gate_up and bf16)) else "gemm_simt")
         if not (s.tc_qkv and s.tc_o and s.tc_down):
             need.append("gemm_simt")

@@ -59,9 +59,10 @@ SPLIT_ROWS_MAX = 512    # with more rows the products are bound by arithmetic an
 
 
 def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dtype,
-           out: torch.Tensor = None, split_k: bool = True) -> torch.Tensor:
+           out: torch.Tensor = None, split_k: bool = True, row_scale=None) -> torch.Tensor:
     """``out`` (a ``[1, N, O]`` view) makes the product write there instead of into the named buffer.
-    ``split_k=False`` is for a caller that does not sum partials: the result is ``[1, N, O]``."""
+    ``split_k=False`` is for a caller that does not sum partials: the result is ``[1, N, O]``.
+    ``row_scale``: what a norm left for the rows of ``x`` (``ops.RowScale``); the product's rows are multiplied by it."""
     ops = ctx.ops
     n, k = x.shape
     o = w.shape[0]
@@ -72,11 +73,17 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dt
             splits = ops.gemm_tc_splits(k, plan_splits(n, o, k, ops.sm_count()))
         if out is None:
             out = ctx.buffer(name, (splits, n, o), out_dtype)
-        ops.gemm_tc(x, w, out)
+        if row_scale is not None:
+            ops.gemm_tc(x, w, out, row_scale=row_scale)
+        else:
+            ops.gemm_tc(x, w, out)
         return out
     if out is None:
         out = ctx.buffer(name, (1, n, o), out_dtype)
-    ops.gemm_simt(x, w, out[0])
+    if row_scale is not None:
+        ops.gemm_simt(x, w, out[0], row_scale=row_scale)
+    else:
+        ops.gemm_simt(x, w, out[0])
     return out
 
 
@@ -94,20 +101,27 @@ def gated_layout(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out.view(2 * pad, hidden)
 
 
-def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor) -> None:
+def gated_linear(ctx, x: torch.Tensor, w_gated: torch.Tensor, out: torch.Tensor, row_scale=None) -> None:
     """out[n, i] = silu(x . gate_i) * (x . up_i) for a gate/up matrix in ``gated_layout``.
 
     On the tensor cores the gating is the epilogue of the product; otherwise the product writes
-    gate and up values and the gating kernel follows."""
+    gate and up values and the gating kernel follows.  ``row_scale`` as in ``linear``: both products' rows are
+    multiplied by it before the gating."""
     ops = ctx.ops
     n = x.shape[0]
     rows = w_gated.shape[0]
     tc = getattr(ops, "gemm_tc_supported", None)
     if tc is not None and tc(x, w_gated) and out.dtype == torch.bfloat16:
-        ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1])
+        if row_scale is not None:
+            ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1], row_scale=row_scale)
+        else:
+            ops.gemm_tc(x, w_gated, out.unsqueeze(0), gated_features=out.shape[1])
         return
     for r0 in range(0, n, _GATED_CHUNK):
         r1 = min(n, r0 + _GATED_CHUNK)
         gu = ctx.buffer("ffn.gate_up", (1, r1 - r0, rows), x.dtype)
-        ops.gemm_simt(x[r0:r1], w_gated, gu[0])
+        if row_scale is not None:
+            ops.gemm_simt(x[r0:r1], w_gated, gu[0], row_scale=row_scale.slice(r0, r1))
+        else:
+            ops.gemm_simt(x[r0:r1], w_gated, gu[0])
         ops.silu_mul(gu, out[r0:r1])

@@ -77,6 +77,40 @@ def _check(lib, rc: int, kernels: int = 1) -> None:
 
 # ---- libraries and prototypes ---------------------------------------------------------
 
+class _RowScale(Structure):
+    _fields_ = [("ss", c_void_p), ("parts", c_int), ("inv_width", c_float), ("eps", c_float)]
+
+
+class RowScale:
+    """What a norm leaves to the consumer of its output when it does not divide by the root mean square itself: the
+    output holds ``x * weight`` and ``ss`` (float32 ``[rows, parts]``) the sums of squares of each row of ``x``, whole
+    or as partial sums; the consumer multiplies row r of its product by ``1 / sqrt(sum(ss[r]) / width + eps)``."""
+
+    def __init__(self, ss: torch.Tensor, width: int, eps: float):
+        if ss.dim() != 2 or ss.dtype != torch.float32:
+            raise KernelError("a row scale's sums are float32 [rows, parts]")
+        self.ss, self.width, self.eps = ss, int(width), float(eps)
+
+    @property
+    def rows(self) -> int:
+        return self.ss.shape[0]
+
+    def slice(self, r0: int, r1: int) -> "RowScale":
+        return RowScale(self.ss[r0:r1], self.width, self.eps)
+
+    def c(self) -> "_RowScale":
+        return _RowScale(_ptr(self.ss, torch.float32), self.ss.shape[1], 1.0 / self.width, self.eps)
+
+
+def _scale_ref(row_scale: Optional[RowScale], rows: int):
+    """ctypes argument for an optional ``const RowScale*``."""
+    if row_scale is None:
+        return None
+    if row_scale.rows != rows:
+        raise KernelError(f"a row scale for {row_scale.rows} rows was given to a product of {rows} rows")
+    return byref(row_scale.c())
+
+
 class _QkPrepArgs(Structure):
     _fields_ = [
         ("qkv", c_void_p), ("qkv_dtype", c_int), ("n_partials", c_int), ("partial_stride", c_longlong),
@@ -89,6 +123,7 @@ class _QkPrepArgs(Structure):
         ("table_width", c_int), ("ring_pages", c_int),
         ("seq_of_token", c_void_p), ("slots", c_void_p),
         ("n_tokens", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int),
+        ("row_scale", _RowScale),
     ]
 
 
@@ -162,7 +197,7 @@ def _load_lib(name: str):
             raise KernelError(f"the kernels use pages of {lib.llg_page_size()} tokens, Python expects {PAGE}")
         lib.llg_embed_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.llg_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float,
-                                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
+                                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.llg_qk_prep.argtypes = [POINTER(_QkPrepArgs), c_int, c_void_p]
         lib.llg_kv_write.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
@@ -171,11 +206,13 @@ def _load_lib(name: str):
         lib.llg_gather_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.llg_zero_rows.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
     elif name == "gemm_simt":
-        lib.llg_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                      POINTER(_RowScale), c_void_p]
     elif name == "gemm_tc":
         lib.llg_gemm_tc_supported.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int]
         lib.llg_gemm_tc_splits.argtypes = [c_int, c_int]
-        lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    POINTER(_RowScale), c_void_p]
         lib.llg_gemm_tc_qkv.argtypes = [c_void_p, c_void_p, c_int, c_int, POINTER(_QkPrepArgs), c_void_p]
     elif name == "attention_simt":
         lib.llg_attn_prefill_simt.argtypes = [POINTER(_PrefillArgs), c_int, c_void_p]
@@ -240,10 +277,13 @@ def embed_rows(table: torch.Tensor, token_ids: torch.Tensor, out_residual: torch
 
 
 def add_rmsnorm(residual: torch.Tensor, branch: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None, ss_out: Optional[torch.Tensor] = None) -> None:
     """residual += sum of branch partials (if any); out[j] = RMSNorm(residual[rows[j] or j]) * weight.
 
     ``residual`` is float32 ``[N, H]``; ``branch`` float32 ``[S, N, H]`` or None; ``out`` ``[M, H]``.
+    With ``ss_out`` (float32 ``[M, norm_ss_parts(M, H)]``) the division is left to whoever consumes ``out``: ``out[j]``
+    is the row times ``weight`` and ``ss_out[j]`` holds the row's sum of squares, whole or as the sums of equal slices
+    of the row in their order (see ``RowScale``).
     """
     lib = _lib("elementwise")
     n, hidden = residual.shape
@@ -253,22 +293,40 @@ def add_rmsnorm(residual: torch.Tensor, branch: Optional[torch.Tensor], weight: 
         assert rows.numel() == m
     else:
         assert m == n
+    if ss_out is not None:
+        assert tuple(ss_out.shape) == (m, norm_ss_parts(m, hidden)), (ss_out.shape, m, hidden)
     n_part, stride = 0, 0
     if branch is not None:
         assert branch.dim() == 3 and branch.shape[1:] == (n, hidden), (branch.shape, residual.shape)
         n_part, stride = branch.shape[0], n * hidden
     _check(lib, lib.llg_add_rmsnorm(_ptr(residual, torch.float32), _ptr(branch, torch.float32), n_part, stride,
                                     _ptr(weight), _dt(weight), float(eps), _ptr(out), _dt(out),
-                                    _ptr(rows, torch.int32), m, hidden, _stream()))
+                                    _ptr(rows, torch.int32), m, hidden, _ptr(ss_out, torch.float32), _stream()))
 
 
-def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n, o] = sum_k x[n, k] w[o, k] on the CUDA cores, float32 accumulation."""
+_ss_parts = {}
+
+
+def norm_ss_parts(n_out: int, hidden: int) -> int:
+    """Sums of squares per row that ``add_rmsnorm(..., ss_out=)`` writes for these sizes: one, or for the few rows
+    of a decode step one per slice of the row (each slice is a block of its own there)."""
+    key = (n_out <= 64, hidden)
+    p = _ss_parts.get(key)
+    if p is None:
+        lib = _lib("elementwise")
+        lib.llg_add_rmsnorm_parts.argtypes = [c_int, c_int]
+        p = _ss_parts[key] = lib.llg_add_rmsnorm_parts(1 if n_out <= 64 else 65, hidden)
+    return p
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, row_scale: Optional[RowScale] = None) -> None:
+    """out[n, o] = sum_k x[n, k] w[o, k] on the CUDA cores, float32 accumulation; rows times ``row_scale`` if given."""
     lib = _lib("gemm_simt")
     n, k = x.shape
     o, k2 = w.shape
     assert k == k2 and out.shape == (n, o), (x.shape, w.shape, out.shape)
-    _check(lib, lib.llg_gemm_simt(_ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(out), _dt(out), n, o, k, _stream()))
+    _check(lib, lib.llg_gemm_simt(_ptr(x), _dt(x), _ptr(w), _dt(w), _ptr(out), _dt(out), n, o, k,
+                                  _scale_ref(row_scale, n), _stream()))
 
 
 def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -297,12 +355,14 @@ def gated_rows(features: int) -> int:
     return -(-features // 128) * 256
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int = 0, gated_features: int = 0) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int = 0, gated_features: int = 0,
+            row_scale: Optional[RowScale] = None) -> None:
     """out[s, n, o] = split-K partials of x[n, k] w[o, k] on the tensor cores (tcgen05, TMA).
 
     ``out`` is ``[S, N, O]`` float32 with S = ``gemm_tc_splits(k, wish)``, or ``[1, N, O]`` bfloat16.
     With ``gated_features = F`` the matrix ``w`` is in the gated layout (``gated_rows(F)`` rows) and
-    ``out`` is ``[1, N, F]`` holding ``silu(gate) * up``.
+    ``out`` is ``[1, N, F]`` holding ``silu(gate) * up``.  ``row_scale``: what a norm left for the rows of ``x``;
+    the rows of the product are multiplied by it (before the gating).
     """
     lib = _lib("gemm_tc")
     n, k = x.shape
@@ -312,7 +372,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int 
     if gemm_tc_splits(k, s) != s:
         raise KernelError(f"gemm_tc: {s} splits cannot be had for k = {k}")
     _check(lib, lib.llg_gemm_tc(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k, s,
-                                tile_n, gated_features, _stream()))
+                                tile_n, gated_features, _scale_ref(row_scale, n), _stream()))
 
 
 def gemm_tc_status() -> int:
@@ -329,12 +389,14 @@ def qk_prep(qkv: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
             k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
             k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
             page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
-            seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
+            seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+            row_scale: Optional[RowScale] = None) -> None:
     """Per-head norm (optional), bias (optional), rotation, and the writes of q, k, v.
 
     ``qkv`` is ``[S, N, (nh + 2 nkv) * hd]`` (partials are summed).  Queries go to ``q_out``;
     keys and values go to ``k_new``/``v_new`` (packed, for a prompt step) and/or straight into
-    the cache pages (for a one-token step).
+    the cache pages (for a one-token step).  ``row_scale``: what a norm left for the token rows; the summed
+    partials are multiplied by it before anything else.
     """
     lib = _lib("elementwise")
     s, n, width = qkv.shape
@@ -342,7 +404,15 @@ def qk_prep(qkv: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
     a = _prep_args(n, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim, pairing,
                    positions, q_out, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
     a.qkv, a.qkv_dtype, a.n_partials, a.partial_stride = _ptr(qkv), _dt(qkv), s, n * width
+    _set_scale(a, row_scale, n)
     _check(lib, lib.llg_qk_prep(byref(a), _dt(q_out), _stream()))
+
+
+def _set_scale(a: "_QkPrepArgs", row_scale: Optional[RowScale], n: int) -> None:
+    if row_scale is not None:
+        if row_scale.rows != n:
+            raise KernelError(f"a row scale for {row_scale.rows} rows was given to {n} token rows")
+        a.row_scale = row_scale.c()
 
 
 def _prep_args(n, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim, pairing,
@@ -391,7 +461,8 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, *, n_heads: int, n_kv_heads: i
                 k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
                 k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
                 page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
-                seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
+                seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+                row_scale: Optional[RowScale] = None) -> None:
     """The q/k/v projection ``x w^T`` on the tensor cores with ``qk_prep`` as its epilogue (one kernel; the float32
     q/k/v array is never written).  Same arguments and results as ``gemm_tc`` followed by ``qk_prep``."""
     lib = _lib("gemm_tc")
@@ -399,6 +470,7 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, *, n_heads: int, n_kv_heads: i
     assert w.shape == ((n_heads + 2 * n_kv_heads) * head_dim, k) and q_out.dtype == torch.bfloat16
     a = _prep_args(n, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim, pairing,
                    positions, q_out, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
+    _set_scale(a, row_scale, n)
     _check(lib, lib.llg_gemm_tc_qkv(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), n, k, byref(a), _stream()))
 
 

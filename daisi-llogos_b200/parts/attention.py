@@ -23,6 +23,8 @@ class Attention(Mixer):
     window (0 = all keys), position (name of a position encoding or None), softmax_scale
     (None = 1/sqrt(head_dim)), own_kv (False: no k/v projections, reads another entry's cache)."""
 
+    TAKES_ROW_SCALE = True
+
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         p = params
@@ -95,23 +97,24 @@ class Attention(Mixer):
                              f"{(need.num_kv_heads, need.head_dim, need.window)}, this reader expects {mine}")
 
     # ---- one step ------------------------------------------------------------------------
-    def forward(self, x, ctx, cache) -> Branch:
+    def forward(self, x, ctx, cache, row_scale=None) -> Branch:
         ops = ctx.ops
         n = x.shape[0]
         nkv_in = self.nkv if self.own_kv else 0
         rot = self.encoding.rotation() if self.encoding is not None else None
         # A large prompt step on the tensor cores prepares q and k in the projection's own epilogue.  Otherwise the
         # projection writes float32 (partials when the product splits K) and a second kernel prepares them; either
-        # way bias, norm and rotation see the unrounded sums, so q and k are rounded once.
+        # way the row scale, bias, norm and rotation see the unrounded sums, so q and k are rounded once.
         fused_qkv = getattr(ops, "gemm_tc_qkv_supported", None)
-        fused = (not ctx.decode and fused_qkv is not None
-                 and fused_qkv(x, self.w_qkv, self.hd, rot.rotary_dim if rot else 0, rot.pairing if rot else 0))
-        if fused:
+        scale_kw = {"row_scale": row_scale} if row_scale is not None else {}
+        if (not ctx.decode and fused_qkv is not None
+                and fused_qkv(x, self.w_qkv, self.hd, rot.rotary_dim if rot else 0, rot.pairing if rot else 0)):
             def prep(qkv_, **kw):
-                ops.gemm_tc_qkv(x, self.w_qkv, **kw)
+                ops.gemm_tc_qkv(x, self.w_qkv, **kw, **scale_kw)
             qkv = None
         else:
-            prep = ops.qk_prep
+            def prep(qkv_, **kw):
+                ops.qk_prep(qkv_, **kw, **scale_kw)
             qkv = linear(ctx, x, self.w_qkv, "attn.qkv", torch.float32)
         q = ctx.buffer("attn.q", (n, self.nh, self.hd))
         out = ctx.buffer("attn.out", (n, self.nh * self.hd))
@@ -122,11 +125,11 @@ class Attention(Mixer):
                       positions=ctx.positions, q_out=q)
         if ctx.decode:
             if self.own_kv:
-                ops.qk_prep(qkv, **common, k_pages=cache.k_pages, v_pages=cache.v_pages,
-                            page_table=cache.page_table, ring_pages=cache.ring_pages,
-                            seq_of_token=ctx.seq_of_token, slots=ctx.slots)
+                prep(qkv, **common, k_pages=cache.k_pages, v_pages=cache.v_pages,
+                     page_table=cache.page_table, ring_pages=cache.ring_pages,
+                     seq_of_token=ctx.seq_of_token, slots=ctx.slots)
             else:
-                ops.qk_prep(qkv, **common)
+                prep(qkv, **common)
             # which kernel runs and how it splits the keys is the kernels' business: the plan says what scratch it wants
             plan = ops.attn_decode_plan(q.dtype, ctx.n_seqs, self.nh, self.nkv, self.hd, ctx.max_len_after)
             scratch = ctx.buffer("attn.scratch", (max(1, plan.scratch_floats),), torch.float32)

@@ -10,6 +10,11 @@ kinds:
 * ``Mixer``            - ``forward(x, ctx, cache) -> Branch``: mixes tokens of one sequence
   (attention here); may keep keys/values or fixed-size state per sequence.
 * ``FeedForward``      - ``forward(x, ctx) -> Branch``: per-token transformation.
+
+One optional refinement: a consumer that sets ``TAKES_ROW_SCALE`` gets ``row_scale=`` beside ``x``, and the norm
+may then leave its division by the root mean square to the consumer's first product (``Norm.forward_unscaled``): a
+product is linear in its rows.  A norm that does so needs no whole row in one place, so the few rows of a decode
+step can be spread over many blocks that never wait for one another.
 * ``PositionEncoding`` - gives mixers a rotation table and/or adds to the embeddings.
 * ``Block``            - arranges norms, a mixer and a feed-forward around the residual stream.
 
@@ -89,8 +94,16 @@ class Norm(Part):
     def forward(self, residual, branch: Optional[Branch], ctx, rows=None) -> torch.Tensor:
         raise NotImplementedError
 
+    def forward_unscaled(self, residual, branch: Optional[Branch], ctx, rows=None):
+        """``(x, row_scale)``: like ``forward``, but the norm may leave a per-row factor to the consumer
+        (``row_scale``, a ``kernels.ops.RowScale``, or ``None`` when ``x`` is finished).  Called instead of
+        ``forward`` for a consumer that sets ``TAKES_ROW_SCALE``."""
+        return self.forward(residual, branch, ctx, rows), None
+
 
 class Mixer(Part):
+    TAKES_ROW_SCALE = False     # True: ``forward`` accepts ``row_scale=`` and applies it to the rows of ``x``
+
     def forward(self, x, ctx, cache) -> Branch:
         raise NotImplementedError
 
@@ -100,6 +113,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    TAKES_ROW_SCALE = False     # as for ``Mixer``
+
     def forward(self, x, ctx) -> Branch:
         raise NotImplementedError
 

@@ -19,10 +19,19 @@ class PreNormBlock(Block):
 
     def forward(self, residual, pending: Optional[Branch], ctx, cache) -> Optional[Branch]:
         p = self.parts
-        h = p["norm1"].forward(residual, pending, ctx)
-        a = p["mixer"].forward(h, ctx, cache)
-        h = p["norm2"].forward(residual, a, ctx)
-        return p["ffn"].forward(h, ctx)
+        h, kw = normed_for(p["norm1"], p["mixer"], residual, pending, ctx)
+        a = p["mixer"].forward(h, ctx, cache, **kw)
+        h, kw = normed_for(p["norm2"], p["ffn"], residual, a, ctx)
+        return p["ffn"].forward(h, ctx, **kw)
+
+
+def normed_for(norm, consumer, residual, pending, ctx, rows=None):
+    """``(x, keyword arguments)`` for ``consumer.forward``: a consumer that takes a row scale lets the norm leave
+    its division to the consumer's first product."""
+    if getattr(consumer, "TAKES_ROW_SCALE", False):
+        x, scale = norm.forward_unscaled(residual, pending, ctx, rows)
+        return x, {"row_scale": scale}
+    return norm.forward(residual, pending, ctx, rows), {}
 
 
 register_part("block", "prenorm", PreNormBlock)

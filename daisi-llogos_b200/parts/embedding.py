@@ -37,6 +37,8 @@ class TokenEmbedding(Part):
 class LinearHead(Part):
     """params: vocab_size, hidden_size, tied_to (full name of the tensor to share, or None)."""
 
+    TAKES_ROW_SCALE = True
+
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.vocab = int(params["vocab_size"])
@@ -55,9 +57,9 @@ class LinearHead(Part):
             raise ValueError(f"output head: shared tensor has shape {tuple(self.weight.shape)}, "
                              f"expected {(self.vocab, self.hidden)}")
 
-    def forward(self, x, ctx) -> torch.Tensor:
+    def forward(self, x, ctx, row_scale=None) -> torch.Tensor:
         # the logits go to samplers and callers as they are: one product, no partial sums to add up
-        return linear(ctx, x, self.weight, "head.logits", torch.float32, split_k=False)[0]
+        return linear(ctx, x, self.weight, "head.logits", torch.float32, split_k=False, row_scale=row_scale)[0]
 
 
 register_part("embedding", "token_embedding", TokenEmbedding)

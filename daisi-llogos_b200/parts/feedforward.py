@@ -16,6 +16,8 @@ from .base import Branch, FeedForward, TensorDecl, register_part
 class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size."""
 
+    TAKES_ROW_SCALE = True
+
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.hidden = int(params["hidden_size"])
@@ -37,9 +39,9 @@ class SwiGLU(FeedForward):
         self.w_gate_up = gated_layout(g, u)
         self.w_down = tensors["down_proj.weight"]
 
-    def forward(self, x, ctx) -> Branch:
+    def forward(self, x, ctx, row_scale=None) -> Branch:
         act = ctx.buffer("ffn.act", (x.shape[0], self.inter))
-        gated_linear(ctx, x, self.w_gate_up, act)
+        gated_linear(ctx, x, self.w_gate_up, act, row_scale)
         return Branch(linear(ctx, act, self.w_down, "ffn.out", torch.float32))
 
 

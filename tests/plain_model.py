@@ -23,11 +23,16 @@ def embedding(table: torch.Tensor, tokens: Sequence[int]) -> torch.Tensor:
     return table.to(F64)[torch.as_tensor(list(tokens), dtype=torch.long)]
 
 
-def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, rnd=None) -> torch.Tensor:
     """x / sqrt(mean(x^2) + eps) * w: eps inside the root, weight after.
-    Daisi.Llogos.Cpu/RmsNorm.cs:14-65 (sum of squares in double, :19-41)."""
+    Daisi.Llogos.Cpu/RmsNorm.cs:14-65 (sum of squares in double, :19-41).
+
+    ``rnd``: a rounding applied to ``x * w`` before the division by the root: what an engine stores when it
+    leaves that division to the product that consumes the norm (a product is linear in its rows)."""
     x = x.to(F64)
     ms = (x * x).mean(dim=-1, keepdim=True)
+    if rnd is not None:
+        return rnd(x * weight.to(F64)) * (1.0 / torch.sqrt(ms + eps))
     return x * (1.0 / torch.sqrt(ms + eps)) * weight.to(F64)
 
 
@@ -163,12 +168,14 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], 
     projection, residual, norm, SwiGLU, residual (ForwardPass.cs:368-404 for the attention part).
 
     ``rounded``: values that a bfloat16 engine keeps in bfloat16 between its kernels are rounded to
-    bfloat16 here as well: the output of every norm, q, k and v after the rotation, the softmax weights
+    bfloat16 here as well: the input of every norm times the norm's weight (the division by the root mean
+    square follows the rounding, see ``rms_norm``), q, k and v after the rotation, the softmax weights
     as they enter the product with the values, the attention output and the gated feed-forward values.
     Sums, statistics, the residual stream and the logits stay unrounded.  The reference keeps every
     activation in 32 bits (Inference/ForwardPass.cs:1046-1047), so this form has no counterpart there;
     it tells a bfloat16 engine's rounding from a fault."""
     r = round_bfloat16 if rounded else (lambda t: t)
+    rnd = round_bfloat16 if rounded else None
     arch = cfg["architectures"][0]
     nh = cfg["num_attention_heads"]
     nkv = cfg.get("num_key_value_heads", nh)
@@ -187,7 +194,7 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], 
     h = embedding(weights["model.embed_tokens.weight"], tokens)
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        x = r(rms_norm(h, weights[p + "input_layernorm.weight"], eps))
+        x = rms_norm(h, weights[p + "input_layernorm.weight"], eps, rnd)
         a = p + "self_attn."
         q = linear(x, weights[a + "q_proj.weight"]).view(t, nh, hd)
         k = linear(x, weights[a + "k_proj.weight"]).view(t, nkv, hd)
@@ -204,11 +211,11 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], 
         v = r(v)
         o = r(attention(q, k, v, 1.0 / math.sqrt(hd), windows[i], r if rounded else None).reshape(t, nh * hd))
         h = h + linear(o, weights[a + "o_proj.weight"])
-        x = r(rms_norm(h, weights[p + "post_attention_layernorm.weight"], eps))
+        x = rms_norm(h, weights[p + "post_attention_layernorm.weight"], eps, rnd)
         m = p + "mlp."
         h = h + swiglu(x, weights[m + "gate_proj.weight"], weights[m + "up_proj.weight"], weights[m + "down_proj.weight"],
                        r if rounded else None)
-    x = r(rms_norm(h, weights["model.norm.weight"], eps))
+    x = rms_norm(h, weights["model.norm.weight"], eps, rnd)
     head = weights["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else weights["lm_head.weight"]
     return linear(x, head)
 

@@ -640,6 +640,76 @@ def test_qkv_product_with_the_preparation_as_its_epilogue(ops, nh, nkv, hd, k, n
         assert float(fkp.abs().sum()) == 0
 
 
+# ---- a norm that leaves its division to the products that consume it ------------------------------------------------
+
+def _scale_of(ss, width, eps):
+    """The factor a row scale stands for: 1 / sqrt(sum(ss) / width + eps) per row, float64."""
+    return 1.0 / torch.sqrt(ss.double().sum(dim=1) / width + eps)
+
+
+@pytest.mark.parametrize("hidden,n", [(70, 4), (72, 5), (1000, 3), (1024, 1), (4096, 8), (4096, 64), (4096, 300), (4100, 2), (8192, 5)])
+def test_add_rmsnorm_without_the_division(ops, hidden, n):
+    """With ``ss_out`` the norm writes the summed row times the weight (no division) and the row's sum of squares,
+    whole or, for the few rows of a decode step, as the sums of equal slices of the row (each slice a block of its
+    own); the residual is updated as always.  Rows gathered through ``rows`` as well."""
+    res = rnd((n, hidden), 1)
+    branch = rnd((9, n, hidden), 2, scale=0.5)
+    w = (rnd((hidden,), 3, torch.bfloat16, 0.1) + 1)
+    v = res.double() + branch.double().sum(0)
+    parts = ops.norm_ss_parts(n, hidden)
+    assert parts == (hidden // 256 if n <= 64 and hidden >= 1024 and hidden % 256 == 0 else 1)
+    r = res.to(DEV)
+    out = torch.empty(n, hidden, dtype=torch.bfloat16, device=DEV)
+    ss = torch.full((n, parts), float("nan"), device=DEV)
+    ops.add_rmsnorm(r, branch.to(DEV), w.to(DEV), 1e-5, out, ss_out=ss)
+    assert float((r.cpu().double() - v).abs().max()) < 2e-5
+    want = P.round_bfloat16(v * w.double())
+    off = out.cpu().double() != want
+    assert float(off.double().mean()) < 0.002                     # a float32 sum within an ulp of a tie
+    assert bool(((out.cpu().double() - want).abs() <= want.abs() * 2.0 ** -7 + 1e-6).all())     # + what a cancelled float32 sum is off by
+    sq = (v * v).view(n, parts, hidden // parts).sum(2)
+    assert float(((ss.cpu().double() - sq) / sq).abs().max()) < 1e-5
+    rows = torch.tensor([n - 1, 0], dtype=torch.int32)
+    out2 = torch.empty(2, hidden, dtype=torch.bfloat16, device=DEV)
+    ss2 = torch.empty(2, ops.norm_ss_parts(2, hidden), device=DEV)
+    ops.add_rmsnorm(r, None, w.to(DEV), 1e-5, out2, rows.to(DEV), ss_out=ss2)
+    assert torch.equal(out2.cpu(), out.cpu()[rows.long()])
+    assert float((ss2.cpu().sum(1) / ss.cpu()[rows.long()].sum(1) - 1).abs().max()) < 1e-6     # another kernel may add in another order
+
+
+@pytest.mark.parametrize("parts", [1, 5])
+@pytest.mark.parametrize("n,o,k", [(1, 200, 72), (16, 384, 1000), (40, 130, 256), (100, 257, 64), (200, 300, 136), (300, 512, 264), (700, 200, 64)])
+def test_products_apply_a_row_scale(ops, n, o, k, parts):
+    """Every product that may follow a norm multiplies its rows by the scale the norm left: the tensor-core product in
+    both orientations, with partial sums and with the gated epilogue, and the CUDA-core product."""
+    x = rnd((n, k), 11, torch.bfloat16)
+    w = rnd((o, k), 12, torch.bfloat16, 1.0 / math.sqrt(k))
+    ss = (rnd((n, parts), 13).abs() * 50 + 1)
+    scale = ops.RowScale(ss.to(DEV), 96, 1e-3)
+    f = _scale_of(ss, 96, 1e-3)[:, None]
+    want = P.linear(x, w) * f
+    for splits in (1, ops.gemm_tc_splits(k, 3)):
+        out = torch.empty(splits, n, o, device=DEV)
+        ops.gemm_tc(x.to(DEV), w.to(DEV), out, row_scale=scale)
+        check(out.sum(0).cpu(), want, torch.float32, f"gemm_tc splits={splits}")
+    out = torch.empty(1, n, o, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x.to(DEV), w.to(DEV), out, row_scale=scale)
+    check(out[0].cpu(), want, torch.bfloat16, "gemm_tc bfloat16")
+    out = torch.empty(n, o, device=DEV)
+    ops.gemm_simt(x.to(DEV), w.to(DEV), out, row_scale=scale)
+    check(out.cpu(), want, torch.float32, "gemm_simt")
+    # gated: silu(scale * gate) * (scale * up)
+    feat = o // 2
+    gate, up = w[:feat], w[feat:2 * feat]
+    g, u = P.linear(x, gate) * f, P.linear(x, up) * f
+    act = torch.empty(1, n, feat, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x.to(DEV), _gated(gate, up).to(DEV), act, gated_features=feat, row_scale=scale)
+    check(act[0].cpu(), g / (1 + torch.exp(-g)) * u, torch.bfloat16, "gated")
+    assert ops.gemm_tc_status() == 0
+    with pytest.raises(ops.KernelError, match="rows"):
+        ops.gemm_simt(x.to(DEV), w.to(DEV), out, row_scale=ops.RowScale(ss[:-1].to(DEV) if n > 1 else torch.ones(2, 1, device=DEV), 96, 1e-3))
+
+
 def test_kernels_refuse_what_they_cannot_do(ops):
     q = torch.zeros(1, 2, 272, device=DEV)
     kp = torch.zeros(1, 1, 64, 272, device=DEV)
