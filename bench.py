@@ -257,6 +257,84 @@ def probe_leave_one_out(torch, L, ops, cfg, batch, context):
     return 0
 
 
+def probe_timeline(torch, L, ops, cfg, batch, context):
+    """One decode step's kernels on one time line, from stamps that the kernels themselves leave (%globaltimer, 32 ns
+    steps) when the library is built with LLOGOS_NVCC_FLAGS=-DLLG_STAMPS: for every launch its number of blocks, when
+    its first and last block started, when their dependency wait returned, when the products were done and when the
+    blocks ended, in microseconds from the step's first stamp.  A stamp costs about a third of a microsecond."""
+    import ctypes
+    import numpy as np
+    if "-DLLG_STAMPS" not in os.environ.get("LLOGOS_NVCC_FLAGS", "").split():
+        print("the time line needs the kernels built with their stamps: run with LLOGOS_NVCC_FLAGS=-DLLG_STAMPS")
+        return 2
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
+    eng = L.engine.Engine(model, max_tokens=batch * context, max_seq_len=context, n_slots=batch)
+    for g in eng.cache.kv_groups:
+        for t in list(g.k.values()) + list(g.v.values()):
+            t.normal_(0.0, 1.0)
+    slots = [eng.open() for _ in range(batch)]
+    for s in slots:
+        eng.assume(s, context - 40)
+    tok = torch.randint(0, cfg["vocab_size"], (13, batch), generator=torch.Generator().manual_seed(1)).tolist()
+    libs = [ops._lib(n) for n in ("gemm_tc", "attention_decode_tma", "elementwise")]
+    cap = 131072
+
+    def read():
+        parts = []
+        for lib in libs:
+            buf = (ctypes.c_ulonglong * (2 * cap))()
+            lib.llg_stamps_read.argtypes = [ctypes.c_void_p, ctypes.c_int]
+            lib.llg_stamps_read.restype = ctypes.c_int
+            k = lib.llg_stamps_read(buf, cap)
+            parts.append(np.frombuffer(buf, dtype=np.uint64)[: 2 * k].reshape(-1, 2).copy())
+        return np.concatenate(parts)
+
+    for i in range(12):
+        eng.step([(s, [tok[i][j]]) for j, s in enumerate(slots)])
+    read()                                       # the warm-up steps' stamps are dropped
+    eng.step([(s, [tok[12][j]]) for j, s in enumerate(slots)])
+    st = read()
+    t, tag = st[:, 0].astype(np.int64), st[:, 1]
+    kern = (tag >> np.uint64(56)).astype(int)
+    phase = ((tag >> np.uint64(48)) & np.uint64(0xff)).astype(int)
+    aux = ((tag >> np.uint64(32)) & np.uint64(0xffff)).astype(int)
+    aux[kern != 1] = 0
+    t = (t - t.min()) / 1000.0
+    h, inter = cfg["hidden_size"], cfg["intermediate_size"]
+    q_rows = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
+    tag_of = lambda k, rows: (((k >> 10) & 0xff) << 8) | ((rows >> 9) & 0xff)
+    names = {tag_of(h, q_rows): "q/k/v", tag_of(cfg["num_attention_heads"] * cfg["head_dim"], h): "output",
+             tag_of(h, 2 * inter): "gate/up", tag_of(inter, h): "down", tag_of(h, cfg["vocab_size"]): "head"}
+    other = {2: "attention", 3: "norm", 4: "qk_prep"}
+    rows = []
+    for key in sorted(set(zip(kern.tolist(), aux.tolist()))):
+        m = (kern == key[0]) & (aux == key[1])
+        tt, ph = t[m], phase[m]
+        order = np.argsort(tt, kind="stable")
+        tt, ph = tt[order], ph[order]
+        starts = tt[ph == 0]
+        # a kernel's launches: a block that starts well after the one before, with a block's end in between, belongs
+        # to the next launch (or to the next wave of a grid larger than the device holds: the head product's)
+        ends = tt[ph == 3]
+        cuts = [0] + [i + 1 for i in range(len(starts) - 1) if starts[i + 1] - starts[i] > 15.0
+                      and ((ends > starts[i]) & (ends < starts[i + 1])).any()] + [len(starts)]
+        for a, b in zip(cuts[:-1], cuts[1:]):
+            nxt = starts[b] if b < len(starts) else float("inf")
+            sel = (tt >= starts[a]) & (tt < nxt)
+            span = lambda q: ((tt[sel & (ph == q)].min(), tt[sel & (ph == q)].max()) if (sel & (ph == q)).any()
+                              else (float("nan"), float("nan")))
+            name = names.get(key[1], f"product {key[1]:#x}") if key[0] == 1 else other.get(key[0], str(key[0]))
+            rows.append((starts[a], name, b - a, (starts[a], starts[b - 1]), span(1), span(2), span(3)))
+    rows.sort(key=lambda r: r[0])
+    print(f"batch {batch} context {context}, {cfg['num_hidden_layers']} layers: {len(t)} stamps; microseconds from the first")
+    print(f"{'kernel':10s} {'blocks':>6s} {'start':>15s} {'wait returned':>15s} {'products done':>15s} {'end':>15s}")
+    for r in rows:
+        print(f"{r[1]:10s} {r[2]:6d} " + " ".join(f"{a:7.1f}-{b:7.1f}" for a, b in r[3:]))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -271,9 +349,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-workloads", action="store_true", help="leave out the workloads of the other shapes and the ragged run")
-    ap.add_argument("--probe", choices=["decode-attention", "leave-one-out"],
-                    help="instead of the bench line, print a table: decode attention alone over batch shapes, or what "
-                         "the decode step loses when each kernel in turn is left out of the recorded graph")
+    ap.add_argument("--probe", choices=["decode-attention", "leave-one-out", "timeline"],
+                    help="instead of the bench line, print a table: decode attention alone over batch shapes; what "
+                         "the decode step loses when each kernel in turn is left out of the recorded graph; or one "
+                         "decode step's launches on a time line (needs LLOGOS_NVCC_FLAGS=-DLLG_STAMPS; --layers, default 6)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -296,6 +375,9 @@ def main():
         return probe_decode_attention(torch, ops, SHAPES[args.shape][1], pk)
     if args.probe == "leave-one-out":
         return probe_leave_one_out(torch, L, ops, dict(SHAPES[args.shape][1]), args.batch, args.context)
+    if args.probe == "timeline":
+        return probe_timeline(torch, L, ops, dict(SHAPES[args.shape][1], num_hidden_layers=args.layers or 6),
+                              args.batch, args.context)
     shape_name, shape = SHAPES[args.shape]
     if args.layers <= 0:
         args.layers = shape["num_hidden_layers"]

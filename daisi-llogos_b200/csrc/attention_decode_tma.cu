@@ -181,6 +181,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) LLG_STAMP(2, 0, 0, blockIdx.x);
   if (tid == WORK_WARPS * 32) {                        // the copying warp's first lane: fetch the tensor maps early
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
@@ -287,6 +288,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   const bf16* qg = (const bf16*)a.q;
   bf16* out = (bf16*)a.out;
   pdl_wait();                                           // the queries come from the kernel ahead
+  if (tid == 0) LLG_STAMP(2, 1, 0, blockIdx.x);
   // a ticket this warp has taken at a head's counter and not looked at yet
   bool pending = false;
   int pend_ticket = 0, pend_parts = 0;
@@ -543,6 +545,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     }
   }
   if (pending && ok) join_if_last();
+  if (tid == 0) LLG_STAMP(2, 3, 0, blockIdx.x);
 }
 
 // ---- host side ---------------------------------------------------------------------------------------

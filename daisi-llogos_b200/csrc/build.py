@@ -44,6 +44,12 @@ NVCC_FLAGS = [
     "--extended-lambda", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
 
+# Further flags for a build of its own, e.g. LLOGOS_NVCC_FLAGS=-DLLG_STAMPS for the kernels' time stamps (common.cuh):
+# they are part of the library's name, so such a build lies beside the ordinary one and neither replaces the other.
+_EXTRA_FLAGS = [f for f in os.environ.get("LLOGOS_NVCC_FLAGS", "").split() if f]
+NVCC_FLAGS += _EXTRA_FLAGS
+_VARIANT = ("." + hashlib.sha256(" ".join(_EXTRA_FLAGS).encode()).hexdigest()[:6]) if _EXTRA_FLAGS else ""
+
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
@@ -85,7 +91,7 @@ def _build_dir() -> str:
 
 
 def library_path(name: str) -> str:
-    return os.path.join(_build_dir(), f"libllogos_{name}-{_digest(name)}.so")
+    return os.path.join(_build_dir(), f"libllogos_{name}{_VARIANT}-{_digest(name)}.so")
 
 
 def _say(msg: str) -> None:
@@ -131,7 +137,7 @@ def compile_library(name: str, *, verbose: bool = True) -> str:
             if verbose:
                 _say(f"built {os.path.basename(out)} in {time.time() - t0:.1f} s")
             # libraries of older source versions are of no use any more
-            prefix = f"libllogos_{name}-"
+            prefix = f"libllogos_{name}{_VARIANT}-"
             for f in os.listdir(os.path.dirname(out)):
                 if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out):
                     try:

@@ -93,6 +93,42 @@ static inline cudaError_t llg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 b
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// ---- time stamps (only when compiled with -DLLG_STAMPS) ------------------------------------
+//
+// For looking at a step's kernels on one time line: a block's thread calls LLG_STAMP(kernel, phase, aux, block) and
+// the library keeps (%globaltimer, tag) pairs in a buffer of its own that llg_stamps_read() hands out and empties.
+// Phases by convention: 0 the block started, 1 its dependency wait returned, 2 its products are done, 3 it ends.
+// A stamp costs about a third of a microsecond (a timer read and an atomic); without the flag the macro is empty.
+#ifdef LLG_STAMPS
+#define LLG_STAMP_CAP 131072
+static __device__ unsigned long long g_stamps[2 * LLG_STAMP_CAP];
+static __device__ unsigned int g_stamp_n;
+__device__ __forceinline__ void llg_stamp(int kernel, int phase, int aux, int block) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const unsigned i = atomicAdd(&g_stamp_n, 1u);
+  if (i < (unsigned)LLG_STAMP_CAP) {
+    g_stamps[2 * i] = t;
+    g_stamps[2 * i + 1] = ((unsigned long long)kernel << 56) | ((unsigned long long)phase << 48) |
+                          ((unsigned long long)(aux & 0xffff) << 32) | (unsigned)block;
+  }
+}
+#define LLG_STAMP(kernel, phase, aux, block) llg_stamp(kernel, phase, aux, block)
+// Copies up to `cap` (time in ns, tag) pairs to `dst` and empties the buffer; returns how many.  Synchronises the device.
+LLG_API int llg_stamps_read(unsigned long long* dst, int cap) {
+  unsigned n = 0, zero = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&n, g_stamp_n, 4);
+  if (n > (unsigned)LLG_STAMP_CAP) n = LLG_STAMP_CAP;
+  if ((int)n > cap) n = cap;
+  if (dst && n) cudaMemcpyFromSymbol(dst, g_stamps, (size_t)n * 16);
+  cudaMemcpyToSymbol(g_stamp_n, &zero, 4);
+  return (int)n;
+}
+#else
+#define LLG_STAMP(kernel, phase, aux, block) ((void)0)
+#endif
+
 // ---- element access ---------------------------------------------------------------
 
 __device__ __forceinline__ float to_f32(float v) { return v; }

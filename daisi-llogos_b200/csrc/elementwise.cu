@@ -121,7 +121,9 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const floa
     const int i = threadIdx.x + k * blockDim.x;
     if (i < nv) vec_load4(weight + 4 * i, wv[k]);
   }
+  if (threadIdx.x == 0) LLG_STAMP(3, 0, 0, blockIdx.x);
   pdl_wait();
+  if (threadIdx.x == 0) LLG_STAMP(3, 1, 0, blockIdx.x);
   const int j = blockIdx.x;
   const int r = rows ? rows[j] : j;
   float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
@@ -179,6 +181,7 @@ __global__ void add_rmsnorm_vec4_kernel(float* __restrict__ residual, const floa
       vec_store4(o + 4 * i, y);
     }
   }
+  if (threadIdx.x == 0) LLG_STAMP(3, 3, 0, blockIdx.x);
 }
 
 // The norm of a step of few rows when the division is left to the consumer: nothing then needs a whole row, so a
@@ -200,7 +203,9 @@ __global__ void __launch_bounds__(PARTS_THREADS) add_rmsnorm_parts_kernel(float*
   float wv[4];
   vec_load4(weight + 4 * i, wv);                                   // no result of an earlier kernel
   const int j = blockIdx.y;
+  if (threadIdx.x == 0) LLG_STAMP(3, 0, 0, blockIdx.x + gridDim.x * blockIdx.y);
   pdl_wait();
+  if (threadIdx.x == 0) LLG_STAMP(3, 1, 0, blockIdx.x + gridDim.x * blockIdx.y);
   const int r = rows ? rows[j] : j;
   float4* res = reinterpret_cast<float4*>(residual + (long long)r * hidden);
   float4 v = res[i];
@@ -224,6 +229,7 @@ __global__ void __launch_bounds__(PARTS_THREADS) add_rmsnorm_parts_kernel(float*
   vec_store4(out + (long long)j * hidden + 4 * i, y);
   const float ss = block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red);
   if (threadIdx.x == 0) ss_out[(long long)j * gridDim.x + blockIdx.x] = ss;
+  if (threadIdx.x == 0) LLG_STAMP(3, 3, 0, blockIdx.x + gridDim.x * blockIdx.y);
 }
 
 // Parts that llg_add_rmsnorm writes per row into ss_out for these sizes (the consumer's RowScale.parts).
@@ -409,7 +415,9 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
   void* pages = kind == 0 ? nullptr : (kind == 1 ? a.k_pages : a.v_pages);
   long long page_row = 0;
   if (pages && live) page_row = kv_row(a.page_table, a.table_width, a.ring_pages, a.slots[a.seq_of_token[n]], pos, kvh, a.nkv);
+  if (threadIdx.x == 0) LLG_STAMP(4, 0, 0, blockIdx.x);
   pdl_wait();
+  if (threadIdx.x == 0) LLG_STAMP(4, 1, 0, blockIdx.x);
   const float rs = row_scale_of(a.row_scale, n);      // the norm's sums: a kernel of this step wrote them, so after the wait
   const IT* src = (const IT*)a.qkv + (long long)n * heads * HD + (long long)h * HD + 4 * l;
   float x0[4] = {0.f, 0.f, 0.f, 0.f}, x1[4] = {0.f, 0.f, 0.f, 0.f};   // elements 4l.. of the first and second half
@@ -498,6 +506,7 @@ __global__ void __launch_bounds__(256) qk_prep_vec_kernel(QkPrepArgs a) {
     vec_store4(o, x0);
     vec_store4(o + HALF, x1);
   }
+  if (threadIdx.x == 0) LLG_STAMP(4, 3, 0, blockIdx.x);
 }
 
 LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stream) {

@@ -171,6 +171,11 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 
   pdl_launch_dependents();      // the next kernel may set itself up while this one runs
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef LLG_STAMPS
+  // which product this is, for the time line: k / 1024 and the first operand's rows / 512
+  const int st_aux = (((p.k >> 10) & 0xff) << 8) | (((SWAP ? p.n : p.o) >> 9) & 0xff), st_blk = blockIdx.x + gridDim.x * blockIdx.z;
+#endif
+  if (tid == 0) LLG_STAMP(1, 0, st_aux, st_blk);
   if (tid == 0) {
     // the first copies need the two descriptors: fetch them while the barriers and the tensor memory are set up
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
@@ -250,6 +255,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
           else load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
         }
         pdl_wait();
+        LLG_STAMP(1, 1, st_aux, st_blk);
         for (int i = 0; i < pre; ++i) {
           if (SWAP) load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
           else load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
@@ -307,6 +313,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     bool have = mbar_wait(&done_bar, round & 1, abortp);
     if (!have && !*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
     __syncthreads();
+    if (tid == 0 && round == 0) LLG_STAMP(1, 2, st_aux, st_blk);
     if (*abortp != 0) break;
     // every stage is free now: request the first ring of the next tile so that it arrives during the epilogue
     preloaded = 0;
@@ -535,6 +542,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (tid == 0) LLG_STAMP(1, 3, st_aux, st_blk);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TMEM_COLS) : "memory");
   }
