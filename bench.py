@@ -257,8 +257,8 @@ def probe_leave_one_out(torch, L, ops, cfg, batch, context):
     return 0
 
 
-def probe_timeline(torch, L, ops, cfg, batch, context):
-    """One decode step's kernels on one time line, from stamps that the kernels themselves leave (%globaltimer, 32 ns
+def probe_timeline(torch, L, ops, cfg, batch, context, prompt_tokens=0):
+    """One decode step's kernels (or, with `prompt_tokens`, those of one prompt step of so many tokens) on one time line, from stamps that the kernels themselves leave (%globaltimer, 32 ns
     steps) when the library is built with LLOGOS_NVCC_FLAGS=-DLLG_STAMPS: for every launch its number of blocks, when
     its first and last block started, when their dependency wait returned, when the products were done and when the
     blocks ended, in microseconds from the step's first stamp.  A stamp costs about a third of a microsecond."""
@@ -274,11 +274,23 @@ def probe_timeline(torch, L, ops, cfg, batch, context):
     for g in eng.cache.kv_groups:
         for t in list(g.k.values()) + list(g.v.values()):
             t.normal_(0.0, 1.0)
-    slots = [eng.open() for _ in range(batch)]
-    for s in slots:
-        eng.assume(s, context - 40)
-    tok = torch.randint(0, cfg["vocab_size"], (13, batch), generator=torch.Generator().manual_seed(1)).tolist()
-    libs = [ops._lib(n) for n in ("gemm_tc", "attention_decode_tma", "elementwise")]
+    gen = torch.Generator().manual_seed(1)
+    if prompt_tokens > 0:
+        prompt = torch.randint(0, cfg["vocab_size"], (prompt_tokens,), generator=gen).tolist()
+
+        def step(i):
+            slot = eng.open()
+            eng.step([(slot, prompt)])
+            eng.close(slot)
+    else:
+        slots = [eng.open() for _ in range(batch)]
+        for s in slots:
+            eng.assume(s, context - 40)
+        tok = torch.randint(0, cfg["vocab_size"], (13, batch), generator=gen).tolist()
+
+        def step(i):
+            eng.step([(s, [tok[i][j]]) for j, s in enumerate(slots)])
+    libs = [ops._lib(n) for n in ("gemm_tc", "attention_decode_tma", "attention_tc", "elementwise")]
     cap = 131072
 
     def read():
@@ -292,9 +304,9 @@ def probe_timeline(torch, L, ops, cfg, batch, context):
         return np.concatenate(parts)
 
     for i in range(12):
-        eng.step([(s, [tok[i][j]]) for j, s in enumerate(slots)])
+        step(i)
     read()                                       # the warm-up steps' stamps are dropped
-    eng.step([(s, [tok[12][j]]) for j, s in enumerate(slots)])
+    step(12)
     st = read()
     t, tag = st[:, 0].astype(np.int64), st[:, 1]
     kern = (tag >> np.uint64(56)).astype(int)
@@ -307,7 +319,7 @@ def probe_timeline(torch, L, ops, cfg, batch, context):
     tag_of = lambda k, rows: (((k >> 10) & 0xff) << 8) | ((rows >> 9) & 0xff)
     names = {tag_of(h, q_rows): "q/k/v", tag_of(cfg["num_attention_heads"] * cfg["head_dim"], h): "output",
              tag_of(h, 2 * inter): "gate/up", tag_of(inter, h): "down", tag_of(h, cfg["vocab_size"]): "head"}
-    other = {2: "attention", 3: "norm", 4: "qk_prep"}
+    other = {2: "attention", 3: "norm", 4: "qk_prep", 5: "attention"}
     rows = []
     for key in sorted(set(zip(kern.tolist(), aux.tolist()))):
         m = (kern == key[0]) & (aux == key[1])
@@ -328,7 +340,8 @@ def probe_timeline(torch, L, ops, cfg, batch, context):
             name = names.get(key[1], f"product {key[1]:#x}") if key[0] == 1 else other.get(key[0], str(key[0]))
             rows.append((starts[a], name, b - a, (starts[a], starts[b - 1]), span(1), span(2), span(3)))
     rows.sort(key=lambda r: r[0])
-    print(f"batch {batch} context {context}, {cfg['num_hidden_layers']} layers: {len(t)} stamps; microseconds from the first")
+    what = f"prompt of {prompt_tokens} tokens" if prompt_tokens > 0 else f"batch {batch} context {context}"
+    print(f"{what}, {cfg['num_hidden_layers']} layers: {len(t)} stamps; microseconds from the first")
     print(f"{'kernel':10s} {'blocks':>6s} {'start':>15s} {'wait returned':>15s} {'products done':>15s} {'end':>15s}")
     for r in rows:
         print(f"{r[1]:10s} {r[2]:6d} " + " ".join(f"{a:7.1f}-{b:7.1f}" for a, b in r[3:]))
@@ -349,6 +362,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--no-workloads", action="store_true", help="leave out the workloads of the other shapes and the ragged run")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="with --probe timeline: the time line of a prompt step of so many tokens instead of a decode step")
     ap.add_argument("--probe", choices=["decode-attention", "leave-one-out", "timeline"],
                     help="instead of the bench line, print a table: decode attention alone over batch shapes; what "
                          "the decode step loses when each kernel in turn is left out of the recorded graph; or one "
@@ -377,7 +392,7 @@ def main():
         return probe_leave_one_out(torch, L, ops, dict(SHAPES[args.shape][1]), args.batch, args.context)
     if args.probe == "timeline":
         return probe_timeline(torch, L, ops, dict(SHAPES[args.shape][1], num_hidden_layers=args.layers or 6),
-                              args.batch, args.context)
+                              args.batch, args.context, args.tokens)
     shape_name, shape = SHAPES[args.shape]
     if args.layers <= 0:
         args.layers = shape["num_hidden_layers"]

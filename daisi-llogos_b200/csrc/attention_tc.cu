@@ -240,6 +240,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
 
   pdl_launch_dependents();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) LLG_STAMP(5, 0, 0, blockIdx.x + gridDim.x * blockIdx.y);
   if ((smem_u32(smem) & 1023u) != 0) {          // uniform over the block
     if (tid == 0) atomicCAS(&g_error, 0, 3);
     return;
@@ -276,6 +277,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
   const uint32_t tmem = tmem_base_slot;
   volatile int* abortp = &abort_flag;
   pdl_wait();
+  if (tid == 0) LLG_STAMP(5, 1, 0, blockIdx.x + gridDim.x * blockIdx.y);
 
   // Blocks start in the order of blockIdx.x, then blockIdx.y: all heads of the list's first tile, then all
   // heads of its second ...  The caller lists the tiles with the most keys first, so that the long blocks
@@ -597,6 +599,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
   // every role comes here, also after a wait that ran out: copies in flight have been waited for above
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  if (tid == 0) LLG_STAMP(5, 3, 0, blockIdx.x + gridDim.x * blockIdx.y);
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
   }

@@ -480,47 +480,74 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
           }
         }
       } else if (EPI == 0) {
+        // Up to 64 columns of the accumulator are asked for before their arrival is waited for: one trip to tensor
+        // memory per 64 tokens instead of one per 16.
+        constexpr int CH = TN < 64 ? TN : 64;
         OT* out = (OT*)p.out + (long long)split * p.n * p.o;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const int o = o0 + mt * BM + warp * 32 + lane;
           if (o0 + mt * BM >= p.o) break;     // uniform: the second tile lies past the matrix
 #pragma unroll
-          for (int c0 = 0; c0 < TN; c0 += 16) {
+          for (int c0 = 0; c0 < TN; c0 += CH) {
             if (n0 + c0 >= p.n) break;        // uniform over the block: the tile's tail holds no tokens
-            uint32_t r[16];
-            tmem_ld16(lane_base + (uint32_t)(mt * TN + c0), r);
+            uint32_t r[CH / 16][16];
+#pragma unroll
+            for (int q = 0; q < CH / 16; ++q)
+              if (n0 + c0 + 16 * q < p.n) tmem_ld16(lane_base + (uint32_t)(mt * TN + c0 + 16 * q), r[q]);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             if (o < p.o) {
 #pragma unroll
-              for (int c = 0; c < 16; ++c) {
-                const int n = n0 + c0 + c;
-                const float v = p.scale.ss ? __uint_as_float(r[c]) * col_scale[c0 + c] : __uint_as_float(r[c]);
-                if (n < p.n) out[(long long)n * p.o + o] = from_f32<OT>(v);
+              for (int q = 0; q < CH / 16; ++q) {
+                if (n0 + c0 + 16 * q >= p.n) break;
+                // every value is worked out before the first is stored: a store through a generic pointer may, for all
+                // the compiler knows, change the scales in shared memory, and would order every element behind the last
+                float v[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                  v[c] = p.scale.ss ? __uint_as_float(r[q][c]) * col_scale[c0 + 16 * q + c] : __uint_as_float(r[q][c]);
+                OT* dst = out + (long long)(n0 + c0 + 16 * q) * p.o + o;
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                  if (n0 + c0 + 16 * q + c < p.n) dst[(long long)c * p.o] = from_f32<OT>(v[c]);
               }
             }
           }
         }
       } else {
         // accumulator 0 holds gate, accumulator 1 up, of feature o0 + lane row (the first gate_rows lanes)
+        constexpr int CH = TN < 64 ? TN : 64;
         OT* out = (OT*)p.out;
         const int row = warp * 32 + lane;
         const int inter = row < p.gate_rows ? p.gated_features : 0;
         const int f = o0 + row;
 #pragma unroll
-        for (int c0 = 0; c0 < TN; c0 += 16) {
+        for (int c0 = 0; c0 < TN; c0 += CH) {
           if (n0 + c0 >= p.n) break;
-          uint32_t rg[16], ru[16];
-          tmem_ld16(lane_base + (uint32_t)c0, rg);
-          tmem_ld16(lane_base + (uint32_t)(TN + c0), ru);
+          uint32_t rg[CH / 16][16], ru[CH / 16][16];
+#pragma unroll
+          for (int q = 0; q < CH / 16; ++q) {
+            if (n0 + c0 + 16 * q < p.n) {
+              tmem_ld16(lane_base + (uint32_t)(c0 + 16 * q), rg[q]);
+              tmem_ld16(lane_base + (uint32_t)(TN + c0 + 16 * q), ru[q]);
+            }
+          }
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           if (f < inter) {
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int n = n0 + c0 + c;
-              const float rs = p.scale.ss ? col_scale[c0 + c] : 1.0f;
-              const float g = __uint_as_float(rg[c]) * rs, u = __uint_as_float(ru[c]) * rs;
-              if (n < p.n) out[(long long)n * inter + f] = from_f32<OT>(__fdividef(g, 1.0f + __expf(-g)) * u);
+            for (int q = 0; q < CH / 16; ++q) {
+              if (n0 + c0 + 16 * q >= p.n) break;
+              float v[16];                  // all worked out before the first store, as above
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                const float rs = p.scale.ss ? col_scale[c0 + 16 * q + c] : 1.0f;
+                const float g = __uint_as_float(rg[q][c]) * rs, u = __uint_as_float(ru[q][c]) * rs;
+                v[c] = __fdividef(g, 1.0f + __expf(-g)) * u;
+              }
+              OT* dst = out + (long long)(n0 + c0 + 16 * q) * inter + f;
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                if (n0 + c0 + 16 * q + c < p.n) dst[(long long)c * inter] = from_f32<OT>(v[c]);
             }
           }
         }
@@ -746,7 +773,7 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   switch (tile_n) {
     case 16: GATED(16, 5); PLAIN(16, 5);
     case 32: GATED(32, 5); PLAIN(32, 5);
-    case 64: GATED(64, 4); PLAIN(64, 4);
+    case 64: GATED(64, 5); PLAIN(64, 4);
     case 128: GATED(128, 4); WIDE(128, 4); PLAIN(128, 6);
     case 256: GATED(256, 3); WIDE(256, 3); PLAIN(256, 4);
     default: return llg_fail("gemm_tc: tile_n %d is not one of 16, 32, 64, 128, 256", tile_n);
