@@ -227,7 +227,7 @@ class BlockRunner:
         s.max_len_after = ctx.max_len_after
         s.tc_qkv, s.tc_o, s.tc_gate_up, s.tc_down = tc(hidden), tc(q_dim), tc(hidden), tc(inter)
         # the rule of kernels/ops.py gemm_tc_qkv_supported, on sizes
-        s.fused_qkv = int(ops.USE_FUSED_QKV and not ctx.decode and bool(s.tc_qkv) and n > 512 and hd in (64, 128)
+        s.fused_qkv = int(ops.USE_FUSED_QKV and not ctx.decode and bool(s.tc_qkv) and n > ops.FUSED_QKV_ABOVE and hd in (64, 128)
                           and g.get("fusable_rotation", 1) == 1)
         s.splits_qkv, s.splits_o, s.splits_down = splits(qkv_dim, hidden), splits(hidden, q_dim), splits(hidden, inter)
         # a bfloat16 step's norms leave their division to the products that consume them (parts/norm.py)
