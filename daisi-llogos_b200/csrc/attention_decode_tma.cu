@@ -47,6 +47,7 @@ constexpr int TK = 64;                       // keys per tile = one cache page
 constexpr int WORK_WARPS = 4;                // each takes 16 keys of every tile
 constexpr int THREADS = (WORK_WARPS + 1) * 32;
 constexpr int MAX_SEQS = 1024;               // sequences whose tile counts fit the plan in shared memory
+constexpr int STAGED_SEQS = 256;             // sequences whose length and slot are kept in shared memory beside the plan
 constexpr int GH = 8;                        // query heads per key/value head, at most (one MMA n-tile)
 constexpr int MERGE_HEADS = 4;               // heads whose four warp results are added up in shared memory at a time
 constexpr int PART_PAD = 4;                  // a partial result is [head size] sums, the maximum, the sum of weights, and 2 unused: rows stay 16-byte aligned
@@ -175,6 +176,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   unsigned char* Vs = smem + STAGES * TILE_BYTES;      // [STAGES][TILE_BYTES]
   __shared__ uint64_t full[STAGES], empty[STAGES];
   __shared__ int cum[MAX_SEQS + 1];                    // tiles of the sequences before b
+  __shared__ int seq_len[STAGED_SEQS], seq_slot[STAGED_SEQS];      // fetched with the plan: the page look-ups start a trip to L2 earlier
   __shared__ int warp_total[THREADS / 32];
   __shared__ int abort_flag;
   __shared__ float merge[WORK_WARPS][MERGE_HEADS][HD + 2];      // the warps' results of up to four heads of a pair
@@ -204,7 +206,14 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int per = (a.n_seqs + THREADS - 1) / THREADS;
     const int b0 = tid * per, b1 = min(a.n_seqs, b0 + per);
     int mine = 0;
-    for (int b = b0; b < b1; ++b) mine += tile_count(a.len_before[b] + 1, a.window);
+    for (int b = b0; b < b1; ++b) {
+      const int len = a.len_before[b] + 1;
+      if (b < STAGED_SEQS) {
+        seq_len[b] = len;
+        seq_slot[b] = a.slots[b];
+      }
+      mine += tile_count(len, a.window);
+    }
     int incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -242,10 +251,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       bool newest = false;
       if (idx < n_units) {
         const Cursor c = locate(cum, a.n_seqs, a.nkv, u0 + idx);
-        const int len = a.len_before[c.b] + 1;
+        const bool staged = c.b < STAGED_SEQS;
+        const int len = staged ? seq_len[c.b] : a.len_before[c.b] + 1;
         const int tile = first_tile(len, a.window) + c.t;
         newest = tile == (len - 1) / TK;                 // the kernel ahead writes the newest position only
-        const int page = a.page_table[(long long)a.slots[c.b] * a.table_width + tile % a.ring_pages];
+        const int page = a.page_table[(long long)(staged ? seq_slot[c.b] : a.slots[c.b]) * a.table_width + tile % a.ring_pages];
         kvh = c.kvh;
         row = (page * a.nkv + kvh) * TK;
       }
