@@ -77,6 +77,11 @@ CONTEXT = 8192
 PREFILL_TOKENS = 2048
 
 
+def pages_of(tokens):
+    """Tokens that a request of so many tokens holds in the cache: whole pages of 64."""
+    return -(-tokens // 64) * 64
+
+
 def peaks():
     """Measured peaks from MEASURED_PEAKS.json beside this file when it exists, else an earlier measurement of a B200."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -215,7 +220,7 @@ def probe_leave_one_out(torch, L, ops, cfg, batch, context):
         for n, f in real.items():
             setattr(ops, n, f)
         patch()
-        eng = L.engine.Engine(model, max_tokens=batch * context, max_seq_len=context, n_slots=batch)
+        eng = L.engine.Engine(model, max_tokens=batch * pages_of(context), max_seq_len=context, n_slots=batch)
         steps, warmup = 16, 4
         slots = [eng.open() for _ in range(batch)]
         for s in slots:
@@ -270,7 +275,7 @@ def probe_timeline(torch, L, ops, cfg, batch, context, prompt_tokens=0):
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
-    eng = L.engine.Engine(model, max_tokens=batch * context, max_seq_len=context, n_slots=batch)
+    eng = L.engine.Engine(model, max_tokens=batch * pages_of(context), max_seq_len=context, n_slots=batch)
     for g in eng.cache.kv_groups:
         for t in list(g.k.values()) + list(g.v.values()):
             t.normal_(0.0, 1.0)
@@ -409,7 +414,7 @@ def main():
     if weight_gb + big * context * nums["kv_bytes_per_token"] / 1e9 > 165.0:
         # the cache of 64 sequences at this context does not fit beside the weights: no batch-64 point
         big = args.batch
-    engine = L.engine.Engine(model, max_tokens=big * context, max_seq_len=context, n_slots=big)
+    engine = L.engine.Engine(model, max_tokens=big * pages_of(context), max_seq_len=context, n_slots=big)
     for g in engine.cache.kv_groups:             # random keys and values: attention over real numbers
         for t in list(g.k.values()) + list(g.v.values()):
             t.normal_(0.0, 1.0)
