@@ -678,3 +678,152 @@ def test_a_block_with_roles_of_its_own(llogos, tmp_path):
         Pt.unregister_part("block", "toy_side_by_side")
         reg._ARCHITECTURES.pop("ToySideForCausalLM", None)
         reg._ARCHITECTURES.pop("ToySideBadForCausalLM", None)
+
+
+@pytest.mark.gpu
+def test_toy_architecture_with_a_configuration_and_a_norm_of_its_own(llogos, tmp_path):
+    """A whole architecture from outside the library: a typed configuration read from config.json keys of its own
+    (none of the dense decoder's names), a norm of its own kind (mean and variance, weight and bias) in every
+    place a norm stands, and a spec put together from it and the stock attention and feed-forward.  It is
+    registered, written with random weights, loaded by name, stepped in both precisions against formulas
+    written here, and generates through the entry point."""
+    from conftest import read_weights, random_tokens
+    import dataclasses
+    reg = importlib.import_module("daisi-llogos_b200.config.registry")
+    Pt = llogos.parts
+    ConfigError = llogos.config.ConfigError
+
+    @dataclasses.dataclass(frozen=True)
+    class ToyConfig:
+        d_model: int
+        n_layer: int
+        n_head: int
+        d_head: int
+        d_ff: int
+        vocab: int
+        ln_eps: float
+        n_ctx: int
+        rope_base: float
+
+        @staticmethod
+        def read(d):
+            missing = [k for k in ("d_model", "n_layer", "n_head", "d_head", "d_ff", "vocab", "ln_eps", "n_ctx") if k not in d]
+            if missing:
+                raise ConfigError(f"config.json: missing key(s) {', '.join(missing)}")
+            return ToyConfig(int(d["d_model"]), int(d["n_layer"]), int(d["n_head"]), int(d["d_head"]), int(d["d_ff"]),
+                             int(d["vocab"]), float(d["ln_eps"]), int(d["n_ctx"]), float(d.get("rope_base", 10000.0)))
+
+    class MeanVarianceNorm(Pt.Norm):
+        """out = (v - mean(v)) / sqrt(var(v) + eps) * weight + bias with v = residual + branch, in float32."""
+
+        def __init__(self, params, prefix, env):
+            super().__init__(params, prefix, env)
+            self.size, self.eps = int(params["size"]), float(params["eps"])
+
+        def tensors(self):
+            return {"weight": Pt.TensorDecl((self.size,), "norm"), "bias": Pt.TensorDecl((self.size,), "bias")}
+
+        def bind(self, tensors):
+            self.weight, self.bias = tensors["weight"].float(), tensors["bias"].float()
+
+        def forward(self, residual, branch, ctx, rows=None):
+            if branch is not None:
+                residual += branch.data.float().sum(0)
+            v = residual if rows is None else residual[rows.long()]
+            mean = v.mean(-1, keepdim=True)
+            var = ((v - mean) ** 2).mean(-1, keepdim=True)
+            return ((v - mean) / torch.sqrt(var + self.eps) * self.weight + self.bias).to(ctx.dtype)
+
+    def build(cfg):
+        norm = {"size": cfg.d_model, "eps": cfg.ln_eps}
+        layers = []
+        for i in range(cfg.n_layer):
+            p = f"blocks.{i}."
+            layers.append(Pt.LayerSpec("prenorm", {
+                "norm1": Pt.PartSpec("toy_mean_variance", dict(norm), p + "ln_1."),
+                "mixer": Pt.PartSpec("attention", {"hidden_size": cfg.d_model, "num_heads": cfg.n_head, "num_kv_heads": cfg.n_head,
+                                                   "head_dim": cfg.d_head, "qkv_bias": False, "qk_norm": False,
+                                                   "qk_norm_eps": cfg.ln_eps, "window": 0, "position": "rope",
+                                                   "softmax_scale": None}, p + "attn."),
+                "norm2": Pt.PartSpec("toy_mean_variance", dict(norm), p + "ln_2."),
+                "ffn": Pt.PartSpec("swiglu", {"hidden_size": cfg.d_model, "intermediate_size": cfg.d_ff}, p + "ff."),
+            }))
+        spec = Pt.ModelSpec(
+            hidden_size=cfg.d_model, vocab_size=cfg.vocab, max_positions=cfg.n_ctx,
+            embedding=Pt.PartSpec("token_embedding", {"vocab_size": cfg.vocab, "hidden_size": cfg.d_model}, "wte."),
+            encodings={"rope": Pt.PartSpec("rotary", {"head_dim": cfg.d_head, "rotary_dim": cfg.d_head, "theta": cfg.rope_base,
+                                                      "scaling": None, "pairing": "half"})},
+            layers=tuple(layers), schedule=tuple(Pt.ScheduleEntry(i) for i in range(cfg.n_layer)),
+            final_norm=Pt.PartSpec("toy_mean_variance", dict(norm), "ln_f."),
+            head=Pt.PartSpec("linear_head", {"vocab_size": cfg.vocab, "hidden_size": cfg.d_model, "tied_to": "wte.weight"}, "head."))
+        spec.validate()
+        return spec
+
+    Pt.register_part("norm", "toy_mean_variance", MeanVarianceNorm)
+    llogos.config.register_architecture("ToyOwnConfigLM", ToyConfig.read, build)
+    try:
+        cfg = {"architectures": ["ToyOwnConfigLM"], "d_model": 56, "n_layer": 3, "n_head": 2, "d_head": 32, "d_ff": 72,
+               "vocab": 123, "ln_eps": 2e-5, "n_ctx": 192, "rope_base": 5000.0}
+        with pytest.raises(ConfigError, match="d_ff"):
+            llogos.config.architecture_of(cfg).read_config({k: v for k, v in cfg.items() if k != "d_ff"})
+        d = str(tmp_path / "own")
+        llogos.weights.write_random_model(d, cfg, seed=17, std=0.2, norm_std=0.1, bias_std=0.1)
+        w = read_weights(llogos, d)
+        assert "blocks.2.ln_2.bias" in w and "ln_f.weight" in w and "wte.weight" in w and "head.weight" not in w
+        assert float(w["blocks.0.ln_1.bias"].abs().max()) > 0
+
+        def norm_plain(v, prefix):
+            mean = v.mean(-1, keepdim=True)
+            var = ((v - mean) ** 2).mean(-1, keepdim=True)
+            return (v - mean) / torch.sqrt(var + 2e-5) * w[prefix + "weight"].double() + w[prefix + "bias"].double()
+
+        def plain(tokens):
+            t, nh, hd = len(tokens), 2, 32
+            inv = P.rope_inverse_frequencies(hd, 5000.0, None)
+            h = P.embedding(w["wte.weight"], tokens)
+            for i in range(3):
+                p = f"blocks.{i}."
+                a, m = p + "attn.", p + "ff."
+                x = norm_plain(h, p + "ln_1.")
+                q = P.rope_rotate(P.linear(x, w[a + "q_proj.weight"]).view(t, nh, hd), range(t), inv, "half")
+                k = P.rope_rotate(P.linear(x, w[a + "k_proj.weight"]).view(t, nh, hd), range(t), inv, "half")
+                v = P.linear(x, w[a + "v_proj.weight"]).view(t, nh, hd)
+                h = h + P.linear(P.attention(q, k, v, 1.0 / math.sqrt(hd)).reshape(t, nh * hd), w[a + "o_proj.weight"])
+                x = norm_plain(h, p + "ln_2.")
+                h = h + P.swiglu(x, w[m + "gate_proj.weight"], w[m + "up_proj.weight"], w[m + "down_proj.weight"])
+            return P.linear(norm_plain(h, "ln_f."), w["wte.weight"])
+
+        seqs = random_tokens(123, [70, 33], 23)
+        refs = [plain(s) for s in seqs]
+        for dtype, tol in ((torch.float32, 1e-4), (torch.bfloat16, None)):
+            model = llogos.weights.load_model(d, dtype=dtype, device="cuda:0")
+            eng = llogos.engine.Engine(model, max_tokens=64 * 4)
+            assert eng.cache.max_seq_len <= 192
+            slots = [eng.open(), eng.open()]
+            bound = [tol if tol else 4e-2 * float(r.abs().max()) for r in refs]
+            lg = eng.step([(slots[0], seqs[0][:60]), (slots[1], seqs[1][:25])], [list(range(60)), list(range(25))])
+            assert float((lg[:60].cpu().double() - refs[0][:60]).abs().max()) < bound[0]
+            assert float((lg[60:].cpu().double() - refs[1][:25]).abs().max()) < bound[1]
+            for j in range(6):
+                lg = eng.step([(slots[0], [seqs[0][60 + j]]), (slots[1], [seqs[1][25 + j]])])
+                assert float((lg[0].cpu().double() - refs[0][60 + j]).abs().max()) < bound[0]
+                assert float((lg[1].cpu().double() - refs[1][25 + j]).abs().max()) < bound[1]
+            eng.close(slots[0])
+            eng.close(slots[1])
+            eng.cache.audit()
+            del eng, model
+        # through the entry point: greedy tokens follow the plain model's largest logits (where the margin is clear)
+        api = importlib.import_module("llogos_b200")
+        lm = api.LlogosModel.load(d, dtype="float32", max_context=128)
+        out = lm.generate([seqs[1][:25]], api.GenerationParams(max_tokens=5, temperature=0.0, repetition_penalty=1.0,
+                                                                  stop_tokens=()))
+        got = list(out.tokens[0])
+        assert len(got) == 5
+        full = plain(seqs[1][:25] + got)
+        for j, tok in enumerate(got):
+            row = full[24 + j]
+            top2 = torch.topk(row, 2).values
+            assert int(row.argmax()) == tok or float(top2[0] - top2[1]) < 1e-4
+    finally:
+        Pt.unregister_part("norm", "toy_mean_variance")
+        reg._ARCHITECTURES.pop("ToyOwnConfigLM", None)
