@@ -131,3 +131,24 @@ def test_register_architecture(llogos):
     finally:
         importlib = __import__("importlib")
         importlib.import_module("daisi-llogos_b200.config.registry")._ARCHITECTURES.pop("ToyForCausalLM")
+
+
+def test_plugin_modules_register_architectures_for_the_command_line(tmp_path):
+    """A module named in LLOGOS_PLUGINS is imported with the library, so what it registers is known wherever a
+    model is chosen by its config.json; a name that cannot be imported is an error that says so."""
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    (tmp_path / "toy_plugin.py").write_text(
+        "import importlib\n"
+        "C = importlib.import_module('daisi-llogos_b200.config')\n"
+        "R = importlib.import_module('daisi-llogos_b200.config.registry')\n"
+        "C.register_architecture('PluginToyLM', R._dense_reader(qk_norm=False, force_bias=False), C.dense_decoder_spec)\n")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(tmp_path), ROOT]), LLOGOS_PLUGINS="toy_plugin")
+    code = "import llogos_b200 as L; print('PluginToyLM' in L.config.known_architectures())"
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert p.returncode == 0 and p.stdout.strip() == "True", p.stderr
+    env["LLOGOS_PLUGINS"] = "toy_plugin, no_such_module_here"
+    p = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, cwd=str(tmp_path))
+    assert p.returncode != 0 and "LLOGOS_PLUGINS" in p.stderr and "no_such_module_here" in p.stderr

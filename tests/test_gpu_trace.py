@@ -17,12 +17,12 @@ TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
 
 
 class Replay:
-    def __init__(self, model_dir, dtype, out_dir, max_tokens, extra=()):
+    def __init__(self, model_dir, dtype, out_dir, max_tokens, extra=(), env=None):
         self.out = out_dir
         self.p = subprocess.Popen(
             [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
              "--out", out_dir, "--max-tokens", str(max_tokens), *extra],
-            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
         self.n = 0
 
     def step(self, entries, end=()):
@@ -137,3 +137,37 @@ def test_replay_rejects_nonsense(model_dirs, tmp_path):
                         "--dtype", "float32", "--out", str(tmp_path), "--max-tokens", "64"],
                        input="", capture_output=True, text=True)
     assert p.returncode != 0 and "config.json" in p.stderr
+
+
+def test_replay_of_an_architecture_that_a_plugin_module_registers(llogos, tmp_path):
+    """The replay program knows an architecture that a module named in LLOGOS_PLUGINS registers: a model folder whose
+    config.json names it is written here (in a child process that has the plugin too), replayed whole and then
+    with its last tokens one by one, and compared with the plain implementation of the dense decoder that the
+    plugin's architecture is built from."""
+    (tmp_path / "toy_plugin.py").write_text(
+        "import importlib\n"
+        "C = importlib.import_module('daisi-llogos_b200.config')\n"
+        "R = importlib.import_module('daisi-llogos_b200.config.registry')\n"
+        "C.register_architecture('PluginToyLM', R._dense_reader(qk_norm=True, force_bias=False), C.dense_decoder_spec)\n")
+    env = dict(os.environ, PYTHONPATH=os.pathsep.join([str(tmp_path), ROOT, os.environ.get("PYTHONPATH", "")]),
+               LLOGOS_PLUGINS="toy_plugin")
+    cfg = dict(TINY["qwen3"], architectures=["PluginToyLM"])
+    d = str(tmp_path / "model")
+    code = ("import json, sys, llogos_b200 as L; "
+            "L.weights.write_random_model(sys.argv[1], json.loads(sys.argv[2]), seed=5, std=0.2, norm_std=0.1)")
+    subprocess.run([sys.executable, "-c", code, d, json.dumps(cfg)], check=True, env=env, cwd=str(tmp_path))
+    # this process does not know the name: the plain implementation reads the folder as the dense decoder it is
+    plain_cfg = dict(cfg, architectures=TINY["qwen3"]["architectures"])
+    w = read_weights(llogos, d)
+    vocab = cfg["vocab_size"]
+    s = random_tokens(vocab, [90], 29)[0]
+    ref = reference(d, w, plain_cfg, s)
+    for dtype in ("float32", "bfloat16"):
+        r = Replay(d, dtype, str(tmp_path / f"out_{dtype}"), max_tokens=64 * 4, env=env)
+        got = r.step([("a", s, list(range(len(s))))], end=["a"]).reshape(len(s), vocab)
+        check(ref, got, range(len(s)), dtype, ("plugin whole",))
+        assert r.step([("b", s[:80], [])]) is None
+        for p in range(80, len(s)):
+            got = r.step([("b", [s[p]], [0])], end=["b"] if p == len(s) - 1 else [])
+            check(ref, got, [p], dtype, ("plugin decode", p))
+        r.finish()
