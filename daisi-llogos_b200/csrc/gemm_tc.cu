@@ -11,9 +11,10 @@
 // accumulator (128 lanes x N columns of float32) lives in tensor memory; four warps read it back
 // with tcgen05.ld and store out[n][o] so that one warp instruction writes 32 consecutive features.
 //
-// Roles in a block of 128 threads: thread 0 issues TMA loads into a ring of stages, thread 32
-// issues the MMAs and commits each stage back to the producer, all four warps run the epilogue.
-// Split-K (blockIdx.z) writes float32 partials that the consumer kernels sum.
+// Roles in a block of 192 threads: a lane of warp 4 issues TMA loads into a ring of stages that runs on across the
+// block's tiles, a lane of warp 5 issues the MMAs and commits each stage back to the producer, warps 0-3 run the
+// epilogue.  Where the accumulator takes at most half of tensor memory there are two, so the next tile's products
+// run while the last tile is read out.  Split-K (blockIdx.z) writes float32 partials that the consumer kernels sum.
 //
 // Every wait on an mbarrier is bounded (two seconds of %globaltimer): on expiry the block records
 // an error code, stops issuing work, waits (bounded) for its own TMA copies in flight, frees its
@@ -39,6 +40,9 @@ constexpr int BM = 128;          // output features per tile (MMA M)
 constexpr int BK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr int EPI_WARPS = 4;     // warps 0-3 read the accumulator out, each its quarter of the lanes
+constexpr int PRODUCER_WARP = 4, MMA_WARP = 5;
+constexpr int GEMM_THREADS = 6 * 32;
 
 __device__ int g_error = 0;      // 0 ok; 1 producer wait, 2 consumer wait, 3 epilogue wait, 4 drain wait
 
@@ -57,6 +61,12 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// the epilogue warps' own barrier (the two other warps do not take part)
+__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); }
 
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -150,21 +160,25 @@ __device__ __forceinline__ float vec_elem(const void* p, int dtype, int i) {
 // are never rounded before that, and the float32 q/k/v array of the two-kernel way is neither written nor read.
 // Order as in the reference: norm, bias, rotation (Inference/ForwardPass.cs:372-385).
 template <int TN, int STAGES, typename OT, int MT, int EPI, int SWAP>
-__global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, GemmParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   constexpr int A_TILE = BM * BK * 2;
   constexpr int A_BYTES = MT * A_TILE;
   constexpr int B_BYTES = TN * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr int TMEM_COLS = MT * TN <= 32 ? 32 : MT * TN <= 64 ? 64 : MT * TN <= 128 ? 128 : MT * TN <= 256 ? 256 : 512;
+  // Two accumulators where tensor memory has room for them: the products of a block's next tile run while its last
+  // one is read out.  An accumulator starts at a multiple of its width rounded up to a power of two.
+  constexpr int ACC_COLS = MT * TN <= 32 ? 32 : MT * TN <= 64 ? 64 : MT * TN <= 128 ? 128 : MT * TN <= 256 ? 256 : 512;
+  constexpr int NACC = ACC_COLS <= 256 ? 2 : 1;
+  constexpr int TMEM_COLS = NACC * ACC_COLS;
   static_assert(MT * TN <= 512, "the accumulators do not fit tensor memory");
   static_assert(TN % 16 == 0, "the second operand's tile is a multiple of 16 rows");
   static_assert(EPI != 1 || (SWAP ? TN % 32 == 0 : MT == 2), "the gated epilogue needs a gate tile and an up tile");
   static_assert(EPI < 2 || (SWAP == 1 && TN % 128 == 0), "the q/k/v epilogue works on token rows and whole heads");
   // 1024-byte alignment of the operand tiles is what the swizzle pattern of TMA and of the MMA assume
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], done_bar;
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[NACC], acc_empty[NACC];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ float col_scale[SWAP ? 1 : TN];      // tokens along the columns: their scales, worked out during the products
@@ -176,7 +190,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int st_aux = (((p.k >> 10) & 0xff) << 8) | (((SWAP ? p.n : p.o) >> 9) & 0xff), st_blk = blockIdx.x + gridDim.x * blockIdx.z;
 #endif
   if (tid == 0) LLG_STAMP(1, 0, st_aux, st_blk);
-  if (tid == 0) {
+  if (tid == PRODUCER_WARP * 32) {
     // the first copies need the two descriptors: fetch them while the barriers and the tensor memory are set up
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
@@ -186,6 +200,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   constexpr bool GATED_ROWS = EPI == 1 && SWAP == 0;       // gate and up tiles fetched separately, gate_rows each
   const int total_tiles = (GATED_ROWS ? (p.gated_features + p.gate_rows - 1) / p.gate_rows
                                       : (p.o + BM * MT - 1) / (BM * MT)) * n_tiles_n;
+  const int m_tiles = total_tiles / n_tiles_n;
   const uint32_t stage_tx = GATED_ROWS ? (uint32_t)(2 * p.gate_rows * BK * 2 + B_BYTES) : (uint32_t)STAGE_BYTES;
   // row of w that the weight tile `mt` of the block at first-operand offset o0 starts at
   auto w_row = [&](int o0, int mt) { return GATED_ROWS ? mt * p.up_offset + o0 : o0 + mt * BM; };
@@ -203,6 +218,10 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) tma_load_2d(dst + mt * A_TILE, &map_w, kb * BK, w_row(o0, mt), bar);
   };
+  // A block works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...: token tiles of one weight tile are neighbours
+  // in that order, so blocks running side by side share the weight tile in L2.
+  auto first_offset = [&](int tile) { return (SWAP ? tile % m_tiles : tile / n_tiles_n) * (GATED_ROWS ? p.gate_rows : BM * MT); };
+  auto second_offset = [&](int tile) { return (SWAP ? tile / m_tiles : tile % n_tiles_n) * TN; };
   const int nkb_total = (p.k + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, nkb_total - kb0);   // >= 1 by construction of the grid
@@ -212,11 +231,14 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&done_bar, 1);
+    for (int b = 0; b < NACC; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], EPI_WARPS);
+    }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                  "r"((uint32_t)TMEM_COLS)
                  : "memory");
@@ -228,349 +250,344 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const uint32_t tmem_d = tmem_base_slot;
   volatile int* abortp = &abort_flag;
 
-  // A block works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...: token tiles of one weight
-  // tile are neighbours in that order, so blocks running side by side share the weight tile in L2.
-  // The ring of stages runs on across tiles (`it` counts k-blocks since the start); the first ring
-  // of the next tile is requested before the epilogue of the current one, so it lands meanwhile.
-  int it_issue = 0;             // producer: k-blocks requested so far
-  int it_mma = 0;               // consumer: k-blocks multiplied so far
-  bool first = true;
-  int preloaded = 0;            // k-blocks of the coming tile that are already requested
-  for (int tile = blockIdx.x, round = 0; tile < total_tiles; tile += gridDim.x, ++round) {
-    // the operand that is shared by neighbouring blocks is the weight tile in both orientations
-    const int m_tiles = total_tiles / n_tiles_n;
-    const int o0 = (SWAP ? tile % m_tiles : tile / n_tiles_n) * (GATED_ROWS ? p.gate_rows : BM * MT);
-    const int n0 = (SWAP ? tile / m_tiles : tile % n_tiles_n) * TN;
-
-    if (tid == 0) {
-      // ---- producer: TMA loads into the ring ------------------------------------------------
-      if (first) {
-        // The weights do not depend on the previous kernel: the first ring of weight tiles is requested
-        // before this kernel waits for its predecessor, the activation tiles right after.  The weights are
-        // the first operand of a decode step's product and the second of a prompt step's.
-        const int pre = min(nkb, STAGES);
-        for (int i = 0; i < pre; ++i) {
-          mbar_expect_tx(&full_bar[i], stage_tx);
-          if (SWAP) load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
-          else load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
+  if (warp == PRODUCER_WARP) {
+    // ---- producer: one lane requests every tile of every stage; the ring of stages runs on across the block's tiles,
+    // so the next tile's operands arrive while this tile's accumulator is read out ----------------------------------
+    if (lane == 0) {
+      int it = 0;                 // k-blocks requested so far
+      bool first = true;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abortp; tile += gridDim.x) {
+        const int o0 = first_offset(tile), n0 = second_offset(tile);
+        int done = 0;
+        if (first) {
+          // The weights do not depend on the previous kernel: the first ring of weight tiles is requested
+          // before this kernel waits for its predecessor, the activation tiles right after.  The weights are
+          // the first operand of a decode step's product and the second of a prompt step's.
+          const int pre = min(nkb, STAGES);
+          for (int i = 0; i < pre; ++i) {
+            mbar_expect_tx(&full_bar[i], stage_tx);
+            if (SWAP) load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
+            else load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
+          }
+          pdl_wait();
+          LLG_STAMP(1, 1, st_aux, st_blk);
+          for (int i = 0; i < pre; ++i) {
+            if (SWAP) load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
+            else load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
+          }
+          it = done = pre;
+          first = false;
         }
-        pdl_wait();
-        LLG_STAMP(1, 1, st_aux, st_blk);
-        for (int i = 0; i < pre; ++i) {
-          if (SWAP) load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
-          else load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
+        for (int i = done; i < nkb && !*abortp; ++i, ++it) {
+          const int s = it % STAGES;
+          const uint32_t parity = ((it / STAGES) & 1) ^ 1;     // a fresh barrier passes a wait on parity 1
+          if (!mbar_wait(&empty_bar[s], parity, abortp)) {
+            if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], stage_tx);
+          unsigned char* a = smem + s * STAGE_BYTES;
+          load_first(a, kb0 + i, o0, &full_bar[s]);
+          load_second(a + A_BYTES, kb0 + i, n0, &full_bar[s]);
         }
-        it_issue = pre;
-        preloaded = pre;
       }
-      for (int i = preloaded; i < nkb && !*abortp; ++i, ++it_issue) {
-        const int s = it_issue % STAGES;
-        const uint32_t parity = ((it_issue / STAGES) & 1) ^ 1;     // a fresh barrier passes a wait on parity 1
-        if (!mbar_wait(&empty_bar[s], parity, abortp)) {
-          if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
-          break;
+      if (*abortp) {
+        // copies already requested still write into this block's shared memory: wait for them, bounded
+        for (int i = max(0, it - STAGES); i < it; ++i) {
+          const unsigned long long t0 = now_ns();
+          while (!mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1)) {
+            if (now_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(&g_error, 1, 4); break; }
+          }
         }
-        mbar_expect_tx(&full_bar[s], stage_tx);
-        unsigned char* a = smem + s * STAGE_BYTES;
-        load_first(a, kb0 + i, o0, &full_bar[s]);
-        load_second(a + A_BYTES, kb0 + i, n0, &full_bar[s]);
       }
-    } else if (first) {
-      pdl_wait();               // every other thread: before anything of the previous kernel is read or overwritten
     }
-    first = false;
-    if (!SWAP && p.scale.ss && tid >= 64) {
-      // two warps have nothing to do until the epilogue: they work out the scales of this tile's tokens meanwhile
-      // (the block-wide barrier before the epilogue makes them visible)
-      for (int c = tid - 64; c < TN; c += 64) col_scale[c] = n0 + c < p.n ? row_scale_of(p.scale, n0 + c) : 0.f;
-    }
-    if (tid == 32) {
-      // ---- consumer: one thread issues every MMA ----------------------------------------------
+  } else if (warp == MMA_WARP) {
+    // ---- products: one lane issues every MMA.  With two accumulators in tensor memory the products of the next tile
+    // run while the four other warps read the last one out. ------------------------------------------------------
+    if (lane == 0) {
       constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-      for (int i = 0; i < nkb; ++i, ++it_mma) {
-        const int s = it_mma % STAGES;
-        if (!mbar_wait(&full_bar[s], (it_mma / STAGES) & 1, abortp)) {
-          if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+      int it = 0, round = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !*abortp; tile += gridDim.x, ++round) {
+        const int b = round % NACC;
+        if (round >= NACC && !mbar_wait(&acc_empty[b], ((round / NACC) - 1) & 1, abortp)) {
+          if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t db = umma_desc(a_addr + A_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < BK / UMMA_K; ++kk) {
-          // 16 k = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-            umma_bf16(tmem_d + mt * TN, umma_desc(a_addr + mt * A_TILE) + 2 * kk, db + 2 * kk, IDESC, (i | kk) != 0);
-        }
-        umma_commit(&empty_bar[s]);       // arrives when the MMAs above have read the stage
-      }
-      umma_commit(&done_bar);             // arrives when every MMA issued so far has finished
-    }
-
-    // ---- epilogue: tensor memory -> registers -> out --------------------------------------------
-    __syncwarp();
-    bool have = mbar_wait(&done_bar, round & 1, abortp);
-    if (!have && !*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
-    __syncthreads();
-    if (tid == 0 && round == 0) LLG_STAMP(1, 2, st_aux, st_blk);
-    if (*abortp != 0) break;
-    // every stage is free now: request the first ring of the next tile so that it arrives during the epilogue
-    preloaded = 0;
-    if (tid == 0 && tile + (int)gridDim.x < total_tiles) {
-      const int nt = tile + gridDim.x;
-      const int no0 = (SWAP ? nt % m_tiles : nt / n_tiles_n) * (GATED_ROWS ? p.gate_rows : BM * MT);
-      const int nn0 = (SWAP ? nt / m_tiles : nt % n_tiles_n) * TN;
-      const int pre = min(nkb, STAGES);
-      for (int i = 0; i < pre; ++i, ++it_issue) {
-        const int s = it_issue % STAGES;
-        mbar_expect_tx(&full_bar[s], stage_tx);
-        unsigned char* a = smem + s * STAGE_BYTES;
-        load_first(a, kb0 + i, no0, &full_bar[s]);
-        load_second(a + A_BYTES, kb0 + i, nn0, &full_bar[s]);
-      }
-      preloaded = pre;
-    }
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    {
-      const uint32_t lane_base = tmem_d + ((uint32_t)(warp * 32) << 16);
-      if (SWAP && EPI >= 2) {
-        // lanes are tokens, columns are the features of whole heads: norm, bias, rotation, and the writes of q, k, v
-        constexpr int HD = EPI == 2 ? 128 : 64, HALF = HD / 2;
-        const QkPrepArgs& a = p.prep;
-        const int heads = a.nh + 2 * a.nkv;
-        typedef __nv_bfloat16 bf;
-#pragma unroll 1
-        for (int mt = 0; mt < MT; ++mt) {
-          if (o0 + mt * BM >= p.o) break;
-          const int tok = o0 + mt * BM + warp * 32 + lane;
-          const bool live = tok < p.o;
-          const int pos = live ? a.positions[tok] : 0;
-          const int slot = (live && a.k_pages) ? a.slots[a.seq_of_token[tok]] : 0;
-          const float rs = live ? row_scale_of(a.row_scale, tok) : 1.0f;
-#pragma unroll 1
-          for (int hb = 0; hb < TN / HD; ++hb) {
-            const int head = n0 / HD + hb;
-            if (head >= heads) break;                   // uniform: the tile's tail lies past the last head
-            float h[HD];
-#pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 16) {
-              uint32_t r[16];
-              tmem_ld16(lane_base + (uint32_t)(mt * TN + hb * HD + c0), r);
-              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-              for (int c = 0; c < 16; ++c) h[c0 + c] = __uint_as_float(r[c]) * rs;
-            }
-            const int kind = head < a.nh ? 0 : (head < a.nh + a.nkv ? 1 : 2);      // query, key, value
-            const void* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
-            if (nw) {
-              float ss = 0.f;
-#pragma unroll
-              for (int d = 0; d < HD; ++d) ss += h[d] * h[d];
-              const float inv = 1.0f / sqrtf(ss / (float)HD + a.norm_eps);
-#pragma unroll
-              for (int d = 0; d < HD; ++d) h[d] = h[d] * inv * vec_elem(nw, a.norm_w_dtype, d);
-            }
-            if (a.bias) {
-#pragma unroll
-              for (int d = 0; d < HD; ++d) h[d] += vec_elem(a.bias, a.bias_dtype, head * HD + d);
-            }
-            if (kind != 2 && a.cos_table) {
-              const int pp = pos < a.table_positions ? pos : a.table_positions - 1;     // bounded; the host checks capacity
-              const float4* cs = reinterpret_cast<const float4*>(a.cos_table + (long long)pp * HALF);
-              const float4* sn = reinterpret_cast<const float4*>(a.sin_table + (long long)pp * HALF);
-#pragma unroll
-              for (int i4 = 0; i4 < HALF / 4; ++i4) {
-                const float4 c = cs[i4], sgn = sn[i4];
-                const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sgn.x, sgn.y, sgn.z, sgn.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int i = 4 * i4 + e;
-                  const float u = h[i], v = h[i + HALF];
-                  h[i] = u * cc[e] - v * sv[e];
-                  h[i + HALF] = u * sv[e] + v * cc[e];
-                }
-              }
-            }
-            if (live) {
-              auto store_head = [&](bf* dst) {
-#pragma unroll
-                for (int q8 = 0; q8 < HD / 8; ++q8) {
-                  __nv_bfloat162 h0 = __floats2bfloat162_rn(h[8 * q8], h[8 * q8 + 1]), h1 = __floats2bfloat162_rn(h[8 * q8 + 2], h[8 * q8 + 3]);
-                  __nv_bfloat162 h2 = __floats2bfloat162_rn(h[8 * q8 + 4], h[8 * q8 + 5]), h3 = __floats2bfloat162_rn(h[8 * q8 + 6], h[8 * q8 + 7]);
-                  uint4 u;
-                  u.x = *reinterpret_cast<uint32_t*>(&h0);
-                  u.y = *reinterpret_cast<uint32_t*>(&h1);
-                  u.z = *reinterpret_cast<uint32_t*>(&h2);
-                  u.w = *reinterpret_cast<uint32_t*>(&h3);
-                  *reinterpret_cast<uint4*>(dst + 8 * q8) = u;
-                }
-              };
-              if (kind == 0) {
-                store_head((bf*)a.q_out + ((long long)tok * a.nh + head) * HD);
-              } else {
-                const int kvh = kind == 1 ? head - a.nh : head - a.nh - a.nkv;
-                bf* packed = (bf*)(kind == 1 ? a.k_new : a.v_new);
-                if (packed) store_head(packed + ((long long)tok * a.nkv + kvh) * HD);
-                bf* pages = (bf*)(kind == 1 ? a.k_pages : a.v_pages);
-                if (pages) store_head(pages + kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv) * HD);
-              }
-            }
+        const uint32_t acc = tmem_d + (uint32_t)(b * ACC_COLS);
+        bool fine = true;
+        for (int i = 0; i < nkb; ++i, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, abortp)) {
+            if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 2); }
+            fine = false;
+            break;
           }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t db = umma_desc(a_addr + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // 16 k = 32 bytes further along the swizzled row: +2 in the descriptor's 16-byte units
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+              umma_bf16(acc + mt * TN, umma_desc(a_addr + mt * A_TILE) + 2 * kk, db + 2 * kk, IDESC, (i | kk) != 0);
+          }
+          umma_commit(&empty_bar[s]);       // arrives when the MMAs above have read the stage
         }
-      } else if (SWAP) {
-        // lanes are tokens (p.o of them), columns are features (p.n, or gate|up blocks of 128 + 128)
-        constexpr int VEC = 16 / (int)sizeof(OT);      // outputs per 16-byte store
-        const int width = EPI == 1 ? p.gated_features : p.n;
-        const bool vec_ok = width % VEC == 0;
-        OT* out = (OT*)p.out + (long long)split * p.n * p.o;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          if (o0 + mt * BM >= p.o) break;
-          const int tok = o0 + mt * BM + warp * 32 + lane;
-          const float rs = tok < p.o ? row_scale_of(p.scale, tok) : 1.0f;
-          OT* row = out + (long long)tok * width;
-          constexpr int COLS = EPI == 1 ? TN / 2 : TN;
-#pragma unroll
-          for (int c0 = 0; c0 < COLS; c0 += 16) {
-            const int f0 = EPI == 1 ? n0 / 2 + c0 : n0 + c0;      // first feature of this run (a gated tile: TN / 2 features)
-            if (f0 >= width) break;
-            float v[16];
-            uint32_t r[16];
-            tmem_ld16(lane_base + (uint32_t)(mt * TN + c0), r);
-            if (EPI == 1) {
-              uint32_t ru[16];
-              tmem_ld16(lane_base + (uint32_t)(mt * TN + TN / 2 + c0), ru);
-              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-              for (int c = 0; c < 16; ++c) {
-                const float g = __uint_as_float(r[c]) * rs;
-                v[c] = __fdividef(g, 1.0f + __expf(-g)) * (__uint_as_float(ru[c]) * rs);
+        if (!fine) break;
+        umma_commit(&acc_full[b]);          // arrives when every MMA issued so far has finished
+      }
+    }
+  } else {
+    // ---- epilogue: warps 0-3, each its quarter of the lanes: tensor memory -> registers -> out ----------------------
+    pdl_wait();                 // before anything of the previous kernel is read or overwritten
+    int round = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
+      const int o0 = first_offset(tile), n0 = second_offset(tile);
+      const int b = round % NACC;
+      if (!SWAP && p.scale.ss) {
+        // tokens along the columns: their scales, worked out while the products run
+        if (round > 0) epi_sync();          // the last tile's readers are done with them
+        for (int c = tid; c < TN; c += EPI_WARPS * 32) col_scale[c] = n0 + c < p.n ? row_scale_of(p.scale, n0 + c) : 0.f;
+        epi_sync();
+      }
+      const bool have = mbar_wait(&acc_full[b], (round / NACC) & 1, abortp);
+      if (!have && !*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
+      if (!have || *abortp) break;
+      if (tid == 0 && round == 0) LLG_STAMP(1, 2, st_aux, st_blk);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      {
+        const uint32_t lane_base = tmem_d + (uint32_t)(b * ACC_COLS) + ((uint32_t)(warp * 32) << 16);
+        if (SWAP && EPI >= 2) {
+          // lanes are tokens, columns are the features of whole heads: norm, bias, rotation, and the writes of q, k, v
+          constexpr int HD = EPI == 2 ? 128 : 64, HALF = HD / 2;
+          const QkPrepArgs& a = p.prep;
+          const int heads = a.nh + 2 * a.nkv;
+          typedef __nv_bfloat16 bf;
+  #pragma unroll 1
+          for (int mt = 0; mt < MT; ++mt) {
+            if (o0 + mt * BM >= p.o) break;
+            const int tok = o0 + mt * BM + warp * 32 + lane;
+            const bool live = tok < p.o;
+            const int pos = live ? a.positions[tok] : 0;
+            const int slot = (live && a.k_pages) ? a.slots[a.seq_of_token[tok]] : 0;
+            const float rs = live ? row_scale_of(a.row_scale, tok) : 1.0f;
+  #pragma unroll 1
+            for (int hb = 0; hb < TN / HD; ++hb) {
+              const int head = n0 / HD + hb;
+              if (head >= heads) break;                   // uniform: the tile's tail lies past the last head
+              float h[HD];
+  #pragma unroll
+              for (int c0 = 0; c0 < HD; c0 += 16) {
+                uint32_t r[16];
+                tmem_ld16(lane_base + (uint32_t)(mt * TN + hb * HD + c0), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  #pragma unroll
+                for (int c = 0; c < 16; ++c) h[c0 + c] = __uint_as_float(r[c]) * rs;
               }
-            } else {
-              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-              for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]) * rs;
-            }
-            if (tok < p.o) {
-              if (vec_ok && f0 + 16 <= width) {
-                if (sizeof(OT) == 4) {
-#pragma unroll
-                  for (int q = 0; q < 4; ++q)
-                    *reinterpret_cast<float4*>((float*)row + f0 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                } else {
-#pragma unroll
-                  for (int q = 0; q < 2; ++q) {
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]), h1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
-                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]), h3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+              const int kind = head < a.nh ? 0 : (head < a.nh + a.nkv ? 1 : 2);      // query, key, value
+              const void* nw = kind == 0 ? a.q_norm_w : (kind == 1 ? a.k_norm_w : nullptr);
+              if (nw) {
+                float ss = 0.f;
+  #pragma unroll
+                for (int d = 0; d < HD; ++d) ss += h[d] * h[d];
+                const float inv = 1.0f / sqrtf(ss / (float)HD + a.norm_eps);
+  #pragma unroll
+                for (int d = 0; d < HD; ++d) h[d] = h[d] * inv * vec_elem(nw, a.norm_w_dtype, d);
+              }
+              if (a.bias) {
+  #pragma unroll
+                for (int d = 0; d < HD; ++d) h[d] += vec_elem(a.bias, a.bias_dtype, head * HD + d);
+              }
+              if (kind != 2 && a.cos_table) {
+                const int pp = pos < a.table_positions ? pos : a.table_positions - 1;     // bounded; the host checks capacity
+                const float4* cs = reinterpret_cast<const float4*>(a.cos_table + (long long)pp * HALF);
+                const float4* sn = reinterpret_cast<const float4*>(a.sin_table + (long long)pp * HALF);
+  #pragma unroll
+                for (int i4 = 0; i4 < HALF / 4; ++i4) {
+                  const float4 c = cs[i4], sgn = sn[i4];
+                  const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sgn.x, sgn.y, sgn.z, sgn.w};
+  #pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int i = 4 * i4 + e;
+                    const float u = h[i], v = h[i + HALF];
+                    h[i] = u * cc[e] - v * sv[e];
+                    h[i + HALF] = u * sv[e] + v * cc[e];
+                  }
+                }
+              }
+              if (live) {
+                auto store_head = [&](bf* dst) {
+  #pragma unroll
+                  for (int q8 = 0; q8 < HD / 8; ++q8) {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(h[8 * q8], h[8 * q8 + 1]), h1 = __floats2bfloat162_rn(h[8 * q8 + 2], h[8 * q8 + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(h[8 * q8 + 4], h[8 * q8 + 5]), h3 = __floats2bfloat162_rn(h[8 * q8 + 6], h[8 * q8 + 7]);
                     uint4 u;
                     u.x = *reinterpret_cast<uint32_t*>(&h0);
                     u.y = *reinterpret_cast<uint32_t*>(&h1);
                     u.z = *reinterpret_cast<uint32_t*>(&h2);
                     u.w = *reinterpret_cast<uint32_t*>(&h3);
-                    *reinterpret_cast<uint4*>((__nv_bfloat16*)row + f0 + 8 * q) = u;
+                    *reinterpret_cast<uint4*>(dst + 8 * q8) = u;
                   }
+                };
+                if (kind == 0) {
+                  store_head((bf*)a.q_out + ((long long)tok * a.nh + head) * HD);
+                } else {
+                  const int kvh = kind == 1 ? head - a.nh : head - a.nh - a.nkv;
+                  bf* packed = (bf*)(kind == 1 ? a.k_new : a.v_new);
+                  if (packed) store_head(packed + ((long long)tok * a.nkv + kvh) * HD);
+                  bf* pages = (bf*)(kind == 1 ? a.k_pages : a.v_pages);
+                  if (pages) store_head(pages + kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, kvh, a.nkv) * HD);
+                }
+              }
+            }
+          }
+        } else if (SWAP) {
+          // lanes are tokens (p.o of them), columns are features (p.n, or gate|up blocks of 128 + 128)
+          constexpr int VEC = 16 / (int)sizeof(OT);      // outputs per 16-byte store
+          const int width = EPI == 1 ? p.gated_features : p.n;
+          const bool vec_ok = width % VEC == 0;
+          OT* out = (OT*)p.out + (long long)split * p.n * p.o;
+  #pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            if (o0 + mt * BM >= p.o) break;
+            const int tok = o0 + mt * BM + warp * 32 + lane;
+            const float rs = tok < p.o ? row_scale_of(p.scale, tok) : 1.0f;
+            OT* row = out + (long long)tok * width;
+            constexpr int COLS = EPI == 1 ? TN / 2 : TN;
+  #pragma unroll
+            for (int c0 = 0; c0 < COLS; c0 += 16) {
+              const int f0 = EPI == 1 ? n0 / 2 + c0 : n0 + c0;      // first feature of this run (a gated tile: TN / 2 features)
+              if (f0 >= width) break;
+              float v[16];
+              uint32_t r[16];
+              tmem_ld16(lane_base + (uint32_t)(mt * TN + c0), r);
+              if (EPI == 1) {
+                uint32_t ru[16];
+                tmem_ld16(lane_base + (uint32_t)(mt * TN + TN / 2 + c0), ru);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  #pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                  const float g = __uint_as_float(r[c]) * rs;
+                  v[c] = __fdividef(g, 1.0f + __expf(-g)) * (__uint_as_float(ru[c]) * rs);
                 }
               } else {
-#pragma unroll
-                for (int c = 0; c < 16; ++c)
-                  if (f0 + c < width) row[f0 + c] = from_f32<OT>(v[c]);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  #pragma unroll
+                for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]) * rs;
+              }
+              if (tok < p.o) {
+                if (vec_ok && f0 + 16 <= width) {
+                  if (sizeof(OT) == 4) {
+  #pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                      *reinterpret_cast<float4*>((float*)row + f0 + 4 * q) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                  } else {
+  #pragma unroll
+                    for (int q = 0; q < 2; ++q) {
+                      __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * q], v[8 * q + 1]), h1 = __floats2bfloat162_rn(v[8 * q + 2], v[8 * q + 3]);
+                      __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * q + 4], v[8 * q + 5]), h3 = __floats2bfloat162_rn(v[8 * q + 6], v[8 * q + 7]);
+                      uint4 u;
+                      u.x = *reinterpret_cast<uint32_t*>(&h0);
+                      u.y = *reinterpret_cast<uint32_t*>(&h1);
+                      u.z = *reinterpret_cast<uint32_t*>(&h2);
+                      u.w = *reinterpret_cast<uint32_t*>(&h3);
+                      *reinterpret_cast<uint4*>((__nv_bfloat16*)row + f0 + 8 * q) = u;
+                    }
+                  }
+                } else {
+  #pragma unroll
+                  for (int c = 0; c < 16; ++c)
+                    if (f0 + c < width) row[f0 + c] = from_f32<OT>(v[c]);
+                }
               }
             }
           }
-        }
-      } else if (EPI == 0) {
-        // Up to 64 columns of the accumulator are asked for before their arrival is waited for: one trip to tensor
-        // memory per 64 tokens instead of one per 16.
-        constexpr int CH = TN < 64 ? TN : 64;
-        OT* out = (OT*)p.out + (long long)split * p.n * p.o;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const int o = o0 + mt * BM + warp * 32 + lane;
-          if (o0 + mt * BM >= p.o) break;     // uniform: the second tile lies past the matrix
-#pragma unroll
+        } else if (EPI == 0) {
+          // Up to 64 columns of the accumulator are asked for before their arrival is waited for: one trip to tensor
+          // memory per 64 tokens instead of one per 16.
+          constexpr int CH = TN < 64 ? TN : 64;
+          OT* out = (OT*)p.out + (long long)split * p.n * p.o;
+  #pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const int o = o0 + mt * BM + warp * 32 + lane;
+            if (o0 + mt * BM >= p.o) break;     // uniform: the second tile lies past the matrix
+  #pragma unroll
+            for (int c0 = 0; c0 < TN; c0 += CH) {
+              if (n0 + c0 >= p.n) break;        // uniform over the block: the tile's tail holds no tokens
+              uint32_t r[CH / 16][16];
+  #pragma unroll
+              for (int q = 0; q < CH / 16; ++q)
+                if (n0 + c0 + 16 * q < p.n) tmem_ld16(lane_base + (uint32_t)(mt * TN + c0 + 16 * q), r[q]);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+              if (o < p.o) {
+  #pragma unroll
+                for (int q = 0; q < CH / 16; ++q) {
+                  if (n0 + c0 + 16 * q >= p.n) break;
+                  // every value is worked out before the first is stored: a store through a generic pointer may, for all
+                  // the compiler knows, change the scales in shared memory, and would order every element behind the last
+                  float v[16];
+  #pragma unroll
+                  for (int c = 0; c < 16; ++c)
+                    v[c] = p.scale.ss ? __uint_as_float(r[q][c]) * col_scale[c0 + 16 * q + c] : __uint_as_float(r[q][c]);
+                  OT* dst = out + (long long)(n0 + c0 + 16 * q) * p.o + o;
+  #pragma unroll
+                  for (int c = 0; c < 16; ++c)
+                    if (n0 + c0 + 16 * q + c < p.n) dst[(long long)c * p.o] = from_f32<OT>(v[c]);
+                }
+              }
+            }
+          }
+        } else {
+          // accumulator 0 holds gate, accumulator 1 up, of feature o0 + lane row (the first gate_rows lanes)
+          constexpr int CH = TN < 64 ? TN : 64;
+          OT* out = (OT*)p.out;
+          const int row = warp * 32 + lane;
+          const int inter = row < p.gate_rows ? p.gated_features : 0;
+          const int f = o0 + row;
+  #pragma unroll
           for (int c0 = 0; c0 < TN; c0 += CH) {
-            if (n0 + c0 >= p.n) break;        // uniform over the block: the tile's tail holds no tokens
-            uint32_t r[CH / 16][16];
-#pragma unroll
-            for (int q = 0; q < CH / 16; ++q)
-              if (n0 + c0 + 16 * q < p.n) tmem_ld16(lane_base + (uint32_t)(mt * TN + c0 + 16 * q), r[q]);
+            if (n0 + c0 >= p.n) break;
+            uint32_t rg[CH / 16][16], ru[CH / 16][16];
+  #pragma unroll
+            for (int q = 0; q < CH / 16; ++q) {
+              if (n0 + c0 + 16 * q < p.n) {
+                tmem_ld16(lane_base + (uint32_t)(c0 + 16 * q), rg[q]);
+                tmem_ld16(lane_base + (uint32_t)(TN + c0 + 16 * q), ru[q]);
+              }
+            }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            if (o < p.o) {
-#pragma unroll
+            if (f < inter) {
+  #pragma unroll
               for (int q = 0; q < CH / 16; ++q) {
                 if (n0 + c0 + 16 * q >= p.n) break;
-                // every value is worked out before the first is stored: a store through a generic pointer may, for all
-                // the compiler knows, change the scales in shared memory, and would order every element behind the last
-                float v[16];
-#pragma unroll
+                float v[16];                  // all worked out before the first store, as above
+  #pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                  const float rs = p.scale.ss ? col_scale[c0 + 16 * q + c] : 1.0f;
+                  const float g = __uint_as_float(rg[q][c]) * rs, u = __uint_as_float(ru[q][c]) * rs;
+                  v[c] = __fdividef(g, 1.0f + __expf(-g)) * u;
+                }
+                OT* dst = out + (long long)(n0 + c0 + 16 * q) * inter + f;
+  #pragma unroll
                 for (int c = 0; c < 16; ++c)
-                  v[c] = p.scale.ss ? __uint_as_float(r[q][c]) * col_scale[c0 + 16 * q + c] : __uint_as_float(r[q][c]);
-                OT* dst = out + (long long)(n0 + c0 + 16 * q) * p.o + o;
-#pragma unroll
-                for (int c = 0; c < 16; ++c)
-                  if (n0 + c0 + 16 * q + c < p.n) dst[(long long)c * p.o] = from_f32<OT>(v[c]);
+                  if (n0 + c0 + 16 * q + c < p.n) dst[(long long)c * inter] = from_f32<OT>(v[c]);
               }
             }
           }
         }
-      } else {
-        // accumulator 0 holds gate, accumulator 1 up, of feature o0 + lane row (the first gate_rows lanes)
-        constexpr int CH = TN < 64 ? TN : 64;
-        OT* out = (OT*)p.out;
-        const int row = warp * 32 + lane;
-        const int inter = row < p.gate_rows ? p.gated_features : 0;
-        const int f = o0 + row;
-#pragma unroll
-        for (int c0 = 0; c0 < TN; c0 += CH) {
-          if (n0 + c0 >= p.n) break;
-          uint32_t rg[CH / 16][16], ru[CH / 16][16];
-#pragma unroll
-          for (int q = 0; q < CH / 16; ++q) {
-            if (n0 + c0 + 16 * q < p.n) {
-              tmem_ld16(lane_base + (uint32_t)(c0 + 16 * q), rg[q]);
-              tmem_ld16(lane_base + (uint32_t)(TN + c0 + 16 * q), ru[q]);
-            }
-          }
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          if (f < inter) {
-#pragma unroll
-            for (int q = 0; q < CH / 16; ++q) {
-              if (n0 + c0 + 16 * q >= p.n) break;
-              float v[16];                  // all worked out before the first store, as above
-#pragma unroll
-              for (int c = 0; c < 16; ++c) {
-                const float rs = p.scale.ss ? col_scale[c0 + 16 * q + c] : 1.0f;
-                const float g = __uint_as_float(rg[q][c]) * rs, u = __uint_as_float(ru[q][c]) * rs;
-                v[c] = __fdividef(g, 1.0f + __expf(-g)) * u;
-              }
-              OT* dst = out + (long long)(n0 + c0 + 16 * q) * inter + f;
-#pragma unroll
-              for (int c = 0; c < 16; ++c)
-                if (n0 + c0 + 16 * q + c < p.n) dst[(long long)c * inter] = from_f32<OT>(v[c]);
-            }
-          }
-        }
       }
-    }
-    // the accumulator may be overwritten by the next tile only after every warp has read it
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  }
-  if (tid == 0 && *abortp) {
-    // copies already requested still write into this block's shared memory: wait for them, bounded
-    for (int i = max(0, it_issue - STAGES); i < it_issue; ++i) {
-      const unsigned long long t0 = now_ns();
-      while (!mbar_try_wait(&full_bar[i % STAGES], (i / STAGES) & 1)) {
-        if (now_ns() - t0 > WAIT_LIMIT_NS) { atomicCAS(&g_error, 1, 4); break; }
-      }
+      // the accumulator may be overwritten only after every warp has read it
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (tid == 0) LLG_STAMP(1, 3, st_aux, st_blk);
-  if (warp == 1) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)TMEM_COLS) : "memory");
   }
 }
@@ -645,7 +662,7 @@ int launch(const CUtensorMap* mw, const CUtensorMap* mx, const GemmParams& p, in
   }
   if (blocks > 2147483647LL) return llg_fail("gemm_tc: too many tiles");
   dim3 grid((unsigned)blocks, 1, splits);
-  cudaError_t le = llg_launch(gemm_tc_kernel<TN, STAGES, OT, MT, EPI, SWAP>, grid, dim3(128), (size_t)smem, stream, *mw, *mx, p);
+  cudaError_t le = llg_launch(gemm_tc_kernel<TN, STAGES, OT, MT, EPI, SWAP>, grid, dim3(GEMM_THREADS), (size_t)smem, stream, *mw, *mx, p);
   if (le != cudaSuccess) return llg_fail("gemm_tc: launch: %s", cudaGetErrorString(le));
   return llg_check_launch("gemm_tc");
 }
