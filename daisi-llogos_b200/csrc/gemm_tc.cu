@@ -226,7 +226,8 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, nkb_total - kb0);   // >= 1 by construction of the grid
 
-  if (tid == 0) {
+  int pre = 0;                  // the producer lane: k-blocks of its first tile whose weight tiles are requested below
+  if (tid == PRODUCER_WARP * 32) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -237,6 +238,19 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The weights do not depend on the previous kernel, and requesting them needs nothing but the barriers above: the
+    // first ring of weight tiles is on its way before the block's tensor memory is there and long before this kernel
+    // waits for its predecessor.  The weights are the first operand of a decode step's product and the second of a
+    // prompt step's.
+    if ((int)blockIdx.x < total_tiles) {
+      const int o0 = first_offset(blockIdx.x), n0 = second_offset(blockIdx.x);
+      pre = min(nkb, STAGES);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], stage_tx);
+        if (SWAP) load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
+        else load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
+      }
+    }
   }
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
@@ -260,15 +274,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
         const int o0 = first_offset(tile), n0 = second_offset(tile);
         int done = 0;
         if (first) {
-          // The weights do not depend on the previous kernel: the first ring of weight tiles is requested
-          // before this kernel waits for its predecessor, the activation tiles right after.  The weights are
-          // the first operand of a decode step's product and the second of a prompt step's.
-          const int pre = min(nkb, STAGES);
-          for (int i = 0; i < pre; ++i) {
-            mbar_expect_tx(&full_bar[i], stage_tx);
-            if (SWAP) load_second(smem + i * STAGE_BYTES + A_BYTES, kb0 + i, n0, &full_bar[i]);
-            else load_first(smem + i * STAGE_BYTES, kb0 + i, o0, &full_bar[i]);
-          }
+          // the first tile's weight tiles are on their way (above); its activation tiles follow the dependency wait
           pdl_wait();
           LLG_STAMP(1, 1, st_aux, st_blk);
           for (int i = 0; i < pre; ++i) {
