@@ -65,9 +65,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// the epilogue warps' own barrier (the two other warps do not take part)
-__device__ __forceinline__ void epi_sync() { asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory"); }
-
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -181,7 +178,11 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[NACC], acc_empty[NACC];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float col_scale[SWAP ? 1 : TN];      // tokens along the columns: their scales, worked out during the products
+  // tokens along the columns: their scales, worked out during the products; a copy for even and one for odd tiles of the
+  // block, and an mbarrier (a bounded wait, unlike a block barrier) on which every epilogue thread arrives once it has
+  // written its share: who writes tile r + 2's copy has passed tile r + 1's barrier, so everybody is done reading tile r's
+  __shared__ float col_scales[2][SWAP ? 1 : TN];
+  __shared__ uint64_t scale_bar;
 
   pdl_launch_dependents();      // the next kernel may set itself up while this one runs
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -236,6 +237,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], EPI_WARPS);
     }
+    mbar_init(&scale_bar, EPI_WARPS * 32);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     // The weights do not depend on the previous kernel, and requesting them needs nothing but the barriers above: the
@@ -352,11 +354,15 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
       const int o0 = first_offset(tile), n0 = second_offset(tile);
       const int b = round % NACC;
+      const float* col_scale = col_scales[round & 1];
       if (!SWAP && p.scale.ss) {
         // tokens along the columns: their scales, worked out while the products run
-        if (round > 0) epi_sync();          // the last tile's readers are done with them
-        for (int c = tid; c < TN; c += EPI_WARPS * 32) col_scale[c] = n0 + c < p.n ? row_scale_of(p.scale, n0 + c) : 0.f;
-        epi_sync();
+        for (int c = tid; c < TN; c += EPI_WARPS * 32) col_scales[round & 1][c] = n0 + c < p.n ? row_scale_of(p.scale, n0 + c) : 0.f;
+        mbar_arrive(&scale_bar);
+        if (!mbar_wait(&scale_bar, round & 1, abortp)) {
+          if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
+          break;
+        }
       }
       const bool have = mbar_wait(&acc_full[b], (round / NACC) & 1, abortp);
       if (!have && !*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
