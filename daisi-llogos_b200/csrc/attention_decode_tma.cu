@@ -137,8 +137,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ float pow2_whole(float d) {
   return d < -126.f ? 0.f : __int_as_float((127 + (int)d) << 23);
 }
-// the working warps' own barrier (the copying warp does not take part)
-__device__ __forceinline__ void work_sync() { asm volatile("bar.sync 1, %0;" ::"n"(WORK_WARPS * 32) : "memory"); }
 
 // 64-key tiles that a sequence of `len` keys reads, and the first of them
 __device__ __forceinline__ int first_tile(int len, int window) { return (window > 0 ? max(0, len - window) : 0) / TK; }
@@ -175,6 +173,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   unsigned char* Ks = smem;                            // [STAGES][TILE_BYTES]
   unsigned char* Vs = smem + STAGES * TILE_BYTES;      // [STAGES][TILE_BYTES]
   __shared__ uint64_t full[STAGES], empty[STAGES];
+  __shared__ uint64_t work_bar;                        // the working warps meet here: a wait with a limit, unlike a block barrier
   __shared__ int cum[MAX_SEQS + 1];                    // tiles of the sequences before b
   __shared__ int seq_len[STAGED_SEQS], seq_slot[STAGED_SEQS];      // fetched with the plan: the page look-ups start a trip to L2 earlier
   __shared__ int warp_total[THREADS / 32];
@@ -197,6 +196,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], WORK_WARPS);
     }
+    mbar_init(&work_bar, WORK_WARPS * 32);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -365,6 +365,16 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
   };
   int i = 0;                                            // tiles consumed so far
   bool ok = true;
+  // The working warps' own meeting point (the copying warp does not take part).  A warp whose wait for a tile ran out
+  // never comes here; the others then leave after their limit, or at once when they see the block's flag.
+  uint32_t work_phase = 0;
+  auto work_sync = [&]() -> bool {
+    mbar_arrive(&work_bar);
+    const bool met = mbar_wait(&work_bar, work_phase & 1, abortp);
+    ++work_phase;
+    if (!met && !*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 1); }
+    return met;
+  };
   long long u = u0;
   while (u < u1 && ok) {
     const int b = cur.b, kvh = cur.kvh;
@@ -496,7 +506,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           }
         }
       }
-      work_sync();
+      if (!work_sync()) { ok = false; break; }
       const int head = h0 + warp;                       // one warp per head
       if (head < G) {
         float mw[WORK_WARPS], M = -INFINITY;
@@ -541,8 +551,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
           pend_row = head_row;
         }
       }
-      work_sync();                                      // the merge area is free for the next four heads
+      if (!work_sync()) { ok = false; break; }          // the merge area is free for the next four heads
     }
+    if (!ok) break;
     u += n_seg;
     cur.t += n_seg;
     if (cur.t == cur.tiles) {
